@@ -1,0 +1,247 @@
+/*
+ * b200_kquant.h -- C ABI of the B200 (sm_100a) K-quant stage library.
+ *
+ * This is the drop-in boundary for the one hot path every mesh-llm serving stage executes: the
+ * quantised forward pass that llama.cpp's scheduler drives through the ggml backend interface
+ * inside `llama-server` / `rpc-server` (spawned by mesh-llm/src/inference/launch.rs:887 and
+ * :1250).  The reference reaches that interface through the calls visible in its patch queue;
+ * each group below cites the call it replaces.  "patches/000N" means
+ * third_party/llama.cpp/patches/000N-*.patch in the reference tree.
+ *
+ * Rules of the ABI: plain pointers and sizes, opaque handles, no exceptions cross it, every
+ * entry point returns a status (or bool where the reference call does) and never aborts.
+ * Device pointers are CUDA device addresses; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  There is no CPU fallback anywhere behind this header:
+ * an unsupported request returns B200_ERR_UNSUPPORTED.
+ */
+#ifndef B200_KQUANT_H
+#define B200_KQUANT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+/* ---- status (ggml_status-like: 0 success, negative failure) -------------------------------- */
+typedef int32_t b200_status;
+enum {
+    B200_OK = 0,
+    B200_ERR_INVALID = -1,     /* bad argument / shape / alignment                            */
+    B200_ERR_ALLOC = -2,       /* device or host allocation failed (GGML_STATUS_ALLOC_FAILED)  */
+    B200_ERR_CUDA = -3,        /* a CUDA runtime call failed; see b200_last_error()            */
+    B200_ERR_UNSUPPORTED = -4, /* op / type not on the hot path                               */
+    B200_ERR_BOUNDS = -5,      /* access outside the owning buffer                            */
+    B200_ERR_TIMEOUT = -6,     /* a bounded device-side wait gave up                          */
+    B200_ERR_STATE = -7        /* call made in the wrong state (e.g. weights not loaded)      */
+};
+B200_API const char *b200_status_string(b200_status s);
+B200_API const char *b200_last_error(void); /* thread-local, valid until the next failing call */
+
+/* ---- tensor types: ggml type ids (mesh-client/src/models/gguf.rs:19-35) -------------------- */
+enum {
+    B200_TYPE_F32 = 0,
+    B200_TYPE_F16 = 1,
+    B200_TYPE_Q4_K = 12, /* 256 elements / 144 bytes */
+    B200_TYPE_Q6_K = 14, /* 256 elements / 210 bytes */
+    B200_TYPE_I32 = 26
+};
+
+/* ---- ops understood by graph_compute (the subset on the hot path) -------------------------- */
+enum {
+    B200_OP_NONE = 0,
+    B200_OP_MUL_MAT,     /* src0 = weights [K, N] (Q4_K/Q6_K/F32), src1 = x [K, M] f32 -> [N, M]  */
+    B200_OP_MUL_MAT_ID,  /* src0 = experts [K, N, E], src1 = x [K, n_used|1, T], src2 = ids i32   */
+    B200_OP_RMS_NORM,    /* op_params[0] = eps (f32 bits)                                         */
+    B200_OP_MUL,         /* broadcast multiply by a row vector (norm weight)                      */
+    B200_OP_ADD,         /* elementwise, or broadcast add of a row vector (bias)                  */
+    B200_OP_ROPE,        /* src1 = positions i32; op_params: [0]=n_dims [1]=mode(0 norm, 2 neox)
+                            [2]=theta (f32 bits)                                                 */
+    B200_OP_SWIGLU,      /* silu(src0) * src1                                                     */
+    B200_OP_GET_ROWS,    /* src0 = table (Q4_K/Q6_K/F32), src1 = ids i32                          */
+    B200_OP_CPY,         /* f32 -> f32 / f16 copy (KV-cache write)                                */
+    B200_OP_ATTN,        /* fused causal attention (FLASH_ATTN_EXT): src0 = q [hd, n_head, T],
+                            src1 = K cache f16 [hd, n_kv, n_ctx], src2 = V cache likewise;
+                            op_params[0] = scale (f32 bits), [1] = pos0                          */
+    B200_OP_MOE_ROUTE,   /* softmax + top-k + renormalise: src0 = logits [E, T];
+                            op_params[0] = k; output = weights f32 [k, T]; ids written to src1   */
+    B200_OP_ARGMAX,
+    B200_OP_COUNT
+};
+
+/* ---- tensor descriptor: field-for-field the wire form `rpc_tensor`
+ *      (patches/0002 lines 1070-1085; 296 bytes packed).  ne[0] is the contiguous dimension,
+ *      nb[] are strides in bytes, `data` is a device address inside `buffer`.               */
+#pragma pack(push, 1)
+typedef struct b200_tensor {
+    uint64_t id;
+    uint32_t type;
+    uint64_t buffer; /* b200_buffer* as integer */
+    uint32_t ne[4];
+    uint32_t nb[4];
+    uint32_t op;
+    int32_t op_params[16];
+    int32_t flags;
+    uint64_t src[10]; /* ids of source tensors, 0 = none */
+    uint64_t view_src;
+    uint64_t view_offs;
+    uint64_t data;
+    char name[64];
+    char padding[4];
+} b200_tensor;
+#pragma pack(pop)
+
+typedef struct b200_buffer b200_buffer;
+typedef struct b200_backend b200_backend;
+typedef struct b200_stage b200_stage;
+
+/* ---- registry and devices: ggml_backend_reg / ggml_backend_dev
+ *      (device selection by name, launch.rs:69-82 and :920-925; ggml_backend_dev_memory,
+ *      patches/0002 lines 464-467).                                                        */
+B200_API const char *b200_reg_name(void); /* "B200" */
+B200_API int32_t b200_reg_device_count(void);
+B200_API b200_status b200_dev_name(int32_t dev, char *out, size_t cap); /* "B200_<i>" */
+B200_API b200_status b200_dev_description(int32_t dev, char *out, size_t cap);
+B200_API b200_status b200_dev_memory(int32_t dev, size_t *free_bytes, size_t *total_bytes);
+/* 1 if graph_compute can run `node` whose sources have the given types, else 0               */
+B200_API int32_t b200_dev_supports_op(uint32_t op, uint32_t type_src0, uint32_t type_src1);
+
+/* ---- buffer type: get_alignment / get_max_size / get_alloc_size
+ *      (patches/0001 lines 96-147, patches/0002 lines 352-371).                             */
+B200_API size_t b200_buft_alignment(void);
+B200_API size_t b200_buft_max_size(int32_t dev);
+/* bytes a tensor occupies on the device; Q6_K rows are padded to 16 bytes by the repack      */
+B200_API size_t b200_buft_alloc_size(uint32_t type, const uint32_t ne[4]);
+
+/* ---- buffers: alloc / free / get_base / clear / init_tensor / set_tensor / get_tensor /
+ *      cpy_tensor (patches/0001 lines 68-91, patches/0002 lines 181-261).  set_tensor repacks
+ *      Q6_K into the device layout and get_tensor returns the original bytes; every access is
+ *      bounds-checked against the owning buffer (patches/0001 lines 228-239).               */
+B200_API b200_status b200_buffer_alloc(int32_t dev, size_t size, b200_buffer **out);
+B200_API void b200_buffer_free(b200_buffer *buf);
+B200_API void *b200_buffer_get_base(b200_buffer *buf);
+B200_API size_t b200_buffer_get_size(b200_buffer *buf);
+B200_API int32_t b200_buffer_get_device(b200_buffer *buf);
+B200_API b200_status b200_buffer_clear(b200_buffer *buf, uint8_t value);
+B200_API b200_status b200_buffer_init_tensor(b200_buffer *buf, b200_tensor *t);
+B200_API b200_status b200_buffer_set_tensor(b200_buffer *buf, const b200_tensor *t,
+                                            const void *host_data, size_t offset, size_t size);
+B200_API b200_status b200_buffer_get_tensor(b200_buffer *buf, const b200_tensor *t,
+                                            void *host_data, size_t offset, size_t size);
+/* Stage-boundary hand-off.  Replaces ggml_backend_rpc_buffer_cpy_tensor ->
+ * RPC_CMD_PUSH_TENSOR_TO_PEER -> RPC_CMD_PEER_TENSOR_DATA (patches/0002 lines 184-259 and
+ * 544-622: device -> host vector -> TCP -> host -> device) by one device-to-device copy over
+ * NVLink.  Copies `size` bytes starting `offset` bytes into both tensors.  Returns 1 on
+ * success and 0 if the copy cannot be done directly, in which case the caller falls back to
+ * get_tensor + set_tensor exactly as the reference does (patches/0002 lines 250-254).       */
+B200_API int32_t b200_buffer_cpy_tensor(const b200_tensor *src, const b200_tensor *dst,
+                                        size_t offset, size_t size);
+
+/* ---- backend: graph_compute / synchronize (patches/0002 lines 443-459).  The graph arrives
+ *      the way the RPC server receives it: node ids in execution order plus the table of all
+ *      tensors they reference.                                                             */
+B200_API b200_status b200_backend_init(int32_t dev, b200_backend **out);
+B200_API void b200_backend_free(b200_backend *be);
+B200_API b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_ids,
+                                                uint32_t n_nodes, const b200_tensor *tensors,
+                                                uint32_t n_tensors);
+B200_API b200_status b200_backend_synchronize(b200_backend *be);
+B200_API void *b200_backend_stream(b200_backend *be);
+
+/* ---- direct kernel entry points (device pointers) -------------------------------------------
+ * Weight matrices passed to these are in DEVICE layout: Q4_K rows are the GGUF bytes
+ * unchanged; Q6_K rows are repacked (b200_repack_q6k) to [ql | qh | scales | d | pad16].    */
+B200_API size_t b200_row_bytes(uint32_t type, int64_t k);        /* GGUF bytes of one row     */
+B200_API size_t b200_device_row_bytes(uint32_t type, int64_t k); /* device bytes of one row   */
+B200_API b200_status b200_repack_q6k(const void *gguf_rows_dev, void *device_rows, int64_t n_rows,
+                                     int64_t k, void *stream);
+B200_API b200_status b200_unpack_q6k(const void *device_rows, void *gguf_rows_dev, int64_t n_rows,
+                                     int64_t k, void *stream);
+
+/* f32 activations -> Q8 blocks of 256: q int8 [M][K], d f32 [M][K/256], bsum16 int16 [M][K/16] */
+B200_API b200_status b200_quantize_act(const float *x, int64_t M, int64_t K, int8_t *q, float *d,
+                                       int16_t *bsum16, void *stream);
+/* bytes of scratch b200_mul_mat needs for M x K activations                                    */
+B200_API size_t b200_mul_mat_scratch_bytes(int64_t M, int64_t K);
+/* y[M][N] = W[N x K] . x[M][K].  MUL_MAT of the ggml op surface for Q4_K / Q6_K weights:
+ * decode GEMV for M <= 8, tiled GEMM above.  `scratch` holds the quantised activations.       */
+B200_API b200_status b200_mul_mat(uint32_t type, const void *W, const float *x, int64_t M,
+                                  int64_t N, int64_t K, float *y, void *scratch,
+                                  size_t scratch_bytes, void *stream);
+/* same contraction on already-quantised activations, with optional fused epilogue:
+ * y = W.x (+ bias[N]) (+ residual[M][N])                                                       */
+B200_API b200_status b200_mul_mat_q8(uint32_t type, const void *W, const int8_t *q, const float *d,
+                                     const int16_t *bsum16, int64_t M, int64_t N, int64_t K,
+                                     float *y, const float *bias, const float *residual,
+                                     void *stream);
+/* exact per-block integer sums [M][N][K/256] (parity instrumentation; summ may be NULL)        */
+B200_API b200_status b200_block_sums(uint32_t type, const void *W, const int8_t *q,
+                                     const int16_t *bsum16, int64_t M, int64_t N, int64_t K,
+                                     int32_t *sumi, int32_t *summ, void *stream);
+
+B200_API b200_status b200_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps,
+                                   float *y, void *stream);
+B200_API b200_status b200_rope(float *x, const int32_t *pos, int64_t T, int64_t n_head, int64_t hd,
+                               float theta, int32_t neox, void *stream);
+B200_API b200_status b200_swiglu(const float *gate, const float *up, int64_t n, float *y,
+                                 void *stream);
+B200_API b200_status b200_add(const float *a, const float *b, int64_t n, float *y, void *stream);
+B200_API b200_status b200_add_bias(float *y, const float *bias, int64_t T, int64_t n, void *stream);
+B200_API b200_status b200_cpy_f32_f16(const float *x, int64_t n, uint16_t *y, void *stream);
+B200_API b200_status b200_attention(const float *q, const uint16_t *k_cache, const uint16_t *v_cache,
+                                    int64_t T, int64_t pos0, int64_t n_head, int64_t n_kv,
+                                    int64_t hd, float *out, void *scratch, size_t scratch_bytes,
+                                    void *stream);
+B200_API size_t b200_attention_scratch_bytes(int64_t T, int64_t n_head, int64_t hd, int64_t n_ctx);
+B200_API b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T,
+                                   int64_t K, float *y, void *stream);
+B200_API b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream);
+B200_API b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k,
+                                    int32_t *ids, float *w, void *stream);
+
+/* ---- stage: one contiguous layer range of a model resident on one GPU ------------------------
+ * This is what a mesh-llm worker is: `rpc-server -d DEV --gguf PATH` holding blk.[a,b) and
+ * loading exactly its own tensors by name from its local GGUF (patches/0001 lines 179-266);
+ * the partition follows election.rs:3095-3114 (contiguous ranges, embeddings on the first
+ * stage, output_norm + output on the last).                                                 */
+typedef struct b200_stage_config {
+    int32_t n_layer, layer_begin, layer_end;
+    int32_t n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab;
+    int32_t n_expert, n_expert_used, n_ff_exp; /* 0 = dense                                   */
+    int32_t n_ctx, n_seq;                      /* KV cache: n_seq sequences of n_ctx tokens   */
+    int32_t rope_neox, qkv_bias, qk_norm;
+    int32_t has_embd, has_output;
+    float rms_eps, rope_theta;
+    int32_t n_ubatch; /* largest number of tokens per forward call                           */
+    int32_t device;
+} b200_stage_config;
+
+B200_API b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out);
+B200_API void b200_stage_free(b200_stage *st);
+/* load one tensor by its GGUF name from host memory in GGUF byte layout                        */
+B200_API b200_status b200_stage_set_tensor(b200_stage *st, const char *name, uint32_t type,
+                                           const void *host_data, size_t nbytes);
+/* read a tensor back in GGUF byte layout (inverse of the device repack)                        */
+B200_API b200_status b200_stage_get_tensor(b200_stage *st, const char *name, void *host_data,
+                                           size_t nbytes);
+/* fill every tensor with seeded N(0, 0.02) weights quantised on the device to the Q4_K_M mix   */
+B200_API b200_status b200_stage_generate(b200_stage *st, uint64_t seed);
+B200_API size_t b200_stage_weight_bytes(b200_stage *st);
+/* Run T tokens per sequence for `n_seq_active` sequences (rows ordered sequence-major) starting
+ * at position pos0.  First stage: tokens (device i32); other stages: hidden_in (device f32
+ * [rows][n_embd]).  Last stage writes logits for the last token of each sequence (or all rows
+ * if all_logits) and the greedy argmax into next_tokens; other stages write hidden_out.        */
+B200_API b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens,
+                                        const float *hidden_in, int32_t n_seq_active, int32_t T,
+                                        int32_t pos0, float *hidden_out, float *logits,
+                                        int32_t all_logits, int32_t *next_tokens, void *stream);
+B200_API b200_status b200_stage_synchronize(b200_stage *st);
+B200_API int64_t b200_stage_kernel_launches(b200_stage *st); /* launches issued so far        */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KQUANT_H */

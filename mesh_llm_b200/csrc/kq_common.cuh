@@ -1,0 +1,115 @@
+// Shared declarations of the B200 K-quant stage library (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200_kquant.h"
+
+#define KQ_QK 256
+#define KQ_Q4K_BYTES 144
+#define KQ_Q6K_BYTES 210
+
+// ---- error plumbing -----------------------------------------------------------------------
+void kq_set_error(const char *fmt, ...);
+
+#define KQ_CUDA(call)                                                                          \
+    do {                                                                                       \
+        cudaError_t e__ = (call);                                                              \
+        if (e__ != cudaSuccess) {                                                              \
+            kq_set_error("%s:%d %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString(e__)); \
+            return B200_ERR_CUDA;                                                              \
+        }                                                                                      \
+    } while (0)
+
+#define KQ_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            kq_set_error(__VA_ARGS__);   \
+            return B200_ERR_INVALID;     \
+        }                                \
+    } while (0)
+
+#define KQ_LAUNCH_CHECK()                                                                   \
+    do {                                                                                    \
+        cudaError_t e__ = cudaGetLastError();                                               \
+        if (e__ != cudaSuccess) {                                                           \
+            kq_set_error("%s:%d launch -> %s", __FILE__, __LINE__, cudaGetErrorString(e__)); \
+            return B200_ERR_CUDA;                                                           \
+        }                                                                                   \
+    } while (0)
+
+// every kernel launch of the library goes through this counter (reported by the bench)
+extern long long g_kq_launches;
+#define KQ_COUNT_LAUNCH() (++g_kq_launches)
+
+static inline int64_t kq_div_up(int64_t a, int64_t b) { return (a + b - 1) / b; }
+int kq_sm_count();
+
+// ---- device row geometry -------------------------------------------------------------------
+static inline __host__ __device__ int64_t kq_row_bytes(uint32_t type, int64_t k) {
+    switch (type) {
+    case B200_TYPE_F32: return k * 4;
+    case B200_TYPE_F16: return k * 2;
+    case B200_TYPE_Q4_K: return k / KQ_QK * KQ_Q4K_BYTES;
+    case B200_TYPE_Q6_K: return k / KQ_QK * KQ_Q6K_BYTES;
+    default: return 0;
+    }
+}
+// Q6_K rows live on the device as [ql nb*128 | qh nb*64 | scales nb*16 | d nb*2 | pad to 16]
+static inline __host__ __device__ int64_t kq_device_row_bytes(uint32_t type, int64_t k) {
+    if (type == B200_TYPE_Q6_K) return (k / KQ_QK * KQ_Q6K_BYTES + 15) / 16 * 16;
+    return kq_row_bytes(type, k);
+}
+
+// ---- device helpers ------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float kq_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float kq_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float kq_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// 16-byte streaming load of weight bytes: read once, keep out of L1
+__device__ __forceinline__ uint4 kq_ld_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// The activation quantiser of the library (same arithmetic as the CPU oracle, operation for
+// operation, so the int8 codes are bit-identical): d = amax / 127, id = 1 / d, q = rint(x * id).
+__device__ __forceinline__ float kq_act_scale(float amax) { return __fdiv_rn(amax, 127.0f); }
+__device__ __forceinline__ float kq_act_inv(float d) { return d > 0.f ? __fdiv_rn(1.0f, d) : 0.f; }
+__device__ __forceinline__ int kq_act_code(float x, float id) {
+    int v = __float2int_rn(__fmul_rn(x, id));
+    return max(-127, min(127, v));
+}
+#endif
+
+// ---- internal launchers shared between translation units -----------------------------------
+struct KqGemvSeg {
+    const uint8_t *W; // device layout rows
+    uint32_t type;
+    int32_t n_rows;
+    float *y;          // [M][ldy], rows of this segment start at column 0 of y
+    const float *bias; // [n_rows] or null
+    int32_t ldy;
+};
+
+b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
+                           const int16_t *bs, int M, int64_t K, const float *residual,
+                           int swiglu_pairs, cudaStream_t st);
+b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
+                           const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
+                           const float *bias, const float *residual, cudaStream_t st);

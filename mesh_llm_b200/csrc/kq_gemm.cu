@@ -1,0 +1,18 @@
+// Prefill contraction (M > 8 tokens).  First form: the token batch is walked in slabs of 8 through
+// the decode kernel, so a weight matrix is streamed once from HBM and then re-read from L2 for the
+// remaining slabs.  Results are identical to the decode path token for token.
+#include "kq_common.cuh"
+
+b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
+                           const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
+                           const float *bias, const float *residual, cudaStream_t st) {
+    const int64_t nb = K / 256;
+    for (int64_t m0 = 0; m0 < M; m0 += 8) {
+        const int mc = (int)(M - m0 < 8 ? M - m0 : 8);
+        KqGemvSeg sg = {W, type, (int32_t)N, y + m0 * N, bias, (int32_t)N};
+        b200_status rc = kq_launch_gemv(&sg, 1, q + m0 * K, d + m0 * nb, bs + m0 * nb * 16, mc, K,
+                                        residual ? residual + m0 * N : nullptr, 0, st);
+        if (rc != B200_OK) return rc;
+    }
+    return B200_OK;
+}

@@ -1,0 +1,411 @@
+// Decode GEMV: y[m][n] = sum_k W[n][k] x[m][k] for M <= 8 tokens, W in Q4_K / Q6_K blocks, x in
+// Q8 blocks of 256.  This is MUL_MAT of the ggml op surface at decode batch sizes; the kernel is
+// bound by HBM bandwidth (0.5625 / 0.8203 bytes per weight), so everything here is about
+// streaming the packed blocks once with 16-byte loads and enough of them in flight.
+//
+// Work split: a warp owns R weight rows; its 32 lanes cover 4 consecutive super-blocks per
+// step (8 lanes x 16 bytes = the 128 quant bytes of one block).  Each lane keeps f32 partial sums
+// for its R rows x M tokens; the activations of a block are loaded once and reused for the R
+// rows.  Long rows are additionally split over the 2 or 4 warps of a CTA and combined in shared
+// memory in a fixed order, so results are deterministic (no float atomics).
+#include "kq_common.cuh"
+
+#include <stdlib.h>
+
+namespace {
+
+struct LaneGeom {
+    int e_lo;   // first element (within the block) of the lane's low-nibble group of 16
+    int e_hi;   // first element of its high-nibble group of 16
+};
+
+// ---- Q4_K: one lane's share of one block -----------------------------------------------------
+// hdr = first 16 bytes of the block (f16 d, f16 dmin, 12 bytes of 6-bit scales/mins); w = the
+// lane's 16 quant bytes (chunk c of 8): low nibbles belong to sub-block 2g, high nibbles to
+// sub-block 2g+1, g = c >> 1.
+struct Q4Scales {
+    int sc0, sc1, m0, m1;
+    float d, dmin;
+};
+
+__device__ __forceinline__ Q4Scales q4k_lane_scales(const uint4 &hdr, int c) {
+    Q4Scales s;
+    const int g = c >> 1;
+    const int sh = (g & 1) * 16;
+    const uint32_t ty = (hdr.y >> sh) & 0xFFFFu, tz = (hdr.z >> sh) & 0xFFFFu,
+                   tw = (hdr.w >> sh) & 0xFFFFu;
+    if (g < 2) {
+        s.sc0 = ty & 63;
+        s.sc1 = (ty >> 8) & 63;
+        s.m0 = tz & 63;
+        s.m1 = (tz >> 8) & 63;
+    } else {
+        s.sc0 = (tw & 0xF) | ((ty >> 2) & 0x30);
+        s.sc1 = ((tw >> 8) & 0xF) | ((ty >> 10) & 0x30);
+        s.m0 = ((tw >> 4) & 0xF) | ((tz >> 2) & 0x30);
+        s.m1 = ((tw >> 12) & 0xF) | ((tz >> 10) & 0x30);
+    }
+    const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
+    const float2 f = __half22float2(dm);
+    s.d = f.x;
+    s.dmin = f.y;
+    return s;
+}
+
+__device__ __forceinline__ void q4k_lane_ints(const uint4 &w, const Q4Scales &s, const int4 &alo,
+                                              const int4 &ahi, int bl, int bh, int &isum,
+                                              int &msum) {
+    int dl = __dp4a((int)(w.x & 0x0F0F0F0Fu), alo.x, 0);
+    dl = __dp4a((int)(w.y & 0x0F0F0F0Fu), alo.y, dl);
+    dl = __dp4a((int)(w.z & 0x0F0F0F0Fu), alo.z, dl);
+    dl = __dp4a((int)(w.w & 0x0F0F0F0Fu), alo.w, dl);
+    int dh = __dp4a((int)((w.x >> 4) & 0x0F0F0F0Fu), ahi.x, 0);
+    dh = __dp4a((int)((w.y >> 4) & 0x0F0F0F0Fu), ahi.y, dh);
+    dh = __dp4a((int)((w.z >> 4) & 0x0F0F0F0Fu), ahi.z, dh);
+    dh = __dp4a((int)((w.w >> 4) & 0x0F0F0F0Fu), ahi.w, dh);
+    isum = s.sc0 * dl + s.sc1 * dh;
+    msum = s.m0 * bl + s.m1 * bh;
+}
+
+// ---- Q6_K (device layout): one lane's share of one block ----------------------------------------
+// ql = the lane's 16 low-nibble bytes (chunk c of 8, half h = c >> 2, cc = c & 3); qh = the 16
+// bytes of 2-bit highs that cover the same 16 positions; the lane's low nibbles are elements
+// 128h + 16cc .. +15 and its high nibbles elements 128h + 64 + 16cc .. +15.
+__device__ __forceinline__ int q6k_lane_ints(const uint4 &ql, const uint4 &qh, int cc, int sc_lo,
+                                             int sc_hi, const int4 &alo, const int4 &ahi, int bl,
+                                             int bh) {
+    const int s_lo = 2 * (cc >> 1), s_hi = 4 + s_lo;
+    int dl = 0, dh = 0;
+#define KQ_Q6_STEP(W, H, AL, AH)                                                            \
+    {                                                                                       \
+        uint32_t vl = ((W) & 0x0F0F0F0Fu) | ((((H) >> s_lo) & 0x03030303u) << 4);           \
+        uint32_t vh = (((W) >> 4) & 0x0F0F0F0Fu) | ((((H) >> s_hi) & 0x03030303u) << 4);    \
+        dl = __dp4a((int)vl, (AL), dl);                                                     \
+        dh = __dp4a((int)vh, (AH), dh);                                                     \
+    }
+    KQ_Q6_STEP(ql.x, qh.x, alo.x, ahi.x)
+    KQ_Q6_STEP(ql.y, qh.y, alo.y, ahi.y)
+    KQ_Q6_STEP(ql.z, qh.z, alo.z, ahi.z)
+    KQ_Q6_STEP(ql.w, qh.w, alo.w, ahi.w)
+#undef KQ_Q6_STEP
+    // codes are stored with +32 bias: sum (q-32) a = sum q a - 32 sum a
+    return sc_lo * (dl - 32 * bl) + sc_hi * (dh - 32 * bh);
+}
+
+struct GemvParams {
+    KqGemvSeg seg[3];
+    int32_t rg_end[3]; // exclusive prefix of row groups per segment
+    int32_t nseg;
+    int32_t n_rg;      // total row groups
+    int32_t nb;        // blocks per row
+    int32_t K;
+    int32_t wk;        // warps of a CTA sharing one row group along K (1, 2 or 4)
+    int32_t swiglu;    // segments 0/1 are gate/up; a warp takes R/2 rows of each
+    const int8_t *aq;
+    const float *ad;
+    const int16_t *abs16;
+    const float *residual; // [M][ldy of segment 0] or null (single segment only)
+};
+
+template <int M, int R>
+__global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
+    __shared__ float red[4][R * M];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wk = p.wk, wn = 4 / wk;
+    const int kslot = warp % wk, nslot = warp / wk;
+    const int sub = lane >> 3, c = lane & 7;
+    const int nb = p.nb;
+
+    for (int base = blockIdx.x * wn; base < p.n_rg; base += gridDim.x * wn) {
+        const int rg = base + nslot;
+        const bool active = rg < p.n_rg;
+        int si = 0, rg0 = 0;
+        if (active) {
+            if (p.nseg > 1 && rg >= p.rg_end[0]) { si = 1; rg0 = p.rg_end[0]; }
+            if (p.nseg > 2 && rg >= p.rg_end[1]) { si = 2; rg0 = p.rg_end[1]; }
+        }
+        const KqGemvSeg &sg = p.seg[si];
+        const uint32_t type = sg.type;
+        const int64_t stride = kq_device_row_bytes(type, p.K);
+        float acc[R][M];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int m = 0; m < M; m++) acc[r][m] = 0.f;
+
+        const uint8_t *rp[R];
+        int row[R];
+        if (active) {
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (p.swiglu) {
+                    row[r] = (rg - rg0) * (R / 2) + (r % (R / 2));
+                    const KqGemvSeg &s2 = p.seg[r / (R / 2)];
+                    rp[r] = s2.W + (int64_t)min(row[r], s2.n_rows - 1) * stride;
+                } else {
+                    row[r] = (rg - rg0) * R + r;
+                    rp[r] = sg.W + (int64_t)min(row[r], sg.n_rows - 1) * stride;
+                }
+            }
+            if (type == B200_TYPE_Q4_K) {
+                const int e_lo = 64 * (c >> 1) + 16 * (c & 1);
+                for (int it = kslot; it * 4 < nb; it += wk) {
+                    const int blk = it * 4 + sub;
+                    if (blk < nb) {
+                        uint4 hdr[R], w[R];
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            const uint8_t *b = rp[r] + (int64_t)blk * KQ_Q4K_BYTES;
+                            hdr[r] = __ldg(reinterpret_cast<const uint4 *>(b));
+                            w[r] = kq_ld_stream(b + 16 + 16 * c);
+                        }
+                        Q4Scales sc[R];
+#pragma unroll
+                        for (int r = 0; r < R; r++) sc[r] = q4k_lane_scales(hdr[r], c);
+#pragma unroll
+                        for (int m = 0; m < M; m++) {
+                            const int8_t *a = p.aq + (int64_t)m * p.K + blk * 256 + e_lo;
+                            const int4 alo = *reinterpret_cast<const int4 *>(a);
+                            const int4 ahi = *reinterpret_cast<const int4 *>(a + 32);
+                            const float da = p.ad[m * nb + blk];
+                            const int16_t *s16 = p.abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+                            const int bl = s16[0], bh = s16[2];
+#pragma unroll
+                            for (int r = 0; r < R; r++) {
+                                int isum, msum;
+                                q4k_lane_ints(w[r], sc[r], alo, ahi, bl, bh, isum, msum);
+                                acc[r][m] = fmaf(sc[r].d * da, (float)isum, acc[r][m]);
+                                acc[r][m] = fmaf(-(sc[r].dmin * da), (float)msum, acc[r][m]);
+                            }
+                        }
+                    }
+                }
+            } else { // Q6_K device layout
+                const int h = c >> 2, cc = c & 3;
+                const int e_lo = 128 * h + 16 * cc;
+                const int64_t off_qh = (int64_t)nb * 128, off_sc = (int64_t)nb * 192,
+                              off_d = (int64_t)nb * 208;
+                for (int it = kslot; it * 4 < nb; it += wk) {
+                    const int blk = it * 4 + sub;
+                    if (blk < nb) {
+                        uint4 ql[R], qh[R];
+                        int scl[R], sch[R];
+                        float dw[R];
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            ql[r] = kq_ld_stream(rp[r] + (int64_t)blk * 128 + 16 * c);
+                            qh[r] = __ldg(reinterpret_cast<const uint4 *>(
+                                rp[r] + off_qh + (int64_t)blk * 64 + 16 * (2 * h + (cc & 1))));
+                            const int8_t *scp =
+                                reinterpret_cast<const int8_t *>(rp[r] + off_sc + (int64_t)blk * 16);
+                            scl[r] = scp[8 * h + cc];
+                            sch[r] = scp[8 * h + 4 + cc];
+                            dw[r] = kq_h2f(*reinterpret_cast<const uint16_t *>(rp[r] + off_d + blk * 2));
+                        }
+#pragma unroll
+                        for (int m = 0; m < M; m++) {
+                            const int8_t *a = p.aq + (int64_t)m * p.K + blk * 256 + e_lo;
+                            const int4 alo = *reinterpret_cast<const int4 *>(a);
+                            const int4 ahi = *reinterpret_cast<const int4 *>(a + 64);
+                            const float da = p.ad[m * nb + blk];
+                            const int16_t *s16 = p.abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+                            const int bl = s16[0], bh = s16[4];
+#pragma unroll
+                            for (int r = 0; r < R; r++) {
+                                const int isum =
+                                    q6k_lane_ints(ql[r], qh[r], cc, scl[r], sch[r], alo, ahi, bl, bh);
+                                acc[r][m] = fmaf(dw[r] * da, (float)isum, acc[r][m]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        // warp reduce, then combine the K-slices of the CTA in a fixed order
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float v = kq_warp_sum(acc[r][m]);
+                if (lane == 0) red[warp][r * M + m] = v;
+            }
+        __syncthreads();
+        if (active && kslot == 0) {
+            if (p.swiglu) {
+                if (lane < (R / 2) * M) {
+                    const int r = lane / M, m = lane % M;
+                    float g = 0.f, u = 0.f;
+                    for (int k = 0; k < wk; k++) {
+                        g += red[warp + k][r * M + m];
+                        u += red[warp + k][(r + R / 2) * M + m];
+                    }
+                    int rw = row[0];
+#pragma unroll
+                    for (int rr = 1; rr < R / 2; rr++)
+                        if (r == rr) rw = row[rr];
+                    if (rw < p.seg[0].n_rows) {
+                        if (p.seg[0].bias) g += p.seg[0].bias[rw];
+                        if (p.seg[1].bias) u += p.seg[1].bias[rw];
+                        p.seg[0].y[(int64_t)m * p.seg[0].ldy + rw] = (g / (1.0f + expf(-g))) * u;
+                    }
+                }
+            } else if (lane < R * M) {
+                const int r = lane / M, m = lane % M;
+                float v = 0.f;
+                for (int k = 0; k < wk; k++) v += red[warp + k][r * M + m];
+                // row[] is register-resident per r; select without dynamic indexing
+                int rw = row[0];
+#pragma unroll
+                for (int rr = 1; rr < R; rr++)
+                    if (r == rr) rw = row[rr];
+                if (rw < sg.n_rows) {
+                    if (sg.bias) v += sg.bias[rw];
+                    if (p.residual) v += p.residual[(int64_t)m * sg.ldy + rw];
+                    sg.y[(int64_t)m * sg.ldy + rw] = v;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- exact per-block integer sums (parity instrumentation) -----------------------------------
+// Uses the same per-lane integer routines as the GEMV; lanes of a block add their shares with
+// integer atomics (exact, order-independent) into zero-initialised outputs.
+__global__ void __launch_bounds__(128) block_sums_kernel(uint32_t type, const uint8_t *W,
+                                                         const int8_t *aq, const int16_t *abs16,
+                                                         int M, int N, int K, int32_t *sumi,
+                                                         int32_t *summ) {
+    const int nb = K / 256;
+    const int lane = threadIdx.x & 31, sub = lane >> 3, c = lane & 7;
+    const int64_t warp = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int groups = (nb + 3) / 4;
+    const int64_t total = (int64_t)M * N * groups;
+    if (warp >= total) return;
+    const int gi = (int)(warp % groups);
+    const int n = (int)((warp / groups) % N);
+    const int m = (int)(warp / groups / N);
+    const int blk = gi * 4 + sub;
+    if (blk >= nb) return;
+    const uint8_t *rp = W + (int64_t)n * kq_device_row_bytes(type, K);
+    const int64_t o = ((int64_t)m * N + n) * nb + blk;
+    if (type == B200_TYPE_Q4_K) {
+        const int e_lo = 64 * (c >> 1) + 16 * (c & 1);
+        const uint8_t *b = rp + (int64_t)blk * KQ_Q4K_BYTES;
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        const uint4 w = kq_ld_stream(b + 16 + 16 * c);
+        const Q4Scales sc = q4k_lane_scales(hdr, c);
+        const int8_t *a = aq + (int64_t)m * K + blk * 256 + e_lo;
+        const int4 alo = *reinterpret_cast<const int4 *>(a);
+        const int4 ahi = *reinterpret_cast<const int4 *>(a + 32);
+        const int16_t *s16 = abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+        int isum, msum;
+        q4k_lane_ints(w, sc, alo, ahi, s16[0], s16[2], isum, msum);
+        atomicAdd(&sumi[o], isum);
+        if (summ) atomicAdd(&summ[o], msum);
+    } else {
+        const int h = c >> 2, cc = c & 3, e_lo = 128 * h + 16 * cc;
+        const uint4 ql = kq_ld_stream(rp + (int64_t)blk * 128 + 16 * c);
+        const uint4 qh = __ldg(reinterpret_cast<const uint4 *>(rp + (int64_t)nb * 128 + (int64_t)blk * 64 +
+                                                               16 * (2 * h + (cc & 1))));
+        const int8_t *scp = reinterpret_cast<const int8_t *>(rp + (int64_t)nb * 192 + (int64_t)blk * 16);
+        const int8_t *a = aq + (int64_t)m * K + blk * 256 + e_lo;
+        const int4 alo = *reinterpret_cast<const int4 *>(a);
+        const int4 ahi = *reinterpret_cast<const int4 *>(a + 64);
+        const int16_t *s16 = abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+        const int isum = q6k_lane_ints(ql, qh, cc, scp[8 * h + cc], scp[8 * h + 4 + cc], alo, ahi,
+                                       s16[0], s16[4]);
+        atomicAdd(&sumi[o], isum);
+    }
+}
+
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+template <int M, int R>
+b200_status launch_mr(const GemvParams &p, int wn, cudaStream_t st) {
+    static int ctas_per_sm = 0;
+    if (!ctas_per_sm) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_kernel<M, R>, 128, 0);
+        if (ctas_per_sm < 1) ctas_per_sm = 1;
+    }
+    int64_t want = kq_div_up(p.n_rg, wn);
+    int64_t cap = (int64_t)kq_sm_count() * ctas_per_sm;
+    int grid = (int)(want < cap ? want : cap);
+    if (grid < 1) grid = 1;
+    gemv_kernel<M, R><<<grid, 128, 0, st>>>(p);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+} // namespace
+
+b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
+                           const int16_t *bs, int M, int64_t K, const float *residual,
+                           int swiglu_pairs, cudaStream_t st) {
+    KQ_REQUIRE(nseg >= 1 && nseg <= 3, "gemv: 1..3 segments");
+    KQ_REQUIRE(M >= 1 && M <= 8, "gemv: M must be 1..8 (got %d)", M);
+    KQ_REQUIRE(K > 0 && K % 256 == 0, "gemv: K must be a positive multiple of 256");
+    KQ_REQUIRE(!swiglu_pairs || (nseg == 2 && segs[0].type == segs[1].type &&
+                                 segs[0].n_rows == segs[1].n_rows),
+               "gemv: swiglu needs two equal segments");
+    KQ_REQUIRE(!residual || nseg == 1, "gemv: residual only with one segment");
+    GemvParams p = {};
+    const int R = M <= 4 ? 4 : 2;
+    const int rows_per_rg = swiglu_pairs ? R / 2 : R;
+    int tot = 0;
+    for (int i = 0; i < nseg; i++) {
+        KQ_REQUIRE(segs[i].type == B200_TYPE_Q4_K || segs[i].type == B200_TYPE_Q6_K,
+                   "gemv: weight type %u not supported", segs[i].type);
+        KQ_REQUIRE(((uintptr_t)segs[i].W & 15) == 0, "gemv: weights must be 16-byte aligned");
+        p.seg[i] = segs[i];
+        if (!(swiglu_pairs && i == 1)) tot += (int)kq_div_up(segs[i].n_rows, rows_per_rg);
+        p.rg_end[i] = tot;
+    }
+    KQ_REQUIRE(((uintptr_t)q & 15) == 0, "gemv: activations must be 16-byte aligned");
+    p.nseg = swiglu_pairs ? 1 : nseg;
+    p.n_rg = tot;
+    p.nb = (int)(K / 256);
+    p.K = (int)K;
+    p.swiglu = swiglu_pairs;
+    p.aq = q;
+    p.ad = d;
+    p.abs16 = bs;
+    p.residual = residual;
+    const int its = (p.nb + 3) / 4;
+    int wk = its >= 16 ? 4 : (its >= 8 ? 2 : 1);
+    wk = env_int("B200_GEMV_WK", wk);
+    if (wk != 1 && wk != 2 && wk != 4) wk = 1;
+    p.wk = wk;
+    const int wn = 4 / wk;
+    switch (M) {
+    case 1: return launch_mr<1, 4>(p, wn, st);
+    case 2: return launch_mr<2, 4>(p, wn, st);
+    case 3: return launch_mr<3, 4>(p, wn, st);
+    case 4: return launch_mr<4, 4>(p, wn, st);
+    case 5: return launch_mr<5, 2>(p, wn, st);
+    case 6: return launch_mr<6, 2>(p, wn, st);
+    case 7: return launch_mr<7, 2>(p, wn, st);
+    default: return launch_mr<8, 2>(p, wn, st);
+    }
+}
+
+extern "C" b200_status b200_block_sums(uint32_t type, const void *W, const int8_t *q,
+                                       const int16_t *bsum16, int64_t M, int64_t N, int64_t K,
+                                       int32_t *sumi, int32_t *summ, void *stream) {
+    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "block_sums: type %u", type);
+    KQ_REQUIRE(K > 0 && K % 256 == 0 && M > 0 && N > 0, "block_sums: bad shape");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t nb = K / 256, cnt = M * N * nb;
+    KQ_CUDA(cudaMemsetAsync(sumi, 0, cnt * 4, st));
+    if (summ) KQ_CUDA(cudaMemsetAsync(summ, 0, cnt * 4, st));
+    const int64_t warps = M * N * ((nb + 3) / 4);
+    block_sums_kernel<<<(unsigned)kq_div_up(warps, 4), 128, 0, st>>>(
+        type, (const uint8_t *)W, q, bsum16, (int)M, (int)N, (int)K, sumi, summ);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}

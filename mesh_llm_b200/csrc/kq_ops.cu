@@ -1,0 +1,511 @@
+// The small ops around the quantised contraction: RoPE, KV-cache write, causal attention over an
+// f16 KV cache (split-KV, GQA-aware), SwiGLU, adds, embedding rows, argmax and the MoE router.
+// All of them are bandwidth-trivial next to the weight stream; they are written to cost few
+// launches and to read the KV cache once per group of query heads.
+#include "kq_common.cuh"
+
+#include <math.h>
+
+namespace {
+
+struct RopeTable {
+    float inv_freq[128]; // head_dim / 2 entries used
+};
+
+// q: [rows][n_head][hd] f32 rotated in place.  k (optional): [rows][n_kv][hd] f32 rotated and
+// stored as f16 into the cache at the row's position; v likewise without rotation.
+__global__ void rope_store_kernel(float *q, const float *k, const float *v, const int32_t *pos,
+                                  int pos0, int T, int n_head, int n_kv, int hd, int neox,
+                                  RopeTable tab, __half *k_cache, __half *v_cache,
+                                  int64_t seq_stride) {
+    const int row = blockIdx.x; // row = seq * T + t
+    const int seq = row / T, t = row % T;
+    const int p = pos ? pos[row] : pos0 + t;
+    const int half = hd / 2;
+    const int n_rot = (n_head + (k ? n_kv : 0)) * half;
+    for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+        const int hidx = i / half, f = i % half;
+        const float ang = (float)p * tab.inv_freq[f];
+        const float c = cosf(ang), s = sinf(ang);
+        const int i0 = neox ? f : 2 * f, i1 = neox ? f + half : 2 * f + 1;
+        if (hidx < n_head) {
+            float *vv = q + ((int64_t)row * n_head + hidx) * hd;
+            const float a = vv[i0], b = vv[i1];
+            vv[i0] = a * c - b * s;
+            vv[i1] = a * s + b * c;
+        } else {
+            const int kh = hidx - n_head;
+            const float *vv = k + ((int64_t)row * n_kv + kh) * hd;
+            __half *dst = k_cache + seq * seq_stride + ((int64_t)p * n_kv + kh) * hd;
+            const float a = vv[i0], b = vv[i1];
+            dst[i0] = __float2half_rn(a * c - b * s);
+            dst[i1] = __float2half_rn(a * s + b * c);
+        }
+    }
+    if (v) {
+        const int n = n_kv * hd;
+        __half *dst = v_cache + seq * seq_stride + (int64_t)p * n;
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            dst[i] = __float2half_rn(v[(int64_t)row * n + i]);
+    }
+}
+
+// ---- attention ---------------------------------------------------------------------------------
+// grid (n_kv, n_split, rows); 128 threads.  A CTA serves the G = n_head / n_kv query heads that
+// share one KV head, for one query row, over one slice of the positions.  Inside a warp each lane
+// scores one position against all G heads (K row read once), the tile's probabilities go through
+// shared memory, and each lane accumulates 4 of the 128 output dims for all G heads.
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q,
+                                                        const __half *__restrict__ kc,
+                                                        const __half *__restrict__ vc, int T, int pos0,
+                                                        int n_head, int n_kv, int64_t seq_stride,
+                                                        int n_split, float scale, float *out,
+                                                        float *part_o, float *part_ml) {
+    constexpr int DPL = HD / 32; // output dims per lane
+    __shared__ float q_s[G][HD];
+    __shared__ float p_s[4][G][32];
+    __shared__ float o_s[4][G][HD];
+    __shared__ float ml_s[4][G][2];
+    const int kh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
+    const int seq = row / T, t = row % T;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int L = pos0 + t + 1;
+    int chunk = (L + n_split - 1) / n_split;
+    chunk = (chunk + 127) / 128 * 128;
+    const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
+
+    for (int i = threadIdx.x; i < G * HD; i += 128)
+        q_s[i / HD][i % HD] = q[((int64_t)row * n_head + kh * G + i / HD) * HD + i % HD] * scale;
+    __syncthreads();
+
+    const __half *kbase = kc + seq * seq_stride + (int64_t)kh * HD;
+    const __half *vbase = vc + seq * seq_stride + (int64_t)kh * HD;
+    const int64_t pstride = (int64_t)n_kv * HD;
+
+    float m[G], l[G], o[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o[g][i] = 0.f;
+    }
+    for (int tb = p_begin + warp * 32; tb < p_end; tb += 128) {
+        const int p = tb + lane;
+        const bool valid = p < p_end;
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) s[g] = 0.f;
+        if (valid) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + p * pstride);
+#pragma unroll 4
+            for (int c8 = 0; c8 < HD / 8; c8++) {
+                const uint4 raw = kr[c8];
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                float kf[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(h2[i]);
+                    kf[2 * i] = f.x;
+                    kf[2 * i + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; g++)
+#pragma unroll
+                    for (int i = 0; i < 8; i++) s[g] = fmaf(q_s[g][c8 * 8 + i], kf[i], s[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float sv = valid ? s[g] : -INFINITY;
+            const float mt = kq_warp_max(sv);
+            const float mn = fmaxf(m[g], mt);
+            const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - mn);
+            const float pv = valid ? expf(sv - mn) : 0.f;
+            l[g] = l[g] * alpha + kq_warp_sum(pv);
+            m[g] = mn;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) o[g][i] *= alpha;
+            p_s[warp][g][lane] = pv;
+        }
+        __syncwarp();
+        const int cnt = min(32, p_end - tb);
+        for (int j = 0; j < cnt; j++) {
+            const __half *vr = vbase + (tb + j) * pstride + lane * DPL;
+            float vf[DPL];
+            if (DPL == 4) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                const float2 a = __half22float2(h2[0]), b = __half22float2(h2[1]);
+                vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPL; i++) vf[i] = __half2float(vr[i]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float pv = p_s[warp][g][j];
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+            }
+        }
+        __syncwarp();
+    }
+    // combine the 4 warps of the CTA
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o_s[warp][g][lane * DPL + i] = o[g][i];
+        if (lane == 0) {
+            ml_s[warp][g][0] = m[g];
+            ml_s[warp][g][1] = l[g];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += 128) {
+        const int g = i / HD, dim = i % HD;
+        float mm = -INFINITY;
+        for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[w][g][0]);
+        float acc = 0.f, ll = 0.f;
+        for (int w = 0; w < 4; w++) {
+            const float mw = ml_s[w][g][0];
+            const float wgt = (mw == -INFINITY) ? 0.f : expf(mw - mm);
+            acc += wgt * o_s[w][g][dim];
+            ll += wgt * ml_s[w][g][1];
+        }
+        const int head = kh * G + g;
+        if (n_split == 1) {
+            out[((int64_t)row * n_head + head) * HD + dim] = acc / ll;
+        } else {
+            const int64_t pi = ((int64_t)row * n_head + head) * n_split + split;
+            part_o[pi * HD + dim] = acc;
+            if (dim == 0) {
+                part_ml[pi * 2] = mm;
+                part_ml[pi * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+template <int HD>
+__global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int n_head,
+                                         int n_split, float *out) {
+    const int head = blockIdx.x, row = blockIdx.y, dim = threadIdx.x;
+    const int64_t base = ((int64_t)row * n_head + head) * n_split;
+    float mm = -INFINITY;
+    for (int s = 0; s < n_split; s++) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < n_split; s++) {
+        const float ms = part_ml[(base + s) * 2];
+        const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - mm);
+        acc += wgt * part_o[(base + s) * HD + dim];
+        ll += wgt * part_ml[(base + s) * 2 + 1];
+    }
+    out[((int64_t)row * n_head + head) * HD + dim] = acc / ll;
+}
+
+__global__ void swiglu_kernel(const float *g, const float *u, int64_t n, float *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float a = g[i];
+        y[i] = (a / (1.0f + expf(-a))) * u[i];
+    }
+}
+__global__ void add_kernel(const float *a, const float *b, int64_t n, float *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = a[i] + b[i];
+}
+__global__ void add_bias_kernel(float *y, const float *bias, int64_t total, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) y[i] += bias[i % n];
+}
+__global__ void cpy_f16_kernel(const float *x, int64_t n, __half *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __float2half_rn(x[i]);
+}
+
+// embedding rows: one thread per element
+__global__ void get_rows_kernel(uint32_t type, const uint8_t *W, const int32_t *ids, int64_t T, int K,
+                                float *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * K) return;
+    const int64_t t = i / K;
+    const int e = (int)(i % K), b = e >> 8, j = e & 255;
+    const int nb = K >> 8;
+    const uint8_t *rp = W + (int64_t)ids[t] * kq_device_row_bytes(type, K);
+    float v;
+    if (type == B200_TYPE_Q4_K) {
+        const uint8_t *blk = rp + (int64_t)b * KQ_Q4K_BYTES;
+        const float d = kq_h2f(*reinterpret_cast<const uint16_t *>(blk));
+        const float dmin = kq_h2f(*reinterpret_cast<const uint16_t *>(blk + 2));
+        const uint8_t *s = blk + 4;
+        const int sb = j >> 5;
+        int sc, mn;
+        if (sb < 4) {
+            sc = s[sb] & 63;
+            mn = s[sb + 4] & 63;
+        } else {
+            sc = (s[sb + 4] & 0xF) | ((s[sb - 4] >> 6) << 4);
+            mn = (s[sb + 4] >> 4) | ((s[sb] >> 6) << 4);
+        }
+        const uint8_t qb = blk[16 + 32 * (j >> 6) + (j & 31)];
+        const int qv = (j & 32) ? (qb >> 4) : (qb & 0xF);
+        v = d * (float)sc * (float)qv - dmin * (float)mn;
+    } else if (type == B200_TYPE_Q6_K) {
+        const int h = j >> 7, r = j & 127, k = r >> 5, i5 = r & 31;
+        const uint8_t lb = rp[(int64_t)b * 128 + 64 * h + 32 * (k & 1) + i5];
+        const uint8_t hb = rp[(int64_t)nb * 128 + (int64_t)b * 64 + 32 * h + i5];
+        const int lo = (k & 2) ? (lb >> 4) : (lb & 0xF);
+        const int qv = (lo | (((hb >> (2 * k)) & 3) << 4)) - 32;
+        const int sc = (int8_t)rp[(int64_t)nb * 192 + b * 16 + (j >> 4)];
+        const float d = kq_h2f(*reinterpret_cast<const uint16_t *>(rp + (int64_t)nb * 208 + b * 2));
+        v = d * (float)sc * (float)qv;
+    } else {
+        v = reinterpret_cast<const float *>(rp)[e];
+    }
+    y[i] = v;
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *x, int64_t n, int32_t *idx) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float *xr = x + (int64_t)blockIdx.x * n;
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = xr[i];
+        if (v > best || (v == best && (int)i < besti)) { best = v; besti = (int)i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = besti; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? bv[threadIdx.x] : -INFINITY;
+        besti = threadIdx.x < (blockDim.x >> 5) ? bi[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if (threadIdx.x == 0) idx[blockIdx.x] = besti == 0x7fffffff ? 0 : besti;
+    }
+}
+
+// router: one warp per token; E <= 256, k <= 32
+__global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int64_t T, int E, int k,
+                                                        int32_t *ids, float *w) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float *lr = logits + t * E;
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        v[i] = e < E ? lr[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = kq_warp_max(mx);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;
+        if (v[i] > 0.f) den += v[i];
+    }
+    den = kq_warp_sum(den);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        if (v[i] >= 0.f) v[i] = v[i] / den;
+    float wsum = 0.f, mine = 0.f;
+    int myid = 0;
+    for (int s = 0; s < k; s++) {
+        float best = -1.f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int e = lane + 32 * i;
+            if (v[i] > best || (v[i] == best && e < be)) { best = v[i]; be = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+        }
+        wsum += best;
+        if (lane == s) { mine = best; myid = be; }
+        if ((be & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (i == (be >> 5)) v[i] = -2.f; // taken
+        }
+    }
+    if (lane < k) {
+        ids[t * k + lane] = myid;
+        w[t * k + lane] = mine / wsum;
+    }
+}
+
+template <int HD>
+b200_status launch_attention_g(int G, dim3 grid, const float *q, const __half *kc, const __half *vc,
+                               int T, int pos0, int n_head, int n_kv, int64_t seq_stride, int n_split,
+                               float scale, float *out, float *po, float *pml, cudaStream_t st) {
+#define KQ_ATT(GG)                                                                                  \
+    attention_kernel<HD, GG><<<grid, 128, 0, st>>>(q, kc, vc, T, pos0, n_head, n_kv, seq_stride,    \
+                                                   n_split, scale, out, po, pml)
+    switch (G) {
+    case 1: KQ_ATT(1); break;
+    case 2: KQ_ATT(2); break;
+    case 4: KQ_ATT(4); break;
+    case 5: KQ_ATT(5); break;
+    case 8: KQ_ATT(8); break;
+    default: kq_set_error("attention: %d query heads per KV head not supported", G); return B200_ERR_UNSUPPORTED;
+    }
+#undef KQ_ATT
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+} // namespace
+
+int kq_attention_splits(int64_t rows, int n_kv, int64_t L) {
+    const int64_t ctas = rows * n_kv;
+    int64_t want = kq_div_up(2 * (int64_t)kq_sm_count(), ctas);
+    int64_t cap = kq_div_up(L, 128);
+    if (want > cap) want = cap;
+    if (want > 64) want = 64;
+    return want < 1 ? 1 : (int)want;
+}
+
+// rows = n_seq * T query rows; caches of sequence s start at s * seq_stride elements.
+b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
+                         int pos0, int n_head, int n_kv, int hd, int64_t seq_stride, float *out,
+                         float *scratch, size_t scratch_bytes, cudaStream_t st) {
+    KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
+    KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
+    const int rows = n_seq * T, G = n_head / n_kv;
+    int n_split = kq_attention_splits(rows, n_kv, pos0 + T);
+    const size_t need = (size_t)rows * n_head * n_split * (hd + 2) * sizeof(float);
+    if (n_split > 1 && need > scratch_bytes) n_split = 1;
+    float *po = scratch, *pml = scratch ? scratch + (size_t)rows * n_head * n_split * hd : nullptr;
+    const float scale = 1.0f / sqrtf((float)hd);
+    dim3 grid(n_kv, n_split, rows);
+    b200_status rc;
+    if (hd == 128)
+        rc = launch_attention_g<128>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0, n_head,
+                                     n_kv, seq_stride, n_split, scale, out, po, pml, st);
+    else
+        rc = launch_attention_g<64>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0, n_head,
+                                    n_kv, seq_stride, n_split, scale, out, po, pml, st);
+    if (rc != B200_OK) return rc;
+    if (n_split > 1) {
+        dim3 g2(n_head, rows);
+        if (hd == 128) attention_combine_kernel<128><<<g2, 128, 0, st>>>(po, pml, n_head, n_split, out);
+        else attention_combine_kernel<64><<<g2, 64, 0, st>>>(po, pml, n_head, n_split, out);
+        KQ_COUNT_LAUNCH();
+        KQ_LAUNCH_CHECK();
+    }
+    return B200_OK;
+}
+
+b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos, int pos0,
+                          int n_seq, int T, int n_head, int n_kv, int hd, float theta, int neox,
+                          uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride, cudaStream_t st) {
+    KQ_REQUIRE(hd % 2 == 0 && hd <= 256, "rope: head_dim %d", hd);
+    RopeTable tab;
+    for (int i = 0; i < hd / 2; i++) tab.inv_freq[i] = (float)pow((double)theta, -2.0 * i / (double)hd);
+    rope_store_kernel<<<n_seq * T, 256, 0, st>>>(q, k, v, pos, pos0, T, n_head, n_kv, hd, neox, tab,
+                                                 (__half *)k_cache, (__half *)v_cache, seq_stride);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+extern "C" {
+
+b200_status b200_rope(float *x, const int32_t *pos, int64_t T, int64_t n_head, int64_t hd, float theta,
+                      int32_t neox, void *stream) {
+    KQ_REQUIRE(T > 0 && pos, "rope: positions required");
+    return kq_rope_store(x, nullptr, nullptr, pos, 0, 1, (int)T, (int)n_head, 0, (int)hd, theta, neox,
+                         nullptr, nullptr, 0, (cudaStream_t)stream);
+}
+
+b200_status b200_swiglu(const float *gate, const float *up, int64_t n, float *y, void *stream) {
+    swiglu_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(gate, up, n, y);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+b200_status b200_add(const float *a, const float *b, int64_t n, float *y, void *stream) {
+    add_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, y);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+b200_status b200_add_bias(float *y, const float *bias, int64_t T, int64_t n, void *stream) {
+    add_bias_kernel<<<(unsigned)kq_div_up(T * n, 256), 256, 0, (cudaStream_t)stream>>>(y, bias, T * n, n);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+b200_status b200_cpy_f32_f16(const float *x, int64_t n, uint16_t *y, void *stream) {
+    cpy_f16_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(x, n, (__half *)y);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+size_t b200_attention_scratch_bytes(int64_t T, int64_t n_head, int64_t hd, int64_t n_ctx) {
+    return (size_t)T * n_head * 64 * (hd + 2) * sizeof(float);
+}
+
+b200_status b200_attention(const float *q, const uint16_t *k_cache, const uint16_t *v_cache, int64_t T,
+                           int64_t pos0, int64_t n_head, int64_t n_kv, int64_t hd, float *out,
+                           void *scratch, size_t scratch_bytes, void *stream) {
+    KQ_REQUIRE(T > 0 && pos0 >= 0, "attention: bad shape");
+    return kq_attention(q, k_cache, v_cache, 1, (int)T, (int)pos0, (int)n_head, (int)n_kv, (int)hd, 0,
+                        out, (float *)scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T, int64_t K,
+                          float *y, void *stream) {
+    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K || type == B200_TYPE_F32,
+               "get_rows: type %u", type);
+    KQ_REQUIRE(type == B200_TYPE_F32 || K % 256 == 0, "get_rows: K %% 256");
+    get_rows_kernel<<<(unsigned)kq_div_up(T * K, 256), 256, 0, (cudaStream_t)stream>>>(
+        type, (const uint8_t *)W, ids, T, (int)K, y);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream) {
+    argmax_kernel<<<(unsigned)T, 1024, 0, (cudaStream_t)stream>>>(x, n, idx);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w,
+                           void *stream) {
+    KQ_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= 32 && k <= E, "moe_route: E <= 256, k <= 32");
+    moe_route_kernel<<<(unsigned)kq_div_up(T, 4), 128, 0, (cudaStream_t)stream>>>(logits, T, (int)E, (int)k,
+                                                                                ids, w);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+} // extern "C"

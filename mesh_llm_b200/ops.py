@@ -1,0 +1,159 @@
+"""Host-side mirror of the op surface: thin wrappers that hand torch CUDA tensors to the C ABI.
+
+Every function launches hand-written sm_100a kernels from libb200kq.so on the current torch
+stream.  Tensors follow ggml's convention with the contiguous dimension last in torch terms:
+weights [N, K-bytes] uint8, activations [M, K] float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import capi
+from .capi import TYPE_F32, TYPE_Q4_K, TYPE_Q6_K, check, lib, ptr, cur_stream
+
+Q4K_BYTES, Q6K_BYTES = 144, 210
+
+
+def _dev(t):
+    if not t.is_cuda:
+        raise ValueError("expected a CUDA tensor: this library has no CPU path")
+    return t
+
+
+def row_bytes(type_, k):
+    return lib().b200_row_bytes(type_, k)
+
+
+def device_row_bytes(type_, k):
+    return lib().b200_device_row_bytes(type_, k)
+
+
+def upload_weights(type_, gguf_rows, n_rows, k, device="cuda"):
+    """GGUF-layout rows (numpy/torch uint8) -> device-layout uint8 tensor [n_rows, device_row_bytes]."""
+    src = torch.as_tensor(gguf_rows).reshape(-1).to(device=device, dtype=torch.uint8)
+    if type_ != TYPE_Q6_K:
+        return src.reshape(n_rows, -1).contiguous()
+    pad = torch.zeros(16, dtype=torch.uint8, device=device)  # keep u16 reads of the tail in bounds
+    src = torch.cat([src, pad])
+    out = torch.zeros((n_rows, device_row_bytes(type_, k)), dtype=torch.uint8, device=device)
+    check(lib().b200_repack_q6k(ptr(src), ptr(out), n_rows, k, cur_stream()))
+    return out
+
+
+def download_weights(type_, dev_rows, n_rows, k):
+    """inverse of upload_weights -> uint8 tensor of GGUF bytes on the device"""
+    if type_ != TYPE_Q6_K:
+        return dev_rows.reshape(-1).clone()
+    out = torch.empty(n_rows * row_bytes(type_, k), dtype=torch.uint8, device=dev_rows.device)
+    check(lib().b200_unpack_q6k(ptr(dev_rows), ptr(out), n_rows, k, cur_stream()))
+    return out
+
+
+def quantize_act(x):
+    x = _dev(x).contiguous().float()
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    d = torch.empty((M, K // 256), dtype=torch.float32, device=x.device)
+    bs = torch.empty((M, K // 16), dtype=torch.int16, device=x.device)
+    check(lib().b200_quantize_act(ptr(x), M, K, ptr(q), ptr(d), ptr(bs), cur_stream()))
+    return q, d, bs
+
+
+def mul_mat(type_, W, x, N, K, scratch=None):
+    x = _dev(x).contiguous().float().reshape(-1, K)
+    M = x.shape[0]
+    need = lib().b200_mul_mat_scratch_bytes(M, K)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    check(lib().b200_mul_mat(type_, ptr(W), ptr(x), M, N, K, ptr(y), ptr(scratch), scratch.numel(),
+                             cur_stream()))
+    return y
+
+
+def mul_mat_q8(type_, W, q, d, bs, N, K, bias=None, residual=None, out=None):
+    M = q.shape[0]
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=q.device)
+    check(lib().b200_mul_mat_q8(type_, ptr(W), ptr(q), ptr(d), ptr(bs), M, N, K, ptr(y), ptr(bias),
+                                ptr(residual), cur_stream()))
+    return y
+
+
+def block_sums(type_, W, q, bs, N, K):
+    M = q.shape[0]
+    sumi = torch.empty((M, N, K // 256), dtype=torch.int32, device=q.device)
+    summ = torch.empty((M, N, K // 256), dtype=torch.int32, device=q.device)
+    check(lib().b200_block_sums(type_, ptr(W), ptr(q), ptr(bs), M, N, K, ptr(sumi), ptr(summ),
+                                cur_stream()))
+    return sumi, summ
+
+
+def rms_norm(x, w, eps):
+    x = _dev(x).contiguous().float()
+    T, h = x.shape
+    y = torch.empty_like(x)
+    check(lib().b200_rms_norm(ptr(x), ptr(w), T, h, eps, ptr(y), cur_stream()))
+    return y
+
+
+def rope(x, pos, theta, neox):
+    """x: [T, n_head, hd] f32 (copied), pos: [T] int32"""
+    x = _dev(x).contiguous().float().clone()
+    T, nh, hd = x.shape
+    pos = pos.to(device=x.device, dtype=torch.int32).contiguous()
+    check(lib().b200_rope(ptr(x), ptr(pos), T, nh, hd, theta, int(neox), cur_stream()))
+    return x
+
+
+def swiglu(g, u):
+    y = torch.empty_like(g)
+    check(lib().b200_swiglu(ptr(g), ptr(u), g.numel(), ptr(y), cur_stream()))
+    return y
+
+
+def add(a, b):
+    y = torch.empty_like(a)
+    check(lib().b200_add(ptr(a), ptr(b), a.numel(), ptr(y), cur_stream()))
+    return y
+
+
+def cpy_f32_f16(x):
+    y = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    check(lib().b200_cpy_f32_f16(ptr(x), x.numel(), ptr(y), cur_stream()))
+    return y
+
+
+def attention(q, k_cache, v_cache, pos0):
+    """q: [T, n_head, hd] f32; caches: [n_ctx, n_kv, hd] f16 holding rows [0, pos0+T)"""
+    q = _dev(q).contiguous().float()
+    T, nh, hd = q.shape
+    n_ctx, nkv, _ = k_cache.shape
+    need = lib().b200_attention_scratch_bytes(T, nh, hd, n_ctx)
+    scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+    out = torch.empty_like(q)
+    check(lib().b200_attention(ptr(q), ptr(k_cache), ptr(v_cache), T, pos0, nh, nkv, hd, ptr(out),
+                               ptr(scratch), need, cur_stream()))
+    return out
+
+
+def get_rows(type_, W, ids, K):
+    ids = ids.to(device=W.device, dtype=torch.int32).contiguous()
+    y = torch.empty((ids.numel(), K), dtype=torch.float32, device=W.device)
+    check(lib().b200_get_rows(type_, ptr(W), ptr(ids), ids.numel(), K, ptr(y), cur_stream()))
+    return y
+
+
+def argmax(x):
+    x = _dev(x).contiguous().float()
+    idx = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    check(lib().b200_argmax(ptr(x), x.shape[0], x.shape[1], ptr(idx), cur_stream()))
+    return idx
+
+
+def moe_route(logits, k):
+    logits = _dev(logits).contiguous().float()
+    T, E = logits.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    check(lib().b200_moe_route(ptr(logits), T, E, k, ptr(ids), ptr(w), cur_stream()))
+    return ids, w

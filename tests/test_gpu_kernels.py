@@ -1,0 +1,235 @@
+"""GPU parity of the individual kernels against the CPU oracle, through the C ABI.
+
+Integer work (activation codes, block sums, repack round trips, argmax, routing ids) must be
+bit-exact; f32 outputs are compared with max |err| <= 1e-3 * max |ref| per tensor, the tolerance
+the hot-path specification states for layer outputs.
+"""
+import numpy as np
+import pytest
+
+from oracle import binding as orc
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-3
+
+
+def rel_err(got, ref):
+    ref = np.asarray(ref, np.float64)
+    got = np.asarray(got, np.float64)
+    return np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+
+    assert torch.cuda.is_available()
+    from mesh_llm_b200 import ops as o
+
+    return o
+
+
+def _weights(ty, N, K, seed, random_bytes=False):
+    rng = np.random.default_rng(seed)
+    if random_bytes:  # any valid block: exercises every scale / min code and negative Q6 scales
+        bpb = 144 if ty == orc.TYPE_Q4_K else 210
+        blk = rng.integers(0, 256, size=(N * K // 256, bpb), dtype=np.uint8)
+        if ty == orc.TYPE_Q4_K:
+            blk[:, 0:2] = rng.uniform(1e-4, 2e-2, N * K // 256).astype(np.float16).view(np.uint8).reshape(-1, 2)
+            blk[:, 2:4] = rng.uniform(0, 2e-2, N * K // 256).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        else:
+            blk[:, 208:210] = rng.uniform(1e-5, 2e-3, N * K // 256).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return blk.reshape(N, -1)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    return orc.quantize_weights(ty, w)
+
+
+def test_activation_codes_bit_exact(ops):
+    import torch
+
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((7, 5120)).astype(np.float32)
+    x[1, :256] = 0
+    x[2, 999] = 3e4
+    x[3] *= 1e-22
+    x[4] = np.round(x[4] * 2) / 2 + 0.5  # many exact .5 ties after scaling candidates
+    q, d, bs = ops.quantize_act(torch.from_numpy(x).cuda())
+    q2, d2, bs2 = orc.quantize_act(x)
+    np.testing.assert_array_equal(d.cpu().numpy(), d2)
+    np.testing.assert_array_equal(q.cpu().numpy(), q2)
+    np.testing.assert_array_equal(bs.cpu().numpy(), bs2)
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+def test_q6k_repack_round_trip_and_q4k_identity(ops, ty):
+    N, K = 37, 1280
+    W = _weights(ty, N, K, 1, random_bytes=True)
+    dev = ops.upload_weights(ty, W, N, K)
+    assert dev.shape[1] == ops.device_row_bytes(ty, K) and dev.shape[1] % 16 == 0
+    back = ops.download_weights(ty, dev, N, K).cpu().numpy()
+    np.testing.assert_array_equal(back, W.reshape(-1))
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+@pytest.mark.parametrize("N,K,M", [(64, 256, 1), (33, 768, 3), (130, 2816, 8), (24, 5120, 5)])
+def test_block_sums_bit_exact(ops, ty, N, K, M):
+    import torch
+
+    W = _weights(ty, N, K, 2, random_bytes=True)
+    x = np.random.default_rng(3).standard_normal((M, K)).astype(np.float32)
+    q, d, bs = orc.quantize_act(x)
+    ref_i, ref_m = orc.block_sums(ty, W, q, bs, N, K)
+    dev = ops.upload_weights(ty, W, N, K)
+    si, sm = ops.block_sums(ty, dev, torch.from_numpy(q).cuda(), torch.from_numpy(bs).cuda(), N, K)
+    np.testing.assert_array_equal(si.cpu().numpy(), ref_i)
+    if ty == orc.TYPE_Q4_K:
+        np.testing.assert_array_equal(sm.cpu().numpy(), ref_m)
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (67, 768), (512, 11008), (256, 8192)])
+def test_gemv_matches_oracle(ops, ty, M, N, K):
+    import torch
+
+    W = _weights(ty, N, K, 4)
+    x = np.random.default_rng(5 + M).standard_normal((M, K)).astype(np.float32)
+    ref = orc.mul_mat(ty, W, x, N, K)
+    dev = ops.upload_weights(ty, W, N, K)
+    y = ops.mul_mat(ty, dev, torch.from_numpy(x).cuda(), N, K).cpu().numpy()
+    assert rel_err(y, ref) <= REL
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+def test_gemv_random_blocks_and_split_k(ops, ty, monkeypatch):
+    import torch
+
+    N, K = 96, 27648  # long rows: K split over the warps of a CTA
+    W = _weights(ty, N, K, 6, random_bytes=True)
+    x = np.random.default_rng(7).standard_normal((2, K)).astype(np.float32)
+    ref = orc.mul_mat(ty, W, x, N, K)
+    dev = ops.upload_weights(ty, W, N, K)
+    xd = torch.from_numpy(x).cuda()
+    outs = []
+    for wk in ("1", "2", "4"):
+        monkeypatch.setenv("B200_GEMV_WK", wk)
+        outs.append(ops.mul_mat(ty, dev, xd, N, K).cpu().numpy())
+        assert rel_err(outs[-1], ref) <= REL
+    # a run is deterministic: same configuration twice gives the same bits
+    again = ops.mul_mat(ty, dev, xd, N, K).cpu().numpy()
+    np.testing.assert_array_equal(again, outs[-1])
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+def test_gemv_fused_bias_residual(ops, ty):
+    import torch
+
+    N, K, M = 300, 1024, 3
+    W = _weights(ty, N, K, 8)
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    ref = orc.mul_mat(ty, W, x, N, K) + bias + res
+    dev = ops.upload_weights(ty, W, N, K)
+    q, d, bs = ops.quantize_act(torch.from_numpy(x).cuda())
+    y = ops.mul_mat_q8(ty, dev, q, d, bs, N, K, bias=torch.from_numpy(bias).cuda(),
+                       residual=torch.from_numpy(res).cuda())
+    assert rel_err(y.cpu().numpy(), ref) <= REL
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+@pytest.mark.parametrize("M", [9, 64, 130])
+def test_prefill_contraction_matches_oracle(ops, ty, M):
+    import torch
+
+    N, K = 384, 2048
+    W = _weights(ty, N, K, 10)
+    x = np.random.default_rng(11).standard_normal((M, K)).astype(np.float32)
+    ref = orc.mul_mat(ty, W, x, N, K)
+    dev = ops.upload_weights(ty, W, N, K)
+    y = ops.mul_mat(ty, dev, torch.from_numpy(x).cuda(), N, K).cpu().numpy()
+    assert rel_err(y, ref) <= REL
+
+
+def test_mul_mat_rejects_bad_arguments(ops):
+    import torch
+    from mesh_llm_b200.capi import B200Error
+
+    W = torch.zeros(144 * 4, dtype=torch.uint8, device="cuda")
+    x = torch.zeros((1, 300), device="cuda")
+    with pytest.raises(B200Error):
+        ops.mul_mat(orc.TYPE_Q4_K, W, x, 4, 300)  # K not a multiple of 256
+    x = torch.zeros((1, 256), device="cuda")
+    with pytest.raises(B200Error):
+        ops.mul_mat(2, W, x, 4, 256)  # type id 2 (Q4_0) is not on the path
+
+
+def test_rms_norm_rope_swiglu_add(ops):
+    import torch
+
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((5, 5120)).astype(np.float32)
+    w = (1 + 0.02 * rng.standard_normal(5120)).astype(np.float32)
+    y = ops.rms_norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-6).cpu().numpy()
+    assert rel_err(y, orc.rms_norm(x, w, 1e-6)) <= 1e-5
+    v = rng.standard_normal((6, 8, 128)).astype(np.float32)
+    pos = np.array([0, 1, 2, 77, 2047, 4351], np.int32)
+    for neox, theta in ((1, 1e6), (0, 5e5)):
+        r = ops.rope(torch.from_numpy(v).cuda(), torch.from_numpy(pos), theta, neox).cpu().numpy()
+        assert rel_err(r, orc.rope(v, pos, theta, neox)) <= 1e-4
+    g = rng.standard_normal(10000).astype(np.float32) * 4
+    u = rng.standard_normal(10000).astype(np.float32)
+    s = ops.swiglu(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()).cpu().numpy()
+    assert rel_err(s, orc.swiglu(g, u)) <= 1e-6
+    a = ops.add(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(a, g + u)
+    h = ops.cpy_f32_f16(torch.from_numpy(g).cuda()).cpu().numpy().view(np.uint16)
+    np.testing.assert_array_equal(h, orc.f32_to_f16(g))
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(40, 8, 128), (16, 2, 128), (8, 2, 64), (4, 4, 128), (32, 4, 128)])
+@pytest.mark.parametrize("pos0,T", [(0, 1), (300, 1), (2047, 1), (0, 37), (100, 5)])
+def test_attention_matches_oracle(ops, nh, nkv, hd, pos0, T):
+    import torch
+
+    rng = np.random.default_rng(13)
+    n_ctx = pos0 + T + 3
+    k = rng.standard_normal((n_ctx, nkv, hd)).astype(np.float32)
+    v = rng.standard_normal((n_ctx, nkv, hd)).astype(np.float32)
+    kc, vc = orc.f32_to_f16(k), orc.f32_to_f16(v)
+    q = rng.standard_normal((T, nh, hd)).astype(np.float32)
+    ref = orc.attention(q, kc, vc, pos0)
+    out = ops.attention(torch.from_numpy(q).cuda(),
+                        torch.from_numpy(kc.view(np.float16)).cuda(),
+                        torch.from_numpy(vc.view(np.float16)).cuda(), pos0).cpu().numpy()
+    assert rel_err(out, ref) <= 1e-4
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+def test_get_rows_exact(ops, ty):
+    import torch
+
+    N, K = 50, 1024
+    W = _weights(ty, N, K, 14, random_bytes=True)
+    ids = np.array([0, 49, 7, 7, 13], np.int32)
+    dev = ops.upload_weights(ty, W, N, K)
+    y = ops.get_rows(ty, dev, torch.from_numpy(ids), K).cpu().numpy()
+    np.testing.assert_allclose(y, orc.get_rows(ty, W, ids, K), rtol=1e-6, atol=0)
+
+
+def test_argmax_and_router(ops):
+    import torch
+
+    rng = np.random.default_rng(15)
+    x = rng.standard_normal((4, 151936)).astype(np.float32)
+    x[1, 5] = x[1, 100000] = 9.0  # tie -> lower index
+    idx = ops.argmax(torch.from_numpy(x).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(idx, orc.argmax(x))
+    for E, k in ((128, 8), (16, 8), (8, 2)):
+        logits = rng.standard_normal((33, E)).astype(np.float32)
+        ids, w = ops.moe_route(torch.from_numpy(logits).cuda(), k)
+        rid, rw = orc.moe_route(logits, k)
+        np.testing.assert_array_equal(ids.cpu().numpy(), rid)
+        assert rel_err(w.cpu().numpy(), rw) <= 1e-5
