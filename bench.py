@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode (and prefill) tokens/s of a Q4_K_M Qwen2.5-32B-shaped decoder.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload cfg2|cfg1|cfg3]
+
+A step is one decode pass (one new token for every in-flight sequence) at context >= 2048.
+With N GPUs (one process per GPU under torch.distributed.run) the model is split into N
+contiguous layer ranges, one per rank, and N sequences are kept in flight so that every stage has
+work in every step (the per-GPU work per step is fixed: "weak" scaling).
+
+Prints ONE JSON line (rank 0).  Weights are synthetic: seeded N(0, 0.02) quantised on the device
+to the Q4_K_M mix; tokens are seeded uniform ids.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[0..2]
+    "cfg1": dict(name="Qwen2.5-3B-shape Q4_K_M", n_layer=36, n_embd=2048, n_head=16, n_head_kv=2,
+                 head_dim=128, n_ff=11008, n_vocab=151936, qkv_bias=1, rope_neox=1, rope_theta=1e6,
+                 rms_eps=1e-6, prefill=512, decode=128),
+    "cfg2": dict(name="Qwen2.5-32B-shape Q4_K_M", n_layer=64, n_embd=5120, n_head=40, n_head_kv=8,
+                 head_dim=128, n_ff=27648, n_vocab=152064, qkv_bias=1, rope_neox=1, rope_theta=1e6,
+                 rms_eps=1e-6, prefill=2048, decode=256),
+    "cfg3": dict(name="Llama-3-70B-shape Q4_K_M", n_layer=80, n_embd=8192, n_head=64, n_head_kv=8,
+                 head_dim=128, n_ff=28672, n_vocab=128256, qkv_bias=0, rope_neox=0, rope_theta=5e5,
+                 rms_eps=1e-5, prefill=4096, decode=256),
+}
+MODEL_KEYS = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
+              "rope_neox", "rope_theta", "rms_eps")
+BPW = {12: 144 / 256, 14: 210 / 256}
+METRIC = "decode tok/s, Q4_K_M 32B-shape, batch 1 per stage (GEMV HBM % of peak in roofline)"
+
+
+def matmuls(w, layer):
+    """(N, K, ggml type) of every quantised matmul of one layer, Q4_K_M mix"""
+    h, nq, nkv, ff = w["n_embd"], w["n_head"] * w["head_dim"], w["n_head_kv"] * w["head_dim"], w["n_ff"]
+    alt = 14 if layer & 1 else 12
+    return [(nq, h, 12), (nkv, h, 12), (nkv, h, alt), (h, nq, 12), (ff, h, 12), (ff, h, 12), (h, ff, alt)]
+
+
+def gemv_bytes(N, K, ty, M=1):
+    return N * K * BPW[ty] + 4 * M * K + 4 * M * N
+
+
+def step_gemv_bytes(w, l0, l1, has_output, M=1):
+    b = sum(gemv_bytes(N, K, ty, M) for l in range(l0, l1) for (N, K, ty) in matmuls(w, l))
+    if has_output:
+        b += gemv_bytes(w["n_vocab"], w["n_embd"], 14, M)
+    return b
+
+
+class ClockSampler:
+    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc:
+            self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ts, line in self.rows:
+            if ts < t0 - 0.05 or ts > t1 + 0.15:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_decode_sample(w, threads=None, reps=2):
+    """times the CPU oracle on one layer of each parity (+ the LM head) at M = 1 and extrapolates
+    to the full depth.  Returns (tok/s, cores, description)."""
+    from oracle import binding as orc
+
+    if threads:
+        orc.lib().orc_set_threads(threads)
+    cores = orc.lib().orc_get_threads()
+    rng = np.random.default_rng(0)
+    shapes = {}
+    for layer in (0, 1):
+        for (N, K, ty) in matmuls(w, layer):
+            shapes[(N, K, ty)] = shapes.get((N, K, ty), 0) + w["n_layer"] / 2
+    shapes[(w["n_vocab"], w["n_embd"], 14)] = 1
+    total = 0.0
+    for (N, K, ty), count in shapes.items():
+        rb = orc.row_bytes(ty, K)
+        W = rng.integers(0, 256, size=(N, rb), dtype=np.uint8)
+        x = rng.standard_normal((1, K)).astype(np.float32)
+        orc.mul_mat(ty, W, x, N, K)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.mul_mat(ty, W, x, N, K)
+        total += count * (time.perf_counter() - t0) / reps
+    return 1.0 / total, cores, (f"CPU oracle, M=1 quantised matmuls of one even + one odd layer and the LM head "
+                                f"({len(shapes)} shapes x {reps} reps), extrapolated x{w['n_layer']} layers; "
+                                f"attention and norms not included")
+
+
+def run_reference(args, w):
+    """--impl reference: the reference's llama.cpp CPU backend cannot be built here (sources are
+    fetched at build time and are not in the tree), so the CPU port of the same arithmetic runs on
+    the host cores.  A step is one bounded sample of the decode workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for i in range(args.warmup + args.steps):
+        toks, cores, sample = cpu_decode_sample(w, reps=1)
+        if i >= args.warmup:
+            vals.append(toks)
+    v = float(np.mean(vals))
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine",
+        "data": "synthetic", "config": {"workload": w["name"] + " decode, batch 1, CPU sample"},
+        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model depth")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["n_layer"] = args.layers
+    if args.impl == "reference":
+        return run_reference(args, w)
+    if max(args.warmup, 0) < 3:
+        args.warmup = 3
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+        args.gpus = world
+    if world > 1:
+        from mesh_llm_b200 import pipeline
+        return pipeline.bench_pipeline(args, w, METRIC, rank, world, local)
+
+    torch.cuda.set_device(local)
+    from mesh_llm_b200.capi import lib, check
+    from mesh_llm_b200.stage import Stage
+    import ctypes as C
+
+    model = {k: w[k] for k in MODEL_KEYS}
+    n_ctx = w["prefill"] + w["decode"] + args.steps + args.warmup + 64
+    n_seq = 8
+    st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local)
+    st.generate(20251125)
+    weight_bytes = st.weight_bytes()
+    dev = torch.device("cuda", local)
+    rng = np.random.default_rng(1234)
+
+    # ---- prefill: prompt of `prefill` uniform-random tokens in ubatches of 512 (sequence 0)
+    prompt = torch.from_numpy(rng.integers(0, w["n_vocab"], w["prefill"]).astype(np.int32)).to(dev)
+    prefill_tok_s = None
+    nxt = torch.zeros(1, dtype=torch.int32, device=dev)
+    logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev)
+    if not args.no_prefill:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for p0 in range(0, w["prefill"], 512):
+            chunk = prompt[p0:p0 + 512]
+            st.forward(tokens=chunk, n_seq=1, T=chunk.numel(), pos0=p0, logits=logits, next_tokens=nxt)
+        e1.record()
+        torch.cuda.synchronize()
+        prefill_tok_s = w["prefill"] / (e0.elapsed_time(e1) * 1e-3)
+    pos = w["prefill"]
+
+    # ---- decode, device resident: the stage feeds itself its own greedy token
+    tok = nxt.clone()
+    def decode_steps(k, pos):
+        for _ in range(k):
+            st.forward(tokens=tok, n_seq=1, T=1, pos0=pos, logits=logits, next_tokens=tok)
+            pos += 1
+        return pos
+    pos = decode_steps(args.warmup, pos)
+    torch.cuda.synchronize()
+    launches0 = st.kernel_launches()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    pos = decode_steps(args.steps, pos)
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    gpu_launches = st.kernel_launches() - launches0
+    value = args.steps / (ms * 1e-3)
+
+    # ---- decode, end to end: token ids arrive from pinned host memory, the result is read back
+    h_tok = torch.zeros(1, dtype=torch.int32).pin_memory()
+    h_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+    d_tok = torch.zeros(1, dtype=torch.int32, device=dev)
+    d_out = torch.zeros(1, dtype=torch.int32, device=dev)
+    h_tok[0] = int(tok.item())
+    def e2e_steps(k, pos):
+        for _ in range(k):
+            d_tok.copy_(h_tok, non_blocking=True)
+            st.forward(tokens=d_tok, n_seq=1, T=1, pos0=pos, logits=logits, next_tokens=d_out)
+            h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            h_tok[0] = h_out[0]
+            pos += 1
+        return pos
+    pos = e2e_steps(3, pos)
+    torch.cuda.synchronize()
+    tw0 = time.perf_counter()
+    e0.record()
+    pos = e2e_steps(args.steps, pos)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - tw0) * 1e3)
+    e2e_value = args.steps / (e2e_ms * 1e-3)
+    clocks = sampler.stop(t0, time.time())
+
+    # ---- the dominant kernel alone: all quantised GEMV launches of one step, replayed from a graph
+    # over the real weights of every layer (19 GB, so nothing is served from L2)
+    ms_gemv, n_gemv = C.c_float(), C.c_int64()
+    check(lib().b200_stage_profile_decode(st.h, 1, pos, 1, 10, C.byref(ms_gemv), C.byref(n_gemv)))
+    ms_all, n_all = C.c_float(), C.c_int64()
+    check(lib().b200_stage_profile_decode(st.h, 1, pos, 7, 10, C.byref(ms_all), C.byref(n_all)))
+    ms_attn, n_attn = C.c_float(), C.c_int64()
+    check(lib().b200_stage_profile_decode(st.h, 1, pos, 2, 10, C.byref(ms_attn), C.byref(n_attn)))
+    algo = step_gemv_bytes(w, 0, w["n_layer"], True, 1)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = algo / (ms_gemv.value * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_kernel (Q4_K/Q6_K x Q8 decode GEMV)", "achieved": achieved, "peak": peak,
+        "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
+        "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
+        "launches_per_step": int(n_gemv.value), "algorithmic_bytes_per_launch": algo / max(1, n_gemv.value),
+        "avg_launch_us": ms_gemv.value * 1e3 / max(1, n_gemv.value),
+        "gemv_ms_per_step": ms_gemv.value, "attention_ms_per_step": ms_attn.value,
+        "whole_step_graph_ms": ms_all.value,
+    }
+
+    # ---- batch-8 decode (8 slots of one server, same positions)
+    b8 = None
+    if n_seq >= 8:
+        tok8 = torch.from_numpy(rng.integers(0, w["n_vocab"], 8).astype(np.int32)).to(dev)
+        lg8 = torch.empty((8, w["n_vocab"]), dtype=torch.float32, device=dev)
+        p8 = pos
+        for _ in range(3):
+            st.forward(tokens=tok8, n_seq=8, T=1, pos0=p8, logits=lg8, next_tokens=tok8); p8 += 1
+        torch.cuda.synchronize()
+        e0.record()
+        k8 = max(8, args.steps // 4)
+        for _ in range(k8):
+            st.forward(tokens=tok8, n_seq=8, T=1, pos0=p8, logits=lg8, next_tokens=tok8); p8 += 1
+        e1.record()
+        torch.cuda.synchronize()
+        b8 = 8 * k8 / (e0.elapsed_time(e1) * 1e-3)
+
+    cpu = None
+    if not args.no_cpu:
+        v, cores, sample = cpu_decode_sample(w)
+        cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+
+    out = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine", "data": "synthetic",
+        "config": {"workload": f"{w['name']} ({w['n_layer']} layers), decode batch 1 at context {w['prefill']}+, "
+                               f"greedy, one stage on one GPU", "weight_bytes": weight_bytes,
+                   "l2": "each step streams all weights (>> 126 MB L2), no flush needed",
+                   "sequences_in_flight": 1},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        "prefill_tok_s": prefill_tok_s, "decode_batch8_tok_s": b8,
+        "decode_weight_stream_frac_of_hbm_peak": (weight_bytes / (ms / args.steps * 1e-3) / 1e9) / peak,
+    }
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -238,6 +238,13 @@ B200_API b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens,
                                         const float *hidden_in, int32_t n_seq_active, int32_t T,
                                         int32_t pos0, float *hidden_out, float *logits,
                                         int32_t all_logits, int32_t *next_tokens, void *stream);
+/* Timing instrumentation: captures one decode step (T = 1, n_seq sequences at position pos0) into
+ * a CUDA graph restricted to the kernel classes in `classes` (1 = quantised GEMV, 2 = attention,
+ * 4 = everything else, 7 = the whole step), replays it `iters` times and reports the mean device
+ * time per step measured with CUDA events.  Outputs of a partial step are meaningless.          */
+B200_API b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos0,
+                                               uint32_t classes, int32_t iters, float *ms_per_step,
+                                               int64_t *launches_per_step);
 B200_API b200_status b200_stage_synchronize(b200_stage *st);
 B200_API int64_t b200_stage_kernel_launches(b200_stage *st); /* launches issued so far        */
 

@@ -1,0 +1,449 @@
+// The ggml-shaped boundary: buffers that own device memory, tensor set/get with the Q6_K repack,
+// the device-to-device stage hand-off (cpy_tensor), and graph_compute over the ops of the hot path.
+//
+// The shape follows what the reference's RPC server does with a backend: alloc_buffer / get_base /
+// set_tensor / get_tensor / copy / graph_compute, every access bounds-checked against the owning
+// buffer (third_party/llama.cpp/patches/0001 lines 228-239, patches/0002 lines 570-582).
+#include "kq_common.cuh"
+
+#include <math.h>
+#include <mutex>
+#include <string.h>
+#include <unordered_map>
+#include <vector>
+
+b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y,
+                        int8_t *q, float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride = 0);
+b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
+                         const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
+                         int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
+                         int force_splits, cudaStream_t st);
+b200_status kq_f32_matmul(const float *W, const float *x, int64_t M, int64_t N, int64_t K, float *y,
+                          cudaStream_t st);
+
+struct b200_buffer {
+    int32_t dev;
+    uint8_t *base;
+    size_t size;
+};
+
+struct b200_backend {
+    int32_t dev;
+    cudaStream_t stream;
+    void *scratch;
+    size_t scratch_bytes;
+    std::mutex mu; // one graph at a time per device, as the reference serialises its backend calls
+};
+
+namespace {
+
+__global__ void mul_rows_kernel(const float *a, const float *b, int64_t total, int64_t n, int64_t nb_elems,
+                                float *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) y[i] = a[i] * b[nb_elems == total ? i : i % n];
+}
+__global__ void add_bcast_kernel(const float *a, const float *b, int64_t total, int64_t n, int64_t nb_elems,
+                                 float *y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) y[i] = a[i] + b[nb_elems == total ? i : i % n];
+}
+
+inline int64_t nelements(const b200_tensor *t) {
+    return (int64_t)t->ne[0] * t->ne[1] * t->ne[2] * t->ne[3];
+}
+inline int64_t nrows(const b200_tensor *t) { return (int64_t)t->ne[1] * t->ne[2] * t->ne[3]; }
+inline size_t gguf_bytes(const b200_tensor *t) {
+    if (t->type == B200_TYPE_I32) return (size_t)nelements(t) * 4;
+    return (size_t)(kq_row_bytes(t->type, t->ne[0]) * nrows(t));
+}
+inline size_t device_bytes(const b200_tensor *t) {
+    if (t->type == B200_TYPE_I32) return (size_t)nelements(t) * 4;
+    return (size_t)(kq_device_row_bytes(t->type, t->ne[0]) * nrows(t));
+}
+
+// tensor [data, data + device_bytes) must lie inside its buffer
+b200_status check_tensor(const b200_tensor *t) {
+    KQ_REQUIRE(t, "null tensor");
+    const b200_buffer *buf = (const b200_buffer *)(uintptr_t)t->buffer;
+    KQ_REQUIRE(buf && buf->base, "tensor %.64s has no buffer", t->name);
+    const uint64_t lo = (uint64_t)(uintptr_t)buf->base, hi = lo + buf->size;
+    const uint64_t need = device_bytes(t);
+    if (t->data < lo || t->data > hi || need > hi - t->data) {
+        kq_set_error("tensor %.64s: [%llx, +%llu) is outside its buffer [%llx, +%zu)", t->name,
+                     (unsigned long long)t->data, (unsigned long long)need, (unsigned long long)lo, buf->size);
+        return B200_ERR_BOUNDS;
+    }
+    if (t->type == B200_TYPE_Q4_K || t->type == B200_TYPE_Q6_K) {
+        KQ_REQUIRE(t->ne[0] % 256 == 0, "tensor %.64s: ne[0] must be a multiple of 256", t->name);
+        KQ_REQUIRE((t->data & 15) == 0, "tensor %.64s: quantised data must be 16-byte aligned", t->name);
+    }
+    return B200_OK;
+}
+
+#define KQ_TRY(expr)                      \
+    do {                                  \
+        b200_status rc__ = (expr);        \
+        if (rc__ != B200_OK) return rc__; \
+    } while (0)
+
+struct DevGuard {
+    int prev = -1;
+    explicit DevGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DevGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// host <-> Q6_K tensor with an arbitrary byte window: work on whole rows through a staging copy
+b200_status q6k_window(b200_buffer *buf, const b200_tensor *t, void *host, size_t offset, size_t size,
+                       bool write) {
+    const int64_t K = t->ne[0];
+    const size_t rb = (size_t)kq_row_bytes(B200_TYPE_Q6_K, K), drb = (size_t)kq_device_row_bytes(B200_TYPE_Q6_K, K);
+    const int64_t r0 = (int64_t)(offset / rb), r1 = (int64_t)((offset + size + rb - 1) / rb);
+    const int64_t n = r1 - r0;
+    uint8_t *dev_rows = (uint8_t *)(uintptr_t)t->data + (size_t)r0 * drb;
+    void *tmp = nullptr;
+    if (cudaMalloc(&tmp, (size_t)n * rb + 16) != cudaSuccess) {
+        cudaGetLastError();
+        kq_set_error("q6k staging allocation of %zu bytes failed", (size_t)n * rb);
+        return B200_ERR_ALLOC;
+    }
+    b200_status rc = B200_OK;
+    const bool whole = offset % rb == 0 && size % rb == 0;
+    const size_t in_off = offset - (size_t)r0 * rb;
+    if (write) {
+        if (!whole) rc = b200_unpack_q6k(dev_rows, tmp, n, K, nullptr);
+        if (rc == B200_OK && cudaMemcpy((uint8_t *)tmp + in_off, host, size, cudaMemcpyHostToDevice) != cudaSuccess)
+            rc = B200_ERR_CUDA;
+        if (rc == B200_OK) rc = b200_repack_q6k(tmp, dev_rows, n, K, nullptr);
+        if (rc == B200_OK && cudaDeviceSynchronize() != cudaSuccess) rc = B200_ERR_CUDA;
+    } else {
+        rc = b200_unpack_q6k(dev_rows, tmp, n, K, nullptr);
+        if (rc == B200_OK && cudaMemcpy(host, (uint8_t *)tmp + in_off, size, cudaMemcpyDeviceToHost) != cudaSuccess)
+            rc = B200_ERR_CUDA;
+    }
+    cudaFree(tmp);
+    if (rc == B200_ERR_CUDA) kq_set_error("q6k window transfer failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return rc;
+}
+
+b200_status window_check(b200_buffer *buf, const b200_tensor *t, const void *host, size_t offset, size_t size) {
+    KQ_REQUIRE(buf && t && (host || size == 0), "null argument");
+    KQ_REQUIRE((b200_buffer *)(uintptr_t)t->buffer == buf, "tensor %.64s does not belong to this buffer", t->name);
+    KQ_TRY(check_tensor(t));
+    const size_t total = gguf_bytes(t);
+    if (offset > total || size > total - offset) {
+        kq_set_error("tensor %.64s: window [%zu, +%zu) exceeds %zu bytes", t->name, offset, size, total);
+        return B200_ERR_BOUNDS;
+    }
+    return B200_OK;
+}
+
+float f32_param(const b200_tensor *t, int i) {
+    float f;
+    memcpy(&f, &t->op_params[i], 4);
+    return f;
+}
+
+} // namespace
+
+extern "C" {
+
+b200_status b200_buffer_alloc(int32_t dev, size_t size, b200_buffer **out) {
+    KQ_REQUIRE(out, "buffer_alloc: null out");
+    *out = nullptr;
+    KQ_REQUIRE(dev >= 0 && dev < b200_reg_device_count(), "buffer_alloc: no device %d", dev);
+    DevGuard g(dev);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, size ? size : 256);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        kq_set_error("buffer_alloc: cudaMalloc(%zu) on device %d failed: %s", size, dev, cudaGetErrorString(e));
+        return B200_ERR_ALLOC;
+    }
+    b200_buffer *b = new b200_buffer();
+    b->dev = dev;
+    b->base = (uint8_t *)p;
+    b->size = size;
+    *out = b;
+    return B200_OK;
+}
+
+void b200_buffer_free(b200_buffer *buf) {
+    if (!buf) return;
+    DevGuard g(buf->dev);
+    cudaFree(buf->base);
+    delete buf;
+}
+
+void *b200_buffer_get_base(b200_buffer *buf) { return buf ? buf->base : nullptr; }
+size_t b200_buffer_get_size(b200_buffer *buf) { return buf ? buf->size : 0; }
+int32_t b200_buffer_get_device(b200_buffer *buf) { return buf ? buf->dev : -1; }
+
+b200_status b200_buffer_clear(b200_buffer *buf, uint8_t value) {
+    KQ_REQUIRE(buf, "buffer_clear: null buffer");
+    DevGuard g(buf->dev);
+    KQ_CUDA(cudaMemset(buf->base, value, buf->size));
+    return B200_OK;
+}
+
+b200_status b200_buffer_init_tensor(b200_buffer *buf, b200_tensor *t) {
+    KQ_REQUIRE(buf && t, "init_tensor: null argument");
+    KQ_REQUIRE((b200_buffer *)(uintptr_t)t->buffer == buf, "init_tensor: tensor %.64s names another buffer", t->name);
+    return check_tensor(t);
+}
+
+b200_status b200_buffer_set_tensor(b200_buffer *buf, const b200_tensor *t, const void *host_data, size_t offset,
+                                   size_t size) {
+    KQ_TRY(window_check(buf, t, host_data, offset, size));
+    if (size == 0) return B200_OK;
+    DevGuard g(buf->dev);
+    if (t->type == B200_TYPE_Q6_K) return q6k_window(buf, t, const_cast<void *>(host_data), offset, size, true);
+    KQ_CUDA(cudaMemcpy((uint8_t *)(uintptr_t)t->data + offset, host_data, size, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+b200_status b200_buffer_get_tensor(b200_buffer *buf, const b200_tensor *t, void *host_data, size_t offset,
+                                   size_t size) {
+    KQ_TRY(window_check(buf, t, host_data, offset, size));
+    if (size == 0) return B200_OK;
+    DevGuard g(buf->dev);
+    if (t->type == B200_TYPE_Q6_K) return q6k_window(buf, t, host_data, offset, size, false);
+    KQ_CUDA(cudaMemcpy(host_data, (const uint8_t *)(uintptr_t)t->data + offset, size, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+int32_t b200_buffer_cpy_tensor(const b200_tensor *src, const b200_tensor *dst, size_t offset, size_t size) {
+    if (!src || !dst) return 0;
+    if (check_tensor(src) != B200_OK || check_tensor(dst) != B200_OK) return 0;
+    if (src->type != dst->type || src->type == B200_TYPE_Q6_K) return 0; // repacked rows: use set/get
+    const size_t ns = gguf_bytes(src), nd = gguf_bytes(dst);
+    if (offset > ns || size > ns - offset || offset > nd || size > nd - offset) {
+        kq_set_error("cpy_tensor: window [%zu, +%zu) exceeds src %zu / dst %zu bytes", offset, size, ns, nd);
+        return 0;
+    }
+    if (size == 0) return 1;
+    const b200_buffer *sb = (const b200_buffer *)(uintptr_t)src->buffer;
+    const b200_buffer *db = (const b200_buffer *)(uintptr_t)dst->buffer;
+    const void *sp = (const uint8_t *)(uintptr_t)src->data + offset;
+    void *dp = (uint8_t *)(uintptr_t)dst->data + offset;
+    DevGuard g(sb->dev);
+    cudaError_t e;
+    if (sb->dev == db->dev) {
+        e = cudaMemcpy(dp, sp, size, cudaMemcpyDeviceToDevice);
+    } else {
+        // the stage boundary: one copy over NVLink, no host bounce
+        e = cudaMemcpyPeer(dp, db->dev, sp, sb->dev, size);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        kq_set_error("cpy_tensor: %s", cudaGetErrorString(e));
+        return 0;
+    }
+    return 1;
+}
+
+b200_status b200_backend_init(int32_t dev, b200_backend **out) {
+    KQ_REQUIRE(out, "backend_init: null out");
+    *out = nullptr;
+    KQ_REQUIRE(dev >= 0 && dev < b200_reg_device_count(), "backend_init: no device %d", dev);
+    DevGuard g(dev);
+    b200_backend *be = new b200_backend();
+    be->dev = dev;
+    be->scratch = nullptr;
+    be->scratch_bytes = 0;
+    if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        kq_set_error("backend_init: stream creation failed");
+        delete be;
+        return B200_ERR_CUDA;
+    }
+    *out = be;
+    return B200_OK;
+}
+
+void b200_backend_free(b200_backend *be) {
+    if (!be) return;
+    DevGuard g(be->dev);
+    cudaStreamSynchronize(be->stream);
+    cudaStreamDestroy(be->stream);
+    if (be->scratch) cudaFree(be->scratch);
+    delete be;
+}
+
+void *b200_backend_stream(b200_backend *be) { return be ? (void *)be->stream : nullptr; }
+
+b200_status b200_backend_synchronize(b200_backend *be) {
+    KQ_REQUIRE(be, "backend_synchronize: null backend");
+    DevGuard g(be->dev);
+    KQ_CUDA(cudaStreamSynchronize(be->stream));
+    return B200_OK;
+}
+
+static b200_status ensure_scratch(b200_backend *be, size_t bytes) {
+    if (bytes <= be->scratch_bytes) return B200_OK;
+    cudaStreamSynchronize(be->stream);
+    if (be->scratch) cudaFree(be->scratch);
+    be->scratch = nullptr;
+    be->scratch_bytes = 0;
+    bytes = (bytes + (1 << 20)) & ~(size_t)((1 << 20) - 1);
+    if (cudaMalloc(&be->scratch, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        kq_set_error("graph_compute: scratch allocation of %zu bytes failed", bytes);
+        return B200_ERR_ALLOC;
+    }
+    be->scratch_bytes = bytes;
+    return B200_OK;
+}
+
+b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_ids, uint32_t n_nodes,
+                                       const b200_tensor *tensors, uint32_t n_tensors) {
+    KQ_REQUIRE(be && (node_ids || n_nodes == 0) && (tensors || n_tensors == 0), "graph_compute: null argument");
+    std::lock_guard<std::mutex> lock(be->mu);
+    DevGuard g(be->dev);
+    std::unordered_map<uint64_t, const b200_tensor *> by_id;
+    for (uint32_t i = 0; i < n_tensors; i++) by_id[tensors[i].id] = &tensors[i];
+    cudaStream_t s = be->stream;
+    auto src = [&](const b200_tensor *t, int i) -> const b200_tensor * {
+        if (!t->src[i]) return nullptr;
+        auto it = by_id.find(t->src[i]);
+        return it == by_id.end() ? nullptr : it->second;
+    };
+    for (uint32_t ni = 0; ni < n_nodes; ni++) {
+        auto it = by_id.find(node_ids[ni]);
+        KQ_REQUIRE(it != by_id.end(), "graph_compute: node id %llu is not in the tensor table",
+                   (unsigned long long)node_ids[ni]);
+        const b200_tensor *t = it->second;
+        if (t->op == B200_OP_NONE) continue;
+        KQ_TRY(check_tensor(t));
+        const b200_tensor *a = src(t, 0), *b = src(t, 1), *c = src(t, 2);
+        KQ_REQUIRE(a, "graph_compute: node %.64s has no src0", t->name);
+        KQ_TRY(check_tensor(a));
+        if (b) KQ_TRY(check_tensor(b));
+        if (c) KQ_TRY(check_tensor(c));
+        if (!b200_dev_supports_op(t->op, a->type, b ? b->type : B200_TYPE_F32)) {
+            kq_set_error("graph_compute: node %.64s: op %u with types %u/%u is not on the hot path", t->name,
+                         t->op, a->type, b ? b->type : 0);
+            return B200_ERR_UNSUPPORTED;
+        }
+        float *y = (float *)(uintptr_t)t->data;
+        const void *pa = (const void *)(uintptr_t)a->data;
+        const void *pb = b ? (const void *)(uintptr_t)b->data : nullptr;
+        switch (t->op) {
+        case B200_OP_MUL_MAT: {
+            KQ_REQUIRE(b && a->ne[0] == b->ne[0], "MUL_MAT %.64s: K mismatch", t->name);
+            const int64_t K = a->ne[0], N = a->ne[1], M = nrows(b);
+            KQ_REQUIRE(t->ne[0] == N && nrows(t) == M && t->type == B200_TYPE_F32, "MUL_MAT %.64s: bad output shape", t->name);
+            if (a->type == B200_TYPE_F32) {
+                KQ_TRY(kq_f32_matmul((const float *)pa, (const float *)pb, M, N, K, y, s));
+            } else {
+                const size_t need = b200_mul_mat_scratch_bytes(M, K);
+                KQ_TRY(ensure_scratch(be, need));
+                KQ_TRY(b200_mul_mat(a->type, pa, (const float *)pb, M, N, K, y, be->scratch, be->scratch_bytes, s));
+            }
+            break;
+        }
+        case B200_OP_MUL_MAT_ID: {
+            KQ_REQUIRE(b && c && c->type == B200_TYPE_I32, "MUL_MAT_ID %.64s: needs x and i32 ids", t->name);
+            const int64_t K = a->ne[0], N = a->ne[1], E = a->ne[2];
+            const int64_t n_used = c->ne[0], T = c->ne[1];
+            KQ_REQUIRE(b->ne[0] == K && b->ne[2] == T && (b->ne[1] == n_used || b->ne[1] == 1),
+                       "MUL_MAT_ID %.64s: x must be [K, n_used|1, T]", t->name);
+            KQ_REQUIRE(t->ne[0] == N && t->ne[1] == n_used && t->ne[2] == T, "MUL_MAT_ID %.64s: bad output shape", t->name);
+            (void)E;
+            const int64_t xrows = b->ne[1] * T;
+            KQ_TRY(ensure_scratch(be, b200_mul_mat_scratch_bytes(xrows, K)));
+            auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+            int8_t *q = (int8_t *)be->scratch;
+            float *d = (float *)((char *)be->scratch + up((size_t)(xrows * K)));
+            int16_t *bs = (int16_t *)((char *)d + up((size_t)(xrows * K / 256 * 4)));
+            KQ_TRY(b200_quantize_act((const float *)pb, xrows, K, q, d, bs, s));
+            KqGemvSeg sg = {(const uint8_t *)pa, a->type, (int32_t)N, y, nullptr, (int32_t)N,
+                            kq_device_row_bytes(a->type, K) * N};
+            KqGemvIndirect ind = {(const int32_t *)(uintptr_t)c->data, (int32_t)(n_used * T),
+                                  (int32_t)(b->ne[1] == 1 ? n_used : 1)};
+            KQ_TRY(kq_launch_gemv(&sg, 1, q, d, bs, 1, K, nullptr, 0, &ind, s));
+            break;
+        }
+        case B200_OP_RMS_NORM:
+            KQ_TRY(kq_rms_norm((const float *)pa, nullptr, nrows(a), a->ne[0], f32_param(t, 0), y, nullptr, nullptr,
+                               nullptr, s));
+            break;
+        case B200_OP_MUL:
+        case B200_OP_ADD: {
+            KQ_REQUIRE(b && b->type == B200_TYPE_F32 && b->ne[0] == a->ne[0], "%.64s: operand shapes", t->name);
+            const int64_t total = nelements(a), nbe = nelements(b);
+            KQ_REQUIRE(nbe == total || nbe == a->ne[0], "%.64s: src1 must match or be one row", t->name);
+            if (t->op == B200_OP_MUL)
+                mul_rows_kernel<<<(unsigned)kq_div_up(total, 256), 256, 0, s>>>((const float *)pa, (const float *)pb,
+                                                                               total, a->ne[0], nbe, y);
+            else
+                add_bcast_kernel<<<(unsigned)kq_div_up(total, 256), 256, 0, s>>>((const float *)pa, (const float *)pb,
+                                                                                total, a->ne[0], nbe, y);
+            KQ_COUNT_LAUNCH();
+            KQ_LAUNCH_CHECK();
+            break;
+        }
+        case B200_OP_ROPE: {
+            KQ_REQUIRE(b && b->ne[0] == a->ne[2], "ROPE %.64s: one position per token", t->name);
+            KQ_REQUIRE(t->op_params[0] == (int32_t)a->ne[0], "ROPE %.64s: partial rotation is not supported", t->name);
+            if (t->data != a->data)
+                KQ_CUDA(cudaMemcpyAsync(y, pa, (size_t)nelements(a) * 4, cudaMemcpyDeviceToDevice, s));
+            KQ_TRY(b200_rope(y, (const int32_t *)pb, a->ne[2], a->ne[1], a->ne[0], f32_param(t, 2),
+                             t->op_params[1] == 2, s));
+            break;
+        }
+        case B200_OP_SWIGLU:
+            KQ_REQUIRE(b && nelements(b) == nelements(a), "SWIGLU %.64s: shapes", t->name);
+            KQ_TRY(b200_swiglu((const float *)pa, (const float *)pb, nelements(a), y, s));
+            break;
+        case B200_OP_GET_ROWS:
+            KQ_REQUIRE(b, "GET_ROWS %.64s: ids", t->name);
+            KQ_TRY(b200_get_rows(a->type, pa, (const int32_t *)pb, nelements(b), a->ne[0], y, s));
+            break;
+        case B200_OP_CPY:
+            if (t->type == B200_TYPE_F16)
+                KQ_TRY(b200_cpy_f32_f16((const float *)pa, nelements(a), (uint16_t *)y, s));
+            else if (t->type == B200_TYPE_F32)
+                KQ_CUDA(cudaMemcpyAsync(y, pa, (size_t)nelements(a) * 4, cudaMemcpyDeviceToDevice, s));
+            else {
+                kq_set_error("CPY %.64s: destination type %u", t->name, t->type);
+                return B200_ERR_UNSUPPORTED;
+            }
+            break;
+        case B200_OP_ATTN: {
+            KQ_REQUIRE(b && c && c->type == B200_TYPE_F16, "ATTN %.64s: K and V caches", t->name);
+            const int hd = a->ne[0], n_head = a->ne[1], T = a->ne[2], n_kv = b->ne[1];
+            const int pos0 = t->op_params[1];
+            KQ_REQUIRE(pos0 >= 0 && (int64_t)pos0 + T <= (int64_t)b->ne[2], "ATTN %.64s: positions exceed the cache", t->name);
+            const size_t need = b200_attention_scratch_bytes(std::min(T, 64), n_head, hd, b->ne[2]);
+            KQ_TRY(ensure_scratch(be, need));
+            KQ_TRY(kq_attention((const float *)pa, (const uint16_t *)pb, (const uint16_t *)(uintptr_t)c->data, 1, T,
+                                nullptr, pos0, n_head, n_kv, hd, 0, y, (float *)be->scratch, be->scratch_bytes, 0, s));
+            break;
+        }
+        case B200_OP_MOE_ROUTE:
+            KQ_REQUIRE(b && b->type == B200_TYPE_I32, "MOE_ROUTE %.64s: src1 receives the ids", t->name);
+            KQ_TRY(b200_moe_route((const float *)pa, a->ne[1], a->ne[0], t->op_params[0],
+                                  (int32_t *)(uintptr_t)b->data, y, s));
+            break;
+        case B200_OP_ARGMAX:
+            KQ_TRY(b200_argmax((const float *)pa, nrows(a), a->ne[0], (int32_t *)y, s));
+            break;
+        default:
+            kq_set_error("graph_compute: node %.64s: op %u is not on the hot path", t->name, t->op);
+            return B200_ERR_UNSUPPORTED;
+        }
+    }
+    cudaError_t e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        kq_set_error("graph_compute: %s", cudaGetErrorString(e));
+        return B200_ERR_CUDA;
+    }
+    return B200_OK;
+}
+
+} // extern "C"

@@ -133,8 +133,8 @@ b200_status b200_mul_mat_q8(uint32_t type, const void *W, const int8_t *q, const
     KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "mul_mat: weight type %u", type);
     cudaStream_t st = (cudaStream_t)stream;
     if (M <= 8) {
-        KqGemvSeg sg = {(const uint8_t *)W, type, (int32_t)N, y, bias, (int32_t)N};
-        return kq_launch_gemv(&sg, 1, q, d, bsum16, (int)M, K, residual, 0, st);
+        KqGemvSeg sg = {(const uint8_t *)W, type, (int32_t)N, y, bias, (int32_t)N, 0};
+        return kq_launch_gemv(&sg, 1, q, d, bsum16, (int)M, K, residual, 0, nullptr, st);
     }
     return kq_launch_gemm(type, (const uint8_t *)W, q, d, bsum16, M, N, K, y, bias, residual, st);
 }

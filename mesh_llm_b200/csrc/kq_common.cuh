@@ -105,11 +105,18 @@ struct KqGemvSeg {
     float *y;          // [M][ldy], rows of this segment start at column 0 of y
     const float *bias; // [n_rows] or null
     int32_t ldy;
+    int64_t expert_stride; // bytes between consecutive expert matrices (expert-indexed mode)
+};
+
+struct KqGemvIndirect {
+    const int32_t *expert_ids; // device, one expert id per (token, slot) pair
+    int32_t n_pairs;
+    int32_t act_div;           // activation row of pair p is p / act_div
 };
 
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
-                           int swiglu_pairs, cudaStream_t st);
+                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st);
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
                            const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
                            const float *bias, const float *residual, cudaStream_t st);

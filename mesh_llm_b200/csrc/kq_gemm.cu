@@ -9,9 +9,9 @@ b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, con
     const int64_t nb = K / 256;
     for (int64_t m0 = 0; m0 < M; m0 += 8) {
         const int mc = (int)(M - m0 < 8 ? M - m0 : 8);
-        KqGemvSeg sg = {W, type, (int32_t)N, y + m0 * N, bias, (int32_t)N};
+        KqGemvSeg sg = {W, type, (int32_t)N, y + m0 * N, bias, (int32_t)N, 0};
         b200_status rc = kq_launch_gemv(&sg, 1, q + m0 * K, d + m0 * nb, bs + m0 * nb * 16, mc, K,
-                                        residual ? residual + m0 * N : nullptr, 0, st);
+                                        residual ? residual + m0 * N : nullptr, 0, nullptr, st);
         if (rc != B200_OK) return rc;
     }
     return B200_OK;

@@ -105,6 +105,10 @@ struct GemvParams {
     const float *ad;
     const int16_t *abs16;
     const float *residual; // [M][ldy of segment 0] or null (single segment only)
+    // expert-indexed mode (MUL_MAT_ID): blockIdx.y walks (token, slot) pairs; pair p uses the
+    // expert matrix ids[p], activation row p / act_div and output row p.  M is 1 in this mode.
+    const int32_t *expert_ids;
+    int32_t act_div;
 };
 
 template <int M, int R>
@@ -115,6 +119,18 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
     const int kslot = warp % wk, nslot = warp / wk;
     const int sub = lane >> 3, c = lane & 7;
     const int nb = p.nb;
+    const int pair = blockIdx.y;
+    int64_t expert = 0;
+    const int8_t *aq = p.aq;
+    const float *ad = p.ad;
+    const int16_t *abs16 = p.abs16;
+    if (p.expert_ids) {
+        expert = p.expert_ids[pair];
+        const int arow = pair / p.act_div;
+        aq += (int64_t)arow * p.K;
+        ad += (int64_t)arow * nb;
+        abs16 += (int64_t)arow * nb * 16;
+    }
 
     for (int base = blockIdx.x * wn; base < p.n_rg; base += gridDim.x * wn) {
         const int rg = base + nslot;
@@ -141,10 +157,10 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                 if (p.swiglu) {
                     row[r] = (rg - rg0) * (R / 2) + (r % (R / 2));
                     const KqGemvSeg &s2 = p.seg[r / (R / 2)];
-                    rp[r] = s2.W + (int64_t)min(row[r], s2.n_rows - 1) * stride;
+                    rp[r] = s2.W + expert * s2.expert_stride + (int64_t)min(row[r], s2.n_rows - 1) * stride;
                 } else {
                     row[r] = (rg - rg0) * R + r;
-                    rp[r] = sg.W + (int64_t)min(row[r], sg.n_rows - 1) * stride;
+                    rp[r] = sg.W + expert * sg.expert_stride + (int64_t)min(row[r], sg.n_rows - 1) * stride;
                 }
             }
             if (type == B200_TYPE_Q4_K) {
@@ -164,11 +180,11 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                         for (int r = 0; r < R; r++) sc[r] = q4k_lane_scales(hdr[r], c);
 #pragma unroll
                         for (int m = 0; m < M; m++) {
-                            const int8_t *a = p.aq + (int64_t)m * p.K + blk * 256 + e_lo;
+                            const int8_t *a = aq + (int64_t)m * p.K + blk * 256 + e_lo;
                             const int4 alo = *reinterpret_cast<const int4 *>(a);
                             const int4 ahi = *reinterpret_cast<const int4 *>(a + 32);
-                            const float da = p.ad[m * nb + blk];
-                            const int16_t *s16 = p.abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+                            const float da = ad[m * nb + blk];
+                            const int16_t *s16 = abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
                             const int bl = s16[0], bh = s16[2];
 #pragma unroll
                             for (int r = 0; r < R; r++) {
@@ -204,11 +220,11 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                         }
 #pragma unroll
                         for (int m = 0; m < M; m++) {
-                            const int8_t *a = p.aq + (int64_t)m * p.K + blk * 256 + e_lo;
+                            const int8_t *a = aq + (int64_t)m * p.K + blk * 256 + e_lo;
                             const int4 alo = *reinterpret_cast<const int4 *>(a);
                             const int4 ahi = *reinterpret_cast<const int4 *>(a + 64);
-                            const float da = p.ad[m * nb + blk];
-                            const int16_t *s16 = p.abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
+                            const float da = ad[m * nb + blk];
+                            const int16_t *s16 = abs16 + ((int64_t)m * nb + blk) * 16 + (e_lo >> 4);
                             const int bl = s16[0], bh = s16[4];
 #pragma unroll
                             for (int r = 0; r < R; r++) {
@@ -246,7 +262,7 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                     if (rw < p.seg[0].n_rows) {
                         if (p.seg[0].bias) g += p.seg[0].bias[rw];
                         if (p.seg[1].bias) u += p.seg[1].bias[rw];
-                        p.seg[0].y[(int64_t)m * p.seg[0].ldy + rw] = (g / (1.0f + expf(-g))) * u;
+                        p.seg[0].y[((int64_t)m + pair) * p.seg[0].ldy + rw] = (g / (1.0f + expf(-g))) * u;
                     }
                 }
             } else if (lane < R * M) {
@@ -260,8 +276,8 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                     if (r == rr) rw = row[rr];
                 if (rw < sg.n_rows) {
                     if (sg.bias) v += sg.bias[rw];
-                    if (p.residual) v += p.residual[(int64_t)m * sg.ldy + rw];
-                    sg.y[(int64_t)m * sg.ldy + rw] = v;
+                    if (p.residual) v += p.residual[((int64_t)m + pair) * sg.ldy + rw];
+                    sg.y[((int64_t)m + pair) * sg.ldy + rw] = v;
                 }
             }
         }
@@ -325,7 +341,7 @@ int env_int(const char *name, int dflt) {
 }
 
 template <int M, int R>
-b200_status launch_mr(const GemvParams &p, int wn, cudaStream_t st) {
+b200_status launch_mr(const GemvParams &p, int wn, int n_pairs, cudaStream_t st) {
     static int ctas_per_sm = 0;
     if (!ctas_per_sm) {
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_kernel<M, R>, 128, 0);
@@ -333,8 +349,10 @@ b200_status launch_mr(const GemvParams &p, int wn, cudaStream_t st) {
     }
     int64_t want = kq_div_up(p.n_rg, wn);
     int64_t cap = (int64_t)kq_sm_count() * ctas_per_sm;
-    int grid = (int)(want < cap ? want : cap);
-    if (grid < 1) grid = 1;
+    if (n_pairs > 1) cap = kq_div_up(cap, n_pairs);
+    int gx = (int)(want < cap ? want : cap);
+    if (gx < 1) gx = 1;
+    dim3 grid(gx, n_pairs);
     gemv_kernel<M, R><<<grid, 128, 0, st>>>(p);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -345,7 +363,7 @@ b200_status launch_mr(const GemvParams &p, int wn, cudaStream_t st) {
 
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
-                           int swiglu_pairs, cudaStream_t st) {
+                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st) {
     KQ_REQUIRE(nseg >= 1 && nseg <= 3, "gemv: 1..3 segments");
     KQ_REQUIRE(M >= 1 && M <= 8, "gemv: M must be 1..8 (got %d)", M);
     KQ_REQUIRE(K > 0 && K % 256 == 0, "gemv: K must be a positive multiple of 256");
@@ -375,6 +393,13 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
     p.ad = d;
     p.abs16 = bs;
     p.residual = residual;
+    int n_pairs = 1;
+    if (ind && ind->expert_ids) {
+        KQ_REQUIRE(M == 1 && ind->n_pairs >= 1 && ind->act_div >= 1, "gemv: expert mode needs M == 1");
+        p.expert_ids = ind->expert_ids;
+        p.act_div = ind->act_div;
+        n_pairs = ind->n_pairs;
+    }
     const int its = (p.nb + 3) / 4;
     int wk = its >= 16 ? 4 : (its >= 8 ? 2 : 1);
     wk = env_int("B200_GEMV_WK", wk);
@@ -382,14 +407,14 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
     p.wk = wk;
     const int wn = 4 / wk;
     switch (M) {
-    case 1: return launch_mr<1, 4>(p, wn, st);
-    case 2: return launch_mr<2, 4>(p, wn, st);
-    case 3: return launch_mr<3, 4>(p, wn, st);
-    case 4: return launch_mr<4, 4>(p, wn, st);
-    case 5: return launch_mr<5, 2>(p, wn, st);
-    case 6: return launch_mr<6, 2>(p, wn, st);
-    case 7: return launch_mr<7, 2>(p, wn, st);
-    default: return launch_mr<8, 2>(p, wn, st);
+    case 1: return launch_mr<1, 4>(p, wn, n_pairs, st);
+    case 2: return launch_mr<2, 4>(p, wn, n_pairs, st);
+    case 3: return launch_mr<3, 4>(p, wn, n_pairs, st);
+    case 4: return launch_mr<4, 4>(p, wn, n_pairs, st);
+    case 5: return launch_mr<5, 2>(p, wn, n_pairs, st);
+    case 6: return launch_mr<6, 2>(p, wn, n_pairs, st);
+    case 7: return launch_mr<7, 2>(p, wn, n_pairs, st);
+    default: return launch_mr<8, 2>(p, wn, n_pairs, st);
     }
 }
 

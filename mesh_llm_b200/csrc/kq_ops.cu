@@ -15,12 +15,12 @@ struct RopeTable {
 // q: [rows][n_head][hd] f32 rotated in place.  k (optional): [rows][n_kv][hd] f32 rotated and
 // stored as f16 into the cache at the row's position; v likewise without rotation.
 __global__ void rope_store_kernel(float *q, const float *k, const float *v, const int32_t *pos,
-                                  int pos0, int T, int n_head, int n_kv, int hd, int neox,
+                                  const int32_t *pos0_dev, int pos0, int T, int n_head, int n_kv, int hd, int neox,
                                   RopeTable tab, __half *k_cache, __half *v_cache,
                                   int64_t seq_stride) {
     const int row = blockIdx.x; // row = seq * T + t
     const int seq = row / T, t = row % T;
-    const int p = pos ? pos[row] : pos0 + t;
+    const int p = pos ? pos[row] : (pos0_dev ? *pos0_dev : pos0) + t;
     const int half = hd / 2;
     const int n_rot = (n_head + (k ? n_kv : 0)) * half;
     for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
@@ -58,8 +58,8 @@ __global__ void rope_store_kernel(float *q, const float *k, const float *v, cons
 template <int HD, int G>
 __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q,
                                                         const __half *__restrict__ kc,
-                                                        const __half *__restrict__ vc, int T, int pos0,
-                                                        int n_head, int n_kv, int64_t seq_stride,
+                                                        const __half *__restrict__ vc, int T,
+                                                        const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int64_t seq_stride,
                                                         int n_split, float scale, float *out,
                                                         float *part_o, float *part_ml) {
     constexpr int DPL = HD / 32; // output dims per lane
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     const int kh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
     const int seq = row / T, t = row % T;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = pos0 + t + 1;
+    const int L = (pos0_dev ? *pos0_dev : pos0) + t + 1;
     int chunk = (L + n_split - 1) / n_split;
     chunk = (chunk + 127) / 128 * 128;
     const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
@@ -356,10 +356,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int
 
 template <int HD>
 b200_status launch_attention_g(int G, dim3 grid, const float *q, const __half *kc, const __half *vc,
-                               int T, int pos0, int n_head, int n_kv, int64_t seq_stride, int n_split,
+                               int T, const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int64_t seq_stride, int n_split,
                                float scale, float *out, float *po, float *pml, cudaStream_t st) {
 #define KQ_ATT(GG)                                                                                  \
-    attention_kernel<HD, GG><<<grid, 128, 0, st>>>(q, kc, vc, T, pos0, n_head, n_kv, seq_stride,    \
+    attention_kernel<HD, GG><<<grid, 128, 0, st>>>(q, kc, vc, T, pos0_dev, pos0, n_head, n_kv, seq_stride, \
                                                    n_split, scale, out, po, pml)
     switch (G) {
     case 1: KQ_ATT(1); break;
@@ -380,7 +380,10 @@ b200_status launch_attention_g(int G, dim3 grid, const float *q, const __half *k
 int kq_attention_splits(int64_t rows, int n_kv, int64_t L) {
     const int64_t ctas = rows * n_kv;
     int64_t want = kq_div_up(2 * (int64_t)kq_sm_count(), ctas);
-    int64_t cap = kq_div_up(L, 128);
+    // the cap follows the context length in powers of two, so a decode loop that captured its
+    // launch configuration keeps it for a long stretch of positions
+    int64_t cap = 1;
+    while (cap * 128 < L) cap *= 2;
     if (want > cap) want = cap;
     if (want > 64) want = 64;
     return want < 1 ? 1 : (int)want;
@@ -388,12 +391,13 @@ int kq_attention_splits(int64_t rows, int n_kv, int64_t L) {
 
 // rows = n_seq * T query rows; caches of sequence s start at s * seq_stride elements.
 b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
-                         int pos0, int n_head, int n_kv, int hd, int64_t seq_stride, float *out,
-                         float *scratch, size_t scratch_bytes, cudaStream_t st) {
+                         const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
+                         int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
+                         int force_splits, cudaStream_t st) {
     KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
     KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
     const int rows = n_seq * T, G = n_head / n_kv;
-    int n_split = kq_attention_splits(rows, n_kv, pos0 + T);
+    int n_split = force_splits > 0 ? force_splits : kq_attention_splits(rows, n_kv, pos0 + T);
     const size_t need = (size_t)rows * n_head * n_split * (hd + 2) * sizeof(float);
     if (n_split > 1 && need > scratch_bytes) n_split = 1;
     float *po = scratch, *pml = scratch ? scratch + (size_t)rows * n_head * n_split * hd : nullptr;
@@ -401,10 +405,10 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
     dim3 grid(n_kv, n_split, rows);
     b200_status rc;
     if (hd == 128)
-        rc = launch_attention_g<128>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0, n_head,
+        rc = launch_attention_g<128>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0_dev, pos0, n_head,
                                      n_kv, seq_stride, n_split, scale, out, po, pml, st);
     else
-        rc = launch_attention_g<64>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0, n_head,
+        rc = launch_attention_g<64>(G, grid, q, (const __half *)kc, (const __half *)vc, T, pos0_dev, pos0, n_head,
                                     n_kv, seq_stride, n_split, scale, out, po, pml, st);
     if (rc != B200_OK) return rc;
     if (n_split > 1) {
@@ -417,13 +421,13 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
     return B200_OK;
 }
 
-b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos, int pos0,
-                          int n_seq, int T, int n_head, int n_kv, int hd, float theta, int neox,
+b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos,
+                          const int32_t *pos0_dev, int pos0, int n_seq, int T, int n_head, int n_kv, int hd, float theta, int neox,
                           uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride, cudaStream_t st) {
     KQ_REQUIRE(hd % 2 == 0 && hd <= 256, "rope: head_dim %d", hd);
     RopeTable tab;
     for (int i = 0; i < hd / 2; i++) tab.inv_freq[i] = (float)pow((double)theta, -2.0 * i / (double)hd);
-    rope_store_kernel<<<n_seq * T, 256, 0, st>>>(q, k, v, pos, pos0, T, n_head, n_kv, hd, neox, tab,
+    rope_store_kernel<<<n_seq * T, 256, 0, st>>>(q, k, v, pos, pos0_dev, pos0, T, n_head, n_kv, hd, neox, tab,
                                                  (__half *)k_cache, (__half *)v_cache, seq_stride);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -435,7 +439,7 @@ extern "C" {
 b200_status b200_rope(float *x, const int32_t *pos, int64_t T, int64_t n_head, int64_t hd, float theta,
                       int32_t neox, void *stream) {
     KQ_REQUIRE(T > 0 && pos, "rope: positions required");
-    return kq_rope_store(x, nullptr, nullptr, pos, 0, 1, (int)T, (int)n_head, 0, (int)hd, theta, neox,
+    return kq_rope_store(x, nullptr, nullptr, pos, nullptr, 0, 1, (int)T, (int)n_head, 0, (int)hd, theta, neox,
                          nullptr, nullptr, 0, (cudaStream_t)stream);
 }
 
@@ -475,8 +479,8 @@ b200_status b200_attention(const float *q, const uint16_t *k_cache, const uint16
                            int64_t pos0, int64_t n_head, int64_t n_kv, int64_t hd, float *out,
                            void *scratch, size_t scratch_bytes, void *stream) {
     KQ_REQUIRE(T > 0 && pos0 >= 0, "attention: bad shape");
-    return kq_attention(q, k_cache, v_cache, 1, (int)T, (int)pos0, (int)n_head, (int)n_kv, (int)hd, 0,
-                        out, (float *)scratch, scratch_bytes, (cudaStream_t)stream);
+    return kq_attention(q, k_cache, v_cache, 1, (int)T, nullptr, (int)pos0, (int)n_head, (int)n_kv, (int)hd,
+                        0, out, (float *)scratch, scratch_bytes, 0, (cudaStream_t)stream);
 }
 
 b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T, int64_t K,
@@ -509,3 +513,28 @@ b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k,
 }
 
 } // extern "C"
+
+// ---- small f32 matmul (router gate, F32 weights): one warp per output element --------------------
+namespace {
+__global__ void __launch_bounds__(128) f32_matmul_kernel(const float *W, const float *x, int64_t M, int64_t N,
+                                                         int K, float *out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= M * N) return;
+    const int64_t m = w / N, n = w % N;
+    const float *wr = W + n * K, *xr = x + m * K;
+    float acc = 0.f;
+    for (int i = lane; i < K; i += 32) acc = fmaf(wr[i], xr[i], acc);
+    acc = kq_warp_sum(acc);
+    if (lane == 0) out[w] = acc;
+}
+} // namespace
+
+b200_status kq_f32_matmul(const float *W, const float *x, int64_t M, int64_t N, int64_t K, float *y,
+                          cudaStream_t st) {
+    KQ_REQUIRE(M > 0 && N > 0 && K > 0, "f32 matmul: bad shape");
+    f32_matmul_kernel<<<(unsigned)kq_div_up(M * N, 4), 128, 0, st>>>(W, x, M, N, (int)K, y);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}

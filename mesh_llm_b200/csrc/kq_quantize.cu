@@ -44,23 +44,27 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float *__restri
 // One CTA of 256 threads per row; h is a multiple of 256 when q != null.
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x,
                                                        const float *__restrict__ w, int h, float eps,
-                                                       float *y, int8_t *q, float *d, int16_t *bs) {
-    __shared__ float part[8];
+                                                       float *y, int8_t *q, float *d, int16_t *bs,
+                                                       int64_t x_row_stride) {
+    __shared__ double part[8];
     __shared__ float s_scale;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float *xr = x + (int64_t)row * h;
-    float ss = 0.f;
+    const float *xr = x + (int64_t)row * x_row_stride;
+    // the sum of squares is carried in double so that the scale does not depend on the order of
+    // the reduction: the normalised values, and with them the Q8 codes, are then reproducible
+    double ss = 0.0;
     for (int i = tid * 4; i < h; i += 1024) {
         const float4 v = *reinterpret_cast<const float4 *>(xr + i);
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
     }
-    ss = kq_warp_sum(ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) part[warp] = ss;
     __syncthreads();
     if (tid == 0) {
-        float t = 0.f;
+        double t = 0.0;
         for (int i = 0; i < 8; i++) t += part[i];
-        s_scale = 1.0f / sqrtf(t / (float)h + eps);
+        s_scale = 1.0f / sqrtf((float)(t / (double)h) + eps);
     }
     __syncthreads();
     const float scale = s_scale;
@@ -248,11 +252,11 @@ b200_status kq_synth_weights(uint32_t type, void *W, int64_t n_rows, int64_t K, 
 }
 
 b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y,
-                        int8_t *q, float *d, int16_t *bs, cudaStream_t st) {
+                        int8_t *q, float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride) {
     KQ_REQUIRE(T > 0 && h > 0 && h % 4 == 0, "rms_norm: bad shape");
     KQ_REQUIRE(!q || h % 256 == 0, "rms_norm: Q8 output needs h %% 256 == 0");
     KQ_REQUIRE(y || q, "rms_norm: no output");
-    rms_norm_kernel<<<(unsigned)T, 256, 0, st>>>(x, w, (int)h, eps, y, q, d, bs);
+    rms_norm_kernel<<<(unsigned)T, 256, 0, st>>>(x, w, (int)h, eps, y, q, d, bs, x_row_stride ? x_row_stride : h);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -272,7 +276,7 @@ extern "C" b200_status b200_quantize_act(const float *x, int64_t M, int64_t K, i
 
 extern "C" b200_status b200_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps,
                                      float *y, void *stream) {
-    return kq_rms_norm(x, w, T, h, eps, y, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+    return kq_rms_norm(x, w, T, h, eps, y, nullptr, nullptr, nullptr, (cudaStream_t)stream, 0);
 }
 
 static b200_status repack(const void *src, void *dst, int64_t n_rows, int64_t k, int inverse,
