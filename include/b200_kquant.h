@@ -177,6 +177,23 @@ B200_API b200_status b200_mul_mat_q8(uint32_t type, const void *W, const int8_t 
                                      const int16_t *bsum16, int64_t M, int64_t N, int64_t K,
                                      float *y, const float *bias, const float *residual,
                                      void *stream);
+/* The same contraction as b200_mul_mat for callers that must not allocate and have no scratch
+ * to lend (no counterpart in the reference; an addition of this library).  Meant for a stage whose
+ * device memory was budgeted in full before it started, for a decode loop that cannot afford
+ * cudaMalloc's device-wide synchronisation, and for hosts that own all device memory through their
+ * own allocator.  The quantised activations go to a fixed array that is part of the library image,
+ * so every GPU that loads the library holds about 292 KiB for it until the process exits.
+ * Limits: M <= 8 tokens and K <= 32768; anything larger returns B200_ERR_INVALID with a message
+ * (use b200_mul_mat with caller scratch instead).  The call itself performs no cudaMalloc /
+ * cudaFree.  The first call on each device looks the array's address up once
+ * (cudaGetSymbolAddress, with that device current); make that first call before starting any
+ * stream capture.  All calls on a device share the one array: calls whose kernels can overlap on
+ * the GPU (different streams) race on it, so serialise them.  Nothing needs clearing between
+ * calls -- each call rewrites every byte it later reads.                                        */
+#define B200_MUL_MAT_STATIC_MAX_TOKENS 8
+#define B200_MUL_MAT_STATIC_MAX_K 32768
+B200_API b200_status b200_mul_mat_static(uint32_t type, const void *W, const float *x, int64_t M,
+                                         int64_t N, int64_t K, float *y, void *stream);
 /* exact per-block integer sums [M][N][K/256] (parity instrumentation; summ may be NULL)        */
 B200_API b200_status b200_block_sums(uint32_t type, const void *W, const int8_t *q,
                                      const int16_t *bsum16, int64_t M, int64_t N, int64_t K,

@@ -1,0 +1,64 @@
+"""b200_mul_mat_static: the MUL_MAT entry point for callers that cannot allocate.
+
+Some users of this library may not call cudaMalloc once they are running: a stage whose VRAM was
+budgeted exactly before launch, a decode loop that cannot take cudaMalloc's device-wide stall, a
+host with its own device allocator.  For them the Q8 scratch lives in a fixed array inside the
+library.  This test calls the entry point through the C ABI twice in a row and checks each result
+against the ordinary entry point (b200_mul_mat with caller-provided scratch).  The second call
+uses a smaller, different problem, so anything left in the shared array by the first call would
+show up as a wrong answer.  It is collected last so that a run stopping at the first failure has
+already covered everything else, and it stands alone in a fresh process as well.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(ty, M, N, K, seed):
+    import torch
+    from mesh_llm_b200 import ops
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    rb = ops.device_row_bytes(ty, K)
+    W = torch.randint(0, 256, (N, rb), dtype=torch.uint8, generator=g)
+    # keep the f16 scale fields finite and small so the products are well conditioned
+    Wn = W.numpy()
+    if ty == 12:
+        blk = Wn.reshape(N, K // 256, 144)
+        blk[:, :, 0:4] = np.array([0.01, 0.005], np.float16).view(np.uint8)
+    else:
+        nb = K // 256
+        Wn[:, nb * 208: nb * 208 + nb * 2] = np.tile(np.array([0.001], np.float16).view(np.uint8), nb)
+    x = torch.randn(M, K, generator=g)
+    return W.cuda(), x.cuda()
+
+
+@pytest.mark.parametrize("ty", [12, 14], ids=["q4_k", "q6_k"])
+def test_static_scratch_entry_matches_the_allocating_one_twice_in_a_row(ty):
+    import torch
+    from mesh_llm_b200 import ops
+    from mesh_llm_b200.capi import check, cur_stream, lib, ptr
+
+    for (M, N, K, seed) in ((8, 320, 8192, 1), (3, 77, 1024, 2)):
+        W, x = _problem(ty, M, N, K, seed)
+        want = ops.mul_mat(ty, W, x, N, K)
+        got = torch.full((M, N), float("nan"), device="cuda")
+        check(lib().b200_mul_mat_static(ty, ptr(W), ptr(x), M, N, K, ptr(got), cur_stream()))
+        torch.cuda.synchronize()
+        ref = want.cpu().numpy()
+        err = np.abs(got.cpu().numpy() - ref).max() / np.abs(ref).max()
+        assert err <= 1e-3, (M, N, K, err)
+
+
+def test_static_scratch_entry_rejects_oversize_calls():
+    import torch
+    from mesh_llm_b200.capi import B200Error, check, cur_stream, lib, ptr
+
+    W = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(16, device="cuda")
+    y = torch.zeros(16, device="cuda")
+    with pytest.raises(B200Error, match="exceed the built-in scratch"):
+        check(lib().b200_mul_mat_static(12, ptr(W), ptr(x), 9, 4, 256, ptr(y), cur_stream()))
+    with pytest.raises(B200Error, match="exceed the built-in scratch"):
+        check(lib().b200_mul_mat_static(12, ptr(W), ptr(x), 1, 4, 32768 + 256, ptr(y), cur_stream()))
