@@ -247,13 +247,13 @@ B200_API b200_status b200_stage_get_tensor(b200_stage *st, const char *name, voi
 /* fill every tensor with seeded N(0, 0.02) weights quantised on the device to the Q4_K_M mix   */
 B200_API b200_status b200_stage_generate(b200_stage *st, uint64_t seed);
 B200_API size_t b200_stage_weight_bytes(b200_stage *st);
-/* Run T tokens per sequence for `n_seq_active` sequences (rows ordered sequence-major) starting
- * at position pos0.  First stage: tokens (device i32); other stages: hidden_in (device f32
+/* Run T tokens per sequence for `n_seq_active` sequences (rows ordered sequence-major; they use
+ * KV-cache slots seq0 .. seq0 + n_seq_active - 1) starting at position pos0.  First stage: tokens (device i32); other stages: hidden_in (device f32
  * [rows][n_embd]).  Last stage writes logits for the last token of each sequence (or all rows
  * if all_logits) and the greedy argmax into next_tokens; other stages write hidden_out.        */
 B200_API b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens,
-                                        const float *hidden_in, int32_t n_seq_active, int32_t T,
-                                        int32_t pos0, float *hidden_out, float *logits,
+                                        const float *hidden_in, int32_t seq0, int32_t n_seq_active,
+                                        int32_t T, int32_t pos0, float *hidden_out, float *logits,
                                         int32_t all_logits, int32_t *next_tokens, void *stream);
 /* Timing instrumentation: captures one decode step (T = 1, n_seq sequences at position pos0) into
  * a CUDA graph restricted to the kernel classes in `classes` (1 = quantised GEMV, 2 = attention,

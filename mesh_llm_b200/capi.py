@@ -109,7 +109,7 @@ SIGNATURES = {
     "b200_stage_get_tensor": (i32, [vp, C.c_char_p, vp, sz]),
     "b200_stage_generate": (i32, [vp, u64]),
     "b200_stage_weight_bytes": (sz, [vp]),
-    "b200_stage_forward": (i32, [vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp]),
+    "b200_stage_forward": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
     "b200_stage_profile_decode": (i32, [vp, i32, i32, u32, i32, C.POINTER(C.c_float), C.POINTER(i64)]),
     "b200_stage_synchronize": (i32, [vp]),
     "b200_stage_kernel_launches": (i64, [vp]),

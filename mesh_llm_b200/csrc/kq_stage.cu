@@ -45,7 +45,7 @@ struct LayerW {
 };
 
 struct GraphKey {
-    int n_seq, n_split;
+    int n_seq, n_split, seq0, pad_;
     const void *tokens, *hidden_in, *hidden_out, *logits, *next;
     bool operator<(const GraphKey &o) const {
         return memcmp(this, &o, sizeof(GraphKey)) < 0;
@@ -193,8 +193,8 @@ enum { CLS_GEMV = 1, CLS_ATTN = 2, CLS_OTHER = 4, CLS_ALL = 7 };
 
 // `classes` selects which kernel classes are launched; anything but CLS_ALL is timing
 // instrumentation (the outputs are then meaningless).
-b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hidden_in, int n_seq, int T,
-                         int pos0, bool pos_from_dev, int force_splits, float *hidden_out, float *logits,
+b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hidden_in, int seq0, int n_seq,
+                         int T, int pos0, bool pos_from_dev, int force_splits, float *hidden_out, float *logits,
                          int all_logits, int32_t *next_tokens, cudaStream_t s, unsigned classes = CLS_ALL) {
 #define GEMV_(expr) do { if (classes & CLS_GEMV) KQ_TRY(expr); } while (0)
 #define ATTN_(expr) do { if (classes & CLS_ATTN) KQ_TRY(expr); } while (0)
@@ -215,8 +215,8 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
     for (int ll = 0; ll < n_local; ll++) {
         const LayerW &L = st->layers[ll];
         const bool last_layer = ll == n_local - 1;
-        uint16_t *kc = st->kc + (int64_t)ll * c.n_seq * seq_stride;
-        uint16_t *vc = st->vc + (int64_t)ll * c.n_seq * seq_stride;
+        uint16_t *kc = st->kc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
+        uint16_t *vc = st->vc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
         // ---- attention block
         OTHER_(kq_rms_norm(xin, L.attn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
         if (rows <= 8) {
@@ -590,12 +590,13 @@ size_t b200_stage_weight_bytes(b200_stage *st) {
     return n;
 }
 
-b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const float *hidden_in,
+b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const float *hidden_in, int32_t seq0,
                                int32_t n_seq, int32_t T, int32_t pos0, float *hidden_out, float *logits,
                                int32_t all_logits, int32_t *next_tokens, void *stream) {
     KQ_REQUIRE(st, "stage_forward: null stage");
     const b200_stage_config &c = st->c;
-    KQ_REQUIRE(n_seq >= 1 && n_seq <= c.n_seq && T >= 1, "stage_forward: n_seq=%d T=%d", n_seq, T);
+    KQ_REQUIRE(n_seq >= 1 && seq0 >= 0 && seq0 + n_seq <= c.n_seq && T >= 1,
+               "stage_forward: seq0=%d n_seq=%d T=%d (cache holds %d sequences)", seq0, n_seq, T, c.n_seq);
     KQ_REQUIRE((int64_t)n_seq * T <= st->rows_max, "stage_forward: %d rows exceed n_ubatch=%d", n_seq * T,
                st->rows_max);
     KQ_REQUIRE(pos0 >= 0 && pos0 + T <= c.n_ctx, "stage_forward: positions [%d,%d) exceed n_ctx=%d", pos0,
@@ -613,6 +614,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
         memset(&key, 0, sizeof(key));
         key.n_seq = n_seq;
         key.n_split = n_split;
+        key.seq0 = seq0;
         key.tokens = tokens;
         key.hidden_in = hidden_in;
         key.hidden_out = hidden_out;
@@ -622,7 +624,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
         if (it == st->graphs.end()) {
             cudaGraph_t graph = nullptr;
             KQ_CUDA(cudaStreamBeginCapture(st->cap_stream, cudaStreamCaptureModeThreadLocal));
-            b200_status rc = forward_body(st, tokens, hidden_in, n_seq, 1, pos0, true, n_split, hidden_out,
+            b200_status rc = forward_body(st, tokens, hidden_in, seq0, n_seq, 1, pos0, true, n_split, hidden_out,
                                           logits, all_logits, next_tokens, st->cap_stream);
             cudaError_t e = cudaStreamEndCapture(st->cap_stream, &graph);
             if (rc != B200_OK) {
@@ -644,7 +646,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
         g_kq_launches = before + it->second.launches + 1;
         return B200_OK;
     }
-    b200_status rc = forward_body(st, tokens, hidden_in, n_seq, T, pos0, false, 0, hidden_out, logits,
+    b200_status rc = forward_body(st, tokens, hidden_in, seq0, n_seq, T, pos0, false, 0, hidden_out, logits,
                                   all_logits, next_tokens, s);
     st->launches += g_kq_launches - before;
     return rc;
@@ -670,7 +672,7 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     KQ_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-    b200_status rc = forward_body(st, tok, hin, n_seq, 1, pos0, true,
+    b200_status rc = forward_body(st, tok, hin, 0, n_seq, 1, pos0, true,
                                   kq_attention_splits(n_seq, c.n_head_kv, pos0 + 1),
                                   c.has_output ? nullptr : hout, nullptr, 0,
                                   c.has_output ? (int32_t *)st->rid_scratch + 32 : nullptr, s, classes);

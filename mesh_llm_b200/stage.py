@@ -67,7 +67,7 @@ class Stage:
 
     # ---- compute ------------------------------------------------------------------------------
     def forward(self, tokens=None, hidden_in=None, n_seq=1, T=None, pos0=0, hidden_out=None,
-                logits=None, all_logits=False, next_tokens=None):
+                logits=None, all_logits=False, next_tokens=None, seq0=0):
         """Device tensors in, device tensors out (allocated when not supplied).
         rows are sequence-major: row = seq * T + t."""
         c = self.cfg
@@ -85,7 +85,7 @@ class Stage:
             if next_tokens is None:
                 next_tokens = torch.empty(rows if all_logits else n_seq, dtype=torch.int32,
                                           device=self.device)
-        check(lib().b200_stage_forward(self.h, ptr(tokens), ptr(hidden_in), n_seq, T, pos0,
+        check(lib().b200_stage_forward(self.h, ptr(tokens), ptr(hidden_in), seq0, n_seq, T, pos0,
                                        ptr(hidden_out), ptr(logits), int(all_logits),
                                        ptr(next_tokens), cur_stream()))
         return hidden_out, logits, next_tokens
