@@ -58,10 +58,37 @@ static inline __host__ __device__ int64_t kq_row_bytes(uint32_t type, int64_t k)
     default: return 0;
     }
 }
-// Q6_K rows live on the device as [ql nb*128 | qh nb*64 | scales nb*16 | d nb*2 | pad to 16]
+// Q6_K rows live on the device as groups of up to 8 blocks, each group laid out as planes
+// [ql g*128 | qh g*64 | scales g*16 | d g*2 (padded to 16)], g = blocks in the group.  A full group
+// is 1680 bytes (a multiple of 16 with no padding), so any 8-block slice of a row is one contiguous,
+// 16-byte aligned run; only the last, partial group of a row carries padding (< 16 bytes).
+#define KQ_Q6_GROUP 8
+#define KQ_Q6_GROUP_BYTES 1680
+static inline __host__ __device__ int64_t kq_q6_group_bytes(int g) {
+    return g == KQ_Q6_GROUP ? KQ_Q6_GROUP_BYTES : (g ? (int64_t)g * 208 + 16 : 0);
+}
 static inline __host__ __device__ int64_t kq_device_row_bytes(uint32_t type, int64_t k) {
-    if (type == B200_TYPE_Q6_K) return (k / KQ_QK * KQ_Q6K_BYTES + 15) / 16 * 16;
+    if (type == B200_TYPE_Q6_K) {
+        const int64_t nb = k / KQ_QK;
+        return nb / KQ_Q6_GROUP * KQ_Q6_GROUP_BYTES + kq_q6_group_bytes((int)(nb % KQ_Q6_GROUP));
+    }
     return kq_row_bytes(type, k);
+}
+// byte offsets, inside a device row of nb blocks, of the four pieces of block `blk`
+struct KqQ6Addr {
+    int64_t ql, qh, sc, d;
+};
+static inline __host__ __device__ KqQ6Addr kq_q6_addr(int nb, int blk) {
+    const int grp = blk / KQ_Q6_GROUP, b8 = blk % KQ_Q6_GROUP;
+    const int left = nb - grp * KQ_Q6_GROUP;
+    const int g = left < KQ_Q6_GROUP ? left : KQ_Q6_GROUP;
+    const int64_t base = (int64_t)grp * KQ_Q6_GROUP_BYTES;
+    KqQ6Addr a;
+    a.ql = base + b8 * 128;
+    a.qh = base + g * 128 + b8 * 64;
+    a.sc = base + g * 192 + b8 * 16;
+    a.d = base + g * 208 + b8 * 2;
+    return a;
 }
 
 // ---- device helpers ------------------------------------------------------------------------
@@ -117,6 +144,10 @@ struct KqGemvIndirect {
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
                            int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st);
+b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
+                                  const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
+                                  cudaStream_t st);
+int kq_stream_error_fetch(); // 0 ok; nonzero = a bounded device-side wait gave up since the last call
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
                            const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
                            const float *bias, const float *residual, cudaStream_t st);

@@ -9,88 +9,11 @@
 // rows.  Long rows are additionally split over the 2 or 4 warps of a CTA and combined in shared
 // memory in a fixed order, so results are deterministic (no float atomics).
 #include "kq_common.cuh"
+#include "kq_lanes.cuh"
 
 #include <stdlib.h>
 
 namespace {
-
-struct LaneGeom {
-    int e_lo;   // first element (within the block) of the lane's low-nibble group of 16
-    int e_hi;   // first element of its high-nibble group of 16
-};
-
-// ---- Q4_K: one lane's share of one block -----------------------------------------------------
-// hdr = first 16 bytes of the block (f16 d, f16 dmin, 12 bytes of 6-bit scales/mins); w = the
-// lane's 16 quant bytes (chunk c of 8): low nibbles belong to sub-block 2g, high nibbles to
-// sub-block 2g+1, g = c >> 1.
-struct Q4Scales {
-    int sc0, sc1, m0, m1;
-    float d, dmin;
-};
-
-__device__ __forceinline__ Q4Scales q4k_lane_scales(const uint4 &hdr, int c) {
-    Q4Scales s;
-    const int g = c >> 1;
-    const int sh = (g & 1) * 16;
-    const uint32_t ty = (hdr.y >> sh) & 0xFFFFu, tz = (hdr.z >> sh) & 0xFFFFu,
-                   tw = (hdr.w >> sh) & 0xFFFFu;
-    if (g < 2) {
-        s.sc0 = ty & 63;
-        s.sc1 = (ty >> 8) & 63;
-        s.m0 = tz & 63;
-        s.m1 = (tz >> 8) & 63;
-    } else {
-        s.sc0 = (tw & 0xF) | ((ty >> 2) & 0x30);
-        s.sc1 = ((tw >> 8) & 0xF) | ((ty >> 10) & 0x30);
-        s.m0 = ((tw >> 4) & 0xF) | ((tz >> 2) & 0x30);
-        s.m1 = ((tw >> 12) & 0xF) | ((tz >> 10) & 0x30);
-    }
-    const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
-    const float2 f = __half22float2(dm);
-    s.d = f.x;
-    s.dmin = f.y;
-    return s;
-}
-
-__device__ __forceinline__ void q4k_lane_ints(const uint4 &w, const Q4Scales &s, const int4 &alo,
-                                              const int4 &ahi, int bl, int bh, int &isum,
-                                              int &msum) {
-    int dl = __dp4a((int)(w.x & 0x0F0F0F0Fu), alo.x, 0);
-    dl = __dp4a((int)(w.y & 0x0F0F0F0Fu), alo.y, dl);
-    dl = __dp4a((int)(w.z & 0x0F0F0F0Fu), alo.z, dl);
-    dl = __dp4a((int)(w.w & 0x0F0F0F0Fu), alo.w, dl);
-    int dh = __dp4a((int)((w.x >> 4) & 0x0F0F0F0Fu), ahi.x, 0);
-    dh = __dp4a((int)((w.y >> 4) & 0x0F0F0F0Fu), ahi.y, dh);
-    dh = __dp4a((int)((w.z >> 4) & 0x0F0F0F0Fu), ahi.z, dh);
-    dh = __dp4a((int)((w.w >> 4) & 0x0F0F0F0Fu), ahi.w, dh);
-    isum = s.sc0 * dl + s.sc1 * dh;
-    msum = s.m0 * bl + s.m1 * bh;
-}
-
-// ---- Q6_K (device layout): one lane's share of one block ----------------------------------------
-// ql = the lane's 16 low-nibble bytes (chunk c of 8, half h = c >> 2, cc = c & 3); qh = the 16
-// bytes of 2-bit highs that cover the same 16 positions; the lane's low nibbles are elements
-// 128h + 16cc .. +15 and its high nibbles elements 128h + 64 + 16cc .. +15.
-__device__ __forceinline__ int q6k_lane_ints(const uint4 &ql, const uint4 &qh, int cc, int sc_lo,
-                                             int sc_hi, const int4 &alo, const int4 &ahi, int bl,
-                                             int bh) {
-    const int s_lo = 2 * (cc >> 1), s_hi = 4 + s_lo;
-    int dl = 0, dh = 0;
-#define KQ_Q6_STEP(W, H, AL, AH)                                                            \
-    {                                                                                       \
-        uint32_t vl = ((W) & 0x0F0F0F0Fu) | ((((H) >> s_lo) & 0x03030303u) << 4);           \
-        uint32_t vh = (((W) >> 4) & 0x0F0F0F0Fu) | ((((H) >> s_hi) & 0x03030303u) << 4);    \
-        dl = __dp4a((int)vl, (AL), dl);                                                     \
-        dh = __dp4a((int)vh, (AH), dh);                                                     \
-    }
-    KQ_Q6_STEP(ql.x, qh.x, alo.x, ahi.x)
-    KQ_Q6_STEP(ql.y, qh.y, alo.y, ahi.y)
-    KQ_Q6_STEP(ql.z, qh.z, alo.z, ahi.z)
-    KQ_Q6_STEP(ql.w, qh.w, alo.w, ahi.w)
-#undef KQ_Q6_STEP
-    // codes are stored with +32 bias: sum (q-32) a = sum q a - 32 sum a
-    return sc_lo * (dl - 32 * bl) + sc_hi * (dh - 32 * bh);
-}
 
 struct GemvParams {
     KqGemvSeg seg[3];
@@ -199,8 +122,6 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
             } else { // Q6_K device layout
                 const int h = c >> 2, cc = c & 3;
                 const int e_lo = 128 * h + 16 * cc;
-                const int64_t off_qh = (int64_t)nb * 128, off_sc = (int64_t)nb * 192,
-                              off_d = (int64_t)nb * 208;
                 for (int it = kslot; it * 4 < nb; it += wk) {
                     const int blk = it * 4 + sub;
                     if (blk < nb) {
@@ -209,14 +130,13 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                         float dw[R];
 #pragma unroll
                         for (int r = 0; r < R; r++) {
-                            ql[r] = kq_ld_stream(rp[r] + (int64_t)blk * 128 + 16 * c);
-                            qh[r] = __ldg(reinterpret_cast<const uint4 *>(
-                                rp[r] + off_qh + (int64_t)blk * 64 + 16 * (2 * h + (cc & 1))));
-                            const int8_t *scp =
-                                reinterpret_cast<const int8_t *>(rp[r] + off_sc + (int64_t)blk * 16);
+                            const KqQ6Addr qa = kq_q6_addr(nb, blk);
+                            ql[r] = kq_ld_stream(rp[r] + qa.ql + 16 * c);
+                            qh[r] = __ldg(reinterpret_cast<const uint4 *>(rp[r] + qa.qh + 16 * (2 * h + (cc & 1))));
+                            const int8_t *scp = reinterpret_cast<const int8_t *>(rp[r] + qa.sc);
                             scl[r] = scp[8 * h + cc];
                             sch[r] = scp[8 * h + 4 + cc];
-                            dw[r] = kq_h2f(*reinterpret_cast<const uint16_t *>(rp[r] + off_d + blk * 2));
+                            dw[r] = kq_h2f(*reinterpret_cast<const uint16_t *>(rp[r] + qa.d));
                         }
 #pragma unroll
                         for (int m = 0; m < M; m++) {
@@ -321,10 +241,10 @@ __global__ void __launch_bounds__(128) block_sums_kernel(uint32_t type, const ui
         if (summ) atomicAdd(&summ[o], msum);
     } else {
         const int h = c >> 2, cc = c & 3, e_lo = 128 * h + 16 * cc;
-        const uint4 ql = kq_ld_stream(rp + (int64_t)blk * 128 + 16 * c);
-        const uint4 qh = __ldg(reinterpret_cast<const uint4 *>(rp + (int64_t)nb * 128 + (int64_t)blk * 64 +
-                                                               16 * (2 * h + (cc & 1))));
-        const int8_t *scp = reinterpret_cast<const int8_t *>(rp + (int64_t)nb * 192 + (int64_t)blk * 16);
+        const KqQ6Addr qa = kq_q6_addr(nb, blk);
+        const uint4 ql = kq_ld_stream(rp + qa.ql + 16 * c);
+        const uint4 qh = __ldg(reinterpret_cast<const uint4 *>(rp + qa.qh + 16 * (2 * h + (cc & 1))));
+        const int8_t *scp = reinterpret_cast<const int8_t *>(rp + qa.sc);
         const int8_t *a = aq + (int64_t)m * K + blk * 256 + e_lo;
         const int4 alo = *reinterpret_cast<const int4 *>(a);
         const int4 ahi = *reinterpret_cast<const int4 *>(a + 64);
@@ -371,6 +291,10 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
                                  segs[0].n_rows == segs[1].n_rows),
                "gemv: swiglu needs two equal segments");
     KQ_REQUIRE(!residual || nseg == 1, "gemv: residual only with one segment");
+    if (!(ind && ind->expert_ids) && M <= 2 && K % 256 == 0) {
+        const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, st);
+        if (rs != B200_ERR_UNSUPPORTED) return rs;
+    }
     GemvParams p = {};
     const int R = M <= 4 ? 4 : 2;
     const int rows_per_rg = swiglu_pairs ? R / 2 : R;

@@ -254,12 +254,13 @@ __global__ void get_rows_kernel(uint32_t type, const uint8_t *W, const int32_t *
         v = d * (float)sc * (float)qv - dmin * (float)mn;
     } else if (type == B200_TYPE_Q6_K) {
         const int h = j >> 7, r = j & 127, k = r >> 5, i5 = r & 31;
-        const uint8_t lb = rp[(int64_t)b * 128 + 64 * h + 32 * (k & 1) + i5];
-        const uint8_t hb = rp[(int64_t)nb * 128 + (int64_t)b * 64 + 32 * h + i5];
+        const KqQ6Addr qa = kq_q6_addr(nb, b);
+        const uint8_t lb = rp[qa.ql + 64 * h + 32 * (k & 1) + i5];
+        const uint8_t hb = rp[qa.qh + 32 * h + i5];
         const int lo = (k & 2) ? (lb >> 4) : (lb & 0xF);
         const int qv = (lo | (((hb >> (2 * k)) & 3) << 4)) - 32;
-        const int sc = (int8_t)rp[(int64_t)nb * 192 + b * 16 + (j >> 4)];
-        const float d = kq_h2f(*reinterpret_cast<const uint16_t *>(rp + (int64_t)nb * 208 + b * 2));
+        const int sc = (int8_t)rp[qa.sc + (j >> 4)];
+        const float d = kq_h2f(*reinterpret_cast<const uint16_t *>(rp + qa.d));
         v = d * (float)sc * (float)qv;
     } else {
         v = reinterpret_cast<const float *>(rp)[e];

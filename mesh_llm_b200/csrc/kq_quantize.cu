@@ -98,11 +98,12 @@ __global__ void repack_q6k_kernel(const uint16_t *__restrict__ src, uint16_t *__
     if (i >= n_rows * per_row) return;
     const int64_t row = i / per_row;
     const int r = (int)(i % per_row), b = r / 105, o = r % 105; // u16 index inside the block
+    const KqQ6Addr qa = kq_q6_addr(nb, b);
     int64_t dev; // u16 offset inside the device row
-    if (o < 64) dev = (int64_t)b * 64 + o;
-    else if (o < 96) dev = (int64_t)nb * 64 + b * 32 + (o - 64);
-    else if (o < 104) dev = (int64_t)nb * 96 + b * 8 + (o - 96);
-    else dev = (int64_t)nb * 104 + b;
+    if (o < 64) dev = qa.ql / 2 + o;
+    else if (o < 96) dev = qa.qh / 2 + (o - 64);
+    else if (o < 104) dev = qa.sc / 2 + (o - 96);
+    else dev = qa.d / 2;
     const int64_t g = row * per_row + r, dv = row * dst_row_u16 + dev;
     if (inverse) dst[g] = src[dv];
     else dst[dv] = src[g];
@@ -211,7 +212,8 @@ __global__ void __launch_bounds__(128) synth_kquant_kernel(uint32_t type, uint8_
             const int byte = lane * 4 + i, h = byte >> 6, k = byte & 63;
             pk |= (uint32_t)((cd[128 * h + k] & 0xF) | ((cd[128 * h + 64 + k] & 0xF) << 4)) << (8 * i);
         }
-        *reinterpret_cast<uint32_t *>(rp + (int64_t)b * 128 + lane * 4) = pk;
+        const KqQ6Addr qa = kq_q6_addr(nb, b);
+        *reinterpret_cast<uint32_t *>(rp + qa.ql + lane * 4) = pk;
         // qh: 64 bytes, lane writes bytes 2l, 2l+1; byte 32h+k = hi2 of elems 128h+k+{0,32,64,96}
         uint16_t ph = 0;
 #pragma unroll
@@ -221,9 +223,9 @@ __global__ void __launch_bounds__(128) synth_kquant_kernel(uint32_t type, uint8_
                                 ((cd[128 * h + 64 + k] >> 4) << 4) | ((cd[128 * h + 96 + k] >> 4) << 6);
             ph |= (uint16_t)(v8 << (8 * i));
         }
-        *reinterpret_cast<uint16_t *>(rp + (int64_t)nb * 128 + (int64_t)b * 64 + lane * 2) = ph;
-        if ((lane & 1) == 0) rp[(int64_t)nb * 192 + b * 16 + (lane >> 1)] = (uint8_t)(int8_t)sc;
-        if (lane == 0) *reinterpret_cast<uint16_t *>(rp + (int64_t)nb * 208 + b * 2) = __half_as_ushort(dh);
+        *reinterpret_cast<uint16_t *>(rp + qa.qh + lane * 2) = ph;
+        if ((lane & 1) == 0) rp[qa.sc + (lane >> 1)] = (uint8_t)(int8_t)sc;
+        if (lane == 0) *reinterpret_cast<uint16_t *>(rp + qa.d) = __half_as_ushort(dh);
     }
 }
 

@@ -710,6 +710,11 @@ b200_status b200_stage_synchronize(b200_stage *st) {
     KQ_REQUIRE(st, "stage_synchronize: null stage");
     KQ_CUDA(cudaSetDevice(st->c.device));
     KQ_CUDA(cudaDeviceSynchronize());
+    const int werr = kq_stream_error_fetch();
+    if (werr) {
+        kq_set_error("stage_synchronize: a bounded device-side wait gave up (code %d)", werr);
+        return B200_ERR_TIMEOUT;
+    }
     return B200_OK;
 }
 

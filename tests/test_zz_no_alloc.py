@@ -16,22 +16,21 @@ pytestmark = pytest.mark.gpu
 
 
 def _problem(ty, M, N, K, seed):
+    """random but valid blocks in GGUF layout (finite, small f16 scales), uploaded to the device"""
     import torch
     from mesh_llm_b200 import ops
 
-    g = torch.Generator(device="cpu").manual_seed(seed)
-    rb = ops.device_row_bytes(ty, K)
-    W = torch.randint(0, 256, (N, rb), dtype=torch.uint8, generator=g)
-    # keep the f16 scale fields finite and small so the products are well conditioned
-    Wn = W.numpy()
+    rng = np.random.default_rng(seed)
+    nblk = N * K // 256
     if ty == 12:
-        blk = Wn.reshape(N, K // 256, 144)
-        blk[:, :, 0:4] = np.array([0.01, 0.005], np.float16).view(np.uint8)
+        blk = rng.integers(0, 256, (nblk, 144), dtype=np.uint8)
+        blk[:, 0:4] = np.array([0.01, 0.005], np.float16).view(np.uint8)
     else:
-        nb = K // 256
-        Wn[:, nb * 208: nb * 208 + nb * 2] = np.tile(np.array([0.001], np.float16).view(np.uint8), nb)
-    x = torch.randn(M, K, generator=g)
-    return W.cuda(), x.cuda()
+        blk = rng.integers(0, 256, (nblk, 210), dtype=np.uint8)
+        blk[:, 208:210] = np.array([0.001], np.float16).view(np.uint8)
+    W = ops.upload_weights(ty, blk.reshape(N, -1), N, K)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda()
+    return W, x
 
 
 @pytest.mark.parametrize("ty", [12, 14], ids=["q4_k", "q6_k"])
