@@ -154,7 +154,8 @@ B200_API void *b200_backend_stream(b200_backend *be);
 /* ---- direct kernel entry points (device pointers) -------------------------------------------
  * Weight matrices passed to these are in DEVICE layout: Q4_K rows are the GGUF bytes
  * unchanged; Q6_K rows are repacked (b200_repack_q6k) into groups of 8 blocks, each group
- * [ql | qh | scales | d], 1680 bytes, so that a row slice is one aligned contiguous run.       */
+ * [ql | qh | scales | d] with chunk-major ql / qh planes, 1680 bytes, so that a row slice is one
+ * aligned contiguous run.                                                                    */
 B200_API size_t b200_row_bytes(uint32_t type, int64_t k);        /* GGUF bytes of one row     */
 B200_API size_t b200_device_row_bytes(uint32_t type, int64_t k); /* device bytes of one row   */
 B200_API b200_status b200_repack_q6k(const void *gguf_rows_dev, void *device_rows, int64_t n_rows,

@@ -39,11 +39,13 @@ namespace {
 
 __global__ void mul_rows_kernel(const float *a, const float *b, int64_t total, int64_t n, int64_t nb_elems,
                                 float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) y[i] = a[i] * b[nb_elems == total ? i : i % n];
 }
 __global__ void add_bcast_kernel(const float *a, const float *b, int64_t total, int64_t n, int64_t nb_elems,
                                  float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) y[i] = a[i] + b[nb_elems == total ? i : i % n];
 }
@@ -383,10 +385,10 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             const int64_t total = nelements(a), nbe = nelements(b);
             KQ_REQUIRE(nbe == total || nbe == a->ne[0], "%.64s: src1 must match or be one row", t->name);
             if (t->op == B200_OP_MUL)
-                mul_rows_kernel<<<(unsigned)kq_div_up(total, 256), 256, 0, s>>>((const float *)pa, (const float *)pb,
+                kq_launch(mul_rows_kernel, (unsigned)kq_div_up(total, 256), 256, 0, s, (const float *)pa, (const float *)pb,
                                                                                total, a->ne[0], nbe, y);
             else
-                add_bcast_kernel<<<(unsigned)kq_div_up(total, 256), 256, 0, s>>>((const float *)pa, (const float *)pb,
+                kq_launch(add_bcast_kernel, (unsigned)kq_div_up(total, 256), 256, 0, s, (const float *)pa, (const float *)pb,
                                                                                 total, a->ne[0], nbe, y);
             KQ_COUNT_LAUNCH();
             KQ_LAUNCH_CHECK();

@@ -3,9 +3,16 @@
 #include "kq_common.cuh"
 
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 long long g_kq_launches = 0;
+
+static int pdl_default() {
+    const char *v = getenv("B200_NO_PDL");
+    return !(v && v[0] == '1');
+}
+int g_kq_pdl = pdl_default();
 
 static thread_local char t_err[512] = "";
 

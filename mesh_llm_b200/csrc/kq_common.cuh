@@ -59,9 +59,12 @@ static inline __host__ __device__ int64_t kq_row_bytes(uint32_t type, int64_t k)
     }
 }
 // Q6_K rows live on the device as groups of up to 8 blocks, each group laid out as planes
-// [ql g*128 | qh g*64 | scales g*16 | d g*2 (padded to 16)], g = blocks in the group.  A full group
-// is 1680 bytes (a multiple of 16 with no padding), so any 8-block slice of a row is one contiguous,
-// 16-byte aligned run; only the last, partial group of a row carries padding (< 16 bytes).
+// [ql g*128 | qh g*64 | scales g*16 | d g*2 (padded to 16)], g = blocks in the group.  Inside the
+// ql and qh planes the 16-byte chunks are stored chunk-major: chunk k of block b sits at
+// (k*g + b)*16, so the lanes that hold neighbouring blocks read neighbouring 16-byte words (no
+// shared-memory bank conflicts, full sectors from global memory).  A full group is 1680 bytes (a
+// multiple of 16 with no padding), so any 8-block slice of a row is one contiguous, 16-byte
+// aligned run; only the last, partial group of a row carries padding (< 16 bytes).
 #define KQ_Q6_GROUP 8
 #define KQ_Q6_GROUP_BYTES 1680
 static inline __host__ __device__ int64_t kq_q6_group_bytes(int g) {
@@ -74,9 +77,11 @@ static inline __host__ __device__ int64_t kq_device_row_bytes(uint32_t type, int
     }
     return kq_row_bytes(type, k);
 }
-// byte offsets, inside a device row of nb blocks, of the four pieces of block `blk`
+// byte offsets, inside a device row of nb blocks, of the four pieces of block `blk`: ql / qh point
+// at chunk 0 of the block, consecutive chunks are `cs` bytes apart
 struct KqQ6Addr {
     int64_t ql, qh, sc, d;
+    int cs;
 };
 static inline __host__ __device__ KqQ6Addr kq_q6_addr(int nb, int blk) {
     const int grp = blk / KQ_Q6_GROUP, b8 = blk % KQ_Q6_GROUP;
@@ -84,12 +89,48 @@ static inline __host__ __device__ KqQ6Addr kq_q6_addr(int nb, int blk) {
     const int g = left < KQ_Q6_GROUP ? left : KQ_Q6_GROUP;
     const int64_t base = (int64_t)grp * KQ_Q6_GROUP_BYTES;
     KqQ6Addr a;
-    a.ql = base + b8 * 128;
-    a.qh = base + g * 128 + b8 * 64;
+    a.cs = g * 16;
+    a.ql = base + b8 * 16;
+    a.qh = base + g * 128 + b8 * 16;
     a.sc = base + g * 192 + b8 * 16;
     a.d = base + g * 208 + b8 * 2;
     return a;
 }
+
+// ---- launches -------------------------------------------------------------------------------
+// Every kernel of the library is launched with programmatic stream serialisation allowed: the
+// next kernel of the stream may be scheduled while this one drains, and blocks in
+// KQ_PDL_WAIT() until its predecessors have completed and their writes are visible.  A decode
+// step is a chain of some 700 short kernels, so taking the launch latency off the critical path
+// is worth about as much as a faster kernel.  Kernels may do work that does not depend on earlier
+// kernels (prefetching weights) before KQ_PDL_WAIT(); they must not read activations or write
+// anything before it.
+extern int g_kq_pdl;
+#ifdef __CUDACC__
+#define KQ_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define KQ_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#define KQ_PDL_ENTER() \
+    do {               \
+        KQ_PDL_TRIGGER(); \
+        KQ_PDL_WAIT();    \
+    } while (0)
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kq_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_kq_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+#endif
 
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__

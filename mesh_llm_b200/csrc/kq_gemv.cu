@@ -36,6 +36,7 @@ struct GemvParams {
 
 template <int M, int R>
 __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
+    KQ_PDL_ENTER();
     __shared__ float red[4][R * M];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wk = p.wk, wn = 4 / wk;
@@ -131,8 +132,8 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
 #pragma unroll
                         for (int r = 0; r < R; r++) {
                             const KqQ6Addr qa = kq_q6_addr(nb, blk);
-                            ql[r] = kq_ld_stream(rp[r] + qa.ql + 16 * c);
-                            qh[r] = __ldg(reinterpret_cast<const uint4 *>(rp[r] + qa.qh + 16 * (2 * h + (cc & 1))));
+                            ql[r] = kq_ld_stream(rp[r] + qa.ql + qa.cs * c);
+                            qh[r] = __ldg(reinterpret_cast<const uint4 *>(rp[r] + qa.qh + qa.cs * (2 * h + (cc & 1))));
                             const int8_t *scp = reinterpret_cast<const int8_t *>(rp[r] + qa.sc);
                             scl[r] = scp[8 * h + cc];
                             sch[r] = scp[8 * h + 4 + cc];
@@ -212,6 +213,7 @@ __global__ void __launch_bounds__(128) block_sums_kernel(uint32_t type, const ui
                                                          const int8_t *aq, const int16_t *abs16,
                                                          int M, int N, int K, int32_t *sumi,
                                                          int32_t *summ) {
+    KQ_PDL_ENTER();
     const int nb = K / 256;
     const int lane = threadIdx.x & 31, sub = lane >> 3, c = lane & 7;
     const int64_t warp = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -242,8 +244,8 @@ __global__ void __launch_bounds__(128) block_sums_kernel(uint32_t type, const ui
     } else {
         const int h = c >> 2, cc = c & 3, e_lo = 128 * h + 16 * cc;
         const KqQ6Addr qa = kq_q6_addr(nb, blk);
-        const uint4 ql = kq_ld_stream(rp + qa.ql + 16 * c);
-        const uint4 qh = __ldg(reinterpret_cast<const uint4 *>(rp + qa.qh + 16 * (2 * h + (cc & 1))));
+        const uint4 ql = kq_ld_stream(rp + qa.ql + qa.cs * c);
+        const uint4 qh = __ldg(reinterpret_cast<const uint4 *>(rp + qa.qh + qa.cs * (2 * h + (cc & 1))));
         const int8_t *scp = reinterpret_cast<const int8_t *>(rp + qa.sc);
         const int8_t *a = aq + (int64_t)m * K + blk * 256 + e_lo;
         const int4 alo = *reinterpret_cast<const int4 *>(a);
@@ -273,7 +275,7 @@ b200_status launch_mr(const GemvParams &p, int wn, int n_pairs, cudaStream_t st)
     int gx = (int)(want < cap ? want : cap);
     if (gx < 1) gx = 1;
     dim3 grid(gx, n_pairs);
-    gemv_kernel<M, R><<<grid, 128, 0, st>>>(p);
+    kq_launch(gemv_kernel<M, R>, grid, 128, 0, st, p);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -352,7 +354,7 @@ extern "C" b200_status b200_block_sums(uint32_t type, const void *W, const int8_
     KQ_CUDA(cudaMemsetAsync(sumi, 0, cnt * 4, st));
     if (summ) KQ_CUDA(cudaMemsetAsync(summ, 0, cnt * 4, st));
     const int64_t warps = M * N * ((nb + 3) / 4);
-    block_sums_kernel<<<(unsigned)kq_div_up(warps, 4), 128, 0, st>>>(
+    kq_launch(block_sums_kernel, (unsigned)kq_div_up(warps, 4), 128, 0, st, 
         type, (const uint8_t *)W, q, bsum16, (int)M, (int)N, (int)K, sumi, summ);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();

@@ -18,6 +18,7 @@ __global__ void rope_store_kernel(float *q, const float *k, const float *v, cons
                                   const int32_t *pos0_dev, int pos0, int T, int n_head, int n_kv, int hd, int neox,
                                   RopeTable tab, __half *k_cache, __half *v_cache,
                                   int64_t seq_stride) {
+    KQ_PDL_ENTER();
     const int row = blockIdx.x; // row = seq * T + t
     const int seq = row / T, t = row % T;
     const int p = pos ? pos[row] : (pos0_dev ? *pos0_dev : pos0) + t;
@@ -62,6 +63,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
                                                         const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int64_t seq_stride,
                                                         int n_split, float scale, float *out,
                                                         float *part_o, float *part_ml) {
+    KQ_PDL_ENTER();
     constexpr int DPL = HD / 32; // output dims per lane
     __shared__ float q_s[G][HD];
     __shared__ float p_s[4][G][32];
@@ -191,6 +193,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
 template <int HD>
 __global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int n_head,
                                          int n_split, float *out) {
+    KQ_PDL_ENTER();
     const int head = blockIdx.x, row = blockIdx.y, dim = threadIdx.x;
     const int64_t base = ((int64_t)row * n_head + head) * n_split;
     float mm = -INFINITY;
@@ -206,6 +209,7 @@ __global__ void attention_combine_kernel(const float *part_o, const float *part_
 }
 
 __global__ void swiglu_kernel(const float *g, const float *u, int64_t n, float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const float a = g[i];
@@ -213,14 +217,17 @@ __global__ void swiglu_kernel(const float *g, const float *u, int64_t n, float *
     }
 }
 __global__ void add_kernel(const float *a, const float *b, int64_t n, float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = a[i] + b[i];
 }
 __global__ void add_bias_kernel(float *y, const float *bias, int64_t total, int64_t n) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) y[i] += bias[i % n];
 }
 __global__ void cpy_f16_kernel(const float *x, int64_t n, __half *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = __float2half_rn(x[i]);
 }
@@ -228,6 +235,7 @@ __global__ void cpy_f16_kernel(const float *x, int64_t n, __half *y) {
 // embedding rows: one thread per element
 __global__ void get_rows_kernel(uint32_t type, const uint8_t *W, const int32_t *ids, int64_t T, int K,
                                 float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= T * K) return;
     const int64_t t = i / K;
@@ -255,8 +263,9 @@ __global__ void get_rows_kernel(uint32_t type, const uint8_t *W, const int32_t *
     } else if (type == B200_TYPE_Q6_K) {
         const int h = j >> 7, r = j & 127, k = r >> 5, i5 = r & 31;
         const KqQ6Addr qa = kq_q6_addr(nb, b);
-        const uint8_t lb = rp[qa.ql + 64 * h + 32 * (k & 1) + i5];
-        const uint8_t hb = rp[qa.qh + 32 * h + i5];
+        const int nl = 64 * h + 32 * (k & 1) + i5, nh = 32 * h + i5; // byte inside the block's ql / qh
+        const uint8_t lb = rp[qa.ql + (nl >> 4) * qa.cs + (nl & 15)];
+        const uint8_t hb = rp[qa.qh + (nh >> 4) * qa.cs + (nh & 15)];
         const int lo = (k & 2) ? (lb >> 4) : (lb & 0xF);
         const int qv = (lo | (((hb >> (2 * k)) & 3) << 4)) - 32;
         const int sc = (int8_t)rp[qa.sc + (j >> 4)];
@@ -269,6 +278,7 @@ __global__ void get_rows_kernel(uint32_t type, const uint8_t *W, const int32_t *
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *x, int64_t n, int32_t *idx) {
+    KQ_PDL_ENTER();
     __shared__ float bv[32];
     __shared__ int bi[32];
     const float *xr = x + (int64_t)blockIdx.x * n;
@@ -302,6 +312,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *x, int64_t n,
 // router: one warp per token; E <= 256, k <= 32
 __global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int64_t T, int E, int k,
                                                         int32_t *ids, float *w) {
+    KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= T) return;
@@ -360,7 +371,7 @@ b200_status launch_attention_g(int G, dim3 grid, const float *q, const __half *k
                                int T, const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int64_t seq_stride, int n_split,
                                float scale, float *out, float *po, float *pml, cudaStream_t st) {
 #define KQ_ATT(GG)                                                                                  \
-    attention_kernel<HD, GG><<<grid, 128, 0, st>>>(q, kc, vc, T, pos0_dev, pos0, n_head, n_kv, seq_stride, \
+    kq_launch(attention_kernel<HD, GG>, grid, 128, 0, st, q, kc, vc, T, pos0_dev, pos0, n_head, n_kv, seq_stride, \
                                                    n_split, scale, out, po, pml)
     switch (G) {
     case 1: KQ_ATT(1); break;
@@ -414,8 +425,8 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
     if (rc != B200_OK) return rc;
     if (n_split > 1) {
         dim3 g2(n_head, rows);
-        if (hd == 128) attention_combine_kernel<128><<<g2, 128, 0, st>>>(po, pml, n_head, n_split, out);
-        else attention_combine_kernel<64><<<g2, 64, 0, st>>>(po, pml, n_head, n_split, out);
+        if (hd == 128) kq_launch(attention_combine_kernel<128>, g2, 128, 0, st, po, pml, n_head, n_split, out);
+        else kq_launch(attention_combine_kernel<64>, g2, 64, 0, st, po, pml, n_head, n_split, out);
         KQ_COUNT_LAUNCH();
         KQ_LAUNCH_CHECK();
     }
@@ -428,7 +439,7 @@ b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_
     KQ_REQUIRE(hd % 2 == 0 && hd <= 256, "rope: head_dim %d", hd);
     RopeTable tab;
     for (int i = 0; i < hd / 2; i++) tab.inv_freq[i] = (float)pow((double)theta, -2.0 * i / (double)hd);
-    rope_store_kernel<<<n_seq * T, 256, 0, st>>>(q, k, v, pos, pos0_dev, pos0, T, n_head, n_kv, hd, neox, tab,
+    kq_launch(rope_store_kernel, n_seq * T, 256, 0, st, q, k, v, pos, pos0_dev, pos0, T, n_head, n_kv, hd, neox, tab,
                                                  (__half *)k_cache, (__half *)v_cache, seq_stride);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -445,28 +456,28 @@ b200_status b200_rope(float *x, const int32_t *pos, int64_t T, int64_t n_head, i
 }
 
 b200_status b200_swiglu(const float *gate, const float *up, int64_t n, float *y, void *stream) {
-    swiglu_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(gate, up, n, y);
+    kq_launch(swiglu_kernel, (unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream, gate, up, n, y);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
 }
 
 b200_status b200_add(const float *a, const float *b, int64_t n, float *y, void *stream) {
-    add_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, y);
+    kq_launch(add_kernel, (unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream, a, b, n, y);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
 }
 
 b200_status b200_add_bias(float *y, const float *bias, int64_t T, int64_t n, void *stream) {
-    add_bias_kernel<<<(unsigned)kq_div_up(T * n, 256), 256, 0, (cudaStream_t)stream>>>(y, bias, T * n, n);
+    kq_launch(add_bias_kernel, (unsigned)kq_div_up(T * n, 256), 256, 0, (cudaStream_t)stream, y, bias, T * n, n);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
 }
 
 b200_status b200_cpy_f32_f16(const float *x, int64_t n, uint16_t *y, void *stream) {
-    cpy_f16_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream>>>(x, n, (__half *)y);
+    kq_launch(cpy_f16_kernel, (unsigned)kq_div_up(n, 256), 256, 0, (cudaStream_t)stream, x, n, (__half *)y);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -489,7 +500,7 @@ b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int6
     KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K || type == B200_TYPE_F32,
                "get_rows: type %u", type);
     KQ_REQUIRE(type == B200_TYPE_F32 || K % 256 == 0, "get_rows: K %% 256");
-    get_rows_kernel<<<(unsigned)kq_div_up(T * K, 256), 256, 0, (cudaStream_t)stream>>>(
+    kq_launch(get_rows_kernel, (unsigned)kq_div_up(T * K, 256), 256, 0, (cudaStream_t)stream, 
         type, (const uint8_t *)W, ids, T, (int)K, y);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -497,7 +508,7 @@ b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int6
 }
 
 b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream) {
-    argmax_kernel<<<(unsigned)T, 1024, 0, (cudaStream_t)stream>>>(x, n, idx);
+    kq_launch(argmax_kernel, (unsigned)T, 1024, 0, (cudaStream_t)stream, x, n, idx);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -506,7 +517,7 @@ b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void
 b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w,
                            void *stream) {
     KQ_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= 32 && k <= E, "moe_route: E <= 256, k <= 32");
-    moe_route_kernel<<<(unsigned)kq_div_up(T, 4), 128, 0, (cudaStream_t)stream>>>(logits, T, (int)E, (int)k,
+    kq_launch(moe_route_kernel, (unsigned)kq_div_up(T, 4), 128, 0, (cudaStream_t)stream, logits, T, (int)E, (int)k,
                                                                                 ids, w);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -519,6 +530,7 @@ b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k,
 namespace {
 __global__ void __launch_bounds__(128) f32_matmul_kernel(const float *W, const float *x, int64_t M, int64_t N,
                                                          int K, float *out) {
+    KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (w >= M * N) return;
@@ -534,7 +546,7 @@ __global__ void __launch_bounds__(128) f32_matmul_kernel(const float *W, const f
 b200_status kq_f32_matmul(const float *W, const float *x, int64_t M, int64_t N, int64_t K, float *y,
                           cudaStream_t st) {
     KQ_REQUIRE(M > 0 && N > 0 && K > 0, "f32 matmul: bad shape");
-    f32_matmul_kernel<<<(unsigned)kq_div_up(M * N, 4), 128, 0, st>>>(W, x, M, N, (int)K, y);
+    kq_launch(f32_matmul_kernel, (unsigned)kq_div_up(M * N, 4), 128, 0, st, W, x, M, N, (int)K, y);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;

@@ -31,6 +31,7 @@ __device__ __forceinline__ void quantize_block_warp(const float (&v)[8], int lan
 
 __global__ void __launch_bounds__(128) quantize_act_kernel(const float *__restrict__ x, int64_t nblocks,
                                                            int8_t *q, float *d, int16_t *bs) {
+    KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
     const int64_t blk = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (blk >= nblocks) return;
@@ -46,6 +47,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
                                                        const float *__restrict__ w, int h, float eps,
                                                        float *y, int8_t *q, float *d, int16_t *bs,
                                                        int64_t x_row_stride) {
+    KQ_PDL_ENTER();
     __shared__ double part[8];
     __shared__ float s_scale;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -93,6 +95,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
 // ---- Q6_K repack: GGUF block-interleaved rows <-> device rows [ql | qh | scales | d | pad] ------
 __global__ void repack_q6k_kernel(const uint16_t *__restrict__ src, uint16_t *__restrict__ dst,
                                   int64_t n_rows, int nb, int64_t dst_row_u16, int inverse) {
+    KQ_PDL_ENTER();
     const int64_t per_row = (int64_t)nb * 105;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * per_row) return;
@@ -100,8 +103,8 @@ __global__ void repack_q6k_kernel(const uint16_t *__restrict__ src, uint16_t *__
     const int r = (int)(i % per_row), b = r / 105, o = r % 105; // u16 index inside the block
     const KqQ6Addr qa = kq_q6_addr(nb, b);
     int64_t dev; // u16 offset inside the device row
-    if (o < 64) dev = qa.ql / 2 + o;
-    else if (o < 96) dev = qa.qh / 2 + (o - 64);
+    if (o < 64) dev = (qa.ql + ((2 * o) >> 4) * qa.cs + ((2 * o) & 15)) / 2;
+    else if (o < 96) dev = (qa.qh + ((2 * (o - 64)) >> 4) * qa.cs + ((2 * (o - 64)) & 15)) / 2;
     else if (o < 104) dev = qa.sc / 2 + (o - 96);
     else dev = qa.d / 2;
     const int64_t g = row * per_row + r, dv = row * dst_row_u16 + dev;
@@ -126,6 +129,7 @@ __device__ __forceinline__ float gauss_at(uint64_t key, uint64_t i) {
 // One warp per 256-element block; writes the block in device layout.
 __global__ void __launch_bounds__(128) synth_kquant_kernel(uint32_t type, uint8_t *W, int64_t n_rows,
                                                            int nb, uint64_t key, float sigma) {
+    KQ_PDL_ENTER();
     __shared__ uint8_t codes[4][256];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t gb = (int64_t)blockIdx.x * 4 + warp;
@@ -213,7 +217,7 @@ __global__ void __launch_bounds__(128) synth_kquant_kernel(uint32_t type, uint8_
             pk |= (uint32_t)((cd[128 * h + k] & 0xF) | ((cd[128 * h + 64 + k] & 0xF) << 4)) << (8 * i);
         }
         const KqQ6Addr qa = kq_q6_addr(nb, b);
-        *reinterpret_cast<uint32_t *>(rp + qa.ql + lane * 4) = pk;
+        *reinterpret_cast<uint32_t *>(rp + qa.ql + ((lane * 4) >> 4) * qa.cs + ((lane * 4) & 15)) = pk;
         // qh: 64 bytes, lane writes bytes 2l, 2l+1; byte 32h+k = hi2 of elems 128h+k+{0,32,64,96}
         uint16_t ph = 0;
 #pragma unroll
@@ -223,13 +227,14 @@ __global__ void __launch_bounds__(128) synth_kquant_kernel(uint32_t type, uint8_
                                 ((cd[128 * h + 64 + k] >> 4) << 4) | ((cd[128 * h + 96 + k] >> 4) << 6);
             ph |= (uint16_t)(v8 << (8 * i));
         }
-        *reinterpret_cast<uint16_t *>(rp + qa.qh + lane * 2) = ph;
+        *reinterpret_cast<uint16_t *>(rp + qa.qh + ((lane * 2) >> 4) * qa.cs + ((lane * 2) & 15)) = ph;
         if ((lane & 1) == 0) rp[qa.sc + (lane >> 1)] = (uint8_t)(int8_t)sc;
         if (lane == 0) *reinterpret_cast<uint16_t *>(rp + qa.d) = __half_as_ushort(dh);
     }
 }
 
 __global__ void synth_f32_kernel(float *w, int64_t n, uint64_t key, float mean, float sigma) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) w[i] = mean + sigma * gauss_at(key, (uint64_t)i);
 }
@@ -240,12 +245,12 @@ b200_status kq_synth_weights(uint32_t type, void *W, int64_t n_rows, int64_t K, 
                              float mean, float sigma, cudaStream_t st) {
     if (type == B200_TYPE_F32) {
         const int64_t n = n_rows * K;
-        synth_f32_kernel<<<(unsigned)kq_div_up(n, 256), 256, 0, st>>>((float *)W, n, key, mean, sigma);
+        kq_launch(synth_f32_kernel, (unsigned)kq_div_up(n, 256), 256, 0, st, (float *)W, n, key, mean, sigma);
     } else {
         KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "synth: type %u", type);
         KQ_REQUIRE(K % 256 == 0, "synth: K %% 256");
         const int64_t blocks = n_rows * (K / 256);
-        synth_kquant_kernel<<<(unsigned)kq_div_up(blocks, 4), 128, 0, st>>>(type, (uint8_t *)W, n_rows,
+        kq_launch(synth_kquant_kernel, (unsigned)kq_div_up(blocks, 4), 128, 0, st, type, (uint8_t *)W, n_rows,
                                                                            (int)(K / 256), key, sigma);
     }
     KQ_COUNT_LAUNCH();
@@ -258,7 +263,7 @@ b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, fl
     KQ_REQUIRE(T > 0 && h > 0 && h % 4 == 0, "rms_norm: bad shape");
     KQ_REQUIRE(!q || h % 256 == 0, "rms_norm: Q8 output needs h %% 256 == 0");
     KQ_REQUIRE(y || q, "rms_norm: no output");
-    rms_norm_kernel<<<(unsigned)T, 256, 0, st>>>(x, w, (int)h, eps, y, q, d, bs, x_row_stride ? x_row_stride : h);
+    kq_launch(rms_norm_kernel, (unsigned)T, 256, 0, st, x, w, (int)h, eps, y, q, d, bs, x_row_stride ? x_row_stride : h);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -269,7 +274,7 @@ extern "C" b200_status b200_quantize_act(const float *x, int64_t M, int64_t K, i
     KQ_REQUIRE(M > 0 && K > 0 && K % 256 == 0, "quantize_act: K must be a multiple of 256");
     KQ_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 15) == 0, "quantize_act: alignment");
     const int64_t nblocks = M * (K / 256);
-    quantize_act_kernel<<<(unsigned)kq_div_up(nblocks, 4), 128, 0, (cudaStream_t)stream>>>(x, nblocks, q, d,
+    kq_launch(quantize_act_kernel, (unsigned)kq_div_up(nblocks, 4), 128, 0, (cudaStream_t)stream, x, nblocks, q, d,
                                                                                         bsum16);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
@@ -286,7 +291,7 @@ static b200_status repack(const void *src, void *dst, int64_t n_rows, int64_t k,
     KQ_REQUIRE(n_rows > 0 && k > 0 && k % 256 == 0, "repack_q6k: bad shape");
     const int nb = (int)(k / 256);
     const int64_t total = n_rows * nb * 105;
-    repack_q6k_kernel<<<(unsigned)kq_div_up(total, 256), 256, 0, st>>>(
+    kq_launch(repack_q6k_kernel, (unsigned)kq_div_up(total, 256), 256, 0, st, 
         (const uint16_t *)src, (uint16_t *)dst, n_rows, nb, kq_device_row_bytes(B200_TYPE_Q6_K, k) / 2,
         inverse);
     KQ_COUNT_LAUNCH();

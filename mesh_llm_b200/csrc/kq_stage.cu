@@ -60,6 +60,7 @@ struct GraphEntry {
 // f32 matvec for the router: one warp per (token, expert)
 __global__ void __launch_bounds__(128) router_logits_kernel(const float *W, const float *x, int T, int E,
                                                             int h, float *out) {
+    KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (w >= (int64_t)T * E) return;
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const float *W, cons
 // out[t] = res[t] + sum_s w[t][s] * y[t*k+s]   (slot order, deterministic)
 __global__ void moe_combine_kernel(const float *y, const float *w, const float *res, int T, int k, int h,
                                    float *out) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)T * h) return;
     const int t = (int)(i / h), c = (int)(i % h);
@@ -88,12 +90,14 @@ __global__ void moe_combine_kernel(const float *y, const float *w, const float *
 
 __global__ void gather_rows_kernel(const float *x, int64_t row_stride, int64_t first, int n_rows, int h,
                                    float *y) {
+    KQ_PDL_ENTER();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)n_rows * h) return;
     y[i] = x[(first + (i / h) * row_stride) * h + i % h];
 }
 
-__global__ void set_pos_kernel(int32_t *p, int v) { *p = v; }
+__global__ void set_pos_kernel(int32_t *p, int v) {
+    KQ_PDL_ENTER(); *p = v; }
 
 uint64_t mix64_host(uint64_t z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -249,7 +253,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             const int E = c.n_expert, ku = c.n_expert_used, fe = c.n_ff_exp, pairs = rows * ku;
             OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, st->xn, st->aq, st->ad, st->abs16, s));
             if (classes & CLS_OTHER) {
-            router_logits_kernel<<<(unsigned)kq_div_up((int64_t)rows * E, 4), 128, 0, s>>>(L.router, st->xn,
+            kq_launch(router_logits_kernel, (unsigned)kq_div_up((int64_t)rows * E, 4), 128, 0, s, L.router, st->xn,
                                                                                           rows, E, h, st->rl);
             KQ_COUNT_LAUNCH();
             KQ_LAUNCH_CHECK();
@@ -269,7 +273,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             KqGemvIndirect ind2 = {st->rid, pairs, 1};
             GEMV_(kq_launch_gemv(&dn, 1, st->aq, st->ad, st->abs16, 1, fe, nullptr, 0, &ind2, s));
             if (classes & CLS_OTHER) {
-            moe_combine_kernel<<<(unsigned)kq_div_up((int64_t)rows * h, 256), 256, 0, s>>>(
+            kq_launch(moe_combine_kernel, (unsigned)kq_div_up((int64_t)rows * h, 256), 256, 0, s, 
                 st->yp, st->rw, st->x, rows, ku, h, xout);
             KQ_COUNT_LAUNCH();
             KQ_LAUNCH_CHECK();
@@ -639,7 +643,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
             KQ_CUDA(e);
             it = st->graphs.emplace(key, ge).first;
         }
-        set_pos_kernel<<<1, 1, 0, s>>>(st->pos0_dev, pos0);
+        kq_launch(set_pos_kernel, 1, 1, 0, s, st->pos0_dev, pos0);
         KQ_LAUNCH_CHECK();
         KQ_CUDA(cudaGraphLaunch(it->second.exec, s));
         st->launches += it->second.launches + 1;
@@ -666,7 +670,7 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
     float *hin = st->xn, *hout = st->att;
     cudaStream_t s = st->cap_stream;
     KQ_CUDA(cudaMemsetAsync(tok, 0, 256, s));
-    set_pos_kernel<<<1, 1, 0, s>>>(st->pos0_dev, pos0);
+    kq_launch(set_pos_kernel, 1, 1, 0, s, st->pos0_dev, pos0);
     KQ_LAUNCH_CHECK();
     const long long before = g_kq_launches;
     cudaGraph_t graph = nullptr;
