@@ -36,9 +36,11 @@ constexpr int MAX_UNITS = 160 * 16;
 constexpr uint32_t SPIN_LIMIT = 1u << 16;
 constexpr int ACT_BLK = 272; // 256 int8 codes + 16 bytes of padding
 
-// cross-warp fix-up scratch: partial sums and ready flags, one line per warp of the grid
-__device__ float g_partials[MAX_UNITS][16];
-__device__ int g_flags[MAX_UNITS];
+// Cross-warp fix-up scratch, one 128-byte line per warp of the grid.  An entry is a partial sum and
+// its ready flag in one 8-byte word (low half: float bits, high half: 1 when valid), written and
+// read with single 64-bit accesses, so publishing needs no fence and collecting costs one round
+// trip to L2.  The collector clears the entry after reading it.
+__device__ unsigned long long g_partials[MAX_UNITS][16];
 __device__ int g_stream_error; // 0 ok, 1 mbarrier wait gave up, 2 partial-sum wait gave up
 
 template <uint32_t TYPE>
@@ -396,32 +398,51 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
                 // the head of this row group belongs to an earlier warp: publish the partial sums
                 if (t == 0)
 #pragma unroll
-                    for (int m = 0; m < M; m++) g_partials[unit][rs * M + m] = v[m];
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicExch(&g_flags[unit], 1);
+                    for (int m = 0; m < M; m++)
+                        *(volatile unsigned long long *)&g_partials[unit][rs * M + m] =
+                            (unsigned long long)__float_as_uint(v[m]) | (1ull << 32);
             } else {
                 if (!last_slice) {
-                    // this warp owns the row group but later warps hold its tail: collect in order
+                    // This warp owns the row group but later warps hold its tail.  The LPR lanes of
+                    // a row each wait for one of the following warps, then the row's first lane adds
+                    // what they fetched in warp order.
                     const int64_t rg_last = rg_first + p.nsteps;
-                    for (int u2 = unit + 1; u2 < n_units; u2++) {
-                        const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
-                        if (b2 >= rg_last) break;
-                        if (e2 <= b2) continue;
-                        bool ok = s_abort != 0;
-                        for (uint32_t spin = 0; !ok && spin < SPIN_LIMIT; spin++) {
-                            ok = *(volatile int *)&g_flags[u2] != 0;
-                            if (!ok) __nanosleep(128);
+                    for (int base = unit + 1; base < n_units; base += F::LPR) {
+                        const int64_t b0 = total * base / n_units;
+                        if (b0 >= rg_last) break;
+                        const int u2 = base + t;
+                        bool mine = false;
+                        if (u2 < n_units) {
+                            const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                            mine = b2 < rg_last && e2 > b2;
                         }
-                        if (!ok) {
-                            s_abort = 1;
-                            atomicExch(&g_stream_error, 2);
-                        }
-                        __threadfence();
+                        float got[M];
 #pragma unroll
-                        for (int m = 0; m < M; m++) v[m] += *(volatile float *)&g_partials[u2][rs * M + m];
-                        __syncwarp();
-                        if (lane == 0) atomicExch(&g_flags[u2], 0);
+                        for (int m = 0; m < M; m++) {
+                            got[m] = 0.f;
+                            if (mine) {
+                                volatile unsigned long long *e = &g_partials[u2][rs * M + m];
+                                unsigned long long w = 0;
+                                bool ok = false;
+                                for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
+                                    w = *e;
+                                    ok = (w >> 32) != 0;
+                                    if (ok || s_abort) break;
+                                    __nanosleep(64);
+                                }
+                                if (!ok && !s_abort) {
+                                    s_abort = 1;
+                                    atomicExch(&g_stream_error, 2);
+                                }
+                                got[m] = __uint_as_float((uint32_t)w);
+                                *e = 0ull;
+                            }
+                        }
+#pragma unroll
+                        for (int m = 0; m < M; m++)
+#pragma unroll
+                            for (int o = 0; o < F::LPR; o++)
+                                v[m] += __shfl_sync(0xffffffffu, got[m], rs * F::LPR + o);
                     }
                 }
                 int seg, row0;
@@ -491,7 +512,7 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127);
     constexpr int WARPS = F::WARPS;
     int cap = F::SMEM_CAP;
-    if (M * act_tok + WARPS * 2 * F::SLOT > cap) cap = 216 * 1024; // long rows: take the whole SM
+    if (M * act_tok + WARPS * F::SLOT + 1024 > cap) cap = 216 * 1024; // long rows: take the whole SM
     int ns = (cap - M * act_tok - WARPS * 8 * 8) / (WARPS * F::SLOT);
     if (ns > 4) ns = 4;
     ns = env_int2("B200_GEMV_NS", ns);
