@@ -1,0 +1,353 @@
+// Decode attention (one new token per sequence) as ONE launch per layer: RoPE of q and k, the f16
+// store of the new K / V row into the cache, split-KV attention over the cache, and the combination
+// of the splits by whichever CTA finishes last.  At batch 1 this op reads a few MB, so its cost is
+// launches, round trips and dependent instruction chains, not bytes; the three kernels it replaces
+// (rope + store, attention, combine) each paid a launch and a drain.  The work is cut fine -- one
+// warp per (query head, 32 positions) -- because a thousand short warps finish sooner than a few
+// hundred long ones.
+#include "kq_common.cuh"
+
+#include <math.h>
+
+namespace {
+
+struct RopeTab {
+    float inv_freq[64];
+};
+
+__device__ int g_attn_error; // set if the split counter misbehaves (never expected)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// grid (n_kv, n_split, n_seq), 4 * G warps: warp (ti, g) serves query head kh * G + g on rows
+// ti*32 .. ti*32+31 of the CTA's current 128-row chunk.  The K and V rows of a chunk are brought
+// into shared memory by bulk asynchronous copies (one 2*HD-byte run per row and tensor), issued for
+// the first chunk before the kernel waits for its predecessor -- rows of earlier positions do not
+// depend on it.  Row pitch HD*2 + 16 bytes keeps the per-lane 16-byte reads of K on distinct banks.
+constexpr int ROWS_PER_CTA = 128;
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__restrict__ q, const float *__restrict__ k_new,
+                                                              const float *__restrict__ v_new, __half *kc, __half *vc,
+                                                              const int32_t *pos_dev, int pos_val, int n_head, int n_kv,
+                                                              int64_t seq_stride, int n_split, float scale, int neox,
+                                                              RopeTab tab, float *out, float *part_o, float *part_ml,
+                                                              int *counters) {
+    KQ_PDL_TRIGGER();
+    constexpr int DPL = HD / 32, HALF = HD / 2, PITCH = HD * 2 + 16, NT = 128 * G;
+    extern __shared__ __align__(128) uint8_t dsm[];
+    uint8_t *k_s = dsm, *v_s = dsm + ROWS_PER_CTA * PITCH;
+    float (*o_s)[G][HD] = reinterpret_cast<float (*)[G][HD]>(dsm + 2 * ROWS_PER_CTA * PITCH); // [4][G][HD]
+    __shared__ float q_s[G][HD];
+    __shared__ float p_s[4 * G][32];
+    __shared__ float ml_s[4][G][2];
+    __shared__ float w_s[G][64];
+    __shared__ float l_s[G][64];
+    __shared__ float inv_s[G];
+    __shared__ uint64_t bar;
+    __shared__ int s_last, s_abort;
+    const int kh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = warp % G, ti = warp / G;
+    const int pos = pos_dev ? *pos_dev : pos_val; // written before this step started
+    const int L = pos + 1;
+    int chunk = (L + n_split - 1) / n_split;
+    chunk = (chunk + ROWS_PER_CTA - 1) / ROWS_PER_CTA * ROWS_PER_CTA;
+    const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
+    __half *kbase = kc + seq * seq_stride + (int64_t)kh * HD;
+    __half *vbase = vc + seq * seq_stride + (int64_t)kh * HD;
+    const int64_t pstride = (int64_t)n_kv * HD;
+    const uint32_t bar_a = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_a), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0;
+    }
+    __syncthreads();
+
+    float m = -INFINITY, l = 0.f, o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; i++) o[i] = 0.f;
+    uint32_t phase = 0;
+    bool first = true;
+    for (int cb = p_begin; cb < p_end || first; cb += ROWS_PER_CTA) {
+        const int ccnt = max(0, min(ROWS_PER_CTA, p_end - cb));
+        const bool has_new = pos >= cb && pos < cb + ccnt;
+        const int n_copy = ccnt - (has_new ? 1 : 0);
+        if (n_copy > 0) { // the row of the new position is not in the cache yet
+            if (threadIdx.x == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(n_copy * 4 * HD)
+                             : "memory");
+            __syncthreads();
+            const int r = threadIdx.x, p = cb + r;
+            if (r < ccnt && p != pos) {
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(k_s + r * PITCH)),
+                             "l"(kbase + p * pstride), "r"(2 * HD), "r"(bar_a)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(v_s + r * PITCH)),
+                             "l"(vbase + p * pstride), "r"(2 * HD), "r"(bar_a)
+                             : "memory");
+            }
+        }
+        if (first) {
+            KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
+            if (ti == 0)
+                for (int f = lane; f < HALF; f += 32) { // query head g, rotated and pre-scaled
+                    const float ang = (float)pos * tab.inv_freq[f];
+                    const float c = cosf(ang), sn = sinf(ang);
+                    const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
+                    const float *qv = q + ((int64_t)seq * n_head + kh * G + g) * HD;
+                    const float a = qv[i0], b = qv[i1];
+                    q_s[g][i0] = (a * c - b * sn) * scale;
+                    q_s[g][i1] = (a * sn + b * c) * scale;
+                }
+            first = false;
+        }
+        if (has_new) {
+            // rotate k, round k and v to f16 as later steps will read them, into the chunk and the cache
+            const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
+            const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
+            __half *kt = reinterpret_cast<__half *>(k_s + (pos - cb) * PITCH);
+            __half *vt = reinterpret_cast<__half *>(v_s + (pos - cb) * PITCH);
+            for (int f = threadIdx.x; f < HALF; f += NT) {
+                const float ang = (float)pos * tab.inv_freq[f];
+                const float c = cosf(ang), sn = sinf(ang);
+                const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
+                const float a = kv[i0], b = kv[i1];
+                const __half r0 = __float2half_rn(a * c - b * sn), r1 = __float2half_rn(a * sn + b * c);
+                kt[i0] = r0;
+                kt[i1] = r1;
+                kbase[pos * pstride + i0] = r0;
+                kbase[pos * pstride + i1] = r1;
+            }
+            for (int i = threadIdx.x; i < HD; i += NT) {
+                const __half r = __float2half_rn(vv[i]);
+                vt[i] = r;
+                vbase[pos * pstride + i] = r;
+            }
+        }
+        __syncthreads();
+        if (ccnt == 0) break;
+        if (n_copy > 0) { // bounded wait for the chunk
+            bool ok = false;
+            for (uint32_t spin = 0; spin < (1u << 16) && !s_abort; spin++) {
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(done)
+                             : "r"(bar_a), "r"(phase)
+                             : "memory");
+                if (done) {
+                    ok = true;
+                    break;
+                }
+                if (spin > 32) __nanosleep(64);
+            }
+            if (!ok && !s_abort) {
+                s_abort = 1;
+                atomicExch(&g_attn_error, 2);
+            }
+            phase ^= 1;
+        }
+        // this warp's tile: rows ti*32 .. +31 of the chunk, lane = position
+        const int cnt = max(0, min(32, ccnt - ti * 32));
+        if (cnt > 0) {
+            const bool valid = lane < cnt;
+            float sc = 0.f;
+            if (valid) {
+                const uint4 *kr = reinterpret_cast<const uint4 *>(k_s + (ti * 32 + lane) * PITCH);
+#pragma unroll
+                for (int c8 = 0; c8 < HD / 8; c8++) {
+                    const uint4 raw = kr[c8];
+                    const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                    const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]), f2 = __half22float2(h2[2]),
+                                 f3 = __half22float2(h2[3]);
+                    const float4 qa = *reinterpret_cast<const float4 *>(&q_s[g][c8 * 8]);
+                    const float4 qb = *reinterpret_cast<const float4 *>(&q_s[g][c8 * 8 + 4]);
+                    sc = fmaf(qa.x, f0.x, sc); sc = fmaf(qa.y, f0.y, sc); sc = fmaf(qa.z, f1.x, sc); sc = fmaf(qa.w, f1.y, sc);
+                    sc = fmaf(qb.x, f2.x, sc); sc = fmaf(qb.y, f2.y, sc); sc = fmaf(qb.z, f3.x, sc); sc = fmaf(qb.w, f3.y, sc);
+                }
+            }
+            const float sv = valid ? sc : -INFINITY;
+            const float mt = kq_warp_max(sv);
+            const float mn = fmaxf(m, mt);
+            const float alpha = (m == -INFINITY) ? 0.f : expf(m - mn);
+            const float pv = valid ? expf(sv - mn) : 0.f;
+            l = l * alpha + kq_warp_sum(pv);
+            m = mn;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) o[i] *= alpha;
+            p_s[warp][lane] = pv;
+            __syncwarp();
+            for (int j = 0; j < cnt; j++) {
+                const __half *vr = reinterpret_cast<const __half *>(v_s + (ti * 32 + j) * PITCH) + lane * DPL;
+                const float pj = p_s[warp][j];
+                if (DPL == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
+                    const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                    const float2 a = __half22float2(h2[0]), b = __half22float2(h2[1]);
+                    o[0] = fmaf(pj, a.x, o[0]); o[1] = fmaf(pj, a.y, o[1]); o[2] = fmaf(pj, b.x, o[2]); o[3] = fmaf(pj, b.y, o[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) o[i] = fmaf(pj, __half2float(vr[i]), o[i]);
+                }
+            }
+        }
+        __syncthreads(); // the chunk may be overwritten by the next one
+    }
+
+    // combine the 4 tiles of each head inside the CTA (tile order)
+#pragma unroll
+    for (int i = 0; i < DPL; i++) o_s[ti][g][lane * DPL + i] = o[i];
+    if (lane == 0) {
+        ml_s[ti][g][0] = m;
+        ml_s[ti][g][1] = l;
+    }
+    __syncthreads();
+    const int head = kh * G + g;
+    if (ti == 0) {
+        float mm = -INFINITY;
+        for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[w][g][0]);
+        float acc[DPL], ll = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+        for (int w = 0; w < 4; w++) {
+            const float mw = ml_s[w][g][0];
+            const float wgt = (mw == -INFINITY) ? 0.f : expf(mw - mm);
+#pragma unroll
+            for (int i = 0; i < DPL; i++) acc[i] += wgt * o_s[w][g][lane * DPL + i];
+            ll += wgt * ml_s[w][g][1];
+        }
+        if (n_split == 1) {
+#pragma unroll
+            for (int i = 0; i < DPL; i++) out[((int64_t)seq * n_head + head) * HD + lane * DPL + i] = acc[i] / ll;
+        } else {
+            const int64_t pi = ((int64_t)seq * n_head + head) * n_split + split;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) part_o[pi * HD + lane * DPL + i] = acc[i];
+            if (lane == 0) {
+                part_ml[pi * 2] = mm;
+                part_ml[pi * 2 + 1] = ll;
+            }
+        }
+    }
+    if (n_split == 1) return;
+    // the CTA that finishes last combines the splits of its G heads (in split order) and re-arms
+    // the counter for the next launch
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&counters[seq * n_kv + kh], 1);
+        if (prev < 0 || prev >= n_split) atomicExch(&g_attn_error, 1);
+        s_last = prev == n_split - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (ti == 0) {
+        // splits were written by other SMs: read them through L2 (ld.cg); max / weights once per head
+        for (int sp = lane; sp < n_split; sp += 32) {
+            const int64_t e = (((int64_t)seq * n_head + head) * n_split + sp) * 2;
+            w_s[g][sp] = __ldcg(&part_ml[e]);
+            l_s[g][sp] = __ldcg(&part_ml[e + 1]);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            float mm = -INFINITY;
+            for (int sp = 0; sp < n_split; sp++) mm = fmaxf(mm, w_s[g][sp]);
+            float ll = 0.f;
+            for (int sp = 0; sp < n_split; sp++) {
+                const float ms = w_s[g][sp];
+                const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - mm);
+                ll += wgt * l_s[g][sp];
+                w_s[g][sp] = wgt;
+            }
+            inv_s[g] = ll;
+        }
+        __syncwarp();
+        const float *po = part_o + (((int64_t)seq * n_head + head) * n_split) * HD + lane * DPL;
+        float acc[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+        for (int s0 = 0; s0 < n_split; s0 += 8) { // 8 splits' loads in flight at a time
+            float t[8][DPL];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+#pragma unroll
+                for (int i = 0; i < DPL; i++) t[u][i] = s0 + u < n_split ? __ldcg(po + (int64_t)(s0 + u) * HD + i) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (s0 + u < n_split)
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) acc[i] += w_s[g][s0 + u] * t[u][i];
+        }
+#pragma unroll
+        for (int i = 0; i < DPL; i++) out[((int64_t)seq * n_head + head) * HD + lane * DPL + i] = acc[i] / inv_s[g];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) counters[seq * n_kv + kh] = 0;
+}
+
+template <int HD>
+b200_status launch_g(int G, dim3 grid, cudaStream_t st, const float *q, const float *k, const float *v, __half *kc,
+                     __half *vc, const int32_t *pos_dev, int pos, int n_head, int n_kv, int64_t seq_stride, int n_split,
+                     float scale, int neox, const RopeTab &tab, float *out, float *po, float *pml, int *counters) {
+    const size_t smem = 2 * ROWS_PER_CTA * (HD * 2 + 16) + (size_t)4 * G * HD * sizeof(float);
+#define KQ_AD(GG)                                                                                              \
+    if (smem > 48 * 1024)                                                                                      \
+        cudaFuncSetAttribute(attn_decode_kernel<HD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    kq_launch(attn_decode_kernel<HD, GG>, grid, 128 * GG, smem, st, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, seq_stride, \
+              n_split, scale, neox, tab, out, po, pml, counters)
+    switch (G) {
+    case 1: KQ_AD(1); break;
+    case 2: KQ_AD(2); break;
+    case 4: KQ_AD(4); break;
+    case 5: KQ_AD(5); break;
+    case 8: KQ_AD(8); break;
+    default: kq_set_error("attention: %d query heads per KV head not supported", G); return B200_ERR_UNSUPPORTED;
+    }
+#undef KQ_AD
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+} // namespace
+
+// Number of position slices for a context of L rows: 128 rows per slice, at most 64 slices, and
+// constant over a power-of-two stretch of L so that a captured launch configuration stays valid.
+int kq_attention_decode_splits(int64_t L) {
+    int64_t cap = 128;
+    while (cap < L) cap *= 2;
+    int64_t n = cap / 128;
+    return (int)(n > 64 ? 64 : n);
+}
+
+// q [n_seq][n_head][hd], k / v [n_seq][n_kv][hd] f32 as they come out of the qkv projection (not yet
+// rotated); caches of sequence s start s * seq_stride elements in.  scratch holds the split
+// partials, counters one zero-initialised int per (sequence, kv head).
+b200_status kq_attention_decode(const float *q, const float *k, const float *v, uint16_t *kc, uint16_t *vc,
+                                int n_seq, const int32_t *pos_dev, int pos, int n_head, int n_kv, int hd,
+                                int64_t seq_stride, float theta, int neox, int n_split, float *out, float *scratch,
+                                size_t scratch_bytes, int *counters, cudaStream_t st) {
+    KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
+    KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
+    if (n_split > 64) n_split = 64;
+    size_t need = (size_t)n_seq * n_head * n_split * (hd + 2) * sizeof(float);
+    while (n_split > 1 && (need > scratch_bytes || !counters)) {
+        n_split /= 2;
+        need = (size_t)n_seq * n_head * n_split * (hd + 2) * sizeof(float);
+    }
+    RopeTab tab;
+    for (int i = 0; i < hd / 2; i++) tab.inv_freq[i] = (float)pow((double)theta, -2.0 * i / (double)hd);
+    float *po = scratch, *pml = scratch ? scratch + (size_t)n_seq * n_head * n_split * hd : nullptr;
+    const float scale = 1.0f / sqrtf((float)hd);
+    dim3 grid(n_kv, n_split, n_seq);
+    const int G = n_head / n_kv;
+    if (hd == 128)
+        return launch_g<128>(G, grid, st, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv, seq_stride,
+                             n_split, scale, neox, tab, out, po, pml, counters);
+    return launch_g<64>(G, grid, st, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv, seq_stride,
+                        n_split, scale, neox, tab, out, po, pml, counters);
+}

@@ -182,12 +182,25 @@ struct KqGemvIndirect {
     int32_t act_div;           // activation row of pair p is p / act_div
 };
 
+// f32 activations to be prepared by the GEMV itself: optional RMSNorm (weight may be null = 1),
+// then the Q8 quantiser.  q / d / bs passed alongside are scratch for the case that the plain
+// kernel has to be used.
+struct KqActPrep {
+    const float *x;      // [M][K]
+    const float *norm_w; // [K] or null
+    float eps;
+    int32_t do_norm;
+};
+
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
-                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st);
+                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st,
+                           const KqActPrep *prep = nullptr);
 b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                                   const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
-                                  cudaStream_t st);
+                                  const KqActPrep *prep, cudaStream_t st);
+b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y, int8_t *q,
+                        float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride);
 int kq_stream_error_fetch(); // 0 ok; nonzero = a bounded device-side wait gave up since the last call
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
                            const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,

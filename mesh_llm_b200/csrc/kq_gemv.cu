@@ -285,7 +285,7 @@ b200_status launch_mr(const GemvParams &p, int wn, int n_pairs, cudaStream_t st)
 
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
-                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st) {
+                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st, const KqActPrep *prep) {
     KQ_REQUIRE(nseg >= 1 && nseg <= 3, "gemv: 1..3 segments");
     KQ_REQUIRE(M >= 1 && M <= 8, "gemv: M must be 1..8 (got %d)", M);
     KQ_REQUIRE(K > 0 && K % 256 == 0, "gemv: K must be a positive multiple of 256");
@@ -294,8 +294,16 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
                "gemv: swiglu needs two equal segments");
     KQ_REQUIRE(!residual || nseg == 1, "gemv: residual only with one segment");
     if (!(ind && ind->expert_ids) && M <= 2 && K % 256 == 0) {
-        const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, st);
+        const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, prep, st);
         if (rs != B200_ERR_UNSUPPORTED) return rs;
+    }
+    if (prep && prep->x) {
+        // the plain kernel wants quantised activations: prepare them into the caller's scratch
+        KQ_REQUIRE(q && d && bs, "gemv: activation scratch required");
+        b200_status rc = prep->do_norm ? kq_rms_norm(prep->x, prep->norm_w, M, K, prep->eps, nullptr, (int8_t *)q, (float *)d,
+                                                     (int16_t *)bs, st, 0)
+                                       : b200_quantize_act(prep->x, M, K, (int8_t *)q, (float *)d, (int16_t *)bs, st);
+        if (rc != B200_OK) return rc;
     }
     GemvParams p = {};
     const int R = M <= 4 ? 4 : 2;

@@ -69,6 +69,12 @@ struct StreamParams {
     const float *ad;
     const int16_t *abs16;
     const float *residual;
+    // fused activation preparation: when x is set the kernel quantises the f32 activations itself
+    // (after an optional RMSNorm with weight norm_w) instead of reading aq / ad / abs16
+    const float *x;
+    const float *norm_w;
+    float eps;
+    int32_t do_norm;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -345,6 +351,72 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
         for (int j = 0; j < pre; j++) iss.post(p, lane, ring_addr + j * F::SLOT, bar_addr + j * 8);
     }
     KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
+    if (p.x) {
+        // Every CTA prepares the activations for itself: K floats per token from L2, RMSNorm with
+        // the sum of squares in double (same reduction tree as the stand-alone kernel: the first 256
+        // threads, 8 partials added in order), then the Q8 quantiser, one warp per 256-block.
+        __shared__ double s_part[8];
+        __shared__ float s_scale[2];
+        for (int m = 0; m < M; m++) {
+            const float *xr = p.x + (int64_t)m * p.K;
+            if (p.do_norm) {
+                if (threadIdx.x < 256) {
+                    double ss = 0.0;
+                    for (int i = threadIdx.x * 4; i < p.K; i += 1024) {
+                        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+                        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (lane == 0) s_part[warp] = ss;
+                }
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    double tsum = 0.0;
+                    for (int i = 0; i < 8; i++) tsum += s_part[i];
+                    s_scale[m] = 1.0f / sqrtf((float)(tsum / (double)p.K) + p.eps);
+                }
+                __syncthreads();
+            }
+            const float scale = p.do_norm ? s_scale[m] : 1.0f;
+            uint8_t *tq = smem + m * act_tok;
+            for (int b = warp; b < nb; b += WARPS) {
+                const int o = b * 256 + lane * 8;
+                const float4 va = *reinterpret_cast<const float4 *>(xr + o);
+                const float4 vb = *reinterpret_cast<const float4 *>(xr + o + 4);
+                float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+                if (p.do_norm) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = v[i] * scale * (p.norm_w ? p.norm_w[o + i] : 1.0f);
+                }
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+                amax = kq_warp_max(amax);
+                const float dq = kq_act_scale(amax), id = kq_act_inv(dq);
+                int c8[8], sum = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    c8[i] = kq_act_code(v[i], id);
+                    sum += c8[i];
+                }
+                uint2 pk;
+                pk.x = (uint32_t)(c8[0] & 0xFF) | ((uint32_t)(c8[1] & 0xFF) << 8) | ((uint32_t)(c8[2] & 0xFF) << 16) |
+                       ((uint32_t)(c8[3] & 0xFF) << 24);
+                pk.y = (uint32_t)(c8[4] & 0xFF) | ((uint32_t)(c8[5] & 0xFF) << 8) | ((uint32_t)(c8[6] & 0xFF) << 16) |
+                       ((uint32_t)(c8[7] & 0xFF) << 24);
+                *reinterpret_cast<uint2 *>(tq + b * ACT_BLK + lane * 8) = pk;
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1); // 16 elements
+                if (TYPE == B200_TYPE_Q4_K) {
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2); // 32 elements
+                    if ((lane & 3) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 8 + (lane >> 2)] = (int16_t)sum;
+                } else {
+                    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 16 + (lane >> 1)] = (int16_t)sum;
+                }
+                if (lane == 0) reinterpret_cast<float *>(tq + act_q + act_s)[b] = dq;
+            }
+        }
+    } else
     for (int m = 0; m < M; m++) {
         uint8_t *tq = smem + m * act_tok;
         const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.K);
@@ -488,7 +560,7 @@ int env_int2(const char *name, int dflt) {
 
 template <uint32_t TYPE, int M>
 b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
-                         int64_t K, const float *residual, int swiglu_pairs, cudaStream_t st) {
+                         int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st) {
     using F = Fmt<TYPE>;
     StreamParams p = {};
     const int rows_per_rg = swiglu_pairs ? F::ROWS / 2 : F::ROWS;
@@ -508,6 +580,12 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     p.ad = d;
     p.abs16 = bs;
     p.residual = residual;
+    if (prep && prep->x) {
+        p.x = prep->x;
+        p.norm_w = prep->norm_w;
+        p.eps = prep->eps;
+        p.do_norm = prep->do_norm;
+    }
     const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
     const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127);
     constexpr int WARPS = F::WARPS;
@@ -549,13 +627,14 @@ int kq_stream_error_fetch() {
 // per type.
 b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                                   const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
-                                  cudaStream_t st) {
+                                  const KqActPrep *prep, cudaStream_t st) {
     if (M < 1 || M > 2 || K % 256 != 0 || env_int2("B200_GEMV_STREAM", 1) == 0) return B200_ERR_UNSUPPORTED;
     for (int i = 0; i < nseg; i++) {
         if (segs[i].type != B200_TYPE_Q4_K && segs[i].type != B200_TYPE_Q6_K) return B200_ERR_UNSUPPORTED;
         if (((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;
     }
-    if (((uintptr_t)q & 15) != 0) return B200_ERR_UNSUPPORTED;
+    if (!(prep && prep->x) && ((uintptr_t)q & 15) != 0) return B200_ERR_UNSUPPORTED;
+    if (prep && prep->x && ((uintptr_t)prep->x & 15) != 0) return B200_ERR_UNSUPPORTED;
     for (uint32_t type : {(uint32_t)B200_TYPE_Q4_K, (uint32_t)B200_TYPE_Q6_K}) {
         KqGemvSeg sel[3];
         int n = 0;
@@ -565,11 +644,11 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
         if (swiglu_pairs && n != 2) return B200_ERR_UNSUPPORTED;
         b200_status rc;
         if (type == B200_TYPE_Q4_K)
-            rc = M == 1 ? launch_block<B200_TYPE_Q4_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, st)
-                        : launch_block<B200_TYPE_Q4_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, st);
+            rc = M == 1 ? launch_block<B200_TYPE_Q4_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st)
+                        : launch_block<B200_TYPE_Q4_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st);
         else
-            rc = M == 1 ? launch_block<B200_TYPE_Q6_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, st)
-                        : launch_block<B200_TYPE_Q6_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, st);
+            rc = M == 1 ? launch_block<B200_TYPE_Q6_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st)
+                        : launch_block<B200_TYPE_Q6_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st);
         if (rc != B200_OK) return rc;
     }
     return B200_OK;

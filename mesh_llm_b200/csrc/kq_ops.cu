@@ -100,22 +100,29 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
 #pragma unroll
         for (int g = 0; g < G; g++) s[g] = 0.f;
         if (valid) {
+            // the whole K row is requested up front (8 loads in flight per lane), q comes from
+            // shared memory as float4 broadcasts
             const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + p * pstride);
-#pragma unroll 4
-            for (int c8 = 0; c8 < HD / 8; c8++) {
-                const uint4 raw = kr[c8];
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-                float kf[8];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(h2[i]);
-                    kf[2 * i] = f.x;
-                    kf[2 * i + 1] = f.y;
+            for (int c0 = 0; c0 < HD / 8; c0 += 8) {
+                uint4 raw[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) raw[u] = kr[c0 + u];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw[u]);
+                    const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]), f2 = __half22float2(h2[2]),
+                                 f3 = __half22float2(h2[3]);
+#pragma unroll
+                    for (int g = 0; g < G; g++) {
+                        const float4 qa = *reinterpret_cast<const float4 *>(&q_s[g][(c0 + u) * 8]);
+                        const float4 qb = *reinterpret_cast<const float4 *>(&q_s[g][(c0 + u) * 8 + 4]);
+                        float t = s[g];
+                        t = fmaf(qa.x, f0.x, t); t = fmaf(qa.y, f0.y, t); t = fmaf(qa.z, f1.x, t); t = fmaf(qa.w, f1.y, t);
+                        t = fmaf(qb.x, f2.x, t); t = fmaf(qb.y, f2.y, t); t = fmaf(qb.z, f3.x, t); t = fmaf(qb.w, f3.y, t);
+                        s[g] = t;
+                    }
                 }
-#pragma unroll
-                for (int g = 0; g < G; g++)
-#pragma unroll
-                    for (int i = 0; i < 8; i++) s[g] = fmaf(q_s[g][c8 * 8 + i], kf[i], s[g]);
             }
         }
 #pragma unroll
@@ -133,23 +140,33 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
         }
         __syncwarp();
         const int cnt = min(32, p_end - tb);
-        for (int j = 0; j < cnt; j++) {
-            const __half *vr = vbase + (tb + j) * pstride + lane * DPL;
-            float vf[DPL];
-            if (DPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-                const float2 a = __half22float2(h2[0]), b = __half22float2(h2[1]);
-                vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
-            } else {
+        // V rows in batches of 8: all loads of a batch are issued before the first is used
+        for (int j0 = 0; j0 < cnt; j0 += 8) {
+            float vf[8][DPL];
 #pragma unroll
-                for (int i = 0; i < DPL; i++) vf[i] = __half2float(vr[i]);
+            for (int u = 0; u < 8; u++) {
+                const bool in = j0 + u < cnt;
+                const __half *vr = vbase + (tb + (in ? j0 + u : 0)) * pstride + lane * DPL;
+                if (DPL == 4) {
+                    const uint2 raw = in ? *reinterpret_cast<const uint2 *>(vr) : make_uint2(0u, 0u);
+                    const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                    const float2 a = __half22float2(h2[0]), b = __half22float2(h2[1]);
+                    vf[u][0] = a.x; vf[u][1] = a.y; vf[u][2] = b.x; vf[u][3] = b.y;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) vf[u][i] = in ? __half2float(vr[i]) : 0.f;
+                }
             }
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float pv = p_s[warp][g][j];
+            for (int u = 0; u < 8; u++) {
+                if (j0 + u < cnt) {
 #pragma unroll
-                for (int i = 0; i < DPL; i++) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+                    for (int g = 0; g < G; g++) {
+                        const float pv = p_s[warp][g][j0 + u];
+#pragma unroll
+                        for (int i = 0; i < DPL; i++) o[g][i] = fmaf(pv, vf[u][i], o[g][i]);
+                    }
+                }
             }
         }
         __syncwarp();

@@ -21,6 +21,11 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
                          int force_splits, cudaStream_t st);
 int kq_attention_splits(int64_t rows, int n_kv, int64_t L);
+int kq_attention_decode_splits(int64_t L);
+b200_status kq_attention_decode(const float *q, const float *k, const float *v, uint16_t *kc, uint16_t *vc,
+                                int n_seq, const int32_t *pos_dev, int pos, int n_head, int n_kv, int hd,
+                                int64_t seq_stride, float theta, int neox, int n_split, float *out, float *scratch,
+                                size_t scratch_bytes, int *counters, cudaStream_t st);
 b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos,
                           const int32_t *pos0_dev, int pos0, int n_seq, int T, int n_head, int n_kv, int hd,
                           float theta, int neox, uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride,
@@ -128,7 +133,7 @@ struct b200_stage {
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr,
           *u = nullptr, *last = nullptr, *logits_int = nullptr, *att_scratch = nullptr, *rl = nullptr,
           *rw = nullptr, *hp = nullptr, *yp = nullptr;
-    int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr;
+    int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
     size_t att_scratch_bytes = 0;
     int8_t *aq = nullptr;
     float *ad = nullptr;
@@ -222,14 +227,17 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
         uint16_t *kc = st->kc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
         uint16_t *vc = st->vc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
         // ---- attention block
-        OTHER_(kq_rms_norm(xin, L.attn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
+        const bool fuse = rows <= 2; // the streaming GEMV normalises and quantises its own input
+        if (!fuse) OTHER_(kq_rms_norm(xin, L.attn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
         if (rows <= 8) {
             KqGemvSeg segs[3] = {
                 {(const uint8_t *)L.wq->dev, L.wq->type, nq, st->q, L.bq, nq, 0},
                 {(const uint8_t *)L.wk->dev, L.wk->type, nkv, st->k, L.bk, nkv, 0},
                 {(const uint8_t *)L.wv->dev, L.wv->type, nkv, st->v, L.bv, nkv, 0},
             };
-            GEMV_(kq_launch_gemv(segs, 3, st->aq, st->ad, st->abs16, rows, h, nullptr, 0, nullptr, s));
+            KqActPrep pr = {xin, L.attn_norm, c.rms_eps, 1};
+            GEMV_(kq_launch_gemv(segs, 3, st->aq, st->ad, st->abs16, rows, h, nullptr, 0, nullptr, s,
+                                 fuse ? &pr : nullptr));
         } else {
             GEMV_(mm(st, L.wq, rows, st->q, L.bq, nullptr, s));
             GEMV_(mm(st, L.wk, rows, st->k, L.bk, nullptr, s));
@@ -241,12 +249,26 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             OTHER_(kq_rms_norm(st->k, L.k_norm, (int64_t)rows * c.n_head_kv, hd, c.rms_eps, st->k, nullptr,
                                nullptr, nullptr, s));
         }
-        OTHER_(kq_rope_store(st->q, st->k, st->v, nullptr, pos_dev, pos0, n_seq, T, c.n_head, c.n_head_kv, hd,
-                             c.rope_theta, c.rope_neox, kc, vc, seq_stride, s));
-        ATTN_(kq_attention(st->q, kc, vc, n_seq, T, pos_dev, pos0, c.n_head, c.n_head_kv, hd, seq_stride,
-                            st->att, st->att_scratch, st->att_scratch_bytes, force_splits, s));
-        OTHER_(b200_quantize_act(st->att, rows, nq, st->aq, st->ad, st->abs16, s));
-        GEMV_(mm(st, L.wo, rows, st->x, nullptr, xin, s)); // x = xin + Wo.att
+        if (T == 1) {
+            // decode: RoPE, KV store, attention and the split combine are one launch
+            const int ns = kq_attention_decode_splits(pos0 + 1);
+            ATTN_(kq_attention_decode(st->q, st->k, st->v, kc, vc, n_seq, pos_dev, pos0, c.n_head, c.n_head_kv, hd,
+                                      seq_stride, c.rope_theta, c.rope_neox, ns, st->att, st->att_scratch,
+                                      st->att_scratch_bytes, st->attn_counters, s));
+        } else {
+            OTHER_(kq_rope_store(st->q, st->k, st->v, nullptr, pos_dev, pos0, n_seq, T, c.n_head, c.n_head_kv, hd,
+                                 c.rope_theta, c.rope_neox, kc, vc, seq_stride, s));
+            ATTN_(kq_attention(st->q, kc, vc, n_seq, T, pos_dev, pos0, c.n_head, c.n_head_kv, hd, seq_stride,
+                               st->att, st->att_scratch, st->att_scratch_bytes, force_splits, s));
+        }
+        if (fuse) {
+            KqGemvSeg so = {(const uint8_t *)L.wo->dev, L.wo->type, h, st->x, nullptr, h, 0};
+            KqActPrep pr = {st->att, nullptr, 0.f, 0};
+            GEMV_(kq_launch_gemv(&so, 1, st->aq, st->ad, st->abs16, rows, nq, xin, 0, nullptr, s, &pr));
+        } else {
+            OTHER_(b200_quantize_act(st->att, rows, nq, st->aq, st->ad, st->abs16, s));
+            GEMV_(mm(st, L.wo, rows, st->x, nullptr, xin, s)); // x = xin + Wo.att
+        }
         // ---- feed-forward block
         float *xout = (last_layer && !c.has_output && hidden_out) ? hidden_out : st->x;
         if (c.n_expert > 0) {
@@ -279,20 +301,28 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             KQ_LAUNCH_CHECK();
             }
         } else {
-            OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
+            if (!fuse) OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
             if (rows <= 8) {
                 KqGemvSeg gu[2] = {
                     {(const uint8_t *)L.gate->dev, L.gate->type, c.n_ff, st->g, nullptr, c.n_ff, 0},
                     {(const uint8_t *)L.up->dev, L.up->type, c.n_ff, st->g, nullptr, c.n_ff, 0},
                 };
-                GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, rows, h, nullptr, 1, nullptr, s));
+                KqActPrep pr = {st->x, L.ffn_norm, c.rms_eps, 1};
+                GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, rows, h, nullptr, 1, nullptr, s,
+                                     fuse ? &pr : nullptr));
             } else {
                 GEMV_(mm(st, L.gate, rows, st->g, nullptr, nullptr, s));
                 GEMV_(mm(st, L.up, rows, st->u, nullptr, nullptr, s));
                 OTHER_(b200_swiglu(st->g, st->u, (int64_t)rows * c.n_ff, st->g, s));
             }
-            OTHER_(b200_quantize_act(st->g, rows, c.n_ff, st->aq, st->ad, st->abs16, s));
-            GEMV_(mm(st, L.down, rows, xout, nullptr, st->x, s)); // x = x + Wdown.act
+            if (fuse) {
+                KqGemvSeg sd = {(const uint8_t *)L.down->dev, L.down->type, h, xout, nullptr, h, 0};
+                KqActPrep pr = {st->g, nullptr, 0.f, 0};
+                GEMV_(kq_launch_gemv(&sd, 1, st->aq, st->ad, st->abs16, rows, c.n_ff, st->x, 0, nullptr, s, &pr));
+            } else {
+                OTHER_(b200_quantize_act(st->g, rows, c.n_ff, st->aq, st->ad, st->abs16, s));
+                GEMV_(mm(st, L.down, rows, xout, nullptr, st->x, s)); // x = x + Wdown.act
+            }
         }
         xin = xout;
     }
@@ -307,9 +337,15 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             KQ_REQUIRE(logits || out_rows <= c.n_seq, "stage: internal logits hold one row per sequence");
             // last token of each sequence: rows T-1, 2T-1, ...
             const float *src = all_logits ? xin : xin + (int64_t)(T - 1) * h;
-            OTHER_(kq_rms_norm(src, st->out_norm, out_rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s,
-                               all_logits ? h : (int64_t)T * h));
-            GEMV_(mm(st, st->out_w, out_rows, lg, nullptr, nullptr, s));
+            if (out_rows <= 2 && (T == 1 || all_logits)) {
+                KqGemvSeg sh = {(const uint8_t *)st->out_w->dev, st->out_w->type, c.n_vocab, lg, nullptr, c.n_vocab, 0};
+                KqActPrep pr = {src, st->out_norm, c.rms_eps, 1};
+                GEMV_(kq_launch_gemv(&sh, 1, st->aq, st->ad, st->abs16, out_rows, h, nullptr, 0, nullptr, s, &pr));
+            } else {
+                OTHER_(kq_rms_norm(src, st->out_norm, out_rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s,
+                                   all_logits ? h : (int64_t)T * h));
+                GEMV_(mm(st, st->out_w, out_rows, lg, nullptr, nullptr, s));
+            }
             if (next_tokens) OTHER_(b200_argmax(lg, out_rows, c.n_vocab, next_tokens, s));
         }
     }
@@ -451,6 +487,7 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
     A((void **)&st->att_scratch, st->att_scratch_bytes);
     A((void **)&st->pos0_dev, 256);
     A((void **)&st->rid_scratch, 1024);
+    A((void **)&st->attn_counters, (size_t)c.n_seq * c.n_head_kv * 4 + 256);
     if (c.has_output) A((void **)&st->logits_int, (size_t)c.n_seq * c.n_vocab * 4);
     if (c.n_expert > 0) {
         A((void **)&st->rl, R * c.n_expert * 4);
@@ -461,6 +498,10 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
     }
     if (rc == B200_OK && cudaStreamCreateWithFlags(&st->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
         kq_set_error("stage: cudaStreamCreate failed");
+        rc = B200_ERR_CUDA;
+    }
+    if (rc == B200_OK && cudaMemset(st->attn_counters, 0, (size_t)c.n_seq * c.n_head_kv * 4 + 256) != cudaSuccess) {
+        kq_set_error("stage: clearing the attention counters failed");
         rc = B200_ERR_CUDA;
     }
     if (rc == B200_OK && kv) {
@@ -613,7 +654,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
     const long long before = g_kq_launches;
     if (T == 1 && st->use_graph) {
         // decode step: positions come from device memory so one captured graph serves every step
-        const int n_split = kq_attention_splits(n_seq, c.n_head_kv, pos0 + 1);
+        const int n_split = kq_attention_decode_splits(pos0 + 1);
         GraphKey key;
         memset(&key, 0, sizeof(key));
         key.n_seq = n_seq;
