@@ -58,6 +58,7 @@ vp, i64, i32, u32, u64, sz = C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_u
 SIGNATURES = {
     "b200_status_string": (C.c_char_p, [i32]),
     "b200_last_error": (C.c_char_p, []),
+    "b200_check_device_waits": (i32, []),
     "b200_reg_name": (C.c_char_p, []),
     "b200_reg_device_count": (i32, []),
     "b200_dev_name": (i32, [i32, C.c_char_p, sz]),

@@ -131,19 +131,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
         __syncthreads();
         if (ccnt == 0) break;
         if (n_copy > 0) { // bounded wait for the chunk
-            bool ok = false;
-            for (uint32_t spin = 0; spin < (1u << 16) && !s_abort; spin++) {
-                uint32_t done;
-                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(done)
-                             : "r"(bar_a), "r"(phase)
-                             : "memory");
-                if (done) {
-                    ok = true;
-                    break;
-                }
-                if (spin > 32) __nanosleep(64);
-            }
+            const bool ok = s_abort ? false : kq_mbar_wait(bar_a, phase, KQ_WAIT_LIMIT_NS);
             if (!ok && !s_abort) {
                 s_abort = 1;
                 atomicExch(&g_attn_error, 2);

@@ -52,6 +52,16 @@ const char *b200_status_string(b200_status s) {
     }
 }
 
+b200_status b200_check_device_waits(void) {
+    KQ_CUDA(cudaDeviceSynchronize());
+    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
+    if (werr) {
+        kq_set_error("a bounded device-side wait gave up (code 0x%x)", werr);
+        return B200_ERR_TIMEOUT;
+    }
+    return B200_OK;
+}
+
 const char *b200_reg_name(void) { return "B200"; }
 
 int32_t b200_reg_device_count(void) {

@@ -155,6 +155,33 @@ __device__ __forceinline__ uint4 kq_ld_stream(const void *p) {
     return v;
 }
 
+// ---- bounded waits ------------------------------------------------------------------------------
+// Every device-side wait of the library is bounded in wall-clock time (not in iterations:
+// mbarrier.try_wait may itself suspend the thread for a system-dependent while), after which the
+// caller records an error and carries on to its exit path.
+__device__ __forceinline__ uint64_t kq_globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool kq_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// true when the phase completed, false after limit_ns without completion
+__device__ __forceinline__ bool kq_mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+    if (kq_mbar_try(bar, parity)) return true;
+    const uint64_t t0 = kq_globaltimer_ns();
+    while (!kq_mbar_try(bar, parity))
+        if (kq_globaltimer_ns() - t0 > limit_ns) return false;
+    return true;
+}
+#define KQ_WAIT_LIMIT_NS 20000000ull /* 20 ms: four orders of magnitude above any healthy wait */
+
 // The activation quantiser of the library (same arithmetic as the CPU oracle, operation for
 // operation, so the int8 codes are bit-identical): d = amax / 127, id = 1 / d, q = rint(x * id).
 __device__ __forceinline__ float kq_act_scale(float amax) { return __fdiv_rn(amax, 127.0f); }
@@ -202,6 +229,7 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
 b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y, int8_t *q,
                         float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride);
 int kq_stream_error_fetch(); // 0 ok; nonzero = a bounded device-side wait gave up since the last call
+int kq_gemm_error_fetch();
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
                            const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
                            const float *bias, const float *residual, cudaStream_t st);

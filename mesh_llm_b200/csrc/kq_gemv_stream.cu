@@ -100,10 +100,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 // bounded wait on a ring slot; after a first give-up the CTA stops waiting altogether
 __device__ __forceinline__ void wait_slot(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (*abort_flag) return;
-    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return;
-        if (i > 64) __nanosleep(64);
-    }
+    if (kq_mbar_wait(bar, parity, KQ_WAIT_LIMIT_NS)) return;
     *abort_flag = 1;
     atomicExch(&g_stream_error, 1);
 }
@@ -496,10 +493,11 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
                                 volatile unsigned long long *e = &g_partials[u2][rs * M + m];
                                 unsigned long long w = 0;
                                 bool ok = false;
-                                for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
+                                const uint64_t t0 = kq_globaltimer_ns();
+                                while (true) {
                                     w = *e;
                                     ok = (w >> 32) != 0;
-                                    if (ok || s_abort) break;
+                                    if (ok || s_abort || kq_globaltimer_ns() - t0 > KQ_WAIT_LIMIT_NS) break;
                                     __nanosleep(64);
                                 }
                                 if (!ok && !s_abort) {

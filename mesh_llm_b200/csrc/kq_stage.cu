@@ -755,7 +755,7 @@ b200_status b200_stage_synchronize(b200_stage *st) {
     KQ_REQUIRE(st, "stage_synchronize: null stage");
     KQ_CUDA(cudaSetDevice(st->c.device));
     KQ_CUDA(cudaDeviceSynchronize());
-    const int werr = kq_stream_error_fetch();
+    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
     if (werr) {
         kq_set_error("stage_synchronize: a bounded device-side wait gave up (code %d)", werr);
         return B200_ERR_TIMEOUT;
