@@ -161,6 +161,53 @@ def run_reference(args, w):
     }))
 
 
+def run_micro(args):
+    """One quantised matmul shape of the isolated sweep (BASELINE.json configs[4]), timed with CUDA
+    events over `--micro-iters` launches captured in a CUDA graph that rotates over enough weight
+    copies to exceed L2.  This is also the command the ncu captures under profiles/ run."""
+    import torch
+    from mesh_llm_b200 import ops
+
+    N, K, M, tname = args.micro.split(",")
+    N, K, M = int(N), int(K), int(M)
+    ty = {"q4_k": 12, "q6_k": 14}[tname.lower()]
+    rb = ops.device_row_bytes(ty, K)
+    copies = max(2, int(400e6 // (N * rb)) + 1)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    Ws = [torch.randint(0, 256, (N, rb), dtype=torch.uint8, device="cuda", generator=g) for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", generator=g)
+    q, d, bs = ops.quantize_act(x)
+    y = torch.empty(M, N, device="cuda")
+    st = torch.cuda.Stream()
+    iters = args.micro_iters
+    with torch.cuda.stream(st):
+        for W in Ws:
+            ops.mul_mat_q8(ty, W, q, d, bs, N, K, out=y)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(iters):
+                ops.mul_mat_q8(ty, Ws[i % copies], q, d, bs, N, K, out=y)
+        graph.replay()
+        torch.cuda.synchronize()
+        best = 1e30
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / iters)
+    sec = best * 1e-3
+    out = {"micro": args.micro, "us_per_launch": best * 1e3, "weight_copies": copies}
+    if M <= 8:
+        out["algorithmic_bytes"] = gemv_bytes(N, K, ty, M)
+        out["GBps"] = out["algorithmic_bytes"] / sec / 1e9
+    else:
+        out["TOPps"] = 2.0 * M * N * K / sec / 1e12
+    print(json.dumps(out))
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -172,7 +219,12 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model depth")
+    ap.add_argument("--micro", default="", help="isolated quantised matmul instead of the model: 'N,K,M,type' "
+                    "(type q4_k|q6_k); prints one line with us per launch and GB/s (M<=8) or TOP/s")
+    ap.add_argument("--micro-iters", type=int, default=20)
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     w = dict(WORKLOADS[args.workload])
     if args.layers:
         w["n_layer"] = args.layers

@@ -19,7 +19,7 @@ SO = os.path.join(HERE, "libb200kq.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "--expt-relaxed-constexpr", *(["-DKQ_GEMM_PROF"] if os.environ.get("KQ_GEMM_PROF") else []),
     "-ccbin", "/usr/bin/g++",
 ]
 

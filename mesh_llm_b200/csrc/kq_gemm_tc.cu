@@ -12,13 +12,18 @@
 // sum_j m_j * bsum_j is one more MMA (kind::f16, K = 16, small integers exact in f16 / f32).
 //
 // One CTA computes a 128-token x 128-row tile.  Tokens are the M (TMEM lane) dimension, weight rows
-// the N (column) dimension.  Per super-block: all warps stage the tile in shared memory in the
-// canonical K-major no-swizzle UMMA layout (activations copied, weights unpacked to the two
-// planes), one thread issues the MMAs, and after the commit barrier all warps run the epilogue out
-// of TMEM; the running f32 result also lives in TMEM (columns 384..511), so registers stay small.
+// the N (column) dimension.  A small kernel first re-tiles the Q8 codes so that one super-block of a
+// token tile is a contiguous 32 KB run in the canonical K-major no-swizzle UMMA layout.  Per
+// super-block the copy engine brings that run and the packed Q4_K blocks of the 128 weight rows
+// (one tiled TMA box out of the row-major matrix; double-buffered, one mbarrier per stage); all warps unpack the weights from
+// shared memory to the two planes, one thread issues the MMAs, and after the commit barrier all
+// warps run the epilogue out of TMEM into the running f32 result in registers.
 // Every barrier wait is bounded; on a time-out the kernel sets an error word, frees its TMEM and
 // returns.
 #include "kq_common.cuh"
+
+#include <cuda.h> // CUtensorMap and the encode entry point's types; the driver is reached through the runtime
+#include <string.h>
 
 namespace {
 
@@ -27,17 +32,26 @@ constexpr int LBO = TM * 16;        // bytes between consecutive 16-byte K chunk
 constexpr int SBO = 128;            // bytes between consecutive groups of 8 rows
 constexpr int OP_BYTES = TM * 256;  // one int8 operand slab: 128 rows x 256 K bytes
 constexpr int MIN_BYTES = TM * 32;  // one f16 operand slab of the min term: 128 rows x 16 halves
-constexpr int SMEM_A = 0, SMEM_BHI = OP_BYTES, SMEM_BLO = 2 * OP_BYTES, SMEM_AMIN = 3 * OP_BYTES,
-              SMEM_BMIN = 3 * OP_BYTES + MIN_BYTES, SMEM_SCAL = 3 * OP_BYTES + 2 * MIN_BYTES,
-              SMEM_TOTAL = SMEM_SCAL + 3 * TM * 4 + 64;
-constexpr uint32_t TMEM_COLS = 512, COL_HI = 0, COL_LO = 128, COL_MIN = 256, COL_Y = 384;
-constexpr uint32_t SPIN = 1u << 20;
+constexpr int RAW_BYTES = TN * KQ_Q4K_BYTES; // packed Q4_K blocks of one super-block column: 128 x 144
+constexpr int SMEM_A = 0, SMEM_A2 = OP_BYTES, SMEM_BHI = 2 * OP_BYTES, SMEM_BLO = 3 * OP_BYTES, SMEM_AMIN = 4 * OP_BYTES,
+              SMEM_BMIN = 4 * OP_BYTES + MIN_BYTES, SMEM_RAW = 4 * OP_BYTES + 2 * MIN_BYTES,
+              SMEM_SCAL = SMEM_RAW + 2 * RAW_BYTES, SMEM_TOTAL = SMEM_SCAL + 3 * TM * 4 + 64;
+constexpr uint32_t TMEM_COLS = 512, COL_HI = 0, COL_LO = 128, COL_MIN = 256;
+constexpr int KQ_MAX_DEVICES = 16;
 
 __device__ int g_gemm_error;
+#ifdef KQ_GEMM_PROF
+__device__ long long g_gemm_prof[8];
+#define PROF_T(var) const long long var = clock64()
+#define PROF_ADD(i, a, b) do { if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 32) g_gemm_prof[i] += (b) - (a); } while (0)
+#else
+#define PROF_T(var)
+#define PROF_ADD(i, a, b)
+#endif
 
 struct GemmParams {
     const uint8_t *W; // device-layout rows
-    const int8_t *aq;
+    const int8_t *aq;  // activations re-tiled for the tensor core: [M/128][K/16][128 rows][16 bytes]
     const float *ad;
     const int16_t *abs16;
     float *y;
@@ -105,10 +119,26 @@ __device__ __forceinline__ void q4_planes(uint32_t nib4, uint32_t sc, uint32_t &
     lo = (p02 & 0x001F001Fu) | ((p13 & 0x001F001Fu) << 8);
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p) {
+// Q8 codes [M][K] -> [M/128][K/16][128 rows][16 bytes]: one super-block of a 128-token tile becomes a
+// contiguous 32 KB run already in the operand layout; rows past M are zero.
+__global__ void __launch_bounds__(256) retile_act_kernel(const int8_t *__restrict__ q, uint4 *__restrict__ out, int M, int K,
+                                                         int64_t n_piece) {
+    KQ_PDL_ENTER();
+    const int kcs = K / 16;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_piece; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i % TM);
+        const int64_t t = i / TM;
+        const int kc = (int)(t % kcs), mt = (int)(t / kcs);
+        const int m = mt * TM + r;
+        out[i] = m < M ? *reinterpret_cast<const uint4 *>(q + (int64_t)m * K + kc * 16) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap wmap) {
     KQ_PDL_ENTER();
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t mbar;
+    __shared__ uint64_t full_bar[2];
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -125,6 +155,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     }
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_a), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[0])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[1])), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0;
     }
@@ -137,16 +169,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     const int chalf = warp >> 2;            // columns [64*chalf, 64*chalf + 64)
     const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
-    { // running result starts at zero
-        uint32_t z[16];
+    float yacc[64]; // running f32 result of this thread's token row x its 64 weight columns
 #pragma unroll
-        for (int i = 0; i < 16; i++) z[i] = 0u;
-#pragma unroll
-        for (int c = 0; c < 64; c += 16) TMEM_ST16(tlane + COL_Y + chalf * 64 + c, z);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    }
+    for (int i = 0; i < 64; i++) yacc[i] = 0.f;
 
-    const uint32_t a_base = smem_u32(smem + SMEM_A), bhi_base = smem_u32(smem + SMEM_BHI),
+    const uint32_t a_base = smem_u32(smem + SMEM_A), a2_base = smem_u32(smem + SMEM_A2), bhi_base = smem_u32(smem + SMEM_BHI),
                    blo_base = smem_u32(smem + SMEM_BLO), amin_base = smem_u32(smem + SMEM_AMIN),
                    bmin_base = smem_u32(smem + SMEM_BMIN);
     const bool q4 = p.type == B200_TYPE_Q4_K;
@@ -154,63 +181,120 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     uint32_t phase = 0;
     bool failed = false;
 
-    for (int b = 0; b < p.nb && !failed; b++) {
-        // ---- stage the tile of super-block b ---------------------------------------------------
-        // activations: 128 rows x 16 chunks
-        for (int i = tid; i < TM * 16; i += NTHREADS) {
-            const int r = i >> 4, kc = i & 15;
-            int4 v = make_int4(0, 0, 0, 0);
-            if (m0 + r < p.M) v = *reinterpret_cast<const int4 *>(p.aq + (int64_t)(m0 + r) * p.K + b * 256 + kc * 16);
-            *reinterpret_cast<int4 *>(smem + SMEM_A + op_off(r, kc)) = v;
+    // ---- software pipeline: the global loads of super-block b+1 (activation tile by cp.async into
+    // the other A buffer, packed weights and per-token scalars into registers) are issued right
+    // after the MMAs of super-block b and land while the tensor core and the epilogue of b run.
+    constexpr int WT4 = TN * 8 / NTHREADS, WT6 = TN * 4 / NTHREADS; // weight tasks per thread
+    uint4 p6_h[WT6], p6_a[WT6], p6_b[WT6]; // Q6_K: qh chunk and its two ql chunks per task
+    uint32_t p6_sc[WT6];
+    float p6_d[WT6];
+    float pf_da = 0.f;
+    int4 pf_bs0 = make_int4(0, 0, 0, 0), pf_bs1 = make_int4(0, 0, 0, 0);
+    auto prefetch = [&](int b) {
+        const int stg = b & 1;
+        if (warp == 1) {
+            // one thread hands the tile to the copy engine: the re-tiled activations are one contiguous
+            // 32 KB run, the packed Q4_K blocks of the 128 weight rows one tiled TMA box
+            const uint32_t bar = smem_u32(&full_bar[stg]);
+            if (lane == 0) {
+                const uint32_t bytes = OP_BYTES + (q4 ? RAW_BYTES : 0);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                const int8_t *src = p.aq + ((int64_t)blockIdx.y * (p.K / 16) + (int64_t)b * 16) * (TM * 16);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(smem + (stg ? SMEM_A2 : SMEM_A))),
+                             "l"(src), "r"(OP_BYTES), "r"(bar)
+                             : "memory");
+                if (q4) // box of 128 rows x 144 bytes out of the row-major matrix; rows past N arrive as zeros
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     smem_u32(smem + SMEM_RAW + stg * RAW_BYTES)),
+                                 "l"(&wmap), "r"(b * KQ_Q4K_BYTES), "r"(n0), "r"(bar)
+                                 : "memory");
+            }
         }
         if (tid < TM) {
             const int r = tid;
-            da_s[r] = m0 + r < p.M ? p.ad[(int64_t)(m0 + r) * p.nb + b] : 0.f;
+            const bool in = m0 + r < p.M;
+            pf_da = in ? p.ad[(int64_t)(m0 + r) * p.nb + b] : 0.f;
+            if (q4) {
+                const int4 *bsp = reinterpret_cast<const int4 *>(p.abs16 + ((int64_t)(m0 + r) * p.nb + b) * 16);
+                pf_bs0 = in ? bsp[0] : make_int4(0, 0, 0, 0);
+                pf_bs1 = in ? bsp[1] : make_int4(0, 0, 0, 0);
+            }
+        }
+        if (!q4) {
+            const KqQ6Addr qa = kq_q6_addr(p.nb, b);
+#pragma unroll
+            for (int t = 0; t < WT6; t++) {
+                const int wt = warp + t * (NTHREADS / 32), r = 8 * wt + (lane & 7), j = lane >> 3;
+                const int hh = j >> 1, c1 = j & 1;
+                p6_h[t] = p6_a[t] = p6_b[t] = make_uint4(0, 0, 0, 0);
+                p6_sc[t] = 0;
+                p6_d[t] = 0.f;
+                if (n0 + r < p.N) {
+                    const uint8_t *rowp = p.W + (int64_t)(n0 + r) * wstride;
+                    p6_h[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.qh + j * qa.cs));
+                    p6_a[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1) * qa.cs));
+                    p6_b[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1 + 2) * qa.cs));
+                    const uint8_t *scp = rowp + qa.sc + 8 * hh + c1; // scale groups 8hh + 2q + c1
+                    p6_sc[t] = (uint32_t)scp[0] | ((uint32_t)scp[2] << 8) | ((uint32_t)scp[4] << 16) | ((uint32_t)scp[6] << 24);
+                    p6_d[t] = kq_h2f(*reinterpret_cast<const uint16_t *>(rowp + qa.d));
+                }
+            }
+        }
+    };
+
+    prefetch(0);
+    int last_pf = 0; // newest super-block handed to the copy engine
+    for (int b = 0; b < p.nb && !failed; b++) {
+        PROF_T(t_0);
+        if (!failed && !kq_mbar_wait(smem_u32(&full_bar[b & 1]), (uint32_t)((b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS)) {
+            s_abort = 1;
+            atomicExch(&g_gemm_error, 2);
+        }
+        // ---- unpack the weights of super-block b into the two int8 planes --------------------------
+        if (tid < TM) {
+            const int r = tid;
+            da_s[r] = pf_da;
             if (q4) { // sums of 16 as f16 (|sum| <= 2032: exact)
+                const int16_t *s16a = reinterpret_cast<const int16_t *>(&pf_bs0);
+                const int16_t *s16b = reinterpret_cast<const int16_t *>(&pf_bs1);
                 __half h[16];
 #pragma unroll
-                for (int k = 0; k < 16; k++)
-                    h[k] = __int2half_rn(m0 + r < p.M ? (int)p.abs16[((int64_t)(m0 + r) * p.nb + b) * 16 + k] : 0);
+                for (int k = 0; k < 8; k++) {
+                    h[k] = __int2half_rn((int)s16a[k]);
+                    h[8 + k] = __int2half_rn((int)s16b[k]);
+                }
                 *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off(r, 0)) = *reinterpret_cast<uint4 *>(&h[0]);
                 *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off(r, 1)) = *reinterpret_cast<uint4 *>(&h[8]);
             }
         }
         if (q4) {
-            // weights: 128 rows x 8 quant chunks; chunk c gives K chunks 4g+h (low nibbles) and 4g+2+h (high)
-            for (int i = tid; i < TN * 8; i += NTHREADS) {
-                const int r = i >> 3, c = i & 7;
-                const int g = c >> 1, h = c & 1;
-                uint4 w = make_uint4(0, 0, 0, 0);
-                uint32_t sc0 = 0, sc1 = 0;
-                if (n0 + r < p.N) {
-                    const uint8_t *blk = p.W + (int64_t)(n0 + r) * wstride + (int64_t)b * KQ_Q4K_BYTES;
-                    const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-                    w = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 16 * c));
-                    const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-                    const uint32_t scw = g < 2 ? sc_lo : sc_hi;
-                    sc0 = (scw >> (8 * ((2 * g) & 3))) & 0xFF;
-                    sc1 = (scw >> (8 * ((2 * g + 1) & 3))) & 0xFF;
-                    if (c == 0) {
-                        const uint32_t m_lo = hdr.z & 0x3F3F3F3Fu, m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-                        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-                        dw_s[r] = dd.x;
-                        dmin_s[r] = dd.y;
-                        __half mh[16]; // m_j against both sums of 16 of sub-block j
+            // chunk c of a block gives K chunks 4g+h (low nibbles, sub-block 2g) and 4g+2+h (high, 2g+1)
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const uint32_t mw = j < 4 ? m_lo : m_hi;
-                            const __half v = __int2half_rn((int)((mw >> (8 * (j & 3))) & 0xFF));
-                            mh[2 * j] = v;
-                            mh[2 * j + 1] = v;
-                        }
-                        *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
-                        *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
+            for (int t = 0; t < WT4; t++) {
+                const int wt = warp + t * (NTHREADS / 32), r = 8 * (wt >> 1) + (lane & 7), c = 4 * (wt & 1) + (lane >> 3);
+                const int g = c >> 1, h = c & 1;
+                const uint8_t *blk = smem + SMEM_RAW + (b & 1) * RAW_BYTES + r * KQ_Q4K_BYTES;
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(blk), w = *reinterpret_cast<const uint4 *>(blk + 16 + 16 * c);
+                const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+                const uint32_t scw = g < 2 ? sc_lo : sc_hi;
+                const uint32_t sc0 = (scw >> (8 * ((2 * g) & 3))) & 0xFF, sc1 = (scw >> (8 * ((2 * g + 1) & 3))) & 0xFF;
+                if (c == 0) {
+                    const uint32_t m_lo = hdr.z & 0x3F3F3F3Fu, m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+                    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+                    dw_s[r] = dd.x;
+                    dmin_s[r] = dd.y;
+                    __half mh[16]; // m_j against both sums of 16 of sub-block j
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t mw = j < 4 ? m_lo : m_hi;
+                        const __half v = __int2half_rn((int)((mw >> (8 * (j & 3))) & 0xFF));
+                        mh[2 * j] = v;
+                        mh[2 * j + 1] = v;
                     }
-                } else if (c == 0) {
-                    dw_s[r] = 0.f;
-                    dmin_s[r] = 0.f;
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 0)) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 1)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
                 }
                 uint4 hi_l, lo_l, hi_h, lo_h;
                 q4_planes(w.x & 0x0F0F0F0Fu, sc0, hi_l.x, lo_l.x);
@@ -230,33 +314,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
         } else {
             // Q6_K: one task per (row, qh chunk j): 4 scale groups of 16 elements, w' = sc * (q - 32)
             // split as hi * 64 + lo with lo in 0..63 (unsigned plane) and hi in -64..64 (signed plane)
-            for (int i = tid; i < TN * 4; i += NTHREADS) {
-                const int r = i >> 2, j = i & 3;
-                const int hh = j >> 1, c1 = j & 1;
-                uint32_t hw[4] = {0, 0, 0, 0}, aw[4] = {0, 0, 0, 0}, bw[4] = {0, 0, 0, 0};
-                int scg[4] = {0, 0, 0, 0};
-                if (n0 + r < p.N) {
-                    const uint8_t *rowp = p.W + (int64_t)(n0 + r) * wstride;
-                    const KqQ6Addr qa = kq_q6_addr(p.nb, b);
-                    const uint4 hv = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.qh + j * qa.cs));
-                    const uint4 la = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1) * qa.cs));
-                    const uint4 lb = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1 + 2) * qa.cs));
-                    hw[0] = hv.x; hw[1] = hv.y; hw[2] = hv.z; hw[3] = hv.w;
-                    aw[0] = la.x; aw[1] = la.y; aw[2] = la.z; aw[3] = la.w;
-                    bw[0] = lb.x; bw[1] = lb.y; bw[2] = lb.z; bw[3] = lb.w;
-                    const int8_t *scp = reinterpret_cast<const int8_t *>(rowp + qa.sc);
 #pragma unroll
-                    for (int q = 0; q < 4; q++) scg[q] = scp[8 * hh + 2 * q + c1];
-                    if (j == 0) {
-                        dw_s[r] = kq_h2f(*reinterpret_cast<const uint16_t *>(rowp + qa.d));
-                        dmin_s[r] = 0.f;
-                    }
-                } else if (j == 0) {
-                    dw_s[r] = 0.f;
+            for (int t = 0; t < WT6; t++) {
+                const int wt = warp + t * (NTHREADS / 32), r = 8 * wt + (lane & 7), j = lane >> 3;
+                const int hh = j >> 1, c1 = j & 1;
+                const uint32_t hw[4] = {p6_h[t].x, p6_h[t].y, p6_h[t].z, p6_h[t].w};
+                const uint32_t aw[4] = {p6_a[t].x, p6_a[t].y, p6_a[t].z, p6_a[t].w};
+                const uint32_t bw[4] = {p6_b[t].x, p6_b[t].y, p6_b[t].z, p6_b[t].w};
+                if (j == 0) {
+                    dw_s[r] = p6_d[t];
                     dmin_s[r] = 0.f;
                 }
 #pragma unroll
                 for (int q = 0; q < 4; q++) { // bit pair q of the qh bytes: elements 128hh + 32q + 16c1 + i
+                    const int scq = (int)(int8_t)((p6_sc[t] >> (8 * q)) & 0xFF);
                     uint32_t hi4[4], lo4[4];
 #pragma unroll
                     for (int wd = 0; wd < 4; wd++) {
@@ -267,7 +338,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                         uint32_t hi = 0, lo = 0;
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            const int wv = scg[q] * ((int)((code >> (8 * k)) & 0xFF) - 32);
+                            const int wv = scq * ((int)((code >> (8 * k)) & 0xFF) - 32);
                             hi |= (uint32_t)((wv >> 6) & 0xFF) << (8 * k);
                             lo |= (uint32_t)(wv & 63) << (8 * k);
                         }
@@ -280,10 +351,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                 }
             }
         }
+        PROF_T(t_1);
         // shared-memory writes of the generic proxy must be visible to the tensor core's async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
+        PROF_T(t_2);
         // ---- MMAs ------------------------------------------------------------------------------
         if (warp == 0) {
           // the whole warp stays here while its first lane issues, so that no lane of the issuing
@@ -293,7 +366,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
             const uint32_t id_hi = idesc_i8(true), id_lo = idesc_i8(q4 ? true : false);
 #pragma unroll
             for (int s = 0; s < 8; s++) { // K = 32 per instruction: chunks 2s, 2s+1
-                const uint64_t ad = make_desc(a_base + 2 * s * LBO);
+                const uint64_t ad = make_desc(((b & 1) ? a2_base : a_base) + 2 * s * LBO);
                 mma_i8(tmem + COL_HI, ad, make_desc(bhi_base + 2 * s * LBO), id_hi, s > 0);
                 mma_i8(tmem + COL_LO, ad, make_desc(blo_base + 2 * s * LBO), id_lo, s > 0);
             }
@@ -303,6 +376,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
           }
           __syncwarp();
         }
+        PROF_T(t_3);
+        if (b + 1 < p.nb) { // the loads of the next super-block fly during MMA + epilogue
+            prefetch(b + 1);
+            last_pf = b + 1;
+        }
+        PROF_T(t_4);
         { // bounded wait for the MMAs of this super-block
             const bool ok = s_abort ? false : kq_mbar_wait(mbar_a, phase, 5 * KQ_WAIT_LIMIT_NS);
             if (!ok) {
@@ -312,18 +391,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
             phase ^= 1;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        PROF_T(t_5);
         if (s_abort) failed = true;
         // ---- epilogue of the super-block: y += d_a * (d_w * (R*hi + lo) - dmin * min) ------------
         if (!failed) {
             const float da = da_s[row];
             const int R = q4 ? 32 : 64;
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < 64; c += 16) {
                 const uint32_t col = chalf * 64 + c;
-                uint32_t hi[16], lo[16], mn[16], yy[16];
+                uint32_t hi[16], lo[16], mn[16];
                 TMEM_LD16(tlane + COL_HI + col, hi);
                 TMEM_LD16(tlane + COL_LO + col, lo);
-                TMEM_LD16(tlane + COL_Y + col, yy);
                 if (q4) TMEM_LD16(tlane + COL_MIN + col, mn);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
@@ -331,34 +410,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                     const int main_i = R * (int)hi[i] + (int)lo[i];
                     float t = dw_s[col + i] * (float)main_i;
                     if (q4) t -= dmin_s[col + i] * __uint_as_float(mn[i]);
-                    yy[i] = __float_as_uint(fmaf(da, t, __uint_as_float(yy[i])));
+                    yacc[c + i] = fmaf(da, t, yacc[c + i]);
                 }
-                TMEM_ST16(tlane + COL_Y + col, yy);
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads(); // accumulators and the staging buffers are free again
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        PROF_T(t_6);
+        PROF_ADD(0, t_0, t_1); PROF_ADD(1, t_1, t_2); PROF_ADD(2, t_2, t_3); PROF_ADD(3, t_3, t_4);
+        PROF_ADD(4, t_4, t_5); PROF_ADD(5, t_5, t_6);
     }
 
+    if (failed) { // never leave with bulk copies still writing this CTA's shared memory
+        kq_mbar_wait(smem_u32(&full_bar[last_pf & 1]), (uint32_t)((last_pf >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+        if (last_pf > 0)
+            kq_mbar_wait(smem_u32(&full_bar[(last_pf - 1) & 1]), (uint32_t)(((last_pf - 1) >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+    }
     // ---- write the tile -------------------------------------------------------------------------
-    if (!failed) { // tcgen05.ld is warp-collective: every lane takes part, only the stores are masked
-#pragma unroll 1
-        for (int c = 0; c < 64; c += 16) {
-            const int col = chalf * 64 + c;
-            uint32_t yy[16];
-            TMEM_LD16(tlane + COL_Y + col, yy);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
+    if (!failed && m0 + row < p.M) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                if (m0 + row < p.M && n0 + col + i < p.N) {
-                    float v = __uint_as_float(yy[i]);
-                    if (p.bias) v += p.bias[n0 + col + i];
-                    if (p.residual) v += p.residual[o + i];
-                    p.y[o + i] = v;
-                }
+        for (int c = 0; c < 64; c++) {
+            const int col = chalf * 64 + c;
+            if (n0 + col < p.N) {
+                const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
+                float v = yacc[c];
+                if (p.bias) v += p.bias[n0 + col];
+                if (p.residual) v += p.residual[o];
+                p.y[o] = v;
             }
         }
     }
@@ -370,6 +449,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
 
 } // namespace
 
+#ifdef KQ_GEMM_PROF
+extern "C" __attribute__((visibility("default"))) void kq_gemm_prof_fetch(long long *out) {
+    cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 8);
+    long long z[8] = {0};
+    cudaMemcpyToSymbol(g_gemm_prof, z, sizeof(z));
+}
+#endif
 int kq_gemm_error_fetch() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
@@ -377,22 +463,80 @@ int kq_gemm_error_fetch() {
     return v;
 }
 
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// bytes of a Q4_K matrix as a 2-D tensor [N rows][row_bytes], box = one super-block column of 128 rows
+b200_status make_weight_map(CUtensorMap *map, const uint8_t *W, int64_t N, int64_t row_bytes) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qr = cudaDriverEntryPointSymbolNotFound;
+        KQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+        KQ_REQUIRE(fn && qr == cudaDriverEntryPointSuccess, "gemm: the driver does not export cuTensorMapEncodeTiled");
+        encode = (EncodeTiledFn)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)KQ_Q4K_BYTES, (cuuint32_t)TN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(W), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KQ_REQUIRE(rc == CUDA_SUCCESS, "gemm: tensor map encode failed (%d)", (int)rc);
+    return B200_OK;
+}
+} // namespace
+
 b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, const float *d, const int16_t *bs,
                               int64_t M, int64_t N, int64_t K, float *y, const float *bias, const float *residual,
                               cudaStream_t st) {
     KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "gemm: weight type %u", type);
     KQ_REQUIRE(K % 256 == 0 && M > 0 && N > 0, "gemm: bad shape");
     KQ_REQUIRE(((uintptr_t)W & 15) == 0 && ((uintptr_t)q & 15) == 0, "gemm: operands must be 16-byte aligned");
-    GemmParams p = {W, q, d, bs, y, bias, residual, (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type};
-    static bool attr = false;
+    // Per-device scratch for the re-tiled activations, grown on demand and kept; launches that share
+    // it are ordered by using one stream per device at a time, as the stage engine and the backend do.
+    static uint4 *tiled[KQ_MAX_DEVICES];
+    static size_t tiled_cap[KQ_MAX_DEVICES];
+    static bool attr[KQ_MAX_DEVICES];
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    KQ_REQUIRE(dev >= 0 && dev < KQ_MAX_DEVICES, "gemm: device %d out of range", dev);
+    const int64_t m_tiles = kq_div_up(M, TM);
+    const size_t need = (size_t)m_tiles * TM * K;
+    if (need > tiled_cap[dev]) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        KQ_CUDA(cudaStreamIsCapturing(st, &cs));
+        KQ_REQUIRE(cs == cudaStreamCaptureStatusNone, "gemm: activation scratch cannot grow during stream capture");
+        KQ_CUDA(cudaDeviceSynchronize());
+        if (tiled[dev]) KQ_CUDA(cudaFree(tiled[dev]));
+        tiled[dev] = nullptr;
+        tiled_cap[dev] = 0;
+        KQ_CUDA(cudaMalloc(&tiled[dev], need));
+        tiled_cap[dev] = need;
+    }
+    const int64_t n_piece = (int64_t)need / 16;
+    kq_launch(retile_act_kernel, dim3((unsigned)kq_div_up(n_piece, 256)), 256, 0, st, q, tiled[dev], (int)M, (int)K, n_piece);
+    KQ_COUNT_LAUNCH();
+    GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled[dev]), d, bs, y, bias, residual,
+                    (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type};
     // 118 KB of dynamic shared memory also keeps a second CTA off the SM: a CTA holds all 512 TMEM columns
     const int smem = SMEM_TOTAL > 118 * 1024 ? SMEM_TOTAL : 118 * 1024;
-    if (!attr) {
+    static_assert(SMEM_TOTAL <= 226 * 1024, "tile does not fit shared memory");
+    if (!attr[dev]) {
         KQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr = true;
+        attr[dev] = true;
+    }
+    CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    if (type == B200_TYPE_Q4_K) {
+        const b200_status rc = make_weight_map(&wmap, W, N, kq_device_row_bytes(type, K));
+        if (rc != B200_OK) return rc;
     }
     dim3 grid((unsigned)kq_div_up(N, TN), (unsigned)kq_div_up(M, TM));
-    kq_launch(gemm_tc_kernel, grid, NTHREADS, smem, st, p);
+    kq_launch(gemm_tc_kernel, grid, NTHREADS, smem, st, p, wmap);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
