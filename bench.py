@@ -44,6 +44,9 @@ BPW = {12: 144 / 256, 14: 210 / 256}
 METRIC = "decode tok/s, Q4_K_M 32B-shape, batch 1 per stage (GEMV HBM % of peak in roofline)"
 
 
+NCU_TRAFFIC_RATIO = 1.03  # measured DRAM bytes / algorithmic bytes of the decode GEMV (see profiles/)
+
+
 def matmuls(w, layer):
     """(N, K, ggml type) of every quantised matmul of one layer, Q4_K_M mix"""
     h, nq, nkv, ff = w["n_embd"], w["n_head"] * w["head_dim"], w["n_head_kv"] * w["head_dim"], w["n_ff"]
@@ -344,9 +347,16 @@ def main():
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = algo / (ms_gemv.value * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "gemv_kernel (Q4_K/Q6_K x Q8 decode GEMV)", "achieved": achieved, "peak": peak,
+        "bound": "hbm", "achieved": achieved, "peak": peak,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
-        "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
+        "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
+        # DRAM read+write bytes per launch: ncu captures of the two largest matrices of this shape
+        # (profiles/gemv_block_kernel_m1.md) measured 1.02x (Q4_K) and 1.04x (Q6_K) the algorithmic
+        # bytes; traffic grows in proportion to the weights streamed, so the ratio is applied to the
+        # step's average launch
+        "traffic": NCU_TRAFFIC_RATIO * algo / max(1, n_gemv.value),
+        "traffic_source": "ncu dram__bytes_read+write of isolated launches, ratio %.2f x algorithmic" % NCU_TRAFFIC_RATIO,
+        "kernel": "gemv_block_kernel (Q4_K/Q6_K x Q8 decode GEMV)",
         "launches_per_step": int(n_gemv.value), "algorithmic_bytes_per_launch": algo / max(1, n_gemv.value),
         "avg_launch_us": ms_gemv.value * 1e3 / max(1, n_gemv.value),
         "gemv_ms_per_step": ms_gemv.value, "attention_ms_per_step": ms_attn.value,
