@@ -41,7 +41,7 @@ WORKLOADS = {
 MODEL_KEYS = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
               "rope_neox", "rope_theta", "rms_eps")
 BPW = {12: 144 / 256, 14: 210 / 256}
-METRIC = "decode tok/s, Q4_K_M 32B-shape, batch 1 per stage (GEMV HBM % of peak in roofline)"
+METRIC = "decode tok/s, Q4_K_M, batch 1 per stage (shape in config.workload; GEMV HBM % of peak in roofline)"
 
 
 NCU_TRAFFIC_RATIO = 1.03  # measured DRAM bytes / algorithmic bytes of the decode GEMV (see profiles/)
