@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(_HERE, "libb200kq.so")
+SO_PATH = os.environ.get("B200_KQ_LIB") or os.path.join(_HERE, "libb200kq.so")
 
 TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K, TYPE_I32 = 0, 1, 12, 14, 26
 

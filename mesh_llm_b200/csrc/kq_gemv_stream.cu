@@ -43,6 +43,23 @@ constexpr int ACT_BLK = 272; // 256 int8 codes + 16 bytes of padding
 __device__ unsigned long long g_partials[MAX_UNITS][16];
 __device__ int g_stream_error; // 0 ok, 1 mbarrier wait gave up, 2 partial-sum wait gave up
 
+#ifndef KQ_GEMV_WARPS
+#define KQ_GEMV_WARPS 16
+#endif
+#ifndef KQ_GEMV_CTAS
+#define KQ_GEMV_CTAS 1
+#endif
+#ifndef KQ_GEMV_GRIDMUL
+#define KQ_GEMV_GRIDMUL 1
+#endif
+#ifdef KQ_GEMV_TRACE
+// debug build only: per CTA and launch, %globaltimer at the phase boundaries of the kernel
+__device__ unsigned long long g_trace[32768][16];
+__device__ unsigned int g_trace_n;
+#define TRACE_MARK(i) do { if (threadIdx.x == 0 && s_trace < 32768u) g_trace[s_trace][i] = (unsigned long long)clock64(); } while (0)
+#else
+#define TRACE_MARK(i)
+#endif
 template <uint32_t TYPE>
 struct Fmt;
 template <>
@@ -50,14 +67,14 @@ struct Fmt<B200_TYPE_Q4_K> {
     static constexpr int ROWS = 8, KB = 4, LPR = 4;          // rows / unit, blocks / slice, lanes / row
     static constexpr int PITCH = KB * KQ_Q4K_BYTES;          // 576: rows land 16 banks apart
     static constexpr int SLOT = ROWS * PITCH;                // 4608
-    static constexpr int WARPS = 16, CTAS_PER_SM = 1, SMEM_CAP = 216 * 1024;
+    static constexpr int WARPS = KQ_GEMV_WARPS, CTAS_PER_SM = KQ_GEMV_CTAS, SMEM_CAP = 216 * 1024 / KQ_GEMV_CTAS;
 };
 template <>
 struct Fmt<B200_TYPE_Q6_K> {
     static constexpr int ROWS = 4, KB = 8, LPR = 8;
     static constexpr int PITCH = KQ_Q6_GROUP_BYTES;          // one 1680-byte group
     static constexpr int SLOT = ROWS * PITCH;                // 6720
-    static constexpr int WARPS = 16, CTAS_PER_SM = 1, SMEM_CAP = 216 * 1024;
+    static constexpr int WARPS = KQ_GEMV_WARPS, CTAS_PER_SM = KQ_GEMV_CTAS, SMEM_CAP = 216 * 1024 / KQ_GEMV_CTAS;
 };
 
 struct StreamParams {
@@ -319,6 +336,18 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     KQ_PDL_TRIGGER();
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_abort;
+#ifdef KQ_GEMV_TRACE
+    __shared__ unsigned int s_trace;
+    if (threadIdx.x == 0) {
+        s_trace = atomicAdd(&g_trace_n, 1u);
+    }
+    __syncthreads();
+    TRACE_MARK(0);
+    if (threadIdx.x == 0 && s_trace < 32768u) {
+        g_trace[s_trace][7] = ((unsigned long long)blockIdx.x << 32) | (unsigned)p.n_rg;
+        g_trace[s_trace][8] = kq_globaltimer_ns();
+    }
+#endif
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rs = lane / F::LPR, t = lane % F::LPR;
     const int nb = p.nb;
@@ -343,93 +372,168 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     const uint32_t ring_addr = smem_u32(ring), bar_addr = smem_u32(bars);
     Issuer<TYPE> iss;
     iss.init(p, begin, lane);
-    {
-        const int pre = min(count, p.ns);
-        for (int j = 0; j < pre; j++) iss.post(p, lane, ring_addr + j * F::SLOT, bar_addr + j * 8);
-    }
+    // The first slot of the ring goes out at once.  Posting blocks while the copy engine's queue is
+    // full (all warps of all SMs fill their rings at the same moment), so the remaining slots are
+    // posted only after the loads of the activations have been issued: those loads then complete
+    // behind the posting instead of after it.
+    const int pre = min(count, p.ns);
+    if (pre > 0) iss.post(p, lane, ring_addr, bar_addr);
+    bool rest_posted = false;
+    auto post_rest = [&]() {
+        if (!rest_posted) {
+            for (int j = 1; j < pre; j++) iss.post(p, lane, ring_addr + j * F::SLOT, bar_addr + j * 8);
+            rest_posted = true;
+        }
+    };
+    TRACE_MARK(1);
     KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
+    TRACE_MARK(2);
     if (p.x) {
-        // Every CTA prepares the activations for itself: K floats per token from L2, RMSNorm with
-        // the sum of squares in double (same reduction tree as the stand-alone kernel: the first 256
-        // threads, 8 partials added in order), then the Q8 quantiser, one warp per 256-block.
-        __shared__ double s_part[8];
+        // Every CTA prepares the activations for itself: RMSNorm with the sum of squares in double,
+        // then the Q8 quantiser, one warp per 256-block, PB blocks per warp in flight.  A row of up
+        // to PB * WARPS blocks is read from L2 once and stays in registers for both steps.
+        constexpr int PB = 4;
+        __shared__ double s_part[WARPS];
         __shared__ float s_scale[2];
+        const bool in_regs = nb <= PB * WARPS;
         for (int m = 0; m < M; m++) {
             const float *xr = p.x + (int64_t)m * p.K;
-            if (p.do_norm) {
-                if (threadIdx.x < 256) {
-                    double ss = 0.0;
-                    for (int i = threadIdx.x * 4; i < p.K; i += 1024) {
-                        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
-                        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                    if (lane == 0) s_part[warp] = ss;
+            uint8_t *tq = smem + m * act_tok;
+            if (p.do_norm && !in_regs) { // long rows: statistics in a pass of their own
+                double ss = 0.0;
+                for (int i = threadIdx.x * 4; i < p.K; i += WARPS * 128) {
+                    const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+                    ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
                 }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) s_part[warp] = ss;
                 __syncthreads();
                 if (threadIdx.x == 0) {
                     double tsum = 0.0;
-                    for (int i = 0; i < 8; i++) tsum += s_part[i];
+                    for (int i = 0; i < WARPS; i++) tsum += s_part[i];
                     s_scale[m] = 1.0f / sqrtf((float)(tsum / (double)p.K) + p.eps);
                 }
                 __syncthreads();
             }
-            const float scale = p.do_norm ? s_scale[m] : 1.0f;
-            uint8_t *tq = smem + m * act_tok;
-            for (int b = warp; b < nb; b += WARPS) {
-                const int o = b * 256 + lane * 8;
-                const float4 va = *reinterpret_cast<const float4 *>(xr + o);
-                const float4 vb = *reinterpret_cast<const float4 *>(xr + o + 4);
-                float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-                if (p.do_norm) {
+            for (int base = 0; base < nb; base += PB * WARPS) {
+                float4 va[PB], vb[PB], wa[PB], wb[PB];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) v[i] = v[i] * scale * (p.norm_w ? p.norm_w[o + i] : 1.0f);
+                for (int i = 0; i < PB; i++) {
+                    const int b = base + warp + i * WARPS;
+                    va[i] = vb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    wa[i] = wb[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (b < nb) {
+                        const int o = b * 256 + lane * 8;
+                        va[i] = *reinterpret_cast<const float4 *>(xr + o);
+                        vb[i] = *reinterpret_cast<const float4 *>(xr + o + 4);
+                        if (p.do_norm && p.norm_w) {
+                            wa[i] = *reinterpret_cast<const float4 *>(p.norm_w + o);
+                            wb[i] = *reinterpret_cast<const float4 *>(p.norm_w + o + 4);
+                        }
+                    }
                 }
-                float amax = 0.f;
+                TRACE_MARK(10);
+                post_rest();
+                TRACE_MARK(11);
+                float scale = 1.0f;
+                if (p.do_norm && in_regs) {
+                    double ss = 0.0;
 #pragma unroll
-                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-                amax = kq_warp_max(amax);
-                const float dq = kq_act_scale(amax), id = kq_act_inv(dq);
-                int c8[8], sum = 0;
+                    for (int i = 0; i < PB; i++)
+                        ss += (double)va[i].x * va[i].x + (double)va[i].y * va[i].y + (double)va[i].z * va[i].z +
+                              (double)va[i].w * va[i].w + (double)vb[i].x * vb[i].x + (double)vb[i].y * vb[i].y +
+                              (double)vb[i].z * vb[i].z + (double)vb[i].w * vb[i].w;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    c8[i] = kq_act_code(v[i], id);
-                    sum += c8[i];
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (m > 0) __syncthreads(); // the partials of the previous token have been read
+                    if (lane == 0) s_part[warp] = ss;
+                    __syncthreads();
+                    double tsum = 0.0;
+#pragma unroll
+                    for (int i = 0; i < WARPS; i++) tsum += s_part[i];
+                    scale = 1.0f / sqrtf((float)(tsum / (double)p.K) + p.eps);
+                } else if (p.do_norm) {
+                    scale = s_scale[m];
                 }
-                uint2 pk;
-                pk.x = (uint32_t)(c8[0] & 0xFF) | ((uint32_t)(c8[1] & 0xFF) << 8) | ((uint32_t)(c8[2] & 0xFF) << 16) |
-                       ((uint32_t)(c8[3] & 0xFF) << 24);
-                pk.y = (uint32_t)(c8[4] & 0xFF) | ((uint32_t)(c8[5] & 0xFF) << 8) | ((uint32_t)(c8[6] & 0xFF) << 16) |
-                       ((uint32_t)(c8[7] & 0xFF) << 24);
-                *reinterpret_cast<uint2 *>(tq + b * ACT_BLK + lane * 8) = pk;
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1); // 16 elements
-                if (TYPE == B200_TYPE_Q4_K) {
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2); // 32 elements
-                    if ((lane & 3) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 8 + (lane >> 2)] = (int16_t)sum;
-                } else {
-                    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 16 + (lane >> 1)] = (int16_t)sum;
+                TRACE_MARK(12);
+#pragma unroll
+                for (int i = 0; i < PB; i++) {
+                    const int b = base + warp + i * WARPS;
+                    if (b >= nb) continue;
+                    float v[8] = {va[i].x, va[i].y, va[i].z, va[i].w, vb[i].x, vb[i].y, vb[i].z, vb[i].w};
+                    if (p.do_norm) {
+                        const float g[8] = {wa[i].x, wa[i].y, wa[i].z, wa[i].w, wb[i].x, wb[i].y, wb[i].z, wb[i].w};
+#pragma unroll
+                        for (int k = 0; k < 8; k++) v[k] = v[k] * scale * g[k];
+                    }
+                    float amax = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(v[k]));
+                    amax = kq_warp_max(amax);
+                    const float dq = kq_act_scale(amax), id = kq_act_inv(dq);
+                    int c8[8], sum = 0;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        c8[k] = kq_act_code(v[k], id);
+                        sum += c8[k];
+                    }
+                    uint2 pk;
+                    pk.x = (uint32_t)(c8[0] & 0xFF) | ((uint32_t)(c8[1] & 0xFF) << 8) | ((uint32_t)(c8[2] & 0xFF) << 16) |
+                           ((uint32_t)(c8[3] & 0xFF) << 24);
+                    pk.y = (uint32_t)(c8[4] & 0xFF) | ((uint32_t)(c8[5] & 0xFF) << 8) | ((uint32_t)(c8[6] & 0xFF) << 16) |
+                           ((uint32_t)(c8[7] & 0xFF) << 24);
+                    *reinterpret_cast<uint2 *>(tq + b * ACT_BLK + lane * 8) = pk;
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1); // 16 elements
+                    if (TYPE == B200_TYPE_Q4_K) {
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 2); // 32 elements
+                        if ((lane & 3) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 8 + (lane >> 2)] = (int16_t)sum;
+                    } else {
+                        if ((lane & 1) == 0) reinterpret_cast<int16_t *>(tq + act_q)[b * 16 + (lane >> 1)] = (int16_t)sum;
+                    }
+                    if (lane == 0) reinterpret_cast<float *>(tq + act_q + act_s)[b] = dq;
                 }
-                if (lane == 0) reinterpret_cast<float *>(tq + act_q + act_s)[b] = dq;
             }
         }
-    } else
-    for (int m = 0; m < M; m++) {
-        uint8_t *tq = smem + m * act_tok;
-        const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.K);
-        for (int i = threadIdx.x; i < nb * 16; i += blockDim.x)
-            *reinterpret_cast<int4 *>(tq + (i >> 4) * ACT_BLK + (i & 15) * 16) = src[i];
-        const int16_t *b16 = p.abs16 + (int64_t)m * nb * 16;
-        if (TYPE == B200_TYPE_Q4_K) {
-            for (int i = threadIdx.x; i < nb * 8; i += blockDim.x)
-                reinterpret_cast<int16_t *>(tq + act_q)[i] = (int16_t)(b16[2 * i] + b16[2 * i + 1]);
-        } else {
-            for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) reinterpret_cast<int16_t *>(tq + act_q)[i] = b16[i];
+    } else {
+        for (int m = 0; m < M; m++) {
+            uint8_t *tq = smem + m * act_tok;
+            const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.K);
+            const int16_t *b16 = p.abs16 + (int64_t)m * nb * 16;
+            const int n16 = nb * 16;
+            // first wave of loads (codes, sums, scales) in flight together, behind the posting
+            constexpr int NT = WARPS * 32;
+            int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, s0 = c0;
+            float d0 = 0.f;
+            const int i0 = threadIdx.x, i1 = threadIdx.x + NT;
+            if (i0 < n16) c0 = src[i0];
+            if (i1 < n16) c1 = src[i1];
+            if (i0 < nb * 2) s0 = reinterpret_cast<const int4 *>(b16)[i0]; // 8 sums of 16
+            if (i0 < nb) d0 = p.ad[m * nb + i0];
+            post_rest();
+            if (i0 < n16) *reinterpret_cast<int4 *>(tq + (i0 >> 4) * ACT_BLK + (i0 & 15) * 16) = c0;
+            if (i1 < n16) *reinterpret_cast<int4 *>(tq + (i1 >> 4) * ACT_BLK + (i1 & 15) * 16) = c1;
+            for (int i = threadIdx.x + 2 * NT; i < n16; i += NT)
+                *reinterpret_cast<int4 *>(tq + (i >> 4) * ACT_BLK + (i & 15) * 16) = src[i];
+            for (int i = threadIdx.x; i < nb * 2; i += NT) {
+                const int4 sv = i == i0 ? s0 : reinterpret_cast<const int4 *>(b16)[i];
+                const int16_t *h = reinterpret_cast<const int16_t *>(&sv);
+                if (TYPE == B200_TYPE_Q4_K) {
+                    int16_t o4[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) o4[k] = (int16_t)(h[2 * k] + h[2 * k + 1]);
+                    *reinterpret_cast<uint2 *>(reinterpret_cast<int16_t *>(tq + act_q) + i * 4) = *reinterpret_cast<uint2 *>(o4);
+                } else {
+                    *reinterpret_cast<int4 *>(reinterpret_cast<int16_t *>(tq + act_q) + i * 8) = sv;
+                }
+            }
+            for (int i = threadIdx.x; i < nb; i += NT)
+                reinterpret_cast<float *>(tq + act_q + act_s)[i] = i == i0 ? d0 : p.ad[m * nb + i];
         }
-        for (int i = threadIdx.x; i < nb; i += blockDim.x)
-            reinterpret_cast<float *>(tq + act_q + act_s)[i] = p.ad[m * nb + i];
     }
+    post_rest();
     __syncthreads();
+    TRACE_MARK(3);
     if (count <= 0) return;
 
     float acc[M];
@@ -439,6 +543,9 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     for (int j = 0; j < count; j++) {
         const int slot = j % p.ns;
         wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), &s_abort);
+#ifdef KQ_GEMV_TRACE
+        if (j == 0) TRACE_MARK(4);
+#endif
         const int blk = ks * F::KB + t;
         if (blk < nb) {
             const uint8_t *row = ring + (size_t)slot * F::SLOT + rs * F::PITCH;
@@ -549,6 +656,13 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
             rg++;
         }
     }
+#ifdef KQ_GEMV_TRACE
+    TRACE_MARK(5);
+    if (lane == 0 && s_trace < 32768u) {
+        atomicMax(&g_trace[s_trace][6], (unsigned long long)clock64());
+        atomicMax(&g_trace[s_trace][9], kq_globaltimer_ns());
+    }
+#endif
 }
 
 int env_int2(const char *name, int dflt) {
@@ -596,7 +710,7 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     p.ns = ns;
     const size_t smem = (size_t)M * act_tok + (size_t)WARPS * ns * F::SLOT + (size_t)WARPS * ns * 8;
     if (smem > 226 * 1024) return B200_ERR_UNSUPPORTED;
-    int grid = kq_sm_count();
+    int grid = kq_sm_count() * KQ_GEMV_GRIDMUL;
     if (grid * WARPS > MAX_UNITS) grid = MAX_UNITS / WARPS;
     const int64_t want = kq_div_up((int64_t)p.n_rg * p.nsteps, WARPS);
     if (want < grid) grid = (int)(want < 1 ? 1 : want);
@@ -613,6 +727,18 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
 
 } // namespace
 
+#ifdef KQ_GEMV_TRACE
+extern "C" __attribute__((visibility("default"))) int kq_gemv_trace_fetch(unsigned long long *out, int max_rec) {
+    unsigned int n = 0, zero = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));
+    if ((int)n > max_rec) n = max_rec;
+    if (n > 32768u) n = 32768u;
+    if (out && n) cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 16 * n);
+    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
 int kq_stream_error_fetch() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
@@ -631,7 +757,7 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
         if (segs[i].type != B200_TYPE_Q4_K && segs[i].type != B200_TYPE_Q6_K) return B200_ERR_UNSUPPORTED;
         if (((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;
     }
-    if (!(prep && prep->x) && ((uintptr_t)q & 15) != 0) return B200_ERR_UNSUPPORTED;
+    if (!(prep && prep->x) && ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0)) return B200_ERR_UNSUPPORTED;
     if (prep && prep->x && ((uintptr_t)prep->x & 15) != 0) return B200_ERR_UNSUPPORTED;
     for (uint32_t type : {(uint32_t)B200_TYPE_Q4_K, (uint32_t)B200_TYPE_Q6_K}) {
         KqGemvSeg sel[3];
