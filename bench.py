@@ -37,9 +37,13 @@ WORKLOADS = {
     "cfg3": dict(name="Llama-3-70B-shape Q4_K_M", n_layer=80, n_embd=8192, n_head=64, n_head_kv=8,
                  head_dim=128, n_ff=28672, n_vocab=128256, qkv_bias=0, rope_neox=0, rope_theta=5e5,
                  rms_eps=1e-5, prefill=4096, decode=256),
+    # configs[3]: MoE; with N GPUs each rank is an independent replica holding n_expert / N experts
+    "cfg4": dict(name="Qwen3-30B-A3B-shape MoE Q4_K_M", n_layer=48, n_embd=2048, n_head=32, n_head_kv=4,
+                 head_dim=128, n_ff=0, n_vocab=151936, qkv_bias=0, rope_neox=1, rope_theta=1e6,
+                 rms_eps=1e-6, n_expert=128, n_expert_used=8, n_ff_exp=768, prefill=1024, decode=256),
 }
 MODEL_KEYS = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
-              "rope_neox", "rope_theta", "rms_eps")
+              "rope_neox", "rope_theta", "rms_eps", "n_expert", "n_expert_used", "n_ff_exp")
 BPW = {12: 144 / 256, 14: 210 / 256}
 METRIC = "decode tok/s, Q4_K_M, batch 1 per stage (shape in config.workload; GEMV HBM % of peak in roofline)"
 
@@ -51,7 +55,11 @@ def matmuls(w, layer):
     """(N, K, ggml type) of every quantised matmul of one layer, Q4_K_M mix"""
     h, nq, nkv, ff = w["n_embd"], w["n_head"] * w["head_dim"], w["n_head_kv"] * w["head_dim"], w["n_ff"]
     alt = 14 if layer & 1 else 12
-    return [(nq, h, 12), (nkv, h, 12), (nkv, h, alt), (h, nq, 12), (ff, h, 12), (ff, h, 12), (h, ff, alt)]
+    attn = [(nq, h, 12), (nkv, h, 12), (nkv, h, alt), (h, nq, 12)]
+    if w.get("n_expert", 0):  # the experts one token activates
+        fe = w["n_ff_exp"]
+        return attn + w["n_expert_used"] * [(fe, h, 12), (fe, h, 12), (h, fe, alt)]
+    return attn + [(ff, h, 12), (ff, h, 12), (h, ff, alt)]
 
 
 def gemv_bytes(N, K, ty, M=1):
@@ -111,6 +119,9 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+_CPU_OPERANDS = {}
+
+
 # ------------------------------------------------------------------------------------------------
 def cpu_decode_sample(w, threads=None, reps=2):
     """times the CPU oracle on one layer of each parity (+ the LM head) at M = 1 and extrapolates
@@ -120,7 +131,6 @@ def cpu_decode_sample(w, threads=None, reps=2):
     if threads:
         orc.lib().orc_set_threads(threads)
     cores = orc.lib().orc_get_threads()
-    rng = np.random.default_rng(0)
     shapes = {}
     for layer in (0, 1):
         for (N, K, ty) in matmuls(w, layer):
@@ -128,10 +138,13 @@ def cpu_decode_sample(w, threads=None, reps=2):
     shapes[(w["n_vocab"], w["n_embd"], 14)] = 1
     total = 0.0
     for (N, K, ty), count in shapes.items():
-        rb = orc.row_bytes(ty, K)
-        W = rng.integers(0, 256, size=(N, rb), dtype=np.uint8)
-        x = rng.standard_normal((1, K)).astype(np.float32)
-        orc.mul_mat(ty, W, x, N, K)
+        if (N, K, ty) not in _CPU_OPERANDS:  # random valid block bytes, made once per process
+            rng = np.random.default_rng(N * 31 + K * 7 + ty)
+            W = rng.integers(0, 256, size=(N, orc.row_bytes(ty, K)), dtype=np.uint8)
+            x = rng.standard_normal((1, K)).astype(np.float32)
+            orc.mul_mat(ty, W, x, N, K)
+            _CPU_OPERANDS[(N, K, ty)] = (W, x)
+        W, x = _CPU_OPERANDS[(N, K, ty)]
         t0 = time.perf_counter()
         for _ in range(reps):
             orc.mul_mat(ty, W, x, N, K)
@@ -164,15 +177,12 @@ def run_reference(args, w):
     }))
 
 
-def run_micro(args):
-    """One quantised matmul shape of the isolated sweep (BASELINE.json configs[4]), timed with CUDA
-    events over `--micro-iters` launches captured in a CUDA graph that rotates over enough weight
-    copies to exceed L2.  This is also the command the ncu captures under profiles/ run."""
+def micro_one(N, K, M, tname, iters):
+    """One quantised matmul shape, timed with CUDA events over `iters` launches captured in a CUDA
+    graph that rotates over enough weight copies to exceed L2."""
     import torch
     from mesh_llm_b200 import ops
 
-    N, K, M, tname = args.micro.split(",")
-    N, K, M = int(N), int(K), int(M)
     ty = {"q4_k": 12, "q6_k": 14}[tname.lower()]
     rb = ops.device_row_bytes(ty, K)
     copies = max(2, int(400e6 // (N * rb)) + 1)
@@ -182,7 +192,6 @@ def run_micro(args):
     q, d, bs = ops.quantize_act(x)
     y = torch.empty(M, N, device="cuda")
     st = torch.cuda.Stream()
-    iters = args.micro_iters
     with torch.cuda.stream(st):
         for W in Ws:
             ops.mul_mat_q8(ty, W, q, d, bs, N, K, out=y)
@@ -202,13 +211,35 @@ def run_micro(args):
             torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1) / iters)
     sec = best * 1e-3
-    out = {"micro": args.micro, "us_per_launch": best * 1e3, "weight_copies": copies}
+    out = {"micro": f"{N},{K},{M},{tname}", "us_per_launch": best * 1e3, "weight_copies": copies}
     if M <= 8:
         out["algorithmic_bytes"] = gemv_bytes(N, K, ty, M)
         out["GBps"] = out["algorithmic_bytes"] / sec / 1e9
     else:
         out["TOPps"] = 2.0 * M * N * K / sec / 1e12
-    print(json.dumps(out))
+    del Ws, x, q, d, bs, y, graph
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_micro(args):
+    """--micro N,K,M,type: one shape of the isolated sweep (BASELINE.json configs[4]); also the command
+    the ncu captures under profiles/ run."""
+    N, K, M, tname = args.micro.split(",")
+    print(json.dumps(micro_one(int(N), int(K), int(M), tname, args.micro_iters)))
+
+
+SWEEP_SHAPES = ((5120, 27648), (27648, 5120), (8192, 28672), (28672, 8192), (151936, 2048))
+SWEEP_M = (1, 8, 64, 512, 4096)
+
+
+def run_sweep(args):
+    """--sweep: the isolated quantised-matmul sweep of BASELINE.json configs[4]: every shape x
+    {Q4_K, Q6_K} x M; GB/s of algorithmic bytes for M <= 8, useful int8 TOP/s above; one JSON line each."""
+    for tname in ("q4_k", "q6_k"):
+        for (N, K) in SWEEP_SHAPES:
+            for M in SWEEP_M:
+                print(json.dumps(micro_one(N, K, M, tname, max(4, args.micro_iters // (1 + M // 64)))), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -225,9 +256,12 @@ def main():
     ap.add_argument("--micro", default="", help="isolated quantised matmul instead of the model: 'N,K,M,type' "
                     "(type q4_k|q6_k); prints one line with us per launch and GB/s (M<=8) or TOP/s")
     ap.add_argument("--micro-iters", type=int, default=20)
+    ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)
+    if args.sweep:
+        return run_sweep(args)
     w = dict(WORKLOADS[args.workload])
     if args.layers:
         w["n_layer"] = args.layers
@@ -247,6 +281,8 @@ def main():
         args.gpus = world
     if world > 1:
         from mesh_llm_b200 import pipeline
+        if w.get("n_expert", 0):
+            return pipeline.bench_expert_replicas(args, w, METRIC, rank, world, local)
         return pipeline.bench_pipeline(args, w, METRIC, rank, world, local)
 
     torch.cuda.set_device(local)
@@ -254,7 +290,7 @@ def main():
     from mesh_llm_b200.stage import Stage
     import ctypes as C
 
-    model = {k: w[k] for k in MODEL_KEYS}
+    model = {k: w[k] for k in MODEL_KEYS if k in w}
     n_ctx = w["prefill"] + w["decode"] + args.steps + args.warmup + 64
     n_seq = 8
     st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local)
@@ -396,7 +432,8 @@ def main():
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "prefill_tok_s": prefill_tok_s, "decode_batch8_tok_s": b8,
-        "decode_weight_stream_frac_of_hbm_peak": (weight_bytes / (ms / args.steps * 1e-3) / 1e9) / peak,
+        "decode_weight_stream_frac_of_hbm_peak": None if w.get("n_expert", 0) else
+        (weight_bytes / (ms / args.steps * 1e-3) / 1e9) / peak,
     }
     print(json.dumps(out))
 

@@ -268,3 +268,100 @@ def bench_pipeline(args, w, metric, rank, world, local):
             "handoff": "torch.distributed send/recv (NCCL P2P over NVLink)",
         }))
     dist.destroy_process_group()
+
+
+def bench_expert_replicas(args, w, metric, rank, world, local):
+    """bench.py body for an MoE model at N > 1: N independent replicas, rank r holding the trunk and
+    experts [r*E/N, (r+1)*E/N) with the router rows of those experts (the layout the reference's
+    expert shards have: patches/0003 llama-moe-split, mesh-llm/src/inference/moe.rs).  No data-path
+    traffic between ranks; every rank decodes its own sequence; value = all tokens / max time."""
+    import torch
+    import torch.distributed as dist
+
+    from .stage import Stage
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    keys = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias", "rope_neox",
+            "rope_theta", "rms_eps", "n_ff_exp")
+    model = {k: w[k] for k in keys}
+    e_local = w["n_expert"] // world
+    model["n_expert"] = e_local
+    model["n_expert_used"] = min(w["n_expert_used"], e_local)
+    steps, warm = args.steps, max(3, args.warmup)
+    st = Stage(**model, n_ctx=w["prefill"] + 2 * (steps + warm) + 72, n_seq=1, n_ubatch=512, device=local)
+    st.generate(20251125 + rank)
+    rng = np.random.default_rng(1234 + rank)
+    prompt = torch.from_numpy(rng.integers(0, w["n_vocab"], w["prefill"]).astype(np.int32)).to(dev)
+    tok = torch.zeros(1, dtype=torch.int32, device=dev)
+    logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def prefill():
+        for p0 in range(0, w["prefill"], 512):
+            chunk = prompt[p0:p0 + 512]
+            st.forward(tokens=chunk, n_seq=1, T=chunk.numel(), pos0=p0, logits=logits, next_tokens=tok)
+
+    t_prefill = None if args.no_prefill else timed(prefill)
+    pos = [w["prefill"]]
+
+    def decode(k):
+        for _ in range(k):
+            st.forward(tokens=tok, n_seq=1, T=1, pos0=pos[0], logits=logits, next_tokens=tok)
+            pos[0] += 1
+
+    h_tok = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    def decode_e2e(k):
+        for _ in range(k):
+            h_tok.copy_(tok, non_blocking=True)  # result to the host ...
+            torch.cuda.current_stream().synchronize()
+            tok.copy_(h_tok, non_blocking=True)  # ... and back in as the next input
+            st.forward(tokens=tok, n_seq=1, T=1, pos0=pos[0], logits=logits, next_tokens=tok)
+            pos[0] += 1
+
+    decode(warm)
+    from bench import ClockSampler
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = st.kernel_launches()
+    t0 = time.time()
+    ms = timed(lambda: decode(steps))
+    t1 = time.time()
+    launches = torch.tensor([st.kernel_launches() - launches0], device=dev, dtype=torch.int64)
+    dist.all_reduce(launches)
+    te = timed(lambda: decode_e2e(steps))
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    if rank == 0:
+        total = steps * world
+        print(json.dumps({
+            "metric": metric, "value": total / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine", "data": "synthetic",
+            "config": {"workload": f"{w['name']} ({w['n_layer']} layers): {world} replicas, each the trunk plus "
+                                   f"{e_local} of {w['n_expert']} experts (top-{model['n_expert_used']}), one sequence "
+                                   f"per replica, decode batch 1 at context {w['prefill']}+; no traffic between GPUs",
+                       "sequences_in_flight": world,
+                       "l2": "active weights per token exceed L2 only in aggregate; experts change every token"},
+            "e2e": {"value": total / (te * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * world,
+                    "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": int(launches.item()), "clocks": clocks,
+            "prefill_tok_s": None if t_prefill is None else world * w["prefill"] / (t_prefill * 1e-3),
+        }))
+    dist.destroy_process_group()
