@@ -5,19 +5,21 @@
 // K-quant scales differ per 32 (Q4_K) or 16 (Q6_K) elements, so int8 products cannot simply be
 // accumulated along K.  Instead the integer scale is folded into the weight:  w' = sc_j * q  is
 // 10 bits (Q4_K, 0..945) or 13 bits signed (Q6_K, sc_t * (q - 32)), and is split into two int8
-// planes, w' = hi * R + lo  (R = 32 / 64).  Two MMAs per 32-element K step accumulate
+// planes, w' = hi * R + lo  (R = 256 / 64; low plane unsigned).  Two MMAs per 32-element K step accumulate
 // sum hi*a and sum lo*a over the whole super-block in int32 (|sum| < 2^26), and the epilogue forms
 // R*acc_hi + acc_lo -- bit-for-bit the integer  sum_j sc_j sum_i q_ij a_ij  of the decode kernels --
 // and applies the f32 scales d_w[n,b] * d_a[m,b] once per super-block.  The Q4_K min term
 // sum_j m_j * bsum_j is one more MMA (kind::f16, K = 16, small integers exact in f16 / f32).
 //
-// One CTA computes a 128-token x 128-row tile.  Tokens are the M (TMEM lane) dimension, weight rows
-// the N (column) dimension.  A small kernel first re-tiles the Q8 codes so that one super-block of a
-// token tile is a contiguous 32 KB run in the canonical K-major no-swizzle UMMA layout.  Per
-// super-block the copy engine brings that run and the packed Q4_K blocks of the 128 weight rows
-// (one tiled TMA box out of the row-major matrix; double-buffered, one mbarrier per stage); all warps unpack the weights from
-// shared memory to the two planes, one thread issues the MMAs, and after the commit barrier all
-// warps run the epilogue out of TMEM into the running f32 result in registers.
+// One CTA computes a 128-token x 64-row tile, and two CTAs share an SM (256 TMEM columns and under
+// half of the shared memory each), so one CTA's unpacking and TMEM draining overlap the other's MMAs
+// and copies.  Tokens are the M (TMEM lane) dimension, weight rows the N (column) dimension.  A small
+// kernel first re-tiles the Q8 codes so that one super-block of a token tile is a contiguous 32 KB
+// run in the canonical K-major no-swizzle UMMA layout.  Per super-block the copy engine brings that
+// run and the packed Q4_K blocks of the 64 weight rows (one tiled TMA box out of the row-major
+// matrix, requested one super-block ahead); all warps unpack the weights from shared memory to the
+// two planes, one thread issues the MMAs, and after the commit barrier all warps run the epilogue
+// out of TMEM into the running f32 result in registers.
 // Every barrier wait is bounded; on a time-out the kernel sets an error word, frees its TMEM and
 // returns.
 #include "kq_common.cuh"
@@ -27,16 +29,20 @@
 
 namespace {
 
-constexpr int TM = 128, TN = 128, NTHREADS = 256;
-constexpr int LBO = TM * 16;        // bytes between consecutive 16-byte K chunks of an operand
+constexpr int TM = 128, TN = 64, NTHREADS = 256, NCOL = TN / 2; // NCOL: result columns per thread
+constexpr int LBO_A = TM * 16;      // bytes between consecutive 16-byte K chunks of the token operand
+constexpr int LBO_B = TN * 16;      // ... of a weight plane
 constexpr int SBO = 128;            // bytes between consecutive groups of 8 rows
-constexpr int OP_BYTES = TM * 256;  // one int8 operand slab: 128 rows x 256 K bytes
-constexpr int MIN_BYTES = TM * 32;  // one f16 operand slab of the min term: 128 rows x 16 halves
-constexpr int RAW_BYTES = TN * KQ_Q4K_BYTES; // packed Q4_K blocks of one super-block column: 128 x 144
-constexpr int SMEM_A = 0, SMEM_A2 = OP_BYTES, SMEM_BHI = 2 * OP_BYTES, SMEM_BLO = 3 * OP_BYTES, SMEM_AMIN = 4 * OP_BYTES,
-              SMEM_BMIN = 4 * OP_BYTES + MIN_BYTES, SMEM_RAW = 4 * OP_BYTES + 2 * MIN_BYTES,
-              SMEM_SCAL = SMEM_RAW + 2 * RAW_BYTES, SMEM_TOTAL = SMEM_SCAL + 3 * TM * 4 + 64;
-constexpr uint32_t TMEM_COLS = 512, COL_HI = 0, COL_LO = 128, COL_MIN = 256;
+constexpr int A_BYTES = TM * 256;   // int8 token slab: 128 rows x 256 K bytes
+constexpr int B_BYTES = TN * 256;   // one int8 weight plane
+constexpr int AMIN_BYTES = TM * 32; // f16 operands of the min term: 16 halves per row
+constexpr int BMIN_BYTES = TN * 32;
+constexpr int RAW_BYTES = TN * KQ_Q4K_BYTES; // packed Q4_K blocks of one super-block column
+constexpr int SMEM_A = 0, SMEM_BHI = A_BYTES, SMEM_BLO = SMEM_BHI + B_BYTES, SMEM_AMIN = SMEM_BLO + B_BYTES,
+              SMEM_BMIN = SMEM_AMIN + AMIN_BYTES, SMEM_RAW = SMEM_BMIN + BMIN_BYTES, SMEM_SCAL = SMEM_RAW + 2 * RAW_BYTES,
+              SMEM_TOTAL = SMEM_SCAL + (TM + 2 * TN) * 4 + 64;
+static_assert(SMEM_RAW % 128 == 0 && RAW_BYTES % 128 == 0, "TMA destinations are 128-byte aligned");
+constexpr uint32_t TMEM_COLS = 256, COL_HI = 0, COL_LO = TN, COL_MIN = 2 * TN;
 constexpr int KQ_MAX_DEVICES = 16;
 
 __device__ int g_gemm_error;
@@ -63,12 +69,13 @@ struct GemmParams {
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // canonical K-major, no swizzle: 16-byte chunk kc of row r
-__device__ __forceinline__ uint32_t op_off(int r, int kc) { return kc * LBO + (r >> 3) * SBO + (r & 7) * 16; }
+__device__ __forceinline__ uint32_t op_off_a(int r, int kc) { return kc * LBO_A + (r >> 3) * SBO + (r & 7) * 16; }
+__device__ __forceinline__ uint32_t op_off_b(int r, int kc) { return kc * LBO_B + (r >> 3) * SBO + (r & 7) * 16; }
 
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-    d |= (uint64_t)(LBO >> 4) << 16;
+    d |= (uint64_t)(lbo >> 4) << 16;
     d |= (uint64_t)(SBO >> 4) << 32;
     d |= (uint64_t)1 << 46; // descriptor version of this architecture
     return d;               // layout type 0: no swizzle
@@ -111,12 +118,14 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b,
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])     \
                  : "memory")
 
-// two 16-bit lanes per word: (q_a | q_b << 16) * sc, split into the planes and interleaved back to bytes
+// Four 4-bit codes (one per byte of nib4) times the sub-block scale, split into the planes
+// hi = (sc*q) >> 8 and lo = (sc*q) & 255.  Two 16-bit lanes per multiply; the products' low and high
+// bytes are then already byte-aligned, so one byte permute per plane puts them back in code order.
 __device__ __forceinline__ void q4_planes(uint32_t nib4, uint32_t sc, uint32_t &hi, uint32_t &lo) {
-    const uint32_t p02 = (nib4 & 0x000F000Fu) * sc;        // bytes 0 and 2
-    const uint32_t p13 = ((nib4 >> 8) & 0x000F000Fu) * sc; // bytes 1 and 3
-    hi = ((p02 >> 5) & 0x00FF00FFu) | (((p13 >> 5) & 0x00FF00FFu) << 8);
-    lo = (p02 & 0x001F001Fu) | ((p13 & 0x001F001Fu) << 8);
+    const uint32_t p02 = (nib4 & 0x000F000Fu) * sc;        // codes 0 and 2: bytes [lo0 hi0 lo2 hi2]
+    const uint32_t p13 = ((nib4 >> 8) & 0x000F000Fu) * sc; // codes 1 and 3: bytes [lo1 hi1 lo3 hi3]
+    lo = __byte_perm(p02, p13, 0x6240);
+    hi = __byte_perm(p02, p13, 0x7351);
 }
 
 // Q8 codes [M][K] -> [M/128][K/16][128 rows][16 bytes]: one super-block of a 128-token tile becomes a
@@ -134,17 +143,18 @@ __global__ void __launch_bounds__(256) retile_act_kernel(const int8_t *__restric
     }
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap wmap) {
+__global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap wmap) {
     KQ_PDL_ENTER();
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ uint64_t mbar;
-    __shared__ uint64_t full_bar[2];
+    __shared__ uint64_t mbar;      // the MMAs of a super-block have completed
+    __shared__ uint64_t full_raw[2]; // packed weight blocks of a stage have landed
+    __shared__ uint64_t full_a;      // the token slab has landed
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
     float *da_s = reinterpret_cast<float *>(smem + SMEM_SCAL);
-    float *dw_s = da_s + TM, *dmin_s = dw_s + TM;
+    float *dw_s = da_s + TM, *dmin_s = dw_s + TN;
     const uint32_t mbar_a = smem_u32(&mbar);
 
     if (warp == 0) {
@@ -155,8 +165,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     }
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_a), "r"(1));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[0])), "r"(1));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[1])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_raw[0])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_raw[1])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_a)), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0;
     }
@@ -166,14 +177,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     const uint32_t tmem = s_tmem;
     // this thread's TMEM window: lanes of its warp quarter, columns of its half of the tile
     const int row = (warp & 3) * 32 + lane; // token row of the tile = TMEM lane
-    const int chalf = warp >> 2;            // columns [64*chalf, 64*chalf + 64)
+    const int chalf = warp >> 2;            // columns [NCOL*chalf, NCOL*chalf + NCOL)
     const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
-    float yacc[64]; // running f32 result of this thread's token row x its 64 weight columns
+    float yacc[NCOL]; // running f32 result of this thread's token row x its weight columns
 #pragma unroll
-    for (int i = 0; i < 64; i++) yacc[i] = 0.f;
+    for (int i = 0; i < NCOL; i++) yacc[i] = 0.f;
 
-    const uint32_t a_base = smem_u32(smem + SMEM_A), a2_base = smem_u32(smem + SMEM_A2), bhi_base = smem_u32(smem + SMEM_BHI),
+    const uint32_t a_base = smem_u32(smem + SMEM_A), bhi_base = smem_u32(smem + SMEM_BHI),
                    blo_base = smem_u32(smem + SMEM_BLO), amin_base = smem_u32(smem + SMEM_AMIN),
                    bmin_base = smem_u32(smem + SMEM_BMIN);
     const bool q4 = p.type == B200_TYPE_Q4_K;
@@ -181,37 +192,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     uint32_t phase = 0;
     bool failed = false;
 
-    // ---- software pipeline: the global loads of super-block b+1 (activation tile by cp.async into
-    // the other A buffer, packed weights and per-token scalars into registers) are issued right
-    // after the MMAs of super-block b and land while the tensor core and the epilogue of b run.
+    // ---- software pipeline.  Two CTAs share an SM, so while this one unpacks or drains TMEM the
+    // tensor core and the copy engine work for the other one.  Inside a CTA the packed weights are
+    // requested one super-block ahead (two raw buffers); the token slab is single-buffered and
+    // requested as soon as the MMAs that read it have completed.
     constexpr int WT4 = TN * 8 / NTHREADS, WT6 = TN * 4 / NTHREADS; // weight tasks per thread
     uint4 p6_h[WT6], p6_a[WT6], p6_b[WT6]; // Q6_K: qh chunk and its two ql chunks per task
     uint32_t p6_sc[WT6];
     float p6_d[WT6];
     float pf_da = 0.f;
     int4 pf_bs0 = make_int4(0, 0, 0, 0), pf_bs1 = make_int4(0, 0, 0, 0);
-    auto prefetch = [&](int b) {
-        const int stg = b & 1;
-        if (warp == 1) {
-            // one thread hands the tile to the copy engine: the re-tiled activations are one contiguous
-            // 32 KB run, the packed Q4_K blocks of the 128 weight rows one tiled TMA box
-            const uint32_t bar = smem_u32(&full_bar[stg]);
-            if (lane == 0) {
-                const uint32_t bytes = OP_BYTES + (q4 ? RAW_BYTES : 0);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                const int8_t *src = p.aq + ((int64_t)blockIdx.y * (p.K / 16) + (int64_t)b * 16) * (TM * 16);
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(smem + (stg ? SMEM_A2 : SMEM_A))),
-                             "l"(src), "r"(OP_BYTES), "r"(bar)
-                             : "memory");
-                if (q4) // box of 128 rows x 144 bytes out of the row-major matrix; rows past N arrive as zeros
-                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                                     smem_u32(smem + SMEM_RAW + stg * RAW_BYTES)),
-                                 "l"(&wmap), "r"(b * KQ_Q4K_BYTES), "r"(n0), "r"(bar)
-                                 : "memory");
-            }
+
+    auto issue_raw = [&](int b) { // one tiled TMA box: 64 rows x 144 bytes; rows past N arrive as zeros
+        if (q4 && warp == 1 && lane == 0) {
+            const uint32_t bar = smem_u32(&full_raw[b & 1]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(RAW_BYTES) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                             smem_u32(smem + SMEM_RAW + (b & 1) * RAW_BYTES)),
+                         "l"(&wmap), "r"(b * KQ_Q4K_BYTES), "r"(n0), "r"(bar)
+                         : "memory");
         }
+    };
+    auto issue_a = [&](int b) { // the re-tiled activations of a super-block are one contiguous 32 KB run
+        if (warp == 1 && lane == 0) {
+            const uint32_t bar = smem_u32(&full_a);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(A_BYTES) : "memory");
+            const int8_t *src = p.aq + ((int64_t)blockIdx.y * (p.K / 16) + (int64_t)b * 16) * (TM * 16);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             a_base),
+                         "l"(src), "r"(A_BYTES), "r"(bar)
+                         : "memory");
+        }
+    };
+    auto prefetch = [&](int b) { // per-token scalars and (Q6_K) the weight pieces, into registers
         if (tid < TM) {
             const int r = tid;
             const bool in = m0 + r < p.M;
@@ -244,11 +258,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
         }
     };
 
+    issue_raw(0);
+    issue_a(0);
     prefetch(0);
-    int last_pf = 0; // newest super-block handed to the copy engine
+    int last_raw = 0, last_a = 0; // newest super-blocks handed to the copy engine
     for (int b = 0; b < p.nb && !failed; b++) {
         PROF_T(t_0);
-        if (!failed && !kq_mbar_wait(smem_u32(&full_bar[b & 1]), (uint32_t)((b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS)) {
+        if (q4 && !kq_mbar_wait(smem_u32(&full_raw[b & 1]), (uint32_t)((b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS)) {
             s_abort = 1;
             atomicExch(&g_gemm_error, 2);
         }
@@ -265,8 +281,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                     h[k] = __int2half_rn((int)s16a[k]);
                     h[8 + k] = __int2half_rn((int)s16b[k]);
                 }
-                *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off(r, 0)) = *reinterpret_cast<uint4 *>(&h[0]);
-                *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off(r, 1)) = *reinterpret_cast<uint4 *>(&h[8]);
+                *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off_a(r, 0)) = *reinterpret_cast<uint4 *>(&h[0]);
+                *reinterpret_cast<uint4 *>(smem + SMEM_AMIN + op_off_a(r, 1)) = *reinterpret_cast<uint4 *>(&h[8]);
             }
         }
         if (q4) {
@@ -293,8 +309,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                         mh[2 * j] = v;
                         mh[2 * j + 1] = v;
                     }
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_b(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_b(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
                 }
                 uint4 hi_l, lo_l, hi_h, lo_h;
                 q4_planes(w.x & 0x0F0F0F0Fu, sc0, hi_l.x, lo_l.x);
@@ -305,7 +321,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                 q4_planes((w.y >> 4) & 0x0F0F0F0Fu, sc1, hi_h.y, lo_h.y);
                 q4_planes((w.z >> 4) & 0x0F0F0F0Fu, sc1, hi_h.z, lo_h.z);
                 q4_planes((w.w >> 4) & 0x0F0F0F0Fu, sc1, hi_h.w, lo_h.w);
-                const uint32_t o_l = op_off(r, 4 * g + h), o_h = op_off(r, 4 * g + 2 + h);
+                const uint32_t o_l = op_off_b(r, 4 * g + h), o_h = op_off_b(r, 4 * g + 2 + h);
                 *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o_l) = hi_l;
                 *reinterpret_cast<uint4 *>(smem + SMEM_BLO + o_l) = lo_l;
                 *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o_h) = hi_h;
@@ -345,7 +361,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
                         hi4[wd] = hi;
                         lo4[wd] = lo;
                     }
-                    const uint32_t o = op_off(r, 8 * hh + 2 * q + c1);
+                    const uint32_t o = op_off_b(r, 8 * hh + 2 * q + c1);
                     *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
                     *reinterpret_cast<uint4 *>(smem + SMEM_BLO + o) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
                 }
@@ -362,24 +378,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
           // the whole warp stays here while its first lane issues, so that no lane of the issuing
           // warp sits in a blocking barrier wait before the MMAs have been handed to the tensor core
           if (lane == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t id_hi = idesc_i8(true), id_lo = idesc_i8(q4 ? true : false);
-#pragma unroll
-            for (int s = 0; s < 8; s++) { // K = 32 per instruction: chunks 2s, 2s+1
-                const uint64_t ad = make_desc(((b & 1) ? a2_base : a_base) + 2 * s * LBO);
-                mma_i8(tmem + COL_HI, ad, make_desc(bhi_base + 2 * s * LBO), id_hi, s > 0);
-                mma_i8(tmem + COL_LO, ad, make_desc(blo_base + 2 * s * LBO), id_lo, s > 0);
+            // the token slab of this super-block must have landed; on a time-out nothing is issued and
+            // the commit below completes at once, so that the other threads find the abort flag
+            const bool a_ok = kq_mbar_wait(smem_u32(&full_a), (uint32_t)(b & 1), 5 * KQ_WAIT_LIMIT_NS);
+            if (!a_ok) {
+                s_abort = 1;
+                atomicExch(&g_gemm_error, 3);
             }
-            if (q4) mma_f16(tmem + COL_MIN, make_desc(amin_base), make_desc(bmin_base), idesc_f16(), 0);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (a_ok && !s_abort) {
+                const uint32_t id_hi = idesc_i8(true), id_lo = idesc_i8(false); // the low plane is unsigned
+#pragma unroll
+                for (int s = 0; s < 8; s++) { // K = 32 per instruction: chunks 2s, 2s+1
+                    const uint64_t ad = make_desc(a_base + 2 * s * LBO_A, LBO_A);
+                    mma_i8(tmem + COL_HI, ad, make_desc(bhi_base + 2 * s * LBO_B, LBO_B), id_hi, s > 0);
+                    mma_i8(tmem + COL_LO, ad, make_desc(blo_base + 2 * s * LBO_B, LBO_B), id_lo, s > 0);
+                }
+                if (q4) mma_f16(tmem + COL_MIN, make_desc(amin_base, LBO_A), make_desc(bmin_base, LBO_B), idesc_f16(), 0);
+            }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a)
                          : "memory");
           }
           __syncwarp();
         }
         PROF_T(t_3);
-        if (b + 1 < p.nb) { // the loads of the next super-block fly during MMA + epilogue
+        if (b + 1 < p.nb) { // weights and scalars of the next super-block fly during MMA + epilogue
+            issue_raw(b + 1);
             prefetch(b + 1);
-            last_pf = b + 1;
+            last_raw = b + 1;
         }
         PROF_T(t_4);
         { // bounded wait for the MMAs of this super-block
@@ -393,24 +419,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         PROF_T(t_5);
         if (s_abort) failed = true;
+        if (!failed && b + 1 < p.nb) { // the slab is free again
+            issue_a(b + 1);
+            last_a = b + 1;
+        }
         // ---- epilogue of the super-block: y += d_a * (d_w * (R*hi + lo) - dmin * min) ------------
         if (!failed) {
             const float da = da_s[row];
-            const int R = q4 ? 32 : 64;
+            const int R = q4 ? 256 : 64;
 #pragma unroll
-            for (int c = 0; c < 64; c += 16) {
-                const uint32_t col = chalf * 64 + c;
+            for (int c = 0; c < NCOL; c += 16) {
+                const uint32_t col = chalf * NCOL + c;
                 uint32_t hi[16], lo[16], mn[16];
                 TMEM_LD16(tlane + COL_HI + col, hi);
                 TMEM_LD16(tlane + COL_LO + col, lo);
                 if (q4) TMEM_LD16(tlane + COL_MIN + col, mn);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int main_i = R * (int)hi[i] + (int)lo[i];
-                    float t = dw_s[col + i] * (float)main_i;
-                    if (q4) t -= dmin_s[col + i] * __uint_as_float(mn[i]);
-                    yacc[c + i] = fmaf(da, t, yacc[c + i]);
+                for (int i4 = 0; i4 < 16; i4 += 4) {
+                    const float4 dw4 = *reinterpret_cast<const float4 *>(&dw_s[col + i4]);
+                    const float4 dm4 = *reinterpret_cast<const float4 *>(&dmin_s[col + i4]);
+                    const float dwv[4] = {dw4.x, dw4.y, dw4.z, dw4.w}, dmv[4] = {dm4.x, dm4.y, dm4.z, dm4.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int i = i4 + k;
+                        const int main_i = R * (int)hi[i] + (int)lo[i];
+                        float t = dwv[k] * (float)main_i;
+                        if (q4) t -= dmv[k] * __uint_as_float(mn[i]);
+                        yacc[c + i] = fmaf(da, t, yacc[c + i]);
+                    }
                 }
             }
         }
@@ -423,15 +460,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const GemmParams p
     }
 
     if (failed) { // never leave with bulk copies still writing this CTA's shared memory
-        kq_mbar_wait(smem_u32(&full_bar[last_pf & 1]), (uint32_t)((last_pf >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
-        if (last_pf > 0)
-            kq_mbar_wait(smem_u32(&full_bar[(last_pf - 1) & 1]), (uint32_t)(((last_pf - 1) >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+        if (q4) {
+            kq_mbar_wait(smem_u32(&full_raw[last_raw & 1]), (uint32_t)((last_raw >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+            if (last_raw > 0)
+                kq_mbar_wait(smem_u32(&full_raw[(last_raw - 1) & 1]), (uint32_t)(((last_raw - 1) >> 1) & 1),
+                             5 * KQ_WAIT_LIMIT_NS);
+        }
+        kq_mbar_wait(smem_u32(&full_a), (uint32_t)(last_a & 1), 5 * KQ_WAIT_LIMIT_NS);
     }
     // ---- write the tile -------------------------------------------------------------------------
     if (!failed && m0 + row < p.M) {
 #pragma unroll
-        for (int c = 0; c < 64; c++) {
-            const int col = chalf * 64 + c;
+        for (int c = 0; c < NCOL; c++) {
+            const int col = chalf * NCOL + c;
             if (n0 + col < p.N) {
                 const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
                 float v = yacc[c];
@@ -522,9 +563,9 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
     KQ_COUNT_LAUNCH();
     GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled[dev]), d, bs, y, bias, residual,
                     (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type};
-    // 118 KB of dynamic shared memory also keeps a second CTA off the SM: a CTA holds all 512 TMEM columns
-    const int smem = SMEM_TOTAL > 118 * 1024 ? SMEM_TOTAL : 118 * 1024;
-    static_assert(SMEM_TOTAL <= 226 * 1024, "tile does not fit shared memory");
+    // two CTAs per SM: each holds 256 of the 512 TMEM columns and under half of the shared memory
+    const int smem = SMEM_TOTAL;
+    static_assert(SMEM_TOTAL <= 112 * 1024, "two tiles must fit the shared memory of an SM");
     if (!attr[dev]) {
         KQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr[dev] = true;
