@@ -268,8 +268,56 @@ B200_API b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens,
 B200_API b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos0,
                                                uint32_t classes, int32_t iters, float *ms_per_step,
                                                int64_t *launches_per_step);
+/* the tensors a stage owns, by GGUF name: what a loader has to supply (ne[0] = row length K,
+ * ne[1] = rows, ne[2] = experts or 1); type is the type currently allocated                      */
+B200_API int64_t b200_stage_tensor_count(b200_stage *st);
+B200_API b200_status b200_stage_tensor_info(b200_stage *st, int64_t i, char *name, size_t name_cap,
+                                            uint32_t *type, int64_t ne[3]);
 B200_API b200_status b200_stage_synchronize(b200_stage *st);
 B200_API int64_t b200_stage_kernel_launches(b200_stage *st); /* launches issued so far        */
+
+/* ---- GGUF container: header scan, tensor index, selective load --------------------------------
+ * Replaces, for this path, the header scanner mesh-llm uses to plan a deployment
+ * (mesh-client/src/models/gguf.rs:319-421 compact metadata, :476-572 resident / expert byte
+ * profile, limits :4-9) and the worker-side load of a stage's own tensors by name from its local
+ * file (SET_TENSOR_GGUF, third_party/llama.cpp/patches/0001 lines 179-266).  Malformed files are
+ * rejected with B200_ERR_INVALID and a message; nothing aborts.                                  */
+typedef struct b200_gguf b200_gguf;
+typedef struct b200_gguf_meta {
+    char architecture[64], tokenizer_model[64];
+    uint32_t context_length, vocab_size, embedding_length, head_count, head_count_kv, block_count;
+    uint32_t feed_forward_length, key_length, value_length;
+    uint32_t expert_count, expert_used_count, expert_feed_forward_length;
+    float rope_freq_base, rope_scale, rms_epsilon;
+} b200_gguf_meta;
+typedef struct b200_gguf_tensor {
+    char name[128];
+    uint32_t type, n_dims; /* ggml type id                                                    */
+    int64_t ne[4];
+    uint64_t file_offset;  /* absolute offset of the tensor's bytes in the file               */
+    uint64_t nbytes;       /* from type and shape; 0 when the type's block size is not known  */
+} b200_gguf_tensor;
+typedef struct b200_gguf_byte_profile_t {
+    uint32_t expert_count, expert_used_count;
+    uint64_t full_model_bytes, base_resident_bytes, expert_tensor_bytes, file_overhead_bytes;
+} b200_gguf_byte_profile_t;
+
+B200_API b200_status b200_gguf_open(const char *path, b200_gguf **out);
+B200_API void b200_gguf_close(b200_gguf *g);
+B200_API b200_status b200_gguf_get_meta(const b200_gguf *g, b200_gguf_meta *out);
+B200_API int64_t b200_gguf_tensor_count(const b200_gguf *g);
+B200_API b200_status b200_gguf_tensor_info(const b200_gguf *g, int64_t i, b200_gguf_tensor *out);
+B200_API int64_t b200_gguf_find_tensor(const b200_gguf *g, const char *name); /* -1: not in the file */
+B200_API b200_status b200_gguf_read_tensor(const b200_gguf *g, int64_t i, void *dst, size_t nbytes);
+B200_API b200_status b200_gguf_byte_profile(const b200_gguf *g, b200_gguf_byte_profile_t *out);
+/* stage configuration for layers [layer_begin, layer_end) of the model in the file (layer_end < 0:
+ * to the last layer); embeddings go with layer 0, output_norm + output with the last layer       */
+B200_API b200_status b200_gguf_stage_config(const b200_gguf *g, int32_t layer_begin, int32_t layer_end,
+                                            int32_t n_ctx, int32_t n_seq, int32_t n_ubatch,
+                                            int32_t device, b200_stage_config *cfg);
+/* reads every tensor the stage owns, and nothing else, from the file and uploads it               */
+B200_API b200_status b200_stage_load_gguf(b200_stage *st, const b200_gguf *g, int64_t *n_loaded,
+                                          int64_t *bytes_read);
 
 #ifdef __cplusplus
 }

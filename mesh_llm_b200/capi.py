@@ -50,6 +50,29 @@ class StageConfig(C.Structure):
     ]
 
 
+class GgufMeta(C.Structure):
+    _fields_ = [
+        ("architecture", C.c_char * 64), ("tokenizer_model", C.c_char * 64),
+        ("context_length", C.c_uint32), ("vocab_size", C.c_uint32), ("embedding_length", C.c_uint32),
+        ("head_count", C.c_uint32), ("head_count_kv", C.c_uint32), ("block_count", C.c_uint32),
+        ("feed_forward_length", C.c_uint32), ("key_length", C.c_uint32), ("value_length", C.c_uint32),
+        ("expert_count", C.c_uint32), ("expert_used_count", C.c_uint32),
+        ("expert_feed_forward_length", C.c_uint32),
+        ("rope_freq_base", C.c_float), ("rope_scale", C.c_float), ("rms_epsilon", C.c_float),
+    ]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("type", C.c_uint32), ("n_dims", C.c_uint32), ("ne", C.c_int64 * 4),
+                ("file_offset", C.c_uint64), ("nbytes", C.c_uint64)]
+
+
+class GgufByteProfile(C.Structure):
+    _fields_ = [("expert_count", C.c_uint32), ("expert_used_count", C.c_uint32),
+                ("full_model_bytes", C.c_uint64), ("base_resident_bytes", C.c_uint64),
+                ("expert_tensor_bytes", C.c_uint64), ("file_overhead_bytes", C.c_uint64)]
+
+
 _lib = None
 
 vp, i64, i32, u32, u64, sz = C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t
@@ -112,6 +135,18 @@ SIGNATURES = {
     "b200_stage_weight_bytes": (sz, [vp]),
     "b200_stage_forward": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
     "b200_stage_profile_decode": (i32, [vp, i32, i32, u32, i32, C.POINTER(C.c_float), C.POINTER(i64)]),
+    "b200_stage_tensor_count": (i64, [vp]),
+    "b200_stage_tensor_info": (i32, [vp, i64, C.c_char_p, sz, C.POINTER(u32), C.POINTER(i64 * 3)]),
+    "b200_gguf_open": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "b200_gguf_close": (None, [vp]),
+    "b200_gguf_get_meta": (i32, [vp, C.POINTER(GgufMeta)]),
+    "b200_gguf_tensor_count": (i64, [vp]),
+    "b200_gguf_tensor_info": (i32, [vp, i64, C.POINTER(GgufTensor)]),
+    "b200_gguf_find_tensor": (i64, [vp, C.c_char_p]),
+    "b200_gguf_read_tensor": (i32, [vp, i64, vp, sz]),
+    "b200_gguf_byte_profile": (i32, [vp, C.POINTER(GgufByteProfile)]),
+    "b200_gguf_stage_config": (i32, [vp, i32, i32, i32, i32, i32, i32, C.POINTER(StageConfig)]),
+    "b200_stage_load_gguf": (i32, [vp, vp, C.POINTER(i64), C.POINTER(i64)]),
     "b200_stage_synchronize": (i32, [vp]),
     "b200_stage_kernel_launches": (i64, [vp]),
 }

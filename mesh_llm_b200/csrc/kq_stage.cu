@@ -531,6 +531,20 @@ void b200_stage_free(b200_stage *st) {
     delete st;
 }
 
+int64_t b200_stage_tensor_count(b200_stage *st) { return st ? (int64_t)st->tensors.size() : -1; }
+
+b200_status b200_stage_tensor_info(b200_stage *st, int64_t i, char *name, size_t name_cap, uint32_t *type, int64_t ne[3]) {
+    KQ_REQUIRE(st && name && name_cap > 0, "stage_tensor_info: null argument");
+    KQ_REQUIRE(i >= 0 && i < (int64_t)st->tensors.size(), "stage_tensor_info: index %lld out of range", (long long)i);
+    const StTensor &t = st->tensors[(size_t)i];
+    KQ_REQUIRE(t.name.size() < name_cap, "stage_tensor_info: name buffer of %zu bytes is too small", name_cap);
+    snprintf(name, name_cap, "%s", t.name.c_str());
+    if (type) *type = t.type;
+    if (ne)
+        for (int d = 0; d < 3; d++) ne[d] = t.ne[d];
+    return B200_OK;
+}
+
 b200_status b200_stage_set_tensor(b200_stage *st, const char *name, uint32_t type, const void *host_data,
                                   size_t nbytes) {
     KQ_REQUIRE(st && name && host_data, "stage_set_tensor: null argument");

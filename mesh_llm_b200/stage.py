@@ -30,6 +30,25 @@ class Stage:
         check(lib().b200_stage_create(C.byref(self.cfg), C.byref(h)))
         self.h = h
 
+    @classmethod
+    def from_gguf(cls, gguf_file, layer_begin=0, layer_end=-1, n_ctx=4096, n_seq=1, n_ubatch=512, device=0):
+        """Stage for blk.[layer_begin, layer_end) of the model in `gguf_file` (a GgufFile), with exactly
+        its own tensors read from the file.  Returns (stage, tensors loaded, bytes read)."""
+        cfg = gguf_file.stage_config(layer_begin, layer_end, n_ctx, n_seq, n_ubatch, device)
+        st = cls(**{name: getattr(cfg, name) for name, _ in StageConfig._fields_})
+        n, nbytes = C.c_int64(), C.c_int64()
+        check(lib().b200_stage_load_gguf(st.h, gguf_file.h, C.byref(n), C.byref(nbytes)))
+        return st, n.value, nbytes.value
+
+    def tensor_names(self):
+        out = []
+        for i in range(lib().b200_stage_tensor_count(self.h)):
+            name = C.create_string_buffer(128)
+            ty, ne = C.c_uint32(), (C.c_int64 * 3)()
+            check(lib().b200_stage_tensor_info(self.h, i, name, 128, C.byref(ty), C.byref(ne)))
+            out.append((name.value.decode(), ty.value, list(ne)))
+        return out
+
     def close(self):
         if getattr(self, "h", None):
             lib().b200_stage_free(self.h)
