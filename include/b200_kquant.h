@@ -224,6 +224,25 @@ B200_API b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *
 B200_API b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream);
 B200_API b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k,
                                     int32_t *ids, float *w, void *stream);
+/* Statistics of the output distribution per row of logits [T][n], computed on the device: what the
+ * reference's server derives on the CPU from the full-vocabulary softmax after the prefill and
+ * after every generated token when its mesh hooks are on (third_party/llama.cpp/patches/0005:
+ * mesh_compute_entropy = -sum p log2 p, margin = p[0] - p[1], the top tokens of the hook payload,
+ * the probability of the sampled token).  chosen (device, optional): the sampled token per row,
+ * default the argmax.  argmax_out (device, optional) receives the greedy token (lowest index on
+ * ties).  scratch: b200_logit_signals_scratch_bytes(T) bytes of device memory, zeroed once by the
+ * caller before the first use; calls that share it must be ordered on one stream.                */
+typedef struct b200_logit_signals_t {
+    float entropy;  /* bits                                                                   */
+    float margin;   /* p(top 1) - p(top 2); 1 for a single-entry row                           */
+    float p_chosen;
+    float top_p[5]; /* probabilities of the five most likely tokens, best first                */
+    int32_t top_id[5];
+} b200_logit_signals_t;
+B200_API size_t b200_logit_signals_scratch_bytes(int64_t T);
+B200_API b200_status b200_logit_signals(const float *logits, int64_t T, int64_t n, const int32_t *chosen,
+                                        b200_logit_signals_t *signals, int32_t *argmax_out,
+                                        void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---- stage: one contiguous layer range of a model resident on one GPU ------------------------
  * This is what a mesh-llm worker is: `rpc-server -d DEV --gguf PATH` holding blk.[a,b) and

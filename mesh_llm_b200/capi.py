@@ -127,6 +127,8 @@ SIGNATURES = {
     "b200_get_rows": (i32, [u32, vp, vp, i64, i64, vp, vp]),
     "b200_argmax": (i32, [vp, i64, i64, vp, vp]),
     "b200_moe_route": (i32, [vp, i64, i64, i64, vp, vp, vp]),
+    "b200_logit_signals_scratch_bytes": (sz, [i64]),
+    "b200_logit_signals": (i32, [vp, i64, i64, vp, vp, vp, vp, sz, vp]),
     "b200_stage_create": (i32, [C.POINTER(StageConfig), C.POINTER(vp)]),
     "b200_stage_free": (None, [vp]),
     "b200_stage_set_tensor": (i32, [vp, C.c_char_p, u32, vp, sz]),

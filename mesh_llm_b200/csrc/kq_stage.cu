@@ -135,6 +135,8 @@ struct b200_stage {
           *rw = nullptr, *hp = nullptr, *yp = nullptr;
     int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
     size_t att_scratch_bytes = 0;
+    void *scan_scratch = nullptr; // slices and counters of the vocabulary scan
+    size_t scan_scratch_bytes = 0;
     int8_t *aq = nullptr;
     float *ad = nullptr;
     int16_t *abs16 = nullptr;
@@ -346,7 +348,11 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
                                    all_logits ? h : (int64_t)T * h));
                 GEMV_(mm(st, st->out_w, out_rows, lg, nullptr, nullptr, s));
             }
-            if (next_tokens) OTHER_(b200_argmax(lg, out_rows, c.n_vocab, next_tokens, s));
+            // greedy token: the sliced vocabulary scan (argmax only here; the same launch can also
+            // leave entropy / margin / top tokens through b200_logit_signals)
+            if (next_tokens)
+                OTHER_(b200_logit_signals(lg, out_rows, c.n_vocab, nullptr, nullptr, next_tokens, st->scan_scratch,
+                                          st->scan_scratch_bytes, s));
         }
     }
     return B200_OK;
@@ -489,6 +495,11 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
     A((void **)&st->rid_scratch, 1024);
     A((void **)&st->attn_counters, (size_t)c.n_seq * c.n_head_kv * 4 + 256);
     if (c.has_output) A((void **)&st->logits_int, (size_t)c.n_seq * c.n_vocab * 4);
+    if (c.has_output) {
+        st->scan_scratch_bytes = b200_logit_signals_scratch_bytes(std::max<int64_t>(R, c.n_seq));
+        A(&st->scan_scratch, st->scan_scratch_bytes);
+        if (rc == B200_OK && cudaMemset(st->scan_scratch, 0, st->scan_scratch_bytes) != cudaSuccess) rc = B200_ERR_CUDA;
+    }
     if (c.n_expert > 0) {
         A((void **)&st->rl, R * c.n_expert * 4);
         A((void **)&st->rw, pairs * 4);

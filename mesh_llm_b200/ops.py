@@ -150,6 +150,21 @@ def argmax(x):
     return idx
 
 
+def logit_signals(logits, chosen=None):
+    """-> dict of device tensors: entropy [T] (bits), margin [T], p_chosen [T], top_p [T][5], top_id [T][5],
+    argmax [T]; the statistics the reference's server takes from the full-vocabulary softmax per token"""
+    logits = _dev(logits).contiguous().float()
+    T, n = logits.shape
+    nb = lib().b200_logit_signals_scratch_bytes(T)
+    scratch = torch.zeros(nb, dtype=torch.uint8, device=logits.device)
+    sig = torch.empty((T, 13), dtype=torch.float32, device=logits.device)  # 3 + 5 floats, 5 int32
+    am = torch.empty(T, dtype=torch.int32, device=logits.device)
+    ch = None if chosen is None else _dev(chosen).to(torch.int32).contiguous()
+    check(lib().b200_logit_signals(ptr(logits), T, n, ptr(ch), ptr(sig), ptr(am), ptr(scratch), nb, cur_stream()))
+    return dict(entropy=sig[:, 0], margin=sig[:, 1], p_chosen=sig[:, 2], top_p=sig[:, 3:8],
+                top_id=sig[:, 8:13].contiguous().view(torch.int32), argmax=am)
+
+
 def moe_route(logits, k):
     logits = _dev(logits).contiguous().float()
     T, E = logits.shape
