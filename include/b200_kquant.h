@@ -338,6 +338,20 @@ B200_API b200_status b200_gguf_stage_config(const b200_gguf *g, int32_t layer_be
 B200_API b200_status b200_stage_load_gguf(b200_stage *st, const b200_gguf *g, int64_t *n_loaded,
                                           int64_t *bytes_read);
 
+/* ---- expert shards of a mixture-of-experts model ----------------------------------------------
+ * Which experts a node holds (mesh-llm/src/inference/moe.rs:535-636: mode 0 = shared core of the
+ * `min_experts` most used experts on every node, the rest round-robin with `overlap` copies each;
+ * mode 1 = shared core + snake draft), and the file a node loads: trunk + the listed experts, the
+ * router rows gathered, expert_count rewritten and expert_used_count clamped (llama-moe-split,
+ * third_party/llama.cpp/patches/0003 lines 945-955, 1040-1113, 1142-1191).                        */
+B200_API b200_status b200_moe_assign(const uint32_t *ranking, int32_t n_expert, int32_t n_nodes,
+                                     int32_t min_experts, int32_t overlap, int32_t mode, int32_t node,
+                                     uint32_t *experts_out, int32_t cap, int32_t *n_out,
+                                     int32_t *n_shared, int32_t *n_unique);
+B200_API b200_status b200_gguf_write_expert_shard(const b200_gguf *g, const int32_t *expert_ids,
+                                                  int32_t n_ids, const char *dst_path,
+                                                  uint64_t *bytes_written);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,6 +37,7 @@ struct TensorInfo {
     int64_t ne[4] = {1, 1, 1, 1};
     uint64_t offset = 0; // relative to the data section
     uint64_t nbytes = 0; // from type and shape; 0 if the type is not known
+    uint64_t pos_dims = 0, pos_offset = 0; // where the shape and the offset sit in the file
 };
 
 // elements per block and bytes per block of the ggml tensor types
@@ -189,6 +190,9 @@ struct b200_gguf {
     uint64_t file_len = 0, data_start = 0, tensor_info_end = 0;
     uint32_t version = 0, alignment = 32;
     b200_gguf_meta meta;
+    // file position and value type of the two counts a shard writer has to change (0: key absent)
+    uint64_t pos_expert_count = 0, pos_expert_used = 0;
+    uint32_t vt_expert_count = 0, vt_expert_used = 0;
     std::vector<TensorInfo> tensors;
     std::map<std::string, int> index;
 };
@@ -256,8 +260,13 @@ b200_status b200_gguf_open(const char *path, b200_gguf **out) {
         else if (ends_with(key, ".attention.key_length")) { ok = r.as_u32(vt, have, u); if (have) m.key_length = u; }
         else if (ends_with(key, ".attention.value_length")) { ok = r.as_u32(vt, have, u); if (have) m.value_length = u; }
         else if (ends_with(key, ".vocab_size")) { ok = r.as_u32(vt, have, u); if (have) m.vocab_size = u; }
-        else if (ends_with(key, ".expert_used_count")) { ok = r.as_u32(vt, have, u); if (have) m.expert_used_count = u; }
-        else if (ends_with(key, ".expert_count")) { ok = r.as_u32(vt, have, u); if (have) m.expert_count = u; }
+        else if (ends_with(key, ".expert_used_count")) {
+            g->pos_expert_used = r.pos; g->vt_expert_used = vt;
+            ok = r.as_u32(vt, have, u); if (have) m.expert_used_count = u;
+        } else if (ends_with(key, ".expert_count")) {
+            g->pos_expert_count = r.pos; g->vt_expert_count = vt;
+            ok = r.as_u32(vt, have, u); if (have) m.expert_count = u;
+        }
         else if (ends_with(key, ".rope.freq_base")) { ok = r.as_f32(vt, have, f); if (have) m.rope_freq_base = f; }
         else if (ends_with(key, ".rope.scale")) { ok = r.as_f32(vt, have, f); if (have) m.rope_scale = f; }
         else if (ends_with(key, ".attention.layer_norm_rms_epsilon")) { ok = r.as_f32(vt, have, f); if (have) m.rms_epsilon = f; }
@@ -278,6 +287,7 @@ b200_status b200_gguf_open(const char *path, b200_gguf **out) {
         if (!r.str(t.name) || !r.get(t.n_dims)) return bad(r.err.c_str());
         if (t.n_dims > MAX_TENSOR_DIMS) return bad("too many tensor dimensions");
         uint64_t elems = 1;
+        t.pos_dims = r.pos;
         for (uint32_t d = 0; d < t.n_dims; d++) {
             uint64_t ne = 0;
             if (!r.get(ne)) return bad(r.err.c_str());
@@ -286,7 +296,9 @@ b200_status b200_gguf_open(const char *path, b200_gguf **out) {
             if (ne != 0 && elems > (1ull << 62) / ne) return bad("tensor too large");
             elems *= ne;
         }
-        if (!r.get(t.type) || !r.get(t.offset)) return bad(r.err.c_str());
+        if (!r.get(t.type)) return bad(r.err.c_str());
+        t.pos_offset = r.pos;
+        if (!r.get(t.offset)) return bad(r.err.c_str());
         uint32_t blck = 0, bytes = 0;
         if (type_size(t.type, blck, bytes) && t.n_dims > 0 && t.ne[0] % blck == 0) t.nbytes = elems / blck * bytes;
         g->index[t.name] = (int)g->tensors.size();
@@ -465,5 +477,157 @@ b200_status b200_stage_load_gguf(b200_stage *st, const b200_gguf *g, int64_t *n_
     }
     if (n_loaded) *n_loaded = loaded;
     if (bytes_read) *bytes_read = total;
+    return B200_OK;
+}
+
+// ---- expert shards ---------------------------------------------------------------------------
+// Which experts each node of a group holds.  The ranking lists expert ids from the most to the
+// least used.  mode 0 (mesh-llm/src/inference/moe.rs:535-591): the first min_experts are a shared
+// core on every node, the others go round-robin, each to `overlap` consecutive nodes.  mode 1
+// (moe.rs:597-636): shared core of min_experts, the others dealt in snake order.  The node's list
+// comes back sorted, without duplicates.
+b200_status b200_moe_assign(const uint32_t *ranking, int32_t n_expert, int32_t n_nodes, int32_t min_experts,
+                            int32_t overlap, int32_t mode, int32_t node, uint32_t *experts_out, int32_t cap,
+                            int32_t *n_out, int32_t *n_shared, int32_t *n_unique) {
+    KQ_REQUIRE(ranking && experts_out && n_out, "moe_assign: null argument");
+    KQ_REQUIRE(n_expert >= 1 && min_experts >= 0 && (mode == 0 || mode == 1), "moe_assign: bad argument");
+    if (n_nodes < 1) n_nodes = 1;
+    KQ_REQUIRE(node >= 0 && node < n_nodes, "moe_assign: node %d of %d", node, n_nodes);
+    std::vector<uint32_t> mine;
+    int shared = 0, unique = 0;
+    if (n_nodes <= 1 || min_experts >= n_expert) { // one node, or the core covers everything
+        mine.assign(ranking, ranking + n_expert); // in ranking order, as the reference returns it
+        shared = n_expert;
+    } else {
+        mine.assign(ranking, ranking + min_experts);
+        shared = min_experts;
+        const int ov = mode == 0 ? std::max(1, std::min(overlap, n_nodes)) : 1;
+        for (int i = 0; i < n_expert - min_experts; i++) {
+            const uint32_t e = ranking[min_experts + i];
+            if (mode == 0) {
+                for (int j = 0; j < ov; j++)
+                    if ((i + j) % n_nodes == node) { mine.push_back(e); unique++; }
+            } else {
+                const int round = i / n_nodes, pos = i % n_nodes;
+                if ((round % 2 == 0 ? pos : n_nodes - 1 - pos) == node) { mine.push_back(e); unique++; }
+            }
+        }
+        std::sort(mine.begin(), mine.end());
+        mine.erase(std::unique(mine.begin(), mine.end()), mine.end());
+    }
+    KQ_REQUIRE((int)mine.size() <= cap, "moe_assign: %zu experts do not fit the caller's %d slots", mine.size(), cap);
+    for (size_t i = 0; i < mine.size(); i++) experts_out[i] = mine[i];
+    *n_out = (int32_t)mine.size();
+    if (n_shared) *n_shared = shared;
+    if (n_unique) *n_unique = unique;
+    return B200_OK;
+}
+
+namespace {
+bool expert_packed(const std::string &n) { // llama-moe-split: patches/0003 lines 945-955
+    return n.find("ffn_gate_exps") != std::string::npos || n.find("ffn_up_exps") != std::string::npos ||
+           n.find("ffn_down_exps") != std::string::npos || n.find("ffn_gate_inp") != std::string::npos;
+}
+bool copy_range(int fd_in, uint64_t src, int fd_out, uint64_t dst, uint64_t n, std::vector<uint8_t> &buf) {
+    buf.resize(1 << 22);
+    while (n > 0) {
+        const size_t c = (size_t)std::min<uint64_t>(n, buf.size());
+        size_t done = 0;
+        while (done < c) {
+            const ssize_t r = pread(fd_in, buf.data() + done, c - done, (off_t)(src + done));
+            if (r <= 0) return false;
+            done += (size_t)r;
+        }
+        done = 0;
+        while (done < c) {
+            const ssize_t w = pwrite(fd_out, buf.data() + done, c - done, (off_t)(dst + done));
+            if (w <= 0) return false;
+            done += (size_t)w;
+        }
+        src += c;
+        dst += c;
+        n -= c;
+    }
+    return true;
+}
+} // namespace
+
+// Writes a GGUF file that holds the trunk of `src` and only the listed experts: the expert-packed
+// tensors are cut on their last dimension, the rows of the router gate are gathered in the same
+// order, expert_count becomes the number of experts kept and expert_used_count is clamped to it
+// (llama-moe-split, patches/0003 lines 1040-1113 and 1142-1191).  Every other byte of the header is
+// carried over unchanged.
+b200_status b200_gguf_write_expert_shard(const b200_gguf *g, const int32_t *expert_ids, int32_t n_ids,
+                                         const char *dst_path, uint64_t *bytes_written) {
+    KQ_REQUIRE(g && expert_ids && dst_path, "write_expert_shard: null argument");
+    const uint32_t E = g->meta.expert_count;
+    KQ_REQUIRE(E > 1 && g->pos_expert_count != 0, "write_expert_shard: the file is not a mixture-of-experts model");
+    KQ_REQUIRE(n_ids >= 1 && (uint32_t)n_ids <= E, "write_expert_shard: %d experts of %u", n_ids, E);
+    for (int i = 0; i < n_ids; i++) {
+        KQ_REQUIRE(expert_ids[i] >= 0 && (uint32_t)expert_ids[i] < E, "write_expert_shard: expert id %d out of range", expert_ids[i]);
+        for (int j = 0; j < i; j++) KQ_REQUIRE(expert_ids[j] != expert_ids[i], "write_expert_shard: expert id %d listed twice", expert_ids[i]);
+    }
+    auto four_byte_int = [](uint32_t vt) { return vt == V_U32 || vt == V_I32; };
+    KQ_REQUIRE(four_byte_int(g->vt_expert_count) && (g->pos_expert_used == 0 || four_byte_int(g->vt_expert_used)),
+               "write_expert_shard: expert counts are not stored as 32-bit integers");
+    std::vector<uint8_t> head((size_t)g->tensor_info_end);
+    {
+        size_t done = 0;
+        while (done < head.size()) {
+            const ssize_t r = pread(g->fd, head.data() + done, head.size() - done, (off_t)done);
+            KQ_REQUIRE(r > 0, "write_expert_shard: cannot re-read the header");
+            done += (size_t)r;
+        }
+    }
+    auto put32 = [&](uint64_t pos, uint32_t v) { memcpy(head.data() + pos, &v, 4); };
+    auto put64 = [&](uint64_t pos, uint64_t v) { memcpy(head.data() + pos, &v, 8); };
+    put32(g->pos_expert_count, (uint32_t)n_ids);
+    if (g->pos_expert_used) put32(g->pos_expert_used, std::min<uint32_t>(g->meta.expert_used_count, (uint32_t)n_ids));
+
+    struct Plan { uint64_t new_off, new_bytes, per_expert; bool cut; };
+    std::vector<Plan> plan(g->tensors.size());
+    uint64_t off = 0;
+    const uint64_t al = g->alignment;
+    for (size_t i = 0; i < g->tensors.size(); i++) {
+        const TensorInfo &t = g->tensors[i];
+        KQ_REQUIRE(t.nbytes != 0, "write_expert_shard: %s has a type (%u) whose size is not known", t.name.c_str(), t.type);
+        Plan &p = plan[i];
+        const uint32_t ed = t.n_dims ? t.n_dims - 1 : 0;
+        const int64_t ne_last = t.n_dims == 0 ? 1 : (ed < 4 ? t.ne[ed] : 1);
+        p.cut = expert_packed(t.name) && t.n_dims >= 2 && ed < 4 && ne_last == (int64_t)E; // other shapes are copied as they are
+        p.per_expert = p.cut ? t.nbytes / E : 0;
+        p.new_bytes = p.cut ? p.per_expert * (uint64_t)n_ids : t.nbytes;
+        p.new_off = off;
+        off += (p.new_bytes + al - 1) / al * al;
+        put64(t.pos_offset, p.new_off);
+        if (p.cut) put64(t.pos_dims + 8ull * ed, (uint64_t)n_ids);
+    }
+    const int fd = open(dst_path, O_WRONLY | O_CREAT | O_TRUNC | O_CLOEXEC, 0644);
+    if (fd < 0) {
+        kq_set_error("write_expert_shard: cannot create %s: %s", dst_path, strerror(errno));
+        return B200_ERR_INVALID;
+    }
+    std::vector<uint8_t> buf;
+    bool ok = pwrite(fd, head.data(), head.size(), 0) == (ssize_t)head.size();
+    const uint64_t total = g->data_start + off;
+    if (ok) ok = ftruncate(fd, (off_t)total) == 0; // alignment gaps read back as zeros
+    for (size_t i = 0; ok && i < g->tensors.size(); i++) {
+        const TensorInfo &t = g->tensors[i];
+        const Plan &p = plan[i];
+        const uint64_t src = g->data_start + t.offset, dst = g->data_start + p.new_off;
+        if (!p.cut) {
+            ok = copy_range(g->fd, src, fd, dst, t.nbytes, buf);
+        } else {
+            for (int e = 0; ok && e < n_ids; e++)
+                ok = copy_range(g->fd, src + (uint64_t)expert_ids[e] * p.per_expert, fd, dst + (uint64_t)e * p.per_expert,
+                                p.per_expert, buf);
+        }
+    }
+    if (close(fd) != 0) ok = false;
+    if (!ok) {
+        kq_set_error("write_expert_shard: I/O error while writing %s", dst_path);
+        return B200_ERR_INVALID;
+    }
+    if (bytes_written) *bytes_written = total;
     return B200_OK;
 }

@@ -77,3 +77,24 @@ class GgufFile:
         check(lib().b200_gguf_stage_config(self.h, layer_begin, layer_end, n_ctx, n_seq, n_ubatch, device,
                                            C.byref(cfg)))
         return cfg
+
+    def write_expert_shard(self, expert_ids, dst_path):
+        """trunk + the listed experts (router rows gathered, counts rewritten) -> bytes written"""
+        ids = np.ascontiguousarray(expert_ids, dtype=np.int32)
+        n = C.c_uint64()
+        check(lib().b200_gguf_write_expert_shard(self.h, ids.ctypes.data, ids.size, str(dst_path).encode(), C.byref(n)))
+        return n.value
+
+
+def moe_assign(ranking, n_nodes, min_experts, overlap=1, mode=0):
+    """Expert ids per node -> list of dict(experts, n_shared, n_unique); mode 0 = shared core +
+    round-robin with overlap, mode 1 = shared core + snake draft"""
+    rk = np.ascontiguousarray(ranking, dtype=np.uint32)
+    out = []
+    for node in range(max(1, n_nodes)):
+        buf = np.zeros(rk.size, np.uint32)
+        n, ns, nu = C.c_int32(), C.c_int32(), C.c_int32()
+        check(lib().b200_moe_assign(rk.ctypes.data, rk.size, n_nodes, min_experts, overlap, mode, node,
+                                    buf.ctypes.data, buf.size, C.byref(n), C.byref(ns), C.byref(nu)))
+        out.append(dict(experts=buf[: n.value].tolist(), n_shared=ns.value, n_unique=nu.value))
+    return out

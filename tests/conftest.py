@@ -10,6 +10,8 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+    # importing the image's gguf package pulls in SWIG-built modules that warn at import time
+    config.addinivalue_line("filterwarnings", "ignore:builtin type .* has no __module__ attribute:DeprecationWarning")
 
 
 def pytest_collection_modifyitems(config, items):

@@ -91,3 +91,31 @@ def test_missing_tensor_and_unsupported_type_are_reported(tmp_path):
     with GgufFile(path2) as g:
         with pytest.raises(B200Error, match="has no tensor"):
             Stage.from_gguf(g, n_ctx=64, n_ubatch=16)
+
+
+def test_expert_shard_stage_matches_oracle_on_the_same_shard(tmp_path):
+    """A shard file written by the library, loaded as a stage, against the CPU oracle holding the same
+    experts (router rows gathered in the same order): the shard is a complete model of its own."""
+    m, path = make(tmp_path, MOE, "qwen3moe")
+    ids = [5, 0, 3, 6]
+    shard_path = tmp_path / "shard.gguf"
+    with GgufFile(path) as g:
+        g.write_expert_shard(ids, shard_path)
+    cfg = dict(MOE, n_expert=len(ids), n_expert_used=min(MOE["n_expert_used"], len(ids)))
+    ref = orc.Model(**cfg)
+    for name in m.tensor_names():
+        ty, data, ne = m.tensor(name)
+        if any(k in name for k in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps", "ffn_gate_inp")):
+            per = data.size // MOE["n_expert"]
+            data = np.concatenate([data[e * per:(e + 1) * per] for e in ids])
+        ref.set_tensor(name, ty, data)
+    with GgufFile(shard_path) as s:
+        st, n_loaded, _ = Stage.from_gguf(s, n_ctx=MOE["n_ctx"], n_ubatch=32)
+    assert st.cfg.n_expert == 4 and st.cfg.n_expert_used == 2 and n_loaded == len(m.tensor_names())
+    toks = np.random.default_rng(4).integers(0, MOE["n_vocab"], 13).astype(np.int32)
+    hid = torch.empty((13, MOE["n_embd"]), device="cuda")
+    _, lg, _ = st.forward(tokens=torch.from_numpy(toks).cuda(), all_logits=True, hidden_out=hid)
+    href, lref = ref.forward(tokens=toks)
+    err = np.abs(hid.cpu().numpy() - href).max(-1) / np.abs(href).max()
+    assert np.median(err) <= 1e-5 and err.max() <= 1e-2
+    assert (lg.cpu().numpy().argmax(-1) == lref.argmax(-1)).mean() >= 0.9
