@@ -5,6 +5,11 @@
 #include "kq_common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
+
+b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
+                                     const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd, int64_t seq_stride,
+                                     float *out, cudaStream_t st);
 
 namespace {
 
@@ -426,6 +431,16 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
     KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
     KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
     const int rows = n_seq * T, G = n_head / n_kv;
+    // batches of new tokens go to the tensor-core kernel (B200_ATTN_MMA=0 keeps the per-row kernel)
+    static int use_mma = -1;
+    if (use_mma < 0) {
+        const char *v = getenv("B200_ATTN_MMA");
+        use_mma = !(v && v[0] == '0');
+    }
+    if (use_mma && T >= 32 && force_splits <= 0) {
+        const b200_status rc = kq_attention_prefill_mma(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, st);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+    }
     int n_split = force_splits > 0 ? force_splits : kq_attention_splits(rows, n_kv, pos0 + T);
     const size_t need = (size_t)rows * n_head * n_split * (hd + 2) * sizeof(float);
     if (n_split > 1 && need > scratch_bytes) n_split = 1;

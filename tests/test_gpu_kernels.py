@@ -190,7 +190,7 @@ def test_rms_norm_rope_swiglu_add(ops):
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(40, 8, 128), (16, 2, 128), (8, 2, 64), (4, 4, 128), (32, 4, 128)])
-@pytest.mark.parametrize("pos0,T", [(0, 1), (300, 1), (2047, 1), (0, 37), (100, 5)])
+@pytest.mark.parametrize("pos0,T", [(0, 1), (300, 1), (2047, 1), (0, 37), (100, 5), (70, 64), (333, 130)])
 def test_attention_matches_oracle(ops, nh, nkv, hd, pos0, T):
     import torch
 
@@ -204,7 +204,11 @@ def test_attention_matches_oracle(ops, nh, nkv, hd, pos0, T):
     out = ops.attention(torch.from_numpy(q).cuda(),
                         torch.from_numpy(kc.view(np.float16)).cuda(),
                         torch.from_numpy(vc.view(np.float16)).cuda(), pos0).cpu().numpy()
-    assert rel_err(out, ref) <= 1e-4
+    # batches of 32 and more rows with head_dim 128 run on the tensor cores with q and the
+    # probabilities rounded to f16 (f32 accumulation): tolerance 1e-3 of max|ref| there, 1e-4 elsewhere
+    err = rel_err(out, ref)
+    print(f"attention nh={nh} nkv={nkv} hd={hd} pos0={pos0} T={T}: rel err {err:.2e}")
+    assert err <= (1e-3 if (T >= 32 and hd == 128) else 1e-4)
 
 
 @pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])

@@ -159,6 +159,22 @@ def test_prefill_small_batch_path_and_ubatches():
     assert kl < 1e-4 and rel_err(got, ref) < 5e-2
 
 
+def test_long_prefill_batch_on_the_tensor_core_paths():
+    """A batch of 80 tokens in two ubatches: the tcgen05 GEMM and the tensor-core attention (batches of
+    32 and more rows, q and probabilities in f16) against the oracle, by KL and top-1 of the logits."""
+    import torch
+
+    m, st = make_pair(dict(DENSE, n_ctx=160), 14, n_ubatch=64)
+    toks = np.random.default_rng(3).integers(0, 2048, 80).astype(np.int32)
+    _, ref = m.forward(tokens=toks)
+    _, l0, _ = st.forward(tokens=torch.from_numpy(toks[:64]).cuda(), all_logits=True)
+    _, l1, _ = st.forward(tokens=torch.from_numpy(toks[64:]).cuda(), pos0=64, all_logits=True)  # 16 rows: per-row kernel
+    got = np.concatenate([l0.cpu().numpy(), l1.cpu().numpy()])
+    kl, top1 = kl_top1(got, ref)
+    print(f"80-token prefill: rel {rel_err(got, ref):.2e} KL {kl:.3e} top1 {top1:.3f}")
+    assert kl < 1e-4 and top1 >= 0.95 and rel_err(got, ref) < 5e-2
+
+
 def test_two_stages_token_identical_to_one_stage():
     import torch
     from mesh_llm_b200.stage import Stage
