@@ -352,6 +352,18 @@ B200_API b200_status b200_gguf_write_expert_shard(const b200_gguf *g, const int3
                                                   int32_t n_ids, const char *dst_path,
                                                   uint64_t *bytes_written);
 
+/* ---- worker front end: the ggml RPC wire protocol (version 4.1) served from this backend ------
+ * What mesh-llm spawns as `rpc-server -d DEV -p PORT --gguf PATH` (mesh-llm/src/inference/launch.rs:
+ * 887-933).  Commands and packed messages as in third_party/llama.cpp/patches/0002 lines 1042-1146
+ * and patches/0001 lines 49-63; REGISTER_PEER / PUSH_TENSOR_TO_PEER / PEER_TENSOR_DATA as in
+ * patches/0002 lines 544-735 (a push between two devices of one server is a single NVLink copy).
+ * port 0 picks a free port.  The server runs on its own threads until it is stopped.              */
+typedef struct b200_rpc_server b200_rpc_server;
+B200_API b200_status b200_rpc_server_start(const char *host, int32_t port, const char *gguf_path,
+                                           b200_rpc_server **out);
+B200_API int32_t b200_rpc_server_port(const b200_rpc_server *srv);
+B200_API void b200_rpc_server_stop(b200_rpc_server *srv);
+
 #ifdef __cplusplus
 }
 #endif

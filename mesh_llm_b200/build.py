@@ -16,6 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 SO = os.path.join(HERE, "libb200kq.so")
+RPC_EXE = os.path.join(HERE, "b200-rpc-server")
+MAIN_SOURCES = ("kq_rpc_main.cu",)  # executables, not part of the library
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -65,12 +67,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, sources()))
+    mains = [o for o in objs if os.path.basename(o)[:-2] in MAIN_SOURCES]
+    objs = [o for o in objs if o not in mains]
     cmd = [nvcc, "-shared", "-o", SO, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
            "-ccbin", "/usr/bin/g++", "-cudart", "static"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")
+    # the worker executable carries the library's objects, so it runs without a library path
+    cmd = [nvcc, "-o", RPC_EXE, *mains, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+           "-ccbin", "/usr/bin/g++", "-cudart", "static", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("link of b200-rpc-server failed")
     return SO
 
 

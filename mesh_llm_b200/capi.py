@@ -149,6 +149,9 @@ SIGNATURES = {
     "b200_gguf_byte_profile": (i32, [vp, C.POINTER(GgufByteProfile)]),
     "b200_gguf_stage_config": (i32, [vp, i32, i32, i32, i32, i32, i32, C.POINTER(StageConfig)]),
     "b200_stage_load_gguf": (i32, [vp, vp, C.POINTER(i64), C.POINTER(i64)]),
+    "b200_rpc_server_start": (i32, [C.c_char_p, i32, C.c_char_p, C.POINTER(vp)]),
+    "b200_rpc_server_port": (i32, [vp]),
+    "b200_rpc_server_stop": (None, [vp]),
     "b200_moe_assign": (i32, [vp, i32, i32, i32, i32, i32, i32, vp, i32, C.POINTER(i32), C.POINTER(i32),
                               C.POINTER(i32)]),
     "b200_gguf_write_expert_shard": (i32, [vp, vp, i32, C.c_char_p, C.POINTER(u64)]),
