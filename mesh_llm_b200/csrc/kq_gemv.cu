@@ -293,9 +293,18 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
                                  segs[0].n_rows == segs[1].n_rows),
                "gemv: swiglu needs two equal segments");
     KQ_REQUIRE(!residual || nseg == 1, "gemv: residual only with one segment");
-    if (!(ind && ind->expert_ids) && M <= 2 && K % 256 == 0) {
+    if (!(ind && ind->expert_ids) && K % 256 == 0) { // M <= 2: streaming kernel; 3..8 tokens of Q4_K: its tensor-core form
         const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, prep, st);
         if (rs != B200_ERR_UNSUPPORTED) return rs;
+        if (M > 2 && nseg > 1 && !swiglu_pairs && !(prep && prep->x)) {
+            // a fused projection of mixed types: its Q4_K matrices still take the tensor-core form,
+            // the others the plain kernel below
+            KqGemvSeg a[3], b[3];
+            int na = 0, nb_ = 0;
+            for (int i = 0; i < nseg; i++) (segs[i].type == B200_TYPE_Q4_K ? a[na++] : b[nb_++]) = segs[i];
+            if (na > 0 && nb_ > 0 && kq_launch_gemv_stream(a, na, q, d, bs, M, K, nullptr, 0, nullptr, st) == B200_OK)
+                return kq_launch_gemv(b, nb_, q, d, bs, M, K, nullptr, 0, nullptr, st, nullptr);
+        }
     }
     if (prep && prep->x) {
         // the plain kernel wants quantised activations: prepare them into the caller's scratch

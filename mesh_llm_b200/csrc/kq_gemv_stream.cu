@@ -41,6 +41,7 @@ constexpr int ACT_BLK = 272; // 256 int8 codes + 16 bytes of padding
 // read with single 64-bit accesses, so publishing needs no fence and collecting costs one round
 // trip to L2.  The collector clears the entry after reading it.
 __device__ unsigned long long g_partials[MAX_UNITS][16];
+__device__ unsigned long long g_partials8[MAX_UNITS][64]; // the same for the 8-token kernel: [row][token]
 __device__ int g_stream_error; // 0 ok, 1 mbarrier wait gave up, 2 partial-sum wait gave up
 
 #ifndef KQ_GEMV_WARPS
@@ -82,6 +83,7 @@ struct StreamParams {
     int32_t rg_end[3];
     int32_t nseg, n_rg, nb, K, nsteps, swiglu;
     int32_t ns; // ring depth per warp
+    int32_t m_actual; // tokens really present (the 8-token kernel pads the rest with zeros)
     const int8_t *aq;
     const float *ad;
     const int16_t *abs16;
@@ -329,6 +331,162 @@ __device__ __forceinline__ void block_q6k(const uint8_t *grp, int g, int bl, con
     }
 }
 
+// ---- 3 to 8 tokens: the integer dot products on the tensor cores --------------------------------
+// With several tokens the dp4a work per weight byte grows with the token count and the kernel turns
+// issue-bound; mma.m16n8k32 (u8 x s8 -> s32) does the 32-element sub-block products of 8 weight rows
+// against 8 tokens in one instruction.  A warp works through the blocks of its unit one at a time:
+// lane (r, t) = (lane / 4, lane % 4) holds row r; the nibbles of 8 consecutive bytes of a 32-byte
+// group are its A fragments for the two sub-blocks of that group (elements 8t .. 8t+7; the same
+// permutation of k is used for the activation fragments, so the sums are unchanged), rows 8..15 of
+// the tile are zero.  The accumulators come back as (row r, tokens 2t, 2t+1); the 6-bit scales, the
+// min term and the f32 combination are the decode kernel's, so results are identical token by token.
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <uint32_t TYPE, int M>
+__device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *smem, int act_tok, int act_q, int act_s,
+                                          const uint8_t *ring, uint32_t ring_addr, uint32_t bar_addr, Issuer<TYPE> &iss,
+                                          int count, int64_t begin, int unit, int n_units, int64_t total,
+                                          volatile int *s_abort) {
+    using F = Fmt<TYPE>;
+    static_assert(TYPE == B200_TYPE_Q4_K, "the tensor-core batch path is built for Q4_K");
+    const int lane = threadIdx.x & 31, r = lane >> 2, t = lane & 3, nb = p.nb;
+    const int tokB = lane >> 2;                       // token whose activations this lane feeds to the MMA
+    const bool tokB_ok = tokB < M;                     // M = tokens staged in shared memory (4 or 8)
+    const uint8_t *actB = smem + (tokB_ok ? tokB : 0) * act_tok;
+    const int tok0 = 2 * t, tok1 = 2 * t + 1;         // tokens of this lane's accumulators
+    const uint8_t *act0 = smem + (tok0 < M ? tok0 : 0) * act_tok, *act1 = smem + (tok1 < M ? tok1 : 0) * act_tok;
+    float acc0 = 0.f, acc1 = 0.f;
+    int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
+    for (int j = 0; j < count; j++) {
+        const int slot = j % p.ns;
+        wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), s_abort);
+        const uint8_t *rowp = ring + (size_t)slot * F::SLOT + r * F::PITCH;
+        const int kbn = min(F::KB, nb - ks * F::KB);
+        for (int kb = 0; kb < kbn; kb++) {
+            const int blk = ks * F::KB + kb;
+            const uint8_t *b = rowp + kb * KQ_Q4K_BYTES;
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(b);
+            const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, m_lo = hdr.z & 0x3F3F3F3Fu;
+            const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+            const uint32_t m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+            const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+            int is0 = 0, is1 = 0;
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                const uint2 w = *reinterpret_cast<const uint2 *>(b + 16 + 32 * g + 8 * t);
+                uint2 x0 = make_uint2(0u, 0u), x1 = make_uint2(0u, 0u);
+                if (tokB_ok) {
+                    x0 = *reinterpret_cast<const uint2 *>(actB + blk * ACT_BLK + 64 * g + 8 * t);
+                    x1 = *reinterpret_cast<const uint2 *>(actB + blk * ACT_BLK + 64 * g + 32 + 8 * t);
+                }
+                const uint32_t scw = g < 2 ? sc_lo : sc_hi;
+                const int s_even = (int)((scw >> (16 * (g & 1))) & 0xFF), s_odd = (int)((scw >> (16 * (g & 1) + 8)) & 0xFF);
+                int c[4] = {0, 0, 0, 0};
+                mma_u8s8(c, w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, x0.x, x0.y); // sub-block 2g
+                is0 += s_even * c[0];
+                is1 += s_even * c[1];
+                int e[4] = {0, 0, 0, 0};
+                mma_u8s8(e, (w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, x1.x, x1.y); // sub-block 2g + 1
+                is0 += s_odd * e[0];
+                is1 += s_odd * e[1];
+            }
+            // min term sum_j m_j * (sum of the 32 codes of sub-block j), per token
+            const int4 q0 = *reinterpret_cast<const int4 *>(act0 + act_q + blk * 16);
+            const int4 q1 = *reinterpret_cast<const int4 *>(act1 + act_q + blk * 16);
+            const uint32_t mw[4] = {__byte_perm(m_lo, 0, 0x4140), __byte_perm(m_lo, 0, 0x4342), __byte_perm(m_hi, 0, 0x4140),
+                                    __byte_perm(m_hi, 0, 0x4342)}; // m_j pairs as 16-bit lanes
+            auto dot16 = [](int x, uint32_t y) { return (int)(int16_t)(x & 0xFFFF) * (int)(y & 0xFFFF) + (x >> 16) * (int)(y >> 16); };
+            const int mn0 = dot16(q0.x, mw[0]) + dot16(q0.y, mw[1]) + dot16(q0.z, mw[2]) + dot16(q0.w, mw[3]);
+            const int mn1 = dot16(q1.x, mw[0]) + dot16(q1.y, mw[1]) + dot16(q1.z, mw[2]) + dot16(q1.w, mw[3]);
+            const float da0 = reinterpret_cast<const float *>(act0 + act_q + act_s)[blk];
+            const float da1 = reinterpret_cast<const float *>(act1 + act_q + act_s)[blk];
+            acc0 = fmaf(da0, dd.x * (float)is0 - dd.y * (float)mn0, acc0);
+            acc1 = fmaf(da1, dd.x * (float)is1 - dd.y * (float)mn1, acc1);
+        }
+        __syncwarp();
+        if (j + p.ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
+        const bool last_slice = ks == p.nsteps - 1, last_unit = j == count - 1;
+        if (last_slice || last_unit) {
+            float v0 = acc0, v1 = acc1;
+            acc0 = acc1 = 0.f;
+            const int64_t rg_first = (int64_t)rg * p.nsteps;
+            if (rg_first < begin) { // the head of this row group belongs to an earlier warp
+                *(volatile unsigned long long *)&g_partials8[unit][r * 8 + tok0] = (unsigned long long)__float_as_uint(v0) | (1ull << 32);
+                *(volatile unsigned long long *)&g_partials8[unit][r * 8 + tok1] = (unsigned long long)__float_as_uint(v1) | (1ull << 32);
+            } else {
+                if (!last_slice) { // later warps hold the tail: every lane collects its own two entries, in unit order
+                    const int64_t rg_last = rg_first + p.nsteps;
+                    for (int u2 = unit + 1; u2 < n_units; u2++) {
+                        const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                        if (b2 >= rg_last) break;
+                        if (e2 <= b2) continue;
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            volatile unsigned long long *e = &g_partials8[u2][r * 8 + tok0 + i];
+                            unsigned long long wv = 0;
+                            bool ok = false;
+                            const uint64_t t0 = kq_globaltimer_ns();
+                            while (true) {
+                                wv = *e;
+                                ok = (wv >> 32) != 0;
+                                if (ok || *s_abort || kq_globaltimer_ns() - t0 > KQ_WAIT_LIMIT_NS) break;
+                                __nanosleep(64);
+                            }
+                            if (!ok && !*s_abort) {
+                                *s_abort = 1;
+                                atomicExch(&g_stream_error, 2);
+                            }
+                            *e = 0ull;
+                            (i == 0 ? v0 : v1) += __uint_as_float((uint32_t)wv);
+                        }
+                    }
+                }
+                int seg, row0;
+                locate<TYPE>(p, rg, seg, row0);
+                if (p.swiglu) { // rows 0..3 of the tile are gate rows, rows 4..7 the same rows of the up matrix
+                    const float u0 = __shfl_down_sync(0xffffffffu, v0, 16), u1 = __shfl_down_sync(0xffffffffu, v1, 16);
+                    const int row = row0 + r;
+                    if (r < F::ROWS / 2 && row < p.seg[0].n_rows) {
+                        const float bg = p.seg[0].bias ? p.seg[0].bias[row] : 0.f, bu = p.seg[1].bias ? p.seg[1].bias[row] : 0.f;
+                        if (tok0 < p.m_actual) {
+                            const float gt = v0 + bg;
+                            p.seg[0].y[(int64_t)tok0 * p.seg[0].ldy + row] = (gt / (1.0f + expf(-gt))) * (u0 + bu);
+                        }
+                        if (tok1 < p.m_actual) {
+                            const float gt = v1 + bg;
+                            p.seg[0].y[(int64_t)tok1 * p.seg[0].ldy + row] = (gt / (1.0f + expf(-gt))) * (u1 + bu);
+                        }
+                    }
+                } else {
+                    const KqGemvSeg &sg = p.seg[seg];
+                    const int row = row0 + r;
+                    if (row < sg.n_rows) {
+                        const float bb = sg.bias ? sg.bias[row] : 0.f;
+                        if (tok0 < p.m_actual) {
+                            float x = v0 + bb;
+                            if (p.residual) x += p.residual[(int64_t)tok0 * sg.ldy + row];
+                            sg.y[(int64_t)tok0 * sg.ldy + row] = x;
+                        }
+                        if (tok1 < p.m_actual) {
+                            float x = v1 + bb;
+                            if (p.residual) x += p.residual[(int64_t)tok1 * sg.ldy + row];
+                            sg.y[(int64_t)tok1 * sg.ldy + row] = x;
+                        }
+                    }
+                }
+            }
+        }
+        if (++ks == p.nsteps) {
+            ks = 0;
+            rg++;
+        }
+    }
+}
+
 template <uint32_t TYPE, int M>
 __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM) gemv_block_kernel(const StreamParams p) {
     using F = Fmt<TYPE>;
@@ -355,7 +513,9 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     // ---- shared memory: per token [padded int8 codes][int16 sums][f32 scales], then rings, then mbarriers
     constexpr int SUMS = TYPE == B200_TYPE_Q4_K ? 16 : 32; // bytes of sums per block
     const int act_q = (nb * ACT_BLK + 127) & ~127, act_s = (nb * SUMS + 127) & ~127, act_d = (nb * 4 + 127) & ~127;
-    const int act_tok = act_q + act_s + act_d;
+    // 8-token kernel: tokens 32 bytes apart modulo 128, so that the B-fragment loads of the eight
+    // token lanes of a warp fall on different banks
+    const int act_tok = act_q + act_s + act_d + (M > 2 ? 32 : 0);
     uint8_t *ring = smem + M * act_tok + (size_t)warp * p.ns * F::SLOT;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + M * act_tok + (size_t)WARPS * p.ns * F::SLOT) + warp * p.ns;
     if (threadIdx.x == 0) s_abort = 0;
@@ -498,6 +658,11 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     } else {
         for (int m = 0; m < M; m++) {
             uint8_t *tq = smem + m * act_tok;
+            if (M > 2 && m >= p.m_actual) { // padding token: all-zero codes, sums and scales
+                for (int i = threadIdx.x * 16; i < act_tok - 32; i += WARPS * 32 * 16)
+                    *reinterpret_cast<int4 *>(tq + i) = make_int4(0, 0, 0, 0);
+                continue;
+            }
             const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.K);
             const int16_t *b16 = p.abs16 + (int64_t)m * nb * 16;
             const int n16 = nb * 16;
@@ -535,6 +700,11 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     __syncthreads();
     TRACE_MARK(3);
     if (count <= 0) return;
+    if constexpr (M > 2) {
+        mma_units<TYPE, M>(p, smem, act_tok, act_q, act_s, ring, ring_addr, bar_addr, iss, count, begin, unit, n_units, total,
+                           &s_abort);
+        return;
+    }
 
     float acc[M];
 #pragma unroll
@@ -672,7 +842,8 @@ int env_int2(const char *name, int dflt) {
 
 template <uint32_t TYPE, int M>
 b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
-                         int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st) {
+                         int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st,
+                         int m_actual = M) {
     using F = Fmt<TYPE>;
     StreamParams p = {};
     const int rows_per_rg = swiglu_pairs ? F::ROWS / 2 : F::ROWS;
@@ -699,7 +870,9 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
         p.do_norm = prep->do_norm;
     }
     const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
-    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127);
+    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) +
+                        (M > 2 ? 32 : 0);
+    p.m_actual = m_actual;
     constexpr int WARPS = F::WARPS;
     int cap = F::SMEM_CAP;
     if (M * act_tok + WARPS * F::SLOT + 1024 > cap) cap = 216 * 1024; // long rows: take the whole SM
@@ -752,7 +925,34 @@ int kq_stream_error_fetch() {
 b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                                   const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
                                   const KqActPrep *prep, cudaStream_t st) {
-    if (M < 1 || M > 2 || K % 256 != 0 || env_int2("B200_GEMV_STREAM", 1) == 0) return B200_ERR_UNSUPPORTED;
+    if (M < 1 || M > 8 || K % 256 != 0 || env_int2("B200_GEMV_STREAM", 1) == 0) return B200_ERR_UNSUPPORTED;
+    if (M > 2) {
+        // 3..8 tokens: the tensor-core kernel, Q4_K only, on activations that are already quantised.
+        // It stages 8 tokens when they fit in shared memory next to the ring, else 4 at a time (the
+        // matrix is then streamed once per group of 4 tokens).
+        if ((prep && prep->x) || env_int2("B200_GEMV_MMA", 1) == 0) return B200_ERR_UNSUPPORTED;
+        for (int i = 0; i < nseg; i++)
+            if (segs[i].type != B200_TYPE_Q4_K || ((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;
+        if ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0) return B200_ERR_UNSUPPORTED;
+        if (M > 4) {
+            const b200_status rc = launch_block<B200_TYPE_Q4_K, 8>(segs, nseg, q, d, bs, K, residual, swiglu_pairs, nullptr, st, M);
+            if (rc != B200_ERR_UNSUPPORTED) return rc;
+        }
+        const int64_t nb = K / 256;
+        for (int m0 = 0; m0 < M; m0 += 4) {
+            KqGemvSeg sh[3];
+            for (int i = 0; i < nseg; i++) {
+                sh[i] = segs[i];
+                sh[i].y = segs[i].y + (int64_t)m0 * segs[i].ldy;
+            }
+            const int mc = M - m0 < 4 ? M - m0 : 4;
+            const b200_status rc = launch_block<B200_TYPE_Q4_K, 4>(sh, nseg, q + (int64_t)m0 * K, d + m0 * nb, bs + m0 * nb * 16, K,
+                                                                   residual ? residual + (int64_t)m0 * segs[0].ldy : nullptr,
+                                                                   swiglu_pairs, nullptr, st, mc);
+            if (rc != B200_OK) return m0 == 0 ? rc : B200_ERR_INVALID; // nothing written yet only for the first group
+        }
+        return B200_OK;
+    }
     for (int i = 0; i < nseg; i++) {
         if (segs[i].type != B200_TYPE_Q4_K && segs[i].type != B200_TYPE_Q6_K) return B200_ERR_UNSUPPORTED;
         if (((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;

@@ -121,6 +121,27 @@ def test_gemv_random_blocks_and_split_k(ops, ty, monkeypatch):
     np.testing.assert_array_equal(again, outs[-1])
 
 
+@pytest.mark.parametrize("M", [3, 5, 8])
+@pytest.mark.parametrize("N,K", [(96, 27648), (200, 5120), (40, 256)])
+def test_gemv_batch_tensor_core_form(ops, M, N, K, monkeypatch):
+    """3..8 tokens of Q4_K run the integer products on mma.m16n8k32; long rows are staged four tokens
+    at a time.  Same integers, same f32 combination as the plain kernel: compared with the oracle and,
+    bit for bit, with the plain kernel's per-token result order (token-wise identical sums)."""
+    import torch
+
+    W = _weights(orc.TYPE_Q4_K, N, K, 16, random_bytes=True)
+    x = np.random.default_rng(17 + M).standard_normal((M, K)).astype(np.float32)
+    ref = orc.mul_mat(orc.TYPE_Q4_K, W, x, N, K)
+    dev = ops.upload_weights(orc.TYPE_Q4_K, W, N, K)
+    xd = torch.from_numpy(x).cuda()
+    y = ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy()
+    assert rel_err(y, ref) <= REL
+    np.testing.assert_array_equal(ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy(), y)  # deterministic
+    monkeypatch.setenv("B200_GEMV_MMA", "0")
+    plain = ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy()
+    assert rel_err(plain, ref) <= REL and rel_err(y, plain) <= 1e-5
+
+
 @pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
 def test_gemv_fused_bias_residual(ops, ty):
     import torch
