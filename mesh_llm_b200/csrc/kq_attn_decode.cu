@@ -7,7 +7,15 @@
 // hundred long ones.
 #include "kq_common.cuh"
 
+#include <cuda.h> // CUtensorMap
 #include <math.h>
+#include <string.h>
+
+#include <map>
+#include <tuple>
+
+b200_status kq_tmap_encode(void *map128, int elem_bytes, int rank, const void *base, const uint64_t *dims,
+                           const uint64_t *strides_bytes, const uint32_t *box, int swizzle128);
 
 namespace {
 
@@ -21,23 +29,37 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 
 // grid (n_kv, n_split, n_seq), 4 * G warps: warp (ti, g) serves query head kh * G + g on rows
 // ti*32 .. ti*32+31 of the CTA's current 128-row chunk.  The K and V rows of a chunk are brought
-// into shared memory by bulk asynchronous copies (one 2*HD-byte run per row and tensor), issued for
-// the first chunk before the kernel waits for its predecessor -- rows of earlier positions do not
-// depend on it.  Row pitch HD*2 + 16 bytes keeps the per-lane 16-byte reads of K on distinct banks.
+// into shared memory by tiled TMA copies out of the cache viewed as [seq][position][kv head][dim]:
+// one box of 128 rows x 64 dims (128 bytes) per instruction, with the 128-byte swizzle, so that the
+// per-lane 16-byte reads of K (lane = row) fall on distinct banks; the copies of the first chunk are
+// issued before the kernel waits for its predecessor -- rows of earlier positions do not depend on
+// it.  The row of the new position is computed here and overwrites its (stale) copy in the chunk.
 constexpr int ROWS_PER_CTA = 128;
 
+// byte offset of 16-byte chunk c of row r inside a 128-row x 128-byte box with the 128-byte swizzle
+__device__ __forceinline__ int sw_off(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+constexpr int BOX_BYTES = ROWS_PER_CTA * 128;
+// address of the half at (row, dim) of a swizzled chunk made of HD/64 boxes
+__device__ __forceinline__ uint8_t *sw_elem(uint8_t *base, int row, int dim) {
+    const int byte = dim * 2, box = byte >> 7, off = byte & 127;
+    return base + box * BOX_BYTES + sw_off(row, off >> 4) + (off & 15);
+}
+
 template <int HD, int G>
-__global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__restrict__ q, const float *__restrict__ k_new,
+__global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                              const __grid_constant__ CUtensorMap vmap,
+                                                              const float *__restrict__ q, const float *__restrict__ k_new,
                                                               const float *__restrict__ v_new, __half *kc, __half *vc,
                                                               const int32_t *pos_dev, int pos_val, int n_head, int n_kv,
                                                               int64_t seq_stride, int n_split, float scale, int neox,
                                                               RopeTab tab, float *out, float *part_o, float *part_ml,
                                                               int *counters) {
     KQ_PDL_TRIGGER();
-    constexpr int DPL = HD / 32, HALF = HD / 2, PITCH = HD * 2 + 16, NT = 128 * G;
-    extern __shared__ __align__(128) uint8_t dsm[];
-    uint8_t *k_s = dsm, *v_s = dsm + ROWS_PER_CTA * PITCH;
-    float (*o_s)[G][HD] = reinterpret_cast<float (*)[G][HD]>(dsm + 2 * ROWS_PER_CTA * PITCH); // [4][G][HD]
+    constexpr int DPL = HD / 32, HALF = HD / 2, NBOX = HD / 64, NT = 128 * G;
+    extern __shared__ __align__(1024) uint8_t dsm_raw[];
+    uint8_t *dsm = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u); // swizzled boxes start on 1 KB
+    uint8_t *k_s = dsm, *v_s = dsm + NBOX * BOX_BYTES;
+    float (*o_s)[G][HD] = reinterpret_cast<float (*)[G][HD]>(dsm + 2 * NBOX * BOX_BYTES); // [4][G][HD]
     __shared__ float q_s[G][HD];
     __shared__ float p_s[4 * G][32];
     __shared__ float ml_s[4][G][2];
@@ -73,21 +95,19 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
     for (int cb = p_begin; cb < p_end || first; cb += ROWS_PER_CTA) {
         const int ccnt = max(0, min(ROWS_PER_CTA, p_end - cb));
         const bool has_new = pos >= cb && pos < cb + ccnt;
-        const int n_copy = ccnt - (has_new ? 1 : 0);
-        if (n_copy > 0) { // the row of the new position is not in the cache yet
-            if (threadIdx.x == 0)
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(n_copy * 4 * HD)
+        if (ccnt > 0 && threadIdx.x == 0) {
+            // whole boxes always: rows past the context arrive as zeros, rows not yet written are never read
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(2 * NBOX * BOX_BYTES) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+            for (int bx = 0; bx < NBOX; bx++) {
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(k_s + bx * BOX_BYTES)),
+                             "l"(&kmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
                              : "memory");
-            __syncthreads();
-            const int r = threadIdx.x, p = cb + r;
-            if (r < ccnt && p != pos) {
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(k_s + r * PITCH)),
-                             "l"(kbase + p * pstride), "r"(2 * HD), "r"(bar_a)
-                             : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(v_s + r * PITCH)),
-                             "l"(vbase + p * pstride), "r"(2 * HD), "r"(bar_a)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(v_s + bx * BOX_BYTES)),
+                             "l"(&vmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
                              : "memory");
             }
         }
@@ -105,32 +125,8 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
                 }
             first = false;
         }
-        if (has_new) {
-            // rotate k, round k and v to f16 as later steps will read them, into the chunk and the cache
-            const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
-            const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
-            __half *kt = reinterpret_cast<__half *>(k_s + (pos - cb) * PITCH);
-            __half *vt = reinterpret_cast<__half *>(v_s + (pos - cb) * PITCH);
-            for (int f = threadIdx.x; f < HALF; f += NT) {
-                const float ang = (float)pos * tab.inv_freq[f];
-                const float c = cosf(ang), sn = sinf(ang);
-                const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
-                const float a = kv[i0], b = kv[i1];
-                const __half r0 = __float2half_rn(a * c - b * sn), r1 = __float2half_rn(a * sn + b * c);
-                kt[i0] = r0;
-                kt[i1] = r1;
-                kbase[pos * pstride + i0] = r0;
-                kbase[pos * pstride + i1] = r1;
-            }
-            for (int i = threadIdx.x; i < HD; i += NT) {
-                const __half r = __float2half_rn(vv[i]);
-                vt[i] = r;
-                vbase[pos * pstride + i] = r;
-            }
-        }
-        __syncthreads();
-        if (ccnt == 0) break;
-        if (n_copy > 0) { // bounded wait for the chunk
+        if (ccnt == 0) break; // CTA-uniform: an empty slice only takes part in the combine below
+        { // bounded wait for the chunk
             const bool ok = s_abort ? false : kq_mbar_wait(bar_a, phase, KQ_WAIT_LIMIT_NS);
             if (!ok && !s_abort) {
                 s_abort = 1;
@@ -138,16 +134,40 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
             }
             phase ^= 1;
         }
+        if (has_new) {
+            // rotate k, round k and v to f16 as later steps will read them, into the cache and over the
+            // stale copy of that row in the chunk
+            const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
+            const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
+            const int rr = pos - cb;
+            for (int f = threadIdx.x; f < HALF; f += NT) {
+                const float ang = (float)pos * tab.inv_freq[f];
+                const float c = cosf(ang), sn = sinf(ang);
+                const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
+                const float a = kv[i0], b = kv[i1];
+                const __half r0 = __float2half_rn(a * c - b * sn), r1 = __float2half_rn(a * sn + b * c);
+                *reinterpret_cast<__half *>(sw_elem(k_s, rr, i0)) = r0;
+                *reinterpret_cast<__half *>(sw_elem(k_s, rr, i1)) = r1;
+                kbase[pos * pstride + i0] = r0;
+                kbase[pos * pstride + i1] = r1;
+            }
+            for (int i = threadIdx.x; i < HD; i += NT) {
+                const __half r = __float2half_rn(vv[i]);
+                *reinterpret_cast<__half *>(sw_elem(v_s, rr, i)) = r;
+                vbase[pos * pstride + i] = r;
+            }
+        }
+        __syncthreads();
         // this warp's tile: rows ti*32 .. +31 of the chunk, lane = position
         const int cnt = max(0, min(32, ccnt - ti * 32));
         if (cnt > 0) {
             const bool valid = lane < cnt;
             float sc = 0.f;
             if (valid) {
-                const uint4 *kr = reinterpret_cast<const uint4 *>(k_s + (ti * 32 + lane) * PITCH);
+                const int kr_row = ti * 32 + lane;
 #pragma unroll
                 for (int c8 = 0; c8 < HD / 8; c8++) {
-                    const uint4 raw = kr[c8];
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(k_s + (c8 >> 3) * BOX_BYTES + sw_off(kr_row, c8 & 7));
                     const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
                     const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]), f2 = __half22float2(h2[2]),
                                  f3 = __half22float2(h2[3]);
@@ -169,7 +189,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
             p_s[warp][lane] = pv;
             __syncwarp();
             for (int j = 0; j < cnt; j++) {
-                const __half *vr = reinterpret_cast<const __half *>(v_s + (ti * 32 + j) * PITCH) + lane * DPL;
+                const __half *vr = reinterpret_cast<const __half *>(sw_elem(v_s, ti * 32 + j, lane * DPL));
                 const float pj = p_s[warp][j];
                 if (DPL == 4) {
                     const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
@@ -278,15 +298,16 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const float *__res
 }
 
 template <int HD>
-b200_status launch_g(int G, dim3 grid, cudaStream_t st, const float *q, const float *k, const float *v, __half *kc,
-                     __half *vc, const int32_t *pos_dev, int pos, int n_head, int n_kv, int64_t seq_stride, int n_split,
-                     float scale, int neox, const RopeTab &tab, float *out, float *po, float *pml, int *counters) {
-    const size_t smem = 2 * ROWS_PER_CTA * (HD * 2 + 16) + (size_t)4 * G * HD * sizeof(float);
+b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap, const CUtensorMap &vmap, const float *q,
+                     const float *k, const float *v, __half *kc, __half *vc, const int32_t *pos_dev, int pos, int n_head,
+                     int n_kv, int64_t seq_stride, int n_split, float scale, int neox, const RopeTab &tab, float *out, float *po,
+                     float *pml, int *counters) {
+    const size_t smem = 2 * (HD / 64) * BOX_BYTES + (size_t)4 * G * HD * sizeof(float) + 1024; // + room to align to 1 KB
 #define KQ_AD(GG)                                                                                              \
     if (smem > 48 * 1024)                                                                                      \
         cudaFuncSetAttribute(attn_decode_kernel<HD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    kq_launch(attn_decode_kernel<HD, GG>, grid, 128 * GG, smem, st, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, seq_stride, \
-              n_split, scale, neox, tab, out, po, pml, counters)
+    kq_launch(attn_decode_kernel<HD, GG>, grid, 128 * GG, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, \
+              seq_stride, n_split, scale, neox, tab, out, po, pml, counters)
     switch (G) {
     case 1: KQ_AD(1); break;
     case 2: KQ_AD(2); break;
@@ -301,15 +322,40 @@ b200_status launch_g(int G, dim3 grid, cudaStream_t st, const float *q, const fl
     return B200_OK;
 }
 
+// tensor maps of a cache, made once per (base, shape): [seq][position][kv head][dim] of 2-byte elements,
+// box = 128 positions x 64 dims of one head, 128-byte swizzle
+struct CacheMaps { CUtensorMap k, v; };
+b200_status cache_maps(const uint16_t *kc, const uint16_t *vc, int n_seq, int n_kv, int hd, int64_t seq_stride, const CacheMaps **out) {
+    static std::map<std::tuple<const void *, const void *, int, int, int, int64_t>, CacheMaps> cache;
+    const auto key = std::make_tuple((const void *)kc, (const void *)vc, n_seq, n_kv, hd, seq_stride);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        KQ_REQUIRE(seq_stride % ((int64_t)n_kv * hd) == 0, "attention: the cache stride is not a whole number of positions");
+        const uint64_t n_ctx = (uint64_t)(seq_stride / ((int64_t)n_kv * hd));
+        const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)n_kv, n_ctx, (uint64_t)n_seq};
+        const uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)n_kv * hd * 2, (uint64_t)seq_stride * 2};
+        const uint32_t box[4] = {64, 1, ROWS_PER_CTA, 1};
+        CacheMaps m;
+        memset(&m, 0, sizeof(m));
+        b200_status rc = kq_tmap_encode(&m.k, 2, 4, kc, dims, strides, box, 1);
+        if (rc != B200_OK) return rc;
+        rc = kq_tmap_encode(&m.v, 2, 4, vc, dims, strides, box, 1);
+        if (rc != B200_OK) return rc;
+        if (cache.size() > 4096) cache.clear(); // a bound, not a policy
+        it = cache.emplace(key, m).first;
+    }
+    *out = &it->second;
+    return B200_OK;
+}
+
 } // namespace
 
-// Number of position slices for a context of L rows: 128 rows per slice, at most 64 slices, and
-// constant over a power-of-two stretch of L so that a captured launch configuration stays valid.
+// Number of position slices for a context of L rows: one per 128 rows, at most 64, so that every
+// CTA of the launch has rows to work on.  A captured decode step is keyed by this number, so a
+// sequence re-captures its step once per 128 positions.
 int kq_attention_decode_splits(int64_t L) {
-    int64_t cap = 128;
-    while (cap < L) cap *= 2;
-    int64_t n = cap / 128;
-    return (int)(n > 64 ? 64 : n);
+    const int64_t n = (L + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+    return (int)(n < 1 ? 1 : (n > 64 ? 64 : n));
 }
 
 // q [n_seq][n_head][hd], k / v [n_seq][n_kv][hd] f32 as they come out of the qkv projection (not yet
@@ -333,9 +379,13 @@ b200_status kq_attention_decode(const float *q, const float *k, const float *v, 
     const float scale = 1.0f / sqrtf((float)hd);
     dim3 grid(n_kv, n_split, n_seq);
     const int G = n_head / n_kv;
+    KQ_REQUIRE((((uintptr_t)kc | (uintptr_t)vc) & 15) == 0, "attention: the cache must be 16-byte aligned");
+    const CacheMaps *maps = nullptr;
+    const b200_status rc = cache_maps(kc, vc, n_seq, n_kv, hd, seq_stride, &maps);
+    if (rc != B200_OK) return rc;
     if (hd == 128)
-        return launch_g<128>(G, grid, st, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv, seq_stride,
-                             n_split, scale, neox, tab, out, po, pml, counters);
-    return launch_g<64>(G, grid, st, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv, seq_stride,
-                        n_split, scale, neox, tab, out, po, pml, counters);
+        return launch_g<128>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
+                             seq_stride, n_split, scale, neox, tab, out, po, pml, counters);
+    return launch_g<64>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
+                        seq_stride, n_split, scale, neox, tab, out, po, pml, counters);
 }
