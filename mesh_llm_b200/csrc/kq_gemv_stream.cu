@@ -340,10 +340,13 @@ __device__ __forceinline__ void block_q6k(const uint8_t *grp, int g, int bl, con
 // permutation of k is used for the activation fragments, so the sums are unchanged), rows 8..15 of
 // the tile are zero.  The accumulators come back as (row r, tokens 2t, 2t+1); the 6-bit scales, the
 // min term and the f32 combination are the decode kernel's, so results are identical token by token.
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+// d = a * b with a zero accumulator: rows 8..15 of the A tile are zero, only d0 / d1 (row lane/4, tokens
+// 2 (lane%4), +1) are used
+__device__ __forceinline__ void mma_u8s8(int &d0, int &d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    int d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "r"(0));
 }
 
 template <uint32_t TYPE, int M>
@@ -374,7 +377,7 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
             const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
             const uint32_t m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
             const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-            int is0 = 0, is1 = 0;
+            int ev0 = 0, ev1 = 0, od0 = 0, od1 = 0; // odd sub-blocks carry a factor 16 (high nibbles left in place)
 #pragma unroll
             for (int g = 0; g < 4; g++) {
                 const uint2 w = *reinterpret_cast<const uint2 *>(b + 16 + 32 * g + 8 * t);
@@ -384,28 +387,32 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
                     x1 = *reinterpret_cast<const uint2 *>(actB + blk * ACT_BLK + 64 * g + 32 + 8 * t);
                 }
                 const uint32_t scw = g < 2 ? sc_lo : sc_hi;
-                const int s_even = (int)((scw >> (16 * (g & 1))) & 0xFF), s_odd = (int)((scw >> (16 * (g & 1) + 8)) & 0xFF);
-                int c[4] = {0, 0, 0, 0};
-                mma_u8s8(c, w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, x0.x, x0.y); // sub-block 2g
-                is0 += s_even * c[0];
-                is1 += s_even * c[1];
-                int e[4] = {0, 0, 0, 0};
-                mma_u8s8(e, (w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, x1.x, x1.y); // sub-block 2g + 1
-                is0 += s_odd * e[0];
-                is1 += s_odd * e[1];
+                const int k0 = (2 * g) & 3;
+                int c0, c1, e0, e1;
+                mma_u8s8(c0, c1, w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, x0.x, x0.y); // sub-block 2g
+                mma_u8s8(e0, e1, w.x & 0xF0F0F0F0u, w.y & 0xF0F0F0F0u, x1.x, x1.y); // 16 x sub-block 2g + 1
+                ev0 += (int)KQ_BYTE(scw, k0) * c0;
+                ev1 += (int)KQ_BYTE(scw, k0) * c1;
+                od0 += (int)KQ_BYTE(scw, k0 + 1) * e0;
+                od1 += (int)KQ_BYTE(scw, k0 + 1) * e1;
             }
-            // min term sum_j m_j * (sum of the 32 codes of sub-block j), per token
-            const int4 q0 = *reinterpret_cast<const int4 *>(act0 + act_q + blk * 16);
-            const int4 q1 = *reinterpret_cast<const int4 *>(act1 + act_q + blk * 16);
-            const uint32_t mw[4] = {__byte_perm(m_lo, 0, 0x4140), __byte_perm(m_lo, 0, 0x4342), __byte_perm(m_hi, 0, 0x4140),
-                                    __byte_perm(m_hi, 0, 0x4342)}; // m_j pairs as 16-bit lanes
-            auto dot16 = [](int x, uint32_t y) { return (int)(int16_t)(x & 0xFFFF) * (int)(y & 0xFFFF) + (x >> 16) * (int)(y >> 16); };
-            const int mn0 = dot16(q0.x, mw[0]) + dot16(q0.y, mw[1]) + dot16(q0.z, mw[2]) + dot16(q0.w, mw[3]);
-            const int mn1 = dot16(q1.x, mw[0]) + dot16(q1.y, mw[1]) + dot16(q1.z, mw[2]) + dot16(q1.w, mw[3]);
+            const int is0 = ev0 + (od0 >> 4), is1 = ev1 + (od1 >> 4);
+            // min term and f32 combination exactly as the one- and two-token kernel does them
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(act0 + act_q + blk * 16);
+            const uint4 q1 = *reinterpret_cast<const uint4 *>(act1 + act_q + blk * 16);
+            int mn0 = __dp2a_lo((int)q0.x, (int)m_lo, 0), mn1 = __dp2a_lo((int)q1.x, (int)m_lo, 0);
+            mn0 = __dp2a_hi((int)q0.y, (int)m_lo, mn0);
+            mn1 = __dp2a_hi((int)q1.y, (int)m_lo, mn1);
+            mn0 = __dp2a_lo((int)q0.z, (int)m_hi, mn0);
+            mn1 = __dp2a_lo((int)q1.z, (int)m_hi, mn1);
+            mn0 = __dp2a_hi((int)q0.w, (int)m_hi, mn0);
+            mn1 = __dp2a_hi((int)q1.w, (int)m_hi, mn1);
             const float da0 = reinterpret_cast<const float *>(act0 + act_q + act_s)[blk];
             const float da1 = reinterpret_cast<const float *>(act1 + act_q + act_s)[blk];
-            acc0 = fmaf(da0, dd.x * (float)is0 - dd.y * (float)mn0, acc0);
-            acc1 = fmaf(da1, dd.x * (float)is1 - dd.y * (float)mn1, acc1);
+            acc0 = fmaf(dd.x * da0, (float)is0, acc0);
+            acc0 = fmaf(-(dd.y * da0), (float)mn0, acc0);
+            acc1 = fmaf(dd.x * da1, (float)is1, acc1);
+            acc1 = fmaf(-(dd.y * da1), (float)mn1, acc1);
         }
         __syncwarp();
         if (j + p.ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
