@@ -58,6 +58,7 @@ struct GraphKey {
 };
 
 struct GraphEntry {
+    int n_split = 0; // attention slices the instantiated graph was last captured / updated for
     cudaGraphExec_t exec = nullptr;
     long long launches = 0;
 };
@@ -683,7 +684,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
         GraphKey key;
         memset(&key, 0, sizeof(key));
         key.n_seq = n_seq;
-        key.n_split = n_split;
+        key.n_split = 0; // the slice count changes every 128 positions: the entry is updated in place, not re-keyed
         key.seq0 = seq0;
         key.tokens = tokens;
         key.hidden_in = hidden_in;
@@ -691,7 +692,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
         key.logits = logits;
         key.next = next_tokens;
         auto it = st->graphs.find(key);
-        if (it == st->graphs.end()) {
+        if (it == st->graphs.end() || it->second.n_split != n_split) {
             cudaGraph_t graph = nullptr;
             KQ_CUDA(cudaStreamBeginCapture(st->cap_stream, cudaStreamCaptureModeThreadLocal));
             b200_status rc = forward_body(st, tokens, hidden_in, seq0, n_seq, 1, pos0, true, n_split, hidden_out,
@@ -702,12 +703,30 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
                 return rc;
             }
             KQ_CUDA(e);
-            GraphEntry ge;
-            ge.launches = g_kq_launches - before;
-            e = cudaGraphInstantiate(&ge.exec, graph, 0);
-            cudaGraphDestroy(graph);
-            KQ_CUDA(e);
-            it = st->graphs.emplace(key, ge).first;
+            const long long n_launch = g_kq_launches - before;
+            if (it != st->graphs.end()) {
+                // same topology, other attention grids: patch the instantiated graph (about a millisecond)
+                // instead of instantiating a new one (tens of milliseconds)
+                cudaGraphExecUpdateResultInfo info;
+                if (cudaGraphExecUpdate(it->second.exec, graph, &info) != cudaSuccess) {
+                    cudaGetLastError();
+                    cudaGraphExecDestroy(it->second.exec);
+                    it->second.exec = nullptr;
+                    e = cudaGraphInstantiate(&it->second.exec, graph, 0);
+                }
+                cudaGraphDestroy(graph);
+                KQ_CUDA(e);
+                it->second.n_split = n_split;
+                it->second.launches = n_launch;
+            } else {
+                GraphEntry ge;
+                ge.launches = n_launch;
+                ge.n_split = n_split;
+                e = cudaGraphInstantiate(&ge.exec, graph, 0);
+                cudaGraphDestroy(graph);
+                KQ_CUDA(e);
+                it = st->graphs.emplace(key, ge).first;
+            }
         }
         kq_launch(set_pos_kernel, 1, 1, 0, s, st->pos0_dev, pos0);
         KQ_LAUNCH_CHECK();

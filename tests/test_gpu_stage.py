@@ -175,6 +175,33 @@ def test_long_prefill_batch_on_the_tensor_core_paths():
     assert kl < 1e-4 and top1 >= 0.95 and rel_err(got, ref) < 5e-2
 
 
+def test_decode_across_an_attention_slice_boundary():
+    """The decode step is a captured graph whose attention launch has one slice per 128 positions; at
+    position 128 the instantiated graph is updated in place.  Logits before and after the boundary
+    against the oracle on the same history."""
+    import torch
+
+    cfg = dict(DENSE, n_layer=2, n_ctx=200)
+    m, st = make_pair(cfg, 15, n_ubatch=64)
+    toks = np.random.default_rng(5).integers(0, 2048, 122).astype(np.int32)
+    for p0 in (0, 64):
+        chunk = toks[p0:p0 + 64] if p0 == 0 else toks[64:122]
+        _, _, nxt = st.forward(tokens=torch.from_numpy(chunk).cuda(), pos0=p0)
+    m.forward(tokens=toks)
+    tok = nxt[-1:].clone()
+    kls, agree = [], 0
+    for step in range(14):  # positions 122 .. 135
+        pos = 122 + step
+        _, lref = m.forward(tokens=tok.cpu().numpy(), pos0=pos)
+        _, lg, nx = st.forward(tokens=tok, pos0=pos)
+        k, t1 = kl_top1(lg.cpu().numpy(), lref)
+        kls.append(k)
+        agree += int(t1)
+        tok = nx.clone()
+    print(f"across the boundary: top-1 {agree}/14, max KL {max(kls):.2e}")
+    assert agree >= 13 and max(kls) < 1e-3
+
+
 def test_two_stages_token_identical_to_one_stage():
     import torch
     from mesh_llm_b200.stage import Stage
