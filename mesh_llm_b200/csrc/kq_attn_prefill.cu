@@ -202,10 +202,12 @@ b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const u
     const int smem = 4 * TILE_BYTES;
 #define KQ_APF(GG)                                                                                                         \
     {                                                                                                                      \
-        static bool attr = false;                                                                                          \
-        if (!attr) {                                                                                                       \
+        static bool attr[16]; /* the attribute belongs to a (kernel, device) pair */                                      \
+        int dev = 0;                                                                                                       \
+        KQ_CUDA(cudaGetDevice(&dev));                                                                                      \
+        if (dev < 0 || dev >= 16 || !attr[dev]) {                                                                          \
             KQ_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));     \
-            attr = true;                                                                                                   \
+            if (dev >= 0 && dev < 16) attr[dev] = true;                                                                    \
         }                                                                                                                  \
         kq_launch(attn_prefill_kernel<GG>, grid, GG * 32, smem, st, q, (const __half *)kc, (const __half *)vc, T, pos0_dev, \
                   pos0, n_head, n_kv, seq_stride, scale_log2, out);                                                        \

@@ -46,6 +46,22 @@ extern long long g_kq_launches;
 #define KQ_COUNT_LAUNCH() (++g_kq_launches)
 
 static inline int64_t kq_div_up(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Makes `dev` current for the lifetime of the object and gives the caller its own device back
+// afterwards: an entry point must not leave the thread's current device changed.
+struct KqDevGuard {
+    int prev = -1;
+    explicit KqDevGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~KqDevGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+    KqDevGuard(const KqDevGuard &) = delete;
+    KqDevGuard &operator=(const KqDevGuard &) = delete;
+};
 int kq_sm_count();
 
 // ---- device row geometry -------------------------------------------------------------------

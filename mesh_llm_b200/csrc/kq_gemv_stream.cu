@@ -894,10 +894,12 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     if (grid * WARPS > MAX_UNITS) grid = MAX_UNITS / WARPS;
     const int64_t want = kq_div_up((int64_t)p.n_rg * p.nsteps, WARPS);
     if (want < grid) grid = (int)(want < 1 ? 1 : want);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[16]; // the attribute belongs to a (kernel, device) pair
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16 || !attr_done[dev]) {
         KQ_CUDA(cudaFuncSetAttribute(gemv_block_kernel<TYPE, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        attr_done = true;
+        if (dev >= 0 && dev < 16) attr_done[dev] = true;
     }
     kq_launch(gemv_block_kernel<TYPE, M>, grid, WARPS * 32, smem, st, p);
     KQ_COUNT_LAUNCH();

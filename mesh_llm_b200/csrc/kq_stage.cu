@@ -423,7 +423,7 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
                "stage: feed-forward sizes must be multiples of 256");
     KQ_REQUIRE(c.n_ctx > 0 && c.n_seq > 0 && c.n_ubatch > 0, "stage: n_ctx, n_seq, n_ubatch");
     KQ_REQUIRE(!c.has_output || c.n_vocab > 0, "stage: n_vocab");
-    KQ_CUDA(cudaSetDevice(c.device));
+    KqDevGuard dev_guard(c.device);
     b200_stage *st = new b200_stage();
     st->c = c;
     const int64_t h = c.n_embd, hd = c.head_dim, nq = (int64_t)c.n_head * hd, nkv = (int64_t)c.n_head_kv * hd;
@@ -534,7 +534,7 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
 
 void b200_stage_free(b200_stage *st) {
     if (!st) return;
-    cudaSetDevice(st->c.device);
+    KqDevGuard dev_guard(st->c.device);
     cudaDeviceSynchronize();
     for (auto &g : st->graphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
@@ -575,7 +575,7 @@ b200_status b200_stage_set_tensor(b200_stage *st, const char *name, uint32_t typ
         kq_set_error("stage_set_tensor: %s expects %zu bytes, got %zu", name, want, nbytes);
         return B200_ERR_BOUNDS;
     }
-    KQ_CUDA(cudaSetDevice(st->c.device));
+    KqDevGuard dev_guard(st->c.device);
     if (type != t->type) { // same shape, other K-quant: reallocate the device rows
         void *p = nullptr;
         const size_t nb = (size_t)(kq_device_row_bytes(type, t->ne[0]) * rows);
@@ -623,7 +623,7 @@ b200_status b200_stage_get_tensor(b200_stage *st, const char *name, void *host_d
         kq_set_error("stage_get_tensor: %s holds %zu bytes, asked for %zu", name, want, nbytes);
         return B200_ERR_BOUNDS;
     }
-    KQ_CUDA(cudaSetDevice(st->c.device));
+    KqDevGuard dev_guard(st->c.device);
     if (t->type == B200_TYPE_Q6_K) {
         void *tmp = nullptr;
         if (cudaMalloc(&tmp, nbytes + 16) != cudaSuccess) {
@@ -642,7 +642,7 @@ b200_status b200_stage_get_tensor(b200_stage *st, const char *name, void *host_d
 
 b200_status b200_stage_generate(b200_stage *st, uint64_t seed) {
     KQ_REQUIRE(st, "stage_generate: null stage");
-    KQ_CUDA(cudaSetDevice(st->c.device));
+    KqDevGuard dev_guard(st->c.device);
     for (auto &t : st->tensors) {
         const uint64_t key = mix64_host(seed ^ name_hash(t.name.c_str()));
         const bool is_norm = t.name.find("norm.weight") != std::string::npos;
@@ -674,7 +674,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
                pos0 + T, c.n_ctx);
     KQ_REQUIRE(c.has_embd ? tokens != nullptr : hidden_in != nullptr, "stage_forward: missing input");
     KQ_REQUIRE(c.has_output || hidden_out, "stage_forward: missing hidden_out");
-    KQ_CUDA(cudaSetDevice(c.device));
+    KqDevGuard dev_guard(c.device);
     KQ_TRY(resolve(st));
     cudaStream_t s = (cudaStream_t)stream;
     const long long before = g_kq_launches;
@@ -748,7 +748,7 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
     KQ_REQUIRE(n_seq >= 1 && n_seq <= c.n_seq && n_seq <= st->rows_max && pos0 >= 0 && pos0 < c.n_ctx,
                "stage_profile_decode: n_seq=%d pos0=%d", n_seq, pos0);
     KQ_REQUIRE((classes & ~CLS_ALL) == 0 && classes != 0, "stage_profile_decode: classes mask");
-    KQ_CUDA(cudaSetDevice(c.device));
+    KqDevGuard dev_guard(c.device);
     KQ_TRY(resolve(st));
     // inputs of the replayed step live in the stage's own scratch (their values do not matter)
     int32_t *tok = (int32_t *)st->rid_scratch;
@@ -797,7 +797,7 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
 
 b200_status b200_stage_synchronize(b200_stage *st) {
     KQ_REQUIRE(st, "stage_synchronize: null stage");
-    KQ_CUDA(cudaSetDevice(st->c.device));
+    KqDevGuard dev_guard(st->c.device);
     KQ_CUDA(cudaDeviceSynchronize());
     const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
     if (werr) {

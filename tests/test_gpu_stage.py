@@ -232,6 +232,42 @@ def test_two_stages_token_identical_to_one_stage():
         tok = nf.clone()
 
 
+def test_two_stages_on_two_devices_of_one_process():
+    """The same split with the second stage on another GPU of the same process: every kernel of the
+    library also runs on a device other than 0, and the result is still identical to one stage."""
+    import torch
+    from mesh_llm_b200.stage import Stage
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m = orc.Model(**DENSE)
+    m.generate(13)
+    tensors = {n: m.tensor(n)[:2] for n in m.tensor_names()}
+    full = Stage(**DENSE, n_ubatch=64)
+    s0 = Stage(**DENSE, n_ubatch=64, layer_end=2, has_output=0, device=0)
+    s1 = Stage(**DENSE, n_ubatch=64, layer_begin=2, layer_end=4, has_embd=0, device=1)
+    for st in (full, s0, s1):
+        for n, (ty, data) in tensors.items():
+            try:
+                st.set_tensor(n, ty, data)
+            except Exception:
+                pass  # tensor belongs to the other stage
+    toks = torch.from_numpy(np.random.default_rng(2).integers(0, 2048, 40).astype(np.int32)).cuda()
+    _, lf, nf = full.forward(tokens=toks)  # 40 rows: tensor-core GEMM and attention
+    h0, _, _ = s0.forward(tokens=toks)
+    with torch.cuda.device(1):
+        _, l2, n2 = s1.forward(hidden_in=h0.to("cuda:1"))
+    assert torch.equal(lf, l2.to("cuda:0")) and torch.equal(nf, n2.to("cuda:0"))
+    tok = nf.clone()
+    for step in range(4):
+        _, lf, nf = full.forward(tokens=tok, pos0=40 + step)
+        h0, _, _ = s0.forward(tokens=tok, pos0=40 + step)
+        with torch.cuda.device(1):
+            _, l2, n2 = s1.forward(hidden_in=h0.to("cuda:1"), pos0=40 + step)
+        assert torch.equal(lf, l2.to("cuda:0")) and torch.equal(nf, n2.to("cuda:0")), step
+        tok = nf.clone()
+
+
 def test_batched_sequences_match_independent_runs():
     import torch
 
