@@ -256,6 +256,8 @@ def main():
     ap.add_argument("--micro", default="", help="isolated quantised matmul instead of the model: 'N,K,M,type' "
                     "(type q4_k|q6_k); prints one line with us per launch and GB/s (M<=8) or TOP/s")
     ap.add_argument("--micro-iters", type=int, default=20)
+    ap.add_argument("--balance", action="store_true", help="N > 1: split layers by weight bytes (the last stage, which "
+                    "holds the output head, gets fewer layers) instead of equal layer counts")
     ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")
     args = ap.parse_args()
     if args.micro:

@@ -38,8 +38,19 @@ class Schedule:
         return i % self.n_seq, i // self.n_seq
 
 
-def layer_range(n_layer, world, rank):
-    """contiguous, as equal as possible; earlier stages take the remainder"""
+def layer_range(n_layer, world, rank, head_cost=0.0):
+    """Contiguous layer range of a stage.  head_cost = 0: as equal as possible, earlier stages take the
+    remainder (the equal split the benchmark configurations name).  head_cost > 0: the output head,
+    which lives on the last stage, counts as that many layers and the last stage gets fewer layers, the
+    way a proportional --tensor-split would place them (mesh-llm/src/inference/election.rs:3095-3114
+    splits in proportion to what each device can hold, not in equal counts)."""
+    if world > 1 and head_cost > 0:
+        target = (n_layer + head_cost) / world
+        last = int(round(target - head_cost))
+        last = max(1, min(last, n_layer - (world - 1)))
+        if rank == world - 1:
+            return n_layer - last, n_layer
+        n_layer, world = n_layer - last, world - 1
     base, rem = divmod(n_layer, world)
     lo = rank * base + min(rank, rem)
     return lo, lo + base + (1 if rank < rem else 0)
@@ -146,7 +157,13 @@ def bench_pipeline(args, w, metric, rank, world, local):
     model_keys = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
                   "rope_neox", "rope_theta", "rms_eps")
     model = {k: w[k] for k in model_keys}
-    lo, hi = layer_range(w["n_layer"], world, rank)
+    head_cost = 0.0
+    if getattr(args, "balance", False):  # the output head in units of an average layer's weight bytes
+        from bench import gemv_bytes, matmuls
+
+        layer_b = sum(gemv_bytes(N, K, ty) for l in (0, 1) for (N, K, ty) in matmuls(w, l)) / 2
+        head_cost = gemv_bytes(w["n_vocab"], w["n_embd"], 14) / layer_b
+    lo, hi = layer_range(w["n_layer"], world, rank, head_cost)
     n_seq = world
     steps, warm = args.steps, max(3, args.warmup)
     n_ctx = w["prefill"] + 2 * (steps + warm) + 72
@@ -256,7 +273,8 @@ def bench_pipeline(args, w, metric, rank, world, local):
             "metric": metric, "value": total / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
             "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine", "data": "synthetic",
-            "config": {"workload": f"{w['name']} ({w['n_layer']} layers) split into {world} contiguous layer ranges, "
+            "config": {"split": "weighted by bytes (output head counted)" if head_cost > 0 else "equal layer counts",
+                       "workload": f"{w['name']} ({w['n_layer']} layers) split into {world} contiguous layer ranges, "
                                    f"one per GPU; {n_seq} sequences in flight, decode batch 1 per stage at context "
                                    f"{w['prefill']}+; f32 [1 x {h}] activation handed to the next stage over NVLink",
                        "sequences_in_flight": n_seq,

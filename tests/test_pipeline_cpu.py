@@ -34,6 +34,12 @@ def test_schedule_and_layer_ranges():
     assert [layer_range(64, 8, r) for r in range(8)] == [(8 * r, 8 * r + 8) for r in range(8)]
     assert [layer_range(7, 3, r) for r in range(3)] == [(0, 3), (3, 5), (5, 7)]
     assert layer_range(80, 1, 0) == (0, 80)
+    # weighted: the head of the 32B shape weighs 2.2 layers, of the 70B shape 1.7
+    assert [layer_range(64, 8, r, 2.2) for r in range(8)] == [(0, 9), (9, 18), (18, 26), (26, 34), (34, 42), (42, 50),
+                                                                (50, 58), (58, 64)]
+    assert [layer_range(64, 2, r, 2.2) for r in range(2)] == [(0, 33), (33, 64)]
+    assert [b - a for a, b in (layer_range(80, 8, r, 1.7) for r in range(8))] == [11, 10, 10, 10, 10, 10, 10, 9]
+    assert layer_range(64, 1, 0, 2.2) == (0, 64)
     s = Schedule(4, 4)
     assert s.work(0, 0) == (0, 0) and s.work(3, 2) is None and s.work(3, 3) == (0, 0)
     assert s.work(0, 4) == (0, 1) and s.work(1, 4) == (3, 0)
