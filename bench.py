@@ -128,8 +128,8 @@ def cpu_decode_sample(w, threads=None, reps=2):
     to the full depth.  Returns (tok/s, cores, description)."""
     from oracle import binding as orc
 
-    if threads:
-        orc.lib().orc_set_threads(threads)
+    # all host cores, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its workers)
+    orc.lib().orc_set_threads(threads or os.cpu_count() or 1)
     cores = orc.lib().orc_get_threads()
     shapes = {}
     for layer in (0, 1):
