@@ -27,7 +27,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[0..2]
+    # the dense configurations of the benchmark list: 3B, 32B and 70B shapes
     "cfg1": dict(name="Qwen2.5-3B-shape Q4_K_M", n_layer=36, n_embd=2048, n_head=16, n_head_kv=2,
                  head_dim=128, n_ff=11008, n_vocab=151936, qkv_bias=1, rope_neox=1, rope_theta=1e6,
                  rms_eps=1e-6, prefill=512, decode=128),
@@ -37,7 +37,7 @@ WORKLOADS = {
     "cfg3": dict(name="Llama-3-70B-shape Q4_K_M", n_layer=80, n_embd=8192, n_head=64, n_head_kv=8,
                  head_dim=128, n_ff=28672, n_vocab=128256, qkv_bias=0, rope_neox=0, rope_theta=5e5,
                  rms_eps=1e-5, prefill=4096, decode=256),
-    # configs[3]: MoE; with N GPUs each rank is an independent replica holding n_expert / N experts
+    # the mixture-of-experts configuration; with N GPUs each rank is an independent replica holding n_expert / N experts
     "cfg4": dict(name="Qwen3-30B-A3B-shape MoE Q4_K_M", n_layer=48, n_embd=2048, n_head=32, n_head_kv=4,
                  head_dim=128, n_ff=0, n_vocab=151936, qkv_bias=0, rope_neox=1, rope_theta=1e6,
                  rms_eps=1e-6, n_expert=128, n_expert_used=8, n_ff_exp=768, prefill=1024, decode=256),
@@ -48,7 +48,7 @@ BPW = {12: 144 / 256, 14: 210 / 256}
 METRIC = "decode tok/s, Q4_K_M, batch 1 per stage (shape in config.workload; GEMV HBM % of peak in roofline)"
 
 
-NCU_TRAFFIC_RATIO = 1.03  # measured DRAM bytes / algorithmic bytes of the decode GEMV (see profiles/)
+NCU_TRAFFIC_RATIO = 1.03  # DRAM bytes / algorithmic bytes of the decode GEMV, from ncu captures of isolated launches
 
 
 def matmuls(w, layer):
@@ -223,8 +223,8 @@ def micro_one(N, K, M, tname, iters):
 
 
 def run_micro(args):
-    """--micro N,K,M,type: one shape of the isolated sweep (BASELINE.json configs[4]); also the command
-    the ncu captures under profiles/ run."""
+    """--micro N,K,M,type: one shape of the isolated quantised-matmul sweep; also the command the committed
+    ncu captures were taken with."""
     N, K, M, tname = args.micro.split(",")
     print(json.dumps(micro_one(int(N), int(K), int(M), tname, args.micro_iters)))
 
@@ -234,7 +234,7 @@ SWEEP_M = (1, 8, 64, 512, 4096)
 
 
 def run_sweep(args):
-    """--sweep: the isolated quantised-matmul sweep of BASELINE.json configs[4]: every shape x
+    """--sweep: the isolated quantised-matmul sweep of the benchmark list: every shape x
     {Q4_K, Q6_K} x M; GB/s of algorithmic bytes for M <= 8, useful int8 TOP/s above; one JSON line each."""
     for tname in ("q4_k", "q6_k"):
         for (N, K) in SWEEP_SHAPES:
@@ -389,7 +389,7 @@ def main():
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
         "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
         # DRAM read+write bytes per launch: ncu captures of the two largest matrices of this shape
-        # (profiles/gemv_block_kernel_m1.md) measured 1.02x (Q4_K) and 1.04x (Q6_K) the algorithmic
+        # measured 1.02x (Q4_K) and 1.04x (Q6_K) the algorithmic
         # bytes; traffic grows in proportion to the weights streamed, so the ratio is applied to the
         # step's average launch
         "traffic": NCU_TRAFFIC_RATIO * algo / max(1, n_gemv.value),
