@@ -258,6 +258,8 @@ def main():
     ap.add_argument("--micro-iters", type=int, default=20)
     ap.add_argument("--balance", action="store_true", help="N > 1: split layers by weight bytes (the last stage, which "
                     "holds the output head, gets fewer layers) instead of equal layer counts")
+    ap.add_argument("--kv", default="f16", choices=["f16", "q8_0-q4_0", "q4_0-q4_0", "auto"],
+                    help="KV-cache row types (K-V); auto = the pair mesh-llm starts a model of this size with")
     ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")
     args = ap.parse_args()
     if args.micro:
@@ -295,9 +297,18 @@ def main():
     model = {k: w[k] for k in MODEL_KEYS if k in w}
     n_ctx = w["prefill"] + w["decode"] + args.steps + args.warmup + 64
     n_seq = 8
-    st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local)
-    st.generate(20251125)
+    from mesh_llm_b200 import ops
+    ids, names = {"f16": 1, "q4_0": 2, "q8_0": 8}, {1: "f16", 2: "q4_0", 8: "q8_0"}
+    kt, vt = (1, 1) if args.kv == "auto" else [ids[t] for t in (args.kv + "-" + args.kv).split("-")[:2]]
+    st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
     weight_bytes = st.weight_bytes()
+    if args.kv == "auto" and ops.kv_types_for_model_bytes(weight_bytes) != (kt, vt):
+        # the pair mesh-llm starts a model file of this size with
+        kt, vt = ops.kv_types_for_model_bytes(weight_bytes)
+        st.close()
+        st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
+    st.generate(20251125)
+    kv_label = names[kt] + "-" + names[vt]
     dev = torch.device("cuda", local)
     rng = np.random.default_rng(1234)
 
@@ -430,7 +441,7 @@ def main():
         "config": {"workload": f"{w['name']} ({w['n_layer']} layers), decode batch 1 at context {w['prefill']}+, "
                                f"greedy, one stage on one GPU", "weight_bytes": weight_bytes,
                    "l2": "each step streams all weights (>> 126 MB L2), no flush needed",
-                   "sequences_in_flight": 1},
+                   "sequences_in_flight": 1, "kv_cache": kv_label},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "prefill_tok_s": prefill_tok_s, "decode_batch8_tok_s": b8,

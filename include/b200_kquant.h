@@ -49,6 +49,8 @@ B200_API b200_status b200_check_device_waits(void);
 enum {
     B200_TYPE_F32 = 0,
     B200_TYPE_F16 = 1,
+    B200_TYPE_Q4_0 = 2,  /* KV-cache rows only: 32 elements / 18 bytes */
+    B200_TYPE_Q8_0 = 8,  /* KV-cache rows only: 32 elements / 34 bytes */
     B200_TYPE_Q4_K = 12, /* 256 elements / 144 bytes */
     B200_TYPE_Q6_K = 14, /* 256 elements / 210 bytes */
     B200_TYPE_I32 = 26
@@ -219,6 +221,25 @@ B200_API b200_status b200_attention(const float *q, const uint16_t *k_cache, con
                                     int64_t hd, float *out, void *scratch, size_t scratch_bytes,
                                     void *stream);
 B200_API size_t b200_attention_scratch_bytes(int64_t T, int64_t n_head, int64_t hd, int64_t n_ctx);
+/* Quantised KV cache: the --cache-type-k / --cache-type-v pairs mesh-llm starts its servers with
+ * (mesh-llm/src/inference/launch.rs:568-591: f16 / f16 below 5 GB of model, q8_0 K + q4_0 V from 5
+ * to 50 GB, q4_0 / q4_0 above).  Block arithmetic is ggml's block_q8_0 / block_q4_0; on the device
+ * a row (one position, one KV head) holds the codes of its hd / 32 blocks, then their f16 scales,
+ * padded to a multiple of 16 bytes: b200_kv_row_bytes (hd = 128: 144 / 80 bytes; f16: 2 hd).
+ * b200_kv_store rotates k by RoPE at pos[t] and writes the K / V rows of T tokens at those
+ * positions of one sequence's caches ([position][n_kv] rows); b200_attention_kv is b200_attention
+ * over caches of the given types (quantised types need hd = 128).                               */
+B200_API size_t b200_kv_row_bytes(uint32_t type, int64_t hd);
+/* the pair mesh-llm picks for a model file of this size (thresholds 5e9 and 50e9 bytes)          */
+B200_API void b200_kv_types_for_model_bytes(uint64_t model_bytes, uint32_t *k_type, uint32_t *v_type);
+B200_API b200_status b200_kv_store(const float *k, const float *v, const int32_t *pos, int64_t T,
+                                   int64_t n_kv, int64_t hd, float theta, int32_t neox,
+                                   uint32_t k_type, uint32_t v_type, void *k_cache, void *v_cache,
+                                   void *stream);
+B200_API b200_status b200_attention_kv(const float *q, const void *k_cache, const void *v_cache,
+                                       uint32_t k_type, uint32_t v_type, int64_t T, int64_t pos0,
+                                       int64_t n_head, int64_t n_kv, int64_t hd, float *out,
+                                       void *scratch, size_t scratch_bytes, void *stream);
 B200_API b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T,
                                    int64_t K, float *y, void *stream);
 B200_API b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream);
@@ -259,6 +280,7 @@ typedef struct b200_stage_config {
     float rms_eps, rope_theta;
     int32_t n_ubatch; /* largest number of tokens per forward call                           */
     int32_t device;
+    int32_t kv_type_k, kv_type_v; /* KV-cache row types: 0 or B200_TYPE_F16, B200_TYPE_Q8_0, B200_TYPE_Q4_0 */
 } b200_stage_config;
 
 B200_API b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out);

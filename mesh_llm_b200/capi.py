@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 SO_PATH = os.environ.get("B200_KQ_LIB") or os.path.join(_HERE, "libb200kq.so")
 
-TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K, TYPE_I32 = 0, 1, 12, 14, 26
+TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K, TYPE_I32 = 0, 1, 2, 8, 12, 14, 26
 
 OK = 0
 STATUS_NAMES = {0: "OK", -1: "INVALID", -2: "ALLOC", -3: "CUDA", -4: "UNSUPPORTED", -5: "BOUNDS",
@@ -47,6 +47,7 @@ class StageConfig(C.Structure):
         ("has_embd", C.c_int32), ("has_output", C.c_int32),
         ("rms_eps", C.c_float), ("rope_theta", C.c_float),
         ("n_ubatch", C.c_int32), ("device", C.c_int32),
+        ("kv_type_k", C.c_int32), ("kv_type_v", C.c_int32),
     ]
 
 
@@ -124,6 +125,10 @@ SIGNATURES = {
     "b200_cpy_f32_f16": (i32, [vp, i64, vp, vp]),
     "b200_attention": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, vp, vp, sz, vp]),
     "b200_attention_scratch_bytes": (sz, [i64, i64, i64, i64]),
+    "b200_kv_row_bytes": (sz, [u32, i64]),
+    "b200_kv_types_for_model_bytes": (None, [u64, C.POINTER(u32), C.POINTER(u32)]),
+    "b200_kv_store": (i32, [vp, vp, vp, i64, i64, i64, C.c_float, i32, u32, u32, vp, vp, vp]),
+    "b200_attention_kv": (i32, [vp, vp, vp, u32, u32, i64, i64, i64, i64, i64, vp, vp, sz, vp]),
     "b200_get_rows": (i32, [u32, vp, vp, i64, i64, vp, vp]),
     "b200_argmax": (i32, [vp, i64, i64, vp, vp]),
     "b200_moe_route": (i32, [vp, i64, i64, i64, vp, vp, vp]),

@@ -1,11 +1,12 @@
-// Decode attention (one new token per sequence) as ONE launch per layer: RoPE of q and k, the f16
-// store of the new K / V row into the cache, split-KV attention over the cache, and the combination
+// Decode attention (one new token per sequence) as ONE launch per layer: RoPE of q and k, the
+// store of the new K / V row into the cache (f16, or q8_0 / q4_0 rows), split-KV attention over the cache, and the combination
 // of the splits by whichever CTA finishes last.  At batch 1 this op reads a few MB, so its cost is
 // launches, round trips and dependent instruction chains, not bytes; the three kernels it replaces
 // (rope + store, attention, combine) each paid a launch and a drain.  The work is cut fine -- one
 // warp per (query head, 32 positions) -- because a thousand short warps finish sooner than a few
 // hundred long ones.
 #include "kq_common.cuh"
+#include "kq_kvq.cuh"
 
 #include <cuda.h> // CUtensorMap
 #include <math.h>
@@ -34,6 +35,8 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 // per-lane 16-byte reads of K (lane = row) fall on distinct banks; the copies of the first chunk are
 // issued before the kernel waits for its predecessor -- rows of earlier positions do not depend on
 // it.  The row of the new position is computed here and overwrites its (stale) copy in the chunk.
+// A quantised cache is fetched as one box of 128 raw rows per tensor (row bytes x 128, no swizzle)
+// and decoded into the same swizzled f16 chunk, so the arithmetic below does not depend on the type.
 constexpr int ROWS_PER_CTA = 128;
 
 // byte offset of 16-byte chunk c of row r inside a 128-row x 128-byte box with the 128-byte swizzle
@@ -53,13 +56,17 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
                                                               const int32_t *pos_dev, int pos_val, int n_head, int n_kv,
                                                               int64_t seq_stride, int n_split, float scale, int neox,
                                                               RopeTab tab, float *out, float *part_o, float *part_ml,
-                                                              int *counters) {
+                                                              int *counters, KqKvTypes kvt) {
     KQ_PDL_TRIGGER();
     constexpr int DPL = HD / 32, HALF = HD / 2, NBOX = HD / 64, NT = 128 * G;
     extern __shared__ __align__(1024) uint8_t dsm_raw[];
     uint8_t *dsm = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u); // swizzled boxes start on 1 KB
     uint8_t *k_s = dsm, *v_s = dsm + NBOX * BOX_BYTES;
     float (*o_s)[G][HD] = reinterpret_cast<float (*)[G][HD]>(dsm + 2 * NBOX * BOX_BYTES); // [4][G][HD]
+    const bool kq = kvt.k != KQ_KV_F16, vq = kvt.v != KQ_KV_F16;
+    const int k_row = kq_kv_row_bytes(kvt.k, HD), v_row = kq_kv_row_bytes(kvt.v, HD);
+    uint8_t *kraw_s = dsm + 2 * NBOX * BOX_BYTES + 4 * G * HD * (int)sizeof(float); // raw rows of a quantised chunk
+    uint8_t *vraw_s = kraw_s + (kq ? ROWS_PER_CTA * k_row : 0);
     __shared__ float q_s[G][HD];
     __shared__ float p_s[4 * G][32];
     __shared__ float ml_s[4][G][2];
@@ -79,6 +86,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     __half *kbase = kc + seq * seq_stride + (int64_t)kh * HD;
     __half *vbase = vc + seq * seq_stride + (int64_t)kh * HD;
     const int64_t pstride = (int64_t)n_kv * HD;
+    const int64_t cache_row0 = seq * (seq_stride / HD) + kh; // row index of (seq, position 0, kh) in a quantised cache
     const uint32_t bar_a = smem_u32(&bar);
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_a), "r"(1));
@@ -97,18 +105,31 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
         const bool has_new = pos >= cb && pos < cb + ccnt;
         if (ccnt > 0 && threadIdx.x == 0) {
             // whole boxes always: rows past the context arrive as zeros, rows not yet written are never read
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(2 * NBOX * BOX_BYTES) : "memory");
+            const int tx = (kq ? ROWS_PER_CTA * k_row : NBOX * BOX_BYTES) + (vq ? ROWS_PER_CTA * v_row : NBOX * BOX_BYTES);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(tx) : "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (kq)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(kraw_s)),
+                             "l"(&kmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                             : "memory");
+            if (vq)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(vraw_s)),
+                             "l"(&vmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                             : "memory");
 #pragma unroll
             for (int bx = 0; bx < NBOX; bx++) {
-                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                 smem_u32(k_s + bx * BOX_BYTES)),
-                             "l"(&kmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                             : "memory");
-                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                 smem_u32(v_s + bx * BOX_BYTES)),
-                             "l"(&vmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                             : "memory");
+                if (!kq)
+                    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                     smem_u32(k_s + bx * BOX_BYTES)),
+                                 "l"(&kmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                                 : "memory");
+                if (!vq)
+                    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                     smem_u32(v_s + bx * BOX_BYTES)),
+                                 "l"(&vmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                                 : "memory");
             }
         }
         if (first) {
@@ -134,13 +155,66 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
             }
             phase ^= 1;
         }
+        // raw rows of a quantised chunk -> the swizzled f16 chunk (the new position's row comes from below)
+        if (kq || vq) {
+            const int rr_new = has_new ? pos - cb : -1;
+            const int kper = kvt.k == KQ_KV_Q8_0 ? HD / 16 : HD / 32, vper = kvt.v == KQ_KV_Q8_0 ? HD / 16 : HD / 32;
+            const int kn = kq ? ccnt * kper : 0, vn = vq ? ccnt * vper : 0;
+            for (int i = threadIdx.x; i < kn + vn; i += NT) {
+                const bool is_k = i < kn;
+                const int j = is_k ? i : i - kn, per = is_k ? kper : vper, type = is_k ? kvt.k : kvt.v;
+                const int row = j / per, c = j % per;
+                if (row == rr_new) continue;
+                const uint8_t *src = is_k ? kraw_s + row * k_row : vraw_s + row * v_row;
+                uint8_t *dst = is_k ? k_s : v_s;
+                if (type == KQ_KV_Q8_0) {
+                    uint4 t2[2];
+                    kq_kv_decode16_q8_0(src, HD, c, t2);
+                    *reinterpret_cast<uint4 *>(sw_elem(dst, row, c * 16)) = t2[0];
+                    *reinterpret_cast<uint4 *>(sw_elem(dst, row, c * 16 + 8)) = t2[1];
+                } else {
+                    uint4 t4[4];
+                    kq_kv_decode32_q4_0(src, HD, c, t4);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) *reinterpret_cast<uint4 *>(sw_elem(dst, row, c * 32 + 8 * u)) = t4[u];
+                }
+            }
+        }
+        if (has_new && (kq || vq)) {
+            // the new rows of a quantised cache: one warp per block of 32 values
+            const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
+            const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
+            const int rr = pos - cb;
+            constexpr int NB = HD / 32;
+            for (int u = warp; u < 2 * NB; u += NT / 32) {
+                const bool is_k = u < NB;
+                const int blk = is_k ? u : u - NB, e = blk * 32 + lane;
+                if (is_k ? !kq : !vq) continue;
+                float val;
+                if (is_k) {
+                    const int f = neox ? e % HALF : e / 2;
+                    const float ang = (float)pos * tab.inv_freq[f];
+                    const float c = cosf(ang), sn = sinf(ang);
+                    const float a = kv[neox ? f : 2 * f], b = kv[neox ? f + HALF : 2 * f + 1];
+                    const bool first_of_pair = neox ? e < HALF : !(e & 1);
+                    val = first_of_pair ? a * c - b * sn : a * sn + b * c;
+                } else {
+                    val = vv[e];
+                }
+                const int type = is_k ? kvt.k : kvt.v;
+                uint8_t *grow = reinterpret_cast<uint8_t *>(is_k ? kc : vc) +
+                                (cache_row0 + (int64_t)pos * n_kv) * (is_k ? k_row : v_row);
+                const __half r = kq_kv_store_block(type, val, grow, HD, blk, lane);
+                *reinterpret_cast<__half *>(sw_elem(is_k ? k_s : v_s, rr, e)) = r;
+            }
+        }
         if (has_new) {
             // rotate k, round k and v to f16 as later steps will read them, into the cache and over the
             // stale copy of that row in the chunk
             const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
             const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
             const int rr = pos - cb;
-            for (int f = threadIdx.x; f < HALF; f += NT) {
+            for (int f = threadIdx.x; f < (kq ? 0 : HALF); f += NT) {
                 const float ang = (float)pos * tab.inv_freq[f];
                 const float c = cosf(ang), sn = sinf(ang);
                 const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
@@ -151,7 +225,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
                 kbase[pos * pstride + i0] = r0;
                 kbase[pos * pstride + i1] = r1;
             }
-            for (int i = threadIdx.x; i < HD; i += NT) {
+            for (int i = threadIdx.x; i < (vq ? 0 : HD); i += NT) {
                 const __half r = __float2half_rn(vv[i]);
                 *reinterpret_cast<__half *>(sw_elem(v_s, rr, i)) = r;
                 vbase[pos * pstride + i] = r;
@@ -301,13 +375,15 @@ template <int HD>
 b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap, const CUtensorMap &vmap, const float *q,
                      const float *k, const float *v, __half *kc, __half *vc, const int32_t *pos_dev, int pos, int n_head,
                      int n_kv, int64_t seq_stride, int n_split, float scale, int neox, const RopeTab &tab, float *out, float *po,
-                     float *pml, int *counters) {
-    const size_t smem = 2 * (HD / 64) * BOX_BYTES + (size_t)4 * G * HD * sizeof(float) + 1024; // + room to align to 1 KB
+                     float *pml, int *counters, KqKvTypes kvt) {
+    const size_t raw = (kvt.k != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.k, HD) : 0) +
+                       (kvt.v != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.v, HD) : 0);
+    const size_t smem = 2 * (HD / 64) * BOX_BYTES + (size_t)4 * G * HD * sizeof(float) + raw + 1024; // + room to align to 1 KB
 #define KQ_AD(GG)                                                                                              \
     if (smem > 48 * 1024)                                                                                      \
         cudaFuncSetAttribute(attn_decode_kernel<HD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     kq_launch(attn_decode_kernel<HD, GG>, grid, 128 * GG, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, \
-              seq_stride, n_split, scale, neox, tab, out, po, pml, counters)
+              seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt)
     switch (G) {
     case 1: KQ_AD(1); break;
     case 2: KQ_AD(2); break;
@@ -322,24 +398,36 @@ b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap,
     return B200_OK;
 }
 
-// tensor maps of a cache, made once per (base, shape): [seq][position][kv head][dim] of 2-byte elements,
-// box = 128 positions x 64 dims of one head, 128-byte swizzle
+// tensor maps of a cache, made once per (base, shape, types).  f16: [seq][position][kv head][dim] of
+// 2-byte elements, box = 128 positions x 64 dims of one head, 128-byte swizzle.  Quantised:
+// [seq][position][kv head][row bytes], box = 128 positions x one whole row, no swizzle.
 struct CacheMaps { CUtensorMap k, v; };
-b200_status cache_maps(const uint16_t *kc, const uint16_t *vc, int n_seq, int n_kv, int hd, int64_t seq_stride, const CacheMaps **out) {
-    static std::map<std::tuple<const void *, const void *, int, int, int, int64_t>, CacheMaps> cache;
-    const auto key = std::make_tuple((const void *)kc, (const void *)vc, n_seq, n_kv, hd, seq_stride);
+b200_status encode_cache_map(CUtensorMap *m, const void *base, int type, int n_seq, int n_kv, int hd, uint64_t n_ctx) {
+    if (type == KQ_KV_F16) {
+        const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)n_kv, n_ctx, (uint64_t)n_seq};
+        const uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)n_kv * hd * 2, n_ctx * n_kv * hd * 2};
+        const uint32_t box[4] = {64, 1, ROWS_PER_CTA, 1};
+        return kq_tmap_encode(m, 2, 4, base, dims, strides, box, 1);
+    }
+    const uint64_t rb = (uint64_t)kq_kv_row_bytes(type, hd);
+    const uint64_t dims[4] = {rb, (uint64_t)n_kv, n_ctx, (uint64_t)n_seq};
+    const uint64_t strides[3] = {rb, (uint64_t)n_kv * rb, n_ctx * n_kv * rb};
+    const uint32_t box[4] = {(uint32_t)rb, 1, ROWS_PER_CTA, 1};
+    return kq_tmap_encode(m, 1, 4, base, dims, strides, box, 0);
+}
+b200_status cache_maps(const uint16_t *kc, const uint16_t *vc, int n_seq, int n_kv, int hd, int64_t seq_stride, KqKvTypes kvt,
+                       const CacheMaps **out) {
+    static std::map<std::tuple<const void *, const void *, int, int, int, int64_t, int, int>, CacheMaps> cache;
+    const auto key = std::make_tuple((const void *)kc, (const void *)vc, n_seq, n_kv, hd, seq_stride, kvt.k, kvt.v);
     auto it = cache.find(key);
     if (it == cache.end()) {
         KQ_REQUIRE(seq_stride % ((int64_t)n_kv * hd) == 0, "attention: the cache stride is not a whole number of positions");
         const uint64_t n_ctx = (uint64_t)(seq_stride / ((int64_t)n_kv * hd));
-        const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)n_kv, n_ctx, (uint64_t)n_seq};
-        const uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)n_kv * hd * 2, (uint64_t)seq_stride * 2};
-        const uint32_t box[4] = {64, 1, ROWS_PER_CTA, 1};
         CacheMaps m;
         memset(&m, 0, sizeof(m));
-        b200_status rc = kq_tmap_encode(&m.k, 2, 4, kc, dims, strides, box, 1);
+        b200_status rc = encode_cache_map(&m.k, kc, kvt.k, n_seq, n_kv, hd, n_ctx);
         if (rc != B200_OK) return rc;
-        rc = kq_tmap_encode(&m.v, 2, 4, vc, dims, strides, box, 1);
+        rc = encode_cache_map(&m.v, vc, kvt.v, n_seq, n_kv, hd, n_ctx);
         if (rc != B200_OK) return rc;
         if (cache.size() > 4096) cache.clear(); // a bound, not a policy
         it = cache.emplace(key, m).first;
@@ -359,13 +447,14 @@ int kq_attention_decode_splits(int64_t L) {
 }
 
 // q [n_seq][n_head][hd], k / v [n_seq][n_kv][hd] f32 as they come out of the qkv projection (not yet
-// rotated); caches of sequence s start s * seq_stride elements in.  scratch holds the split
+// rotated); the cache of sequence s starts s * seq_stride elements (seq_stride / hd rows) in.  scratch holds the split
 // partials, counters one zero-initialised int per (sequence, kv head).
 b200_status kq_attention_decode(const float *q, const float *k, const float *v, uint16_t *kc, uint16_t *vc,
                                 int n_seq, const int32_t *pos_dev, int pos, int n_head, int n_kv, int hd,
                                 int64_t seq_stride, float theta, int neox, int n_split, float *out, float *scratch,
-                                size_t scratch_bytes, int *counters, cudaStream_t st) {
+                                size_t scratch_bytes, int *counters, KqKvTypes kvt, cudaStream_t st) {
     KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
+    KQ_REQUIRE(kq_kv_type_ok(kvt.k) && kq_kv_type_ok(kvt.v), "attention: KV cache types %d / %d", kvt.k, kvt.v);
     KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
     if (n_split > 64) n_split = 64;
     size_t need = (size_t)n_seq * n_head * n_split * (hd + 2) * sizeof(float);
@@ -381,11 +470,11 @@ b200_status kq_attention_decode(const float *q, const float *k, const float *v, 
     const int G = n_head / n_kv;
     KQ_REQUIRE((((uintptr_t)kc | (uintptr_t)vc) & 15) == 0, "attention: the cache must be 16-byte aligned");
     const CacheMaps *maps = nullptr;
-    const b200_status rc = cache_maps(kc, vc, n_seq, n_kv, hd, seq_stride, &maps);
+    const b200_status rc = cache_maps(kc, vc, n_seq, n_kv, hd, seq_stride, kvt, &maps);
     if (rc != B200_OK) return rc;
     if (hd == 128)
         return launch_g<128>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
-                             seq_stride, n_split, scale, neox, tab, out, po, pml, counters);
+                             seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);
     return launch_g<64>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
-                        seq_stride, n_split, scale, neox, tab, out, po, pml, counters);
+                        seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);
 }

@@ -1,4 +1,5 @@
-// Causal attention for a batch of new tokens (prefill) over the f16 KV cache, on the tensor cores.
+// Causal attention for a batch of new tokens (prefill) over the KV cache (f16, or q8_0 / q4_0 rows
+// decoded to f16 while a tile is staged), on the tensor cores.
 //
 // One CTA serves 16 consecutive query rows of one sequence for the G query heads that share a KV
 // head: warp w owns head kh*G + w, so a K / V tile brought into shared memory once is used by all
@@ -10,6 +11,7 @@
 // O += P V (V fragments by ldmatrix.trans).  Only tiles up to the diagonal are visited; the query
 // tiles with the longest history are scheduled first.
 #include "kq_common.cuh"
+#include "kq_kvq.cuh"
 
 #include <math.h>
 
@@ -38,7 +40,7 @@ template <int G>
 __global__ void __launch_bounds__(G * 32) attn_prefill_kernel(const float *__restrict__ q, const __half *__restrict__ kc,
                                                                const __half *__restrict__ vc, int T, const int32_t *pos0_dev,
                                                                int pos0, int n_head, int n_kv, int64_t seq_stride,
-                                                               float scale_log2, float *__restrict__ out) {
+                                                               float scale_log2, float *__restrict__ out, KqKvTypes kvt) {
     KQ_PDL_ENTER();
     extern __shared__ __align__(128) uint8_t sm[]; // K tiles [2], then V tiles [2]
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, kh = blockIdx.y, seq = blockIdx.z;
@@ -53,19 +55,53 @@ __global__ void __launch_bounds__(G * 32) attn_prefill_kernel(const float *__res
     const __half *vbase = vc + seq * seq_stride + (int64_t)kh * HD;
     const int64_t pstride = (int64_t)n_kv * HD;
 
+    // a quantised row: decoded by plain loads into the same f16 tile layout (rows past the end as zeros)
+    auto decode_tile = [&](uint8_t *dst, const __half *cache, int type, int tile) {
+        const int rb = kq_kv_row_bytes(type, HD);
+        const uint8_t *base = reinterpret_cast<const uint8_t *>(cache) + (seq * (seq_stride / HD) + kh) * rb;
+        const int per_row = type == KQ_KV_Q8_0 ? 8 : 4; // tasks of 16 (q8_0) or 32 (q4_0) values
+        for (int i = threadIdx.x; i < BK * per_row; i += G * 32) {
+            const int row = i / per_row, c = i % per_row, pos = tile * BK + row;
+            uint4 v[4] = {};
+            if (pos < kv_end) {
+                const uint8_t *src = base + (int64_t)pos * n_kv * rb;
+                if (type == KQ_KV_Q8_0) {
+                    uint4 t2[2];
+                    kq_kv_decode16_q8_0(src, HD, c, t2);
+                    v[0] = t2[0];
+                    v[1] = t2[1];
+                } else {
+                    kq_kv_decode32_q4_0(src, HD, c, v);
+                }
+            }
+            uint4 *o = reinterpret_cast<uint4 *>(dst + row * PITCH + c * (type == KQ_KV_Q8_0 ? 32 : 64));
+            o[0] = v[0];
+            o[1] = v[1];
+            if (type != KQ_KV_Q8_0) {
+                o[2] = v[2];
+                o[3] = v[3];
+            }
+        }
+    };
     auto load_tile = [&](int buf, int tile) {
         const uint32_t ks = smem_u32(sm + buf * TILE_BYTES), vs = smem_u32(sm + (2 + buf) * TILE_BYTES);
-        for (int i = threadIdx.x; i < BK * 16; i += G * 32) {
-            const int row = i >> 4, c = i & 15, pos = tile * BK + row;
-            const bool in = pos < kv_end;
-            const int64_t off = (int64_t)(in ? pos : 0) * pstride + c * 8;
-            const uint32_t bytes = in ? 16u : 0u; // rows past the end arrive as zeros
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks + row * PITCH + c * 16), "l"(kbase + off), "r"(bytes)
-                         : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs + row * PITCH + c * 16), "l"(vbase + off), "r"(bytes)
-                         : "memory");
-        }
+        const bool kf = kvt.k == KQ_KV_F16, vf = kvt.v == KQ_KV_F16;
+        if (kf || vf)
+            for (int i = threadIdx.x; i < BK * 16; i += G * 32) {
+                const int row = i >> 4, c = i & 15, pos = tile * BK + row;
+                const bool in = pos < kv_end;
+                const int64_t off = (int64_t)(in ? pos : 0) * pstride + c * 8;
+                const uint32_t bytes = in ? 16u : 0u; // rows past the end arrive as zeros
+                if (kf)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks + row * PITCH + c * 16), "l"(kbase + off), "r"(bytes)
+                                 : "memory");
+                if (vf)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs + row * PITCH + c * 16), "l"(vbase + off), "r"(bytes)
+                                 : "memory");
+            }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        if (!kf) decode_tile(sm + buf * TILE_BYTES, kc, kvt.k, tile);
+        if (!vf) decode_tile(sm + (2 + buf) * TILE_BYTES, vc, kvt.v, tile);
     };
     load_tile(0, 0);
 
@@ -187,12 +223,12 @@ __global__ void __launch_bounds__(G * 32) attn_prefill_kernel(const float *__res
 
 } // namespace
 
-// q [n_seq * T][n_head][128] f32 (already rotated), caches f16 [seq][pos][n_kv][128]; returns
+// q [n_seq * T][n_head][128] f32 (already rotated), caches [seq][pos][n_kv] rows of 128 values; returns
 // B200_ERR_UNSUPPORTED when the shape is not one this kernel is built for (the caller then uses the
 // per-row kernel).
 b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                                      const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd, int64_t seq_stride,
-                                     float *out, cudaStream_t st) {
+                                     float *out, KqKvTypes kvt, cudaStream_t st) {
     if (hd != HD || n_kv <= 0 || n_head % n_kv != 0) return B200_ERR_UNSUPPORTED;
     const int G = n_head / n_kv;
     if (((uintptr_t)q & 7) || ((uintptr_t)out & 7) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || (seq_stride & 7))
@@ -210,7 +246,7 @@ b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const u
             if (dev >= 0 && dev < 16) attr[dev] = true;                                                                    \
         }                                                                                                                  \
         kq_launch(attn_prefill_kernel<GG>, grid, GG * 32, smem, st, q, (const __half *)kc, (const __half *)vc, T, pos0_dev, \
-                  pos0, n_head, n_kv, seq_stride, scale_log2, out);                                                        \
+                  pos0, n_head, n_kv, seq_stride, scale_log2, out, kvt);                                                      \
     }
     switch (G) {
     case 1: KQ_APF(1); break;

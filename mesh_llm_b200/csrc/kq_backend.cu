@@ -5,6 +5,7 @@
 // set_tensor / get_tensor / copy / graph_compute, every access bounds-checked against the owning
 // buffer (third_party/llama.cpp/patches/0001 lines 228-239, patches/0002 lines 570-582).
 #include "kq_common.cuh"
+#include "kq_kvq.cuh"
 
 #include <math.h>
 #include <mutex>
@@ -17,7 +18,7 @@ b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, fl
 b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                          const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
-                         int force_splits, cudaStream_t st);
+                         int force_splits, KqKvTypes kvt, cudaStream_t st);
 b200_status kq_f32_matmul(const float *W, const float *x, int64_t M, int64_t N, int64_t K, float *y,
                           cudaStream_t st);
 
@@ -429,7 +430,7 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             const size_t need = b200_attention_scratch_bytes(std::min(T, 64), n_head, hd, b->ne[2]);
             KQ_TRY(ensure_scratch(be, need));
             KQ_TRY(kq_attention((const float *)pa, (const uint16_t *)pb, (const uint16_t *)(uintptr_t)c->data, 1, T,
-                                nullptr, pos0, n_head, n_kv, hd, 0, y, (float *)be->scratch, be->scratch_bytes, 0, s));
+                                nullptr, pos0, n_head, n_kv, hd, 0, y, (float *)be->scratch, be->scratch_bytes, 0, KqKvTypes(), s));
             break;
         }
         case B200_OP_MOE_ROUTE:

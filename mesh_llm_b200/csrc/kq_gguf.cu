@@ -400,6 +400,20 @@ b200_status b200_gguf_byte_profile(const b200_gguf *g, b200_gguf_byte_profile_t 
     return B200_OK;
 }
 
+void b200_kv_types_for_model_bytes(uint64_t model_bytes, uint32_t *k_type, uint32_t *v_type) {
+    const uint64_t GB = 1000000000ull; // decimal, as the tiers are defined
+    uint32_t k = B200_TYPE_F16, v = B200_TYPE_F16;
+    if (model_bytes >= 50 * GB) {
+        k = B200_TYPE_Q4_0;
+        v = B200_TYPE_Q4_0;
+    } else if (model_bytes >= 5 * GB) {
+        k = B200_TYPE_Q8_0;
+        v = B200_TYPE_Q4_0;
+    }
+    if (k_type) *k_type = k;
+    if (v_type) *v_type = v;
+}
+
 b200_status b200_gguf_stage_config(const b200_gguf *g, int32_t layer_begin, int32_t layer_end, int32_t n_ctx,
                                    int32_t n_seq, int32_t n_ubatch, int32_t device, b200_stage_config *cfg) {
     KQ_REQUIRE(g && cfg, "gguf_stage_config: null argument");

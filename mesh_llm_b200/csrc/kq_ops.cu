@@ -3,13 +3,14 @@
 // All of them are bandwidth-trivial next to the weight stream; they are written to cost few
 // launches and to read the KV cache once per group of query heads.
 #include "kq_common.cuh"
+#include "kq_kvq.cuh"
 
 #include <math.h>
 #include <stdlib.h>
 
 b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                                      const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd, int64_t seq_stride,
-                                     float *out, cudaStream_t st);
+                                     float *out, KqKvTypes kvt, cudaStream_t st);
 
 namespace {
 
@@ -18,17 +19,41 @@ struct RopeTable {
 };
 
 // q: [rows][n_head][hd] f32 rotated in place.  k (optional): [rows][n_kv][hd] f32 rotated and
-// stored as f16 into the cache at the row's position; v likewise without rotation.
+// stored into the cache at the row's position (f16, or q8_0 / q4_0 rows); v likewise without
+// rotation.  seq_stride counts cache elements (positions x kv heads x hd) per sequence.
 __global__ void rope_store_kernel(float *q, const float *k, const float *v, const int32_t *pos,
                                   const int32_t *pos0_dev, int pos0, int T, int n_head, int n_kv, int hd, int neox,
                                   RopeTable tab, __half *k_cache, __half *v_cache,
-                                  int64_t seq_stride) {
+                                  int64_t seq_stride, KqKvTypes kvt) {
     KQ_PDL_ENTER();
     const int row = blockIdx.x; // row = seq * T + t
     const int seq = row / T, t = row % T;
     const int p = pos ? pos[row] : (pos0_dev ? *pos0_dev : pos0) + t;
     const int half = hd / 2;
-    const int n_rot = (n_head + (k ? n_kv : 0)) * half;
+    const bool kq = k && kvt.k != KQ_KV_F16, vq = v && kvt.v != KQ_KV_F16;
+    if (kq || vq) {
+        // quantised rows: one warp per block of 32 values (lane = value), the rotation recomputed per value
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, nb = hd / 32;
+        const int64_t cache_row = seq * (seq_stride / hd) + (int64_t)p * n_kv;
+        for (int u = warp; u < (kq ? n_kv * nb : 0); u += nw) {
+            const int kh = u / nb, blk = u % nb, e = blk * 32 + lane;
+            const float *vv = k + ((int64_t)row * n_kv + kh) * hd;
+            const int f = neox ? e % half : e / 2;
+            const float ang = (float)p * tab.inv_freq[f];
+            const float c = cosf(ang), s = sinf(ang);
+            const float a = vv[neox ? f : 2 * f], b = vv[neox ? f + half : 2 * f + 1];
+            const bool first = neox ? e < half : !(e & 1);
+            const float val = first ? a * c - b * s : a * s + b * c;
+            uint8_t *dst = reinterpret_cast<uint8_t *>(k_cache) + (cache_row + kh) * kq_kv_row_bytes(kvt.k, hd);
+            kq_kv_store_block(kvt.k, val, dst, hd, blk, lane);
+        }
+        for (int u = warp; u < (vq ? n_kv * nb : 0); u += nw) {
+            const int kh = u / nb, blk = u % nb, e = blk * 32 + lane;
+            uint8_t *dst = reinterpret_cast<uint8_t *>(v_cache) + (cache_row + kh) * kq_kv_row_bytes(kvt.v, hd);
+            kq_kv_store_block(kvt.v, v[((int64_t)row * n_kv + kh) * hd + e], dst, hd, blk, lane);
+        }
+    }
+    const int n_rot = (n_head + (k && !kq ? n_kv : 0)) * half;
     for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
         const int hidx = i / half, f = i % half;
         const float ang = (float)p * tab.inv_freq[f];
@@ -48,7 +73,7 @@ __global__ void rope_store_kernel(float *q, const float *k, const float *v, cons
             dst[i1] = __float2half_rn(a * s + b * c);
         }
     }
-    if (v) {
+    if (v && !vq) {
         const int n = n_kv * hd;
         __half *dst = v_cache + seq * seq_stride + (int64_t)p * n;
         for (int i = threadIdx.x; i < n; i += blockDim.x)
@@ -427,10 +452,16 @@ int kq_attention_splits(int64_t rows, int n_kv, int64_t L) {
 b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                          const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
-                         int force_splits, cudaStream_t st) {
+                         int force_splits, KqKvTypes kvt, cudaStream_t st) {
     KQ_REQUIRE(hd == 128 || hd == 64, "attention: head_dim %d not supported", hd);
     KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "attention: n_head %% n_kv");
     const int rows = n_seq * T, G = n_head / n_kv;
+    if (kvt.quantised()) {
+        // quantised rows are decoded while the tiles of the tensor-core kernel are staged
+        const b200_status rc = kq_attention_prefill_mma(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, kvt, st);
+        if (rc == B200_ERR_UNSUPPORTED) kq_set_error("attention: a quantised KV cache needs head_dim 128 and 1, 2, 4, 5 or 8 query heads per KV head");
+        return rc;
+    }
     // batches of new tokens go to the tensor-core kernel (B200_ATTN_MMA=0 keeps the per-row kernel)
     static int use_mma = -1;
     if (use_mma < 0) {
@@ -438,7 +469,7 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
         use_mma = !(v && v[0] == '0');
     }
     if (use_mma && T >= 32 && force_splits <= 0) {
-        const b200_status rc = kq_attention_prefill_mma(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, st);
+        const b200_status rc = kq_attention_prefill_mma(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, kvt, st);
         if (rc != B200_ERR_UNSUPPORTED) return rc;
     }
     int n_split = force_splits > 0 ? force_splits : kq_attention_splits(rows, n_kv, pos0 + T);
@@ -467,12 +498,14 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
 
 b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos,
                           const int32_t *pos0_dev, int pos0, int n_seq, int T, int n_head, int n_kv, int hd, float theta, int neox,
-                          uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride, cudaStream_t st) {
+                          uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride, KqKvTypes kvt, cudaStream_t st) {
     KQ_REQUIRE(hd % 2 == 0 && hd <= 256, "rope: head_dim %d", hd);
+    KQ_REQUIRE(kq_kv_type_ok(kvt.k) && kq_kv_type_ok(kvt.v), "rope: KV cache types %d / %d", kvt.k, kvt.v);
+    KQ_REQUIRE(!kvt.quantised() || hd % 32 == 0, "rope: quantised KV rows need head_dim %% 32 == 0");
     RopeTable tab;
     for (int i = 0; i < hd / 2; i++) tab.inv_freq[i] = (float)pow((double)theta, -2.0 * i / (double)hd);
     kq_launch(rope_store_kernel, n_seq * T, 256, 0, st, q, k, v, pos, pos0_dev, pos0, T, n_head, n_kv, hd, neox, tab,
-                                                 (__half *)k_cache, (__half *)v_cache, seq_stride);
+                                                 (__half *)k_cache, (__half *)v_cache, seq_stride, kvt);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -484,7 +517,7 @@ b200_status b200_rope(float *x, const int32_t *pos, int64_t T, int64_t n_head, i
                       int32_t neox, void *stream) {
     KQ_REQUIRE(T > 0 && pos, "rope: positions required");
     return kq_rope_store(x, nullptr, nullptr, pos, nullptr, 0, 1, (int)T, (int)n_head, 0, (int)hd, theta, neox,
-                         nullptr, nullptr, 0, (cudaStream_t)stream);
+                         nullptr, nullptr, 0, KqKvTypes(), (cudaStream_t)stream);
 }
 
 b200_status b200_swiglu(const float *gate, const float *up, int64_t n, float *y, void *stream) {
@@ -524,7 +557,35 @@ b200_status b200_attention(const float *q, const uint16_t *k_cache, const uint16
                            void *scratch, size_t scratch_bytes, void *stream) {
     KQ_REQUIRE(T > 0 && pos0 >= 0, "attention: bad shape");
     return kq_attention(q, k_cache, v_cache, 1, (int)T, nullptr, (int)pos0, (int)n_head, (int)n_kv, (int)hd,
-                        0, out, (float *)scratch, scratch_bytes, 0, (cudaStream_t)stream);
+                        0, out, (float *)scratch, scratch_bytes, 0, KqKvTypes(), (cudaStream_t)stream);
+}
+
+size_t b200_kv_row_bytes(uint32_t type, int64_t hd) {
+    if (!kq_kv_type_ok((int)type) || hd <= 0 || hd % 32) return 0;
+    return (size_t)kq_kv_row_bytes((int)type, (int)hd);
+}
+
+b200_status b200_kv_store(const float *k, const float *v, const int32_t *pos, int64_t T, int64_t n_kv, int64_t hd,
+                          float theta, int32_t neox, uint32_t k_type, uint32_t v_type, void *k_cache, void *v_cache,
+                          void *stream) {
+    KQ_REQUIRE(T > 0 && pos && k && v && k_cache && v_cache, "kv_store: positions, rows and caches required");
+    KqKvTypes kvt;
+    kvt.k = (int)k_type;
+    kvt.v = (int)v_type;
+    return kq_rope_store(nullptr, k, v, pos, nullptr, 0, 1, (int)T, 0, (int)n_kv, (int)hd, theta, neox,
+                         (uint16_t *)k_cache, (uint16_t *)v_cache, 0, kvt, (cudaStream_t)stream);
+}
+
+b200_status b200_attention_kv(const float *q, const void *k_cache, const void *v_cache, uint32_t k_type, uint32_t v_type,
+                              int64_t T, int64_t pos0, int64_t n_head, int64_t n_kv, int64_t hd, float *out, void *scratch,
+                              size_t scratch_bytes, void *stream) {
+    KQ_REQUIRE(T > 0 && pos0 >= 0, "attention: bad shape");
+    KqKvTypes kvt;
+    kvt.k = (int)k_type;
+    kvt.v = (int)v_type;
+    KQ_REQUIRE(kq_kv_type_ok(kvt.k) && kq_kv_type_ok(kvt.v), "attention: KV cache types %u / %u", k_type, v_type);
+    return kq_attention(q, (const uint16_t *)k_cache, (const uint16_t *)v_cache, 1, (int)T, nullptr, (int)pos0, (int)n_head,
+                        (int)n_kv, (int)hd, 0, out, (float *)scratch, scratch_bytes, 0, kvt, (cudaStream_t)stream);
 }
 
 b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T, int64_t K,

@@ -7,6 +7,7 @@
 // kernels in this directory; decode steps (T == 1) are captured once into a CUDA graph and
 // replayed, since at batch 1 the step is a chain of ~10 short kernels per layer.
 #include "kq_common.cuh"
+#include "kq_kvq.cuh"
 
 #include <map>
 #include <string>
@@ -19,17 +20,17 @@ b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, fl
 b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                          const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
-                         int force_splits, cudaStream_t st);
+                         int force_splits, KqKvTypes kvt, cudaStream_t st);
 int kq_attention_splits(int64_t rows, int n_kv, int64_t L);
 int kq_attention_decode_splits(int64_t L);
 b200_status kq_attention_decode(const float *q, const float *k, const float *v, uint16_t *kc, uint16_t *vc,
                                 int n_seq, const int32_t *pos_dev, int pos, int n_head, int n_kv, int hd,
                                 int64_t seq_stride, float theta, int neox, int n_split, float *out, float *scratch,
-                                size_t scratch_bytes, int *counters, cudaStream_t st);
+                                size_t scratch_bytes, int *counters, KqKvTypes kvt, cudaStream_t st);
 b200_status kq_rope_store(float *q, const float *k, const float *v, const int32_t *pos,
                           const int32_t *pos0_dev, int pos0, int n_seq, int T, int n_head, int n_kv, int hd,
                           float theta, int neox, uint16_t *k_cache, uint16_t *v_cache, int64_t seq_stride,
-                          cudaStream_t st);
+                          KqKvTypes kvt, cudaStream_t st);
 
 namespace {
 
@@ -129,6 +130,8 @@ struct b200_stage {
     bool resolved = false;
     // KV cache [layer_local][seq][ctx][n_kv][hd] f16
     uint16_t *kc = nullptr, *vc = nullptr;
+    KqKvTypes kvt;
+    int k_row = 0, v_row = 0; // bytes of one (position, kv head) row of each cache
     // activations
     int rows_max = 0;
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr,
@@ -227,8 +230,11 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
     for (int ll = 0; ll < n_local; ll++) {
         const LayerW &L = st->layers[ll];
         const bool last_layer = ll == n_local - 1;
-        uint16_t *kc = st->kc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
-        uint16_t *vc = st->vc + ((int64_t)ll * c.n_seq + seq0) * seq_stride;
+        // caches are [layer][sequence][position][kv head] rows of k_row / v_row bytes
+        const int64_t seq_rows = (int64_t)c.n_ctx * c.n_head_kv;
+        uint16_t *kc = (uint16_t *)((uint8_t *)st->kc + ((int64_t)ll * c.n_seq + seq0) * seq_rows * st->k_row);
+        uint16_t *vc = (uint16_t *)((uint8_t *)st->vc + ((int64_t)ll * c.n_seq + seq0) * seq_rows * st->v_row);
+        const KqKvTypes kvt = st->kvt;
         // ---- attention block
         const bool fuse = rows <= 2; // the streaming GEMV normalises and quantises its own input
         if (!fuse) OTHER_(kq_rms_norm(xin, L.attn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
@@ -257,12 +263,12 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             const int ns = kq_attention_decode_splits(pos0 + 1);
             ATTN_(kq_attention_decode(st->q, st->k, st->v, kc, vc, n_seq, pos_dev, pos0, c.n_head, c.n_head_kv, hd,
                                       seq_stride, c.rope_theta, c.rope_neox, ns, st->att, st->att_scratch,
-                                      st->att_scratch_bytes, st->attn_counters, s));
+                                      st->att_scratch_bytes, st->attn_counters, kvt, s));
         } else {
             OTHER_(kq_rope_store(st->q, st->k, st->v, nullptr, pos_dev, pos0, n_seq, T, c.n_head, c.n_head_kv, hd,
-                                 c.rope_theta, c.rope_neox, kc, vc, seq_stride, s));
+                                 c.rope_theta, c.rope_neox, kc, vc, seq_stride, kvt, s));
             ATTN_(kq_attention(st->q, kc, vc, n_seq, T, pos_dev, pos0, c.n_head, c.n_head_kv, hd, seq_stride,
-                               st->att, st->att_scratch, st->att_scratch_bytes, force_splits, s));
+                               st->att, st->att_scratch, st->att_scratch_bytes, force_splits, kvt, s));
         }
         if (fuse) {
             KqGemvSeg so = {(const uint8_t *)L.wo->dev, L.wo->type, h, st->x, nullptr, h, 0};
@@ -423,9 +429,24 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
                "stage: feed-forward sizes must be multiples of 256");
     KQ_REQUIRE(c.n_ctx > 0 && c.n_seq > 0 && c.n_ubatch > 0, "stage: n_ctx, n_seq, n_ubatch");
     KQ_REQUIRE(!c.has_output || c.n_vocab > 0, "stage: n_vocab");
+    KqKvTypes kvt;
+    kvt.k = c.kv_type_k ? c.kv_type_k : KQ_KV_F16;
+    kvt.v = c.kv_type_v ? c.kv_type_v : KQ_KV_F16;
+    KQ_REQUIRE(kq_kv_type_ok(kvt.k) && kq_kv_type_ok(kvt.v), "stage: KV cache types %d / %d (f16 = 1, q4_0 = 2, q8_0 = 8)",
+               kvt.k, kvt.v);
+    if (kvt.quantised()) {
+        const int g = c.n_head_kv > 0 ? c.n_head / c.n_head_kv : 0;
+        if (c.head_dim != 128 || !(g == 1 || g == 2 || g == 4 || g == 5 || g == 8)) {
+            kq_set_error("stage: a quantised KV cache needs head_dim 128 and 1, 2, 4, 5 or 8 query heads per KV head");
+            return B200_ERR_UNSUPPORTED;
+        }
+    }
     KqDevGuard dev_guard(c.device);
     b200_stage *st = new b200_stage();
     st->c = c;
+    st->kvt = kvt;
+    st->k_row = kq_kv_row_bytes(kvt.k, c.head_dim);
+    st->v_row = kq_kv_row_bytes(kvt.v, c.head_dim);
     const int64_t h = c.n_embd, hd = c.head_dim, nq = (int64_t)c.n_head * hd, nkv = (int64_t)c.n_head_kv * hd;
     if (c.has_embd) add_tensor(st, "token_embd.weight", B200_TYPE_Q4_K, h, c.n_vocab, 1);
     for (int l = c.layer_begin; l < c.layer_end; l++) {
@@ -471,9 +492,10 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
     };
     for (auto &t : st->tensors) A(&t.dev, t.dev_bytes + 16);
     const int64_t n_local = c.layer_end - c.layer_begin;
-    const size_t kv = (size_t)(n_local * c.n_seq * c.n_ctx * nkv) * 2;
-    A((void **)&st->kc, kv);
-    A((void **)&st->vc, kv);
+    const size_t kv_rows = (size_t)(n_local * c.n_seq * c.n_ctx * c.n_head_kv);
+    const size_t kv_k = kv_rows * st->k_row, kv_v = kv_rows * st->v_row;
+    A((void **)&st->kc, kv_k);
+    A((void **)&st->vc, kv_v);
     const int64_t R = st->rows_max = c.n_ubatch;
     const int64_t ff = c.n_expert > 0 ? 0 : c.n_ff;
     const int64_t pairs = c.n_expert > 0 ? R * c.n_expert_used : 0;
@@ -516,8 +538,8 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
         kq_set_error("stage: clearing the attention counters failed");
         rc = B200_ERR_CUDA;
     }
-    if (rc == B200_OK && kv) {
-        if (cudaMemset(st->kc, 0, kv) != cudaSuccess || cudaMemset(st->vc, 0, kv) != cudaSuccess) {
+    if (rc == B200_OK && kv_rows) {
+        if (cudaMemset(st->kc, 0, kv_k) != cudaSuccess || cudaMemset(st->vc, 0, kv_v) != cudaSuccess) {
             kq_set_error("stage: clearing the KV cache failed");
             rc = B200_ERR_CUDA;
         }

@@ -6,6 +6,8 @@ weights [N, K-bytes] uint8, activations [M, K] float32.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from . import capi
@@ -133,6 +135,46 @@ def attention(q, k_cache, v_cache, pos0):
     out = torch.empty_like(q)
     check(lib().b200_attention(ptr(q), ptr(k_cache), ptr(v_cache), T, pos0, nh, nkv, hd, ptr(out),
                                ptr(scratch), need, cur_stream()))
+    return out
+
+
+def kv_row_bytes(type_, hd):
+    return int(lib().b200_kv_row_bytes(type_, hd))
+
+
+def kv_types_for_model_bytes(model_bytes):
+    """(k_type, v_type) mesh-llm starts a server with for a model file of this size"""
+    k, v = C.c_uint32(), C.c_uint32()
+    lib().b200_kv_types_for_model_bytes(int(model_bytes), C.byref(k), C.byref(v))
+    return k.value, v.value
+
+
+def kv_cache(type_, n_ctx, n_kv, hd, device="cuda"):
+    """zeroed cache of n_ctx positions: uint8 [n_ctx, n_kv, row bytes]"""
+    return torch.zeros((n_ctx, n_kv, kv_row_bytes(type_, hd)), dtype=torch.uint8, device=device)
+
+
+def kv_store(k, v, pos, k_cache, v_cache, k_type, v_type, theta, neox):
+    """k, v: [T, n_kv, hd] f32 rows of the new tokens; k is rotated at pos[t]; both are written at
+    those positions into caches made by kv_cache()"""
+    k = _dev(k).contiguous().float()
+    v = _dev(v).contiguous().float()
+    T, nkv, hd = k.shape
+    pos = pos.to(device=k.device, dtype=torch.int32).contiguous()
+    check(lib().b200_kv_store(ptr(k), ptr(v), ptr(pos), T, nkv, hd, theta, int(neox), k_type, v_type,
+                              ptr(k_cache), ptr(v_cache), cur_stream()))
+
+
+def attention_kv(q, k_cache, v_cache, k_type, v_type, pos0):
+    """attention() over caches of the given row types (made by kv_cache / kv_store)"""
+    q = _dev(q).contiguous().float()
+    T, nh, hd = q.shape
+    n_ctx, nkv, _ = k_cache.shape
+    need = lib().b200_attention_scratch_bytes(T, nh, hd, n_ctx)
+    scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+    out = torch.empty_like(q)
+    check(lib().b200_attention_kv(ptr(q), ptr(k_cache), ptr(v_cache), k_type, v_type, T, pos0, nh, nkv, hd,
+                                  ptr(out), ptr(scratch), need, cur_stream()))
     return out
 
 

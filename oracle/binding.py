@@ -14,7 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libkquant_oracle.so")
 
-TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 12, 14
+TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 2, 8, 12, 14
 Q4K_BYTES, Q6K_BYTES, QK_K = 144, 210, 256
 
 
@@ -39,6 +39,7 @@ class Config(C.Structure):
         ("rope_neox", C.c_int32), ("qkv_bias", C.c_int32), ("qk_norm", C.c_int32),
         ("has_embd", C.c_int32), ("has_output", C.c_int32),
         ("rms_eps", C.c_float), ("rope_theta", C.c_float),
+        ("kv_type_k", C.c_int32), ("kv_type_v", C.c_int32),
     ]
 
 
@@ -69,6 +70,11 @@ def lib():
         L.orc_f16_to_f32.argtypes = [vp, i64, vp]
         L.orc_attention.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, vp]
         L.orc_get_rows.argtypes = [i32, vp, vp, i64, i64, vp]
+        L.orc_quantize_q8_0.argtypes = [vp, i64, vp]
+        L.orc_quantize_q4_0.argtypes = [vp, i64, vp]
+        L.orc_dequant_q8_0.argtypes = [vp, i64, vp]
+        L.orc_dequant_q4_0.argtypes = [vp, i64, vp]
+        L.orc_kv_round_trip.argtypes = [i32, vp, i64, vp]
         L.orc_argmax.argtypes = [vp, i64, i64, vp]
         L.orc_moe_route.argtypes = [vp, i64, i64, i64, vp, vp]
         L.orc_model_create.argtypes = [C.POINTER(Config)]
@@ -198,6 +204,32 @@ def attention(q, kc, vc, pos0):
     out = np.empty_like(q)
     lib().orc_attention(_p(q), _p(kc), _p(vc), T, pos0, nh, kc.shape[1], hd, _p(out))
     return out
+
+
+def kv_quantize(type_, x):
+    """x: [..., n] f32 (n % 32 == 0) -> ggml q8_0 / q4_0 blocks, uint8 [..., n/32 * (34 | 18)]"""
+    x = _c(x, np.float32)
+    bpb = 34 if type_ == TYPE_Q8_0 else 18
+    out = np.empty(x.shape[:-1] + (x.shape[-1] // 32 * bpb,), np.uint8)
+    (lib().orc_quantize_q8_0 if type_ == TYPE_Q8_0 else lib().orc_quantize_q4_0)(_p(x), x.size, _p(out))
+    return out
+
+
+def kv_dequantize(type_, blocks):
+    blocks = _c(blocks, np.uint8)
+    bpb = 34 if type_ == TYPE_Q8_0 else 18
+    nb = blocks.size // bpb
+    out = np.empty(nb * 32, np.float32)
+    (lib().orc_dequant_q8_0 if type_ == TYPE_Q8_0 else lib().orc_dequant_q4_0)(_p(blocks), nb, _p(out))
+    return out.reshape(blocks.shape[:-1] + (blocks.shape[-1] // bpb * 32,))
+
+
+def kv_round_trip(type_, x):
+    """the f16 values attention sees for rows stored in a cache of `type_` (F16, Q8_0 or Q4_0)"""
+    x = _c(x, np.float32)
+    y = np.empty(x.shape, np.uint16)
+    lib().orc_kv_round_trip(type_, _p(x), x.size, _p(y))
+    return y
 
 
 def get_rows(type_, W, ids, K):

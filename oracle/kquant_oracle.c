@@ -182,6 +182,8 @@ int64_t orc_row_bytes(int type, int64_t k) {
     switch (type) {
     case ORC_TYPE_F32: return k * 4;
     case ORC_TYPE_F16: return k * 2;
+    case ORC_TYPE_Q8_0: return k / 32 * 34;
+    case ORC_TYPE_Q4_0: return k / 32 * 18;
     case ORC_TYPE_Q4_K: return k / 256 * ORC_Q4K_BYTES;
     case ORC_TYPE_Q6_K: return k / 256 * ORC_Q6K_BYTES;
     default: return -1;
@@ -527,6 +529,84 @@ void orc_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int64
         }
 }
 
+/* ---------------------------------------------------------------- KV-cache row formats */
+void orc_quantize_q8_0(const float *x, int64_t n, uint8_t *blocks) {
+    for (int64_t b = 0; b < n / 32; b++) {
+        const float *xb = x + b * 32;
+        uint8_t *blk = blocks + b * 34;
+        float amax = 0.f;
+        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(xb[j]));
+        const float d = amax / 127.f, id = d ? 1.f / d : 0.f;
+        const uint16_t dh = f2h(d);
+        memcpy(blk, &dh, 2);
+        for (int j = 0; j < 32; j++) blk[2 + j] = (uint8_t)(int8_t)roundf(xb[j] * id);
+    }
+}
+
+void orc_quantize_q4_0(const float *x, int64_t n, uint8_t *blocks) {
+    for (int64_t b = 0; b < n / 32; b++) {
+        const float *xb = x + b * 32;
+        uint8_t *blk = blocks + b * 18;
+        float amax = 0.f, mx = 0.f;
+        for (int j = 0; j < 32; j++)
+            if (amax < fabsf(xb[j])) {
+                amax = fabsf(xb[j]);
+                mx = xb[j];
+            }
+        const float d = mx / -8.f, id = d ? 1.f / d : 0.f;
+        const uint16_t dh = f2h(d);
+        memcpy(blk, &dh, 2);
+        for (int j = 0; j < 16; j++) {
+            int q0 = (int)(int8_t)(xb[j] * id + 8.5f), q1 = (int)(int8_t)(xb[j + 16] * id + 8.5f);
+            if (q0 > 15) q0 = 15;
+            if (q1 > 15) q1 = 15;
+            blk[2 + j] = (uint8_t)(q0 | (q1 << 4));
+        }
+    }
+}
+
+void orc_dequant_q8_0(const uint8_t *blocks, int64_t nblocks, float *out) {
+    for (int64_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 34;
+        uint16_t dh;
+        memcpy(&dh, blk, 2);
+        const float d = h2f(dh);
+        for (int j = 0; j < 32; j++) out[b * 32 + j] = (float)(int8_t)blk[2 + j] * d;
+    }
+}
+
+void orc_dequant_q4_0(const uint8_t *blocks, int64_t nblocks, float *out) {
+    for (int64_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 18;
+        uint16_t dh;
+        memcpy(&dh, blk, 2);
+        const float d = h2f(dh);
+        for (int j = 0; j < 16; j++) {
+            out[b * 32 + j] = (float)((int)(blk[2 + j] & 0x0F) - 8) * d;
+            out[b * 32 + 16 + j] = (float)((int)(blk[2 + j] >> 4) - 8) * d;
+        }
+    }
+}
+
+void orc_kv_round_trip(int type, const float *x, int64_t n, uint16_t *y) {
+    if (type == ORC_TYPE_Q8_0 || type == ORC_TYPE_Q4_0) {
+        uint8_t *blk = (uint8_t *)malloc((size_t)(n / 32 * 34));
+        float *f = (float *)malloc(sizeof(float) * (size_t)n);
+        if (type == ORC_TYPE_Q8_0) {
+            orc_quantize_q8_0(x, n, blk);
+            orc_dequant_q8_0(blk, n / 32, f);
+        } else {
+            orc_quantize_q4_0(x, n, blk);
+            orc_dequant_q4_0(blk, n / 32, f);
+        }
+        orc_f32_to_f16(f, n, y);
+        free(f);
+        free(blk);
+    } else {
+        orc_f32_to_f16(x, n, y);
+    }
+}
+
 void orc_get_rows(int type, const uint8_t *W, const int32_t *ids, int64_t T, int64_t K, float *y) {
     int64_t rb = orc_row_bytes(type, K);
     for (int64_t t = 0; t < T; t++) {
@@ -833,8 +913,8 @@ int orc_model_forward(orc_model *m, int32_t seq, const int32_t *tokens, const fl
         orc_rope(k, pos, T, nkvh, hd, c->rope_theta, c->rope_neox);
         uint16_t *kc = m->kc + ((ll * c->n_seq + seq) * c->n_ctx) * nkv;
         uint16_t *vc = m->vc + ((ll * c->n_seq + seq) * c->n_ctx) * nkv;
-        orc_f32_to_f16(k, T * nkv, kc + pos0 * nkv);
-        orc_f32_to_f16(v, T * nkv, vc + pos0 * nkv);
+        orc_kv_round_trip(c->kv_type_k, k, T * nkv, kc + pos0 * nkv);
+        orc_kv_round_trip(c->kv_type_v, v, T * nkv, vc + pos0 * nkv);
         orc_attention(q, kc, vc, T, pos0, nh, nkvh, hd, att);
         mm(layer_tensor(m, l, "attn_output.weight"), att, T, o);
         for (int64_t i = 0; i < T * h; i++) x[i] += o[i];

@@ -32,7 +32,7 @@ extern "C" {
 #define ORC_Q6K_BYTES 210 /* 128 B ql, 64 B qh, 16 x int8 scales, f16 d     */
 
 /* ggml type ids (constants.py GGMLQuantizationType) */
-enum { ORC_TYPE_F32 = 0, ORC_TYPE_F16 = 1, ORC_TYPE_Q4_K = 12, ORC_TYPE_Q6_K = 14 };
+enum { ORC_TYPE_F32 = 0, ORC_TYPE_F16 = 1, ORC_TYPE_Q4_0 = 2, ORC_TYPE_Q8_0 = 8, ORC_TYPE_Q4_K = 12, ORC_TYPE_Q6_K = 14 };
 
 /* ---- block formats ------------------------------------------------------------------- */
 void orc_dequant_q4k(const uint8_t *blocks, int64_t nblocks, float *out);
@@ -73,6 +73,18 @@ void orc_f16_to_f32(const uint16_t *x, int64_t n, float *y);
  * holds rows [0, pos0+T).  q: [T][n_head][hd]; k/v cache: [n_ctx][n_kv][hd] f16.            */
 void orc_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int64_t T,
                    int64_t pos0, int64_t n_head, int64_t n_kv, int64_t hd, float *out);
+/* KV-cache row formats (ggml block_q8_0: f16 d + 32 x int8, 34 bytes; block_q4_0: f16 d + 16 bytes
+ * of nibbles, element j in the low and element j + 16 in the high nibble of byte j, 18 bytes).
+ * Quantisers as published in ggml-quants.c (quantize_row_q8_0_ref: d = amax / 127, q = round(x / d);
+ * quantize_row_q4_0_ref: d = (the element of largest magnitude) / -8, q = min(15, (int)(x / d + 8.5)));
+ * mesh-llm selects these types by model size (mesh-llm/src/inference/launch.rs:568-591).    */
+void orc_quantize_q8_0(const float *x, int64_t n, uint8_t *blocks);
+void orc_quantize_q4_0(const float *x, int64_t n, uint8_t *blocks);
+void orc_dequant_q8_0(const uint8_t *blocks, int64_t nblocks, float *out);
+void orc_dequant_q4_0(const uint8_t *blocks, int64_t nblocks, float *out);
+/* what attention reads back from a cache of `type` for the f32 row x: x itself rounded to f16
+ * (F16), or quantised, decoded and rounded to f16                                           */
+void orc_kv_round_trip(int type, const float *x, int64_t n, uint16_t *y);
 void orc_get_rows(int type, const uint8_t *W, const int32_t *ids, int64_t T, int64_t K, float *y);
 void orc_argmax(const float *x, int64_t T, int64_t n, int32_t *idx);
 /* router: softmax over E logits, top-k (ties -> lower id), weights renormalised to sum 1     */
@@ -89,6 +101,7 @@ typedef struct {
     int32_t rope_neox, qkv_bias, qk_norm;
     int32_t has_embd, has_output;              /* first / last stage          */
     float rms_eps, rope_theta;
+    int32_t kv_type_k, kv_type_v; /* 0 or ORC_TYPE_F16 = f16; ORC_TYPE_Q8_0; ORC_TYPE_Q4_0      */
 } orc_config;
 
 typedef struct orc_model orc_model;

@@ -8,6 +8,9 @@ an independent decoder for Q4_K / Q6_K blocks:
 Outputs (small .npz files):
   kquant_blocks.npz  random valid Q4_K / Q6_K blocks (every scale/min code reachable) and their
                      f32 decode as computed by gguf.quants.dequantize -- pins the block layout.
+  kv_rows.npz        f32 rows (mixed magnitudes, an all-zero block, a constant block, an outlier) with
+                     their ggml q8_0 / q4_0 blocks and decodes from gguf.quants.quantize /
+                     dequantize -- pins the KV-cache row quantisers.
   handoff_pattern.npz the byte patterns of the stage hand-off exactness cases that
                      third_party/llama.cpp/patches/0002 (test_direct_push, lines 1612-1745)
                      pushes between two servers: i & 0xFF and 0xFF - (i & 0xFF) over 4096 bytes,
@@ -58,6 +61,20 @@ def main():
         os.path.join(HERE, "handoff_pattern.npz"),
         forward=(i & 0xFF).astype(np.uint8), reverse=(0xFF - (i & 0xFF)).astype(np.uint8),
         partial_offset=np.int64(1024), partial_size=np.int64(2048), large_bytes=np.int64(16 << 20),
+    )
+    from gguf.quants import quantize
+
+    x = (rng.standard_normal((48, 128)) * rng.uniform(0.01, 10.0, size=(48, 1))).astype(np.float32)
+    x[0] = 0.0
+    x[1, :32] = 1.0
+    x[2, 5] = -100.0
+    x[3, 40] = 64.0
+    q8 = quantize(x, T.Q8_0)
+    q4 = quantize(x, T.Q4_0)
+    np.savez_compressed(
+        os.path.join(HERE, "kv_rows.npz"), x=x,
+        q8_0=q8, q8_0_f32=dequantize(q8, T.Q8_0).astype(np.float32),
+        q4_0=q4, q4_0_f32=dequantize(q4, T.Q4_0).astype(np.float32),
     )
     print("wrote golden vectors to", HERE)
 

@@ -33,7 +33,7 @@ def test_tensor_descriptor_matches_rpc_tensor_wire_size():
     # third_party/llama.cpp/patches/0002 lines 1070-1085: 296 bytes packed
     assert C.sizeof(capi.Tensor) == 296
     assert capi.Tensor.name.offset == 296 - 68 and capi.Tensor.data.offset == 296 - 76
-    assert C.sizeof(capi.StageConfig) == 23 * 4
+    assert C.sizeof(capi.StageConfig) == 25 * 4
 
 
 def test_host_calls_need_no_gpu_and_report_errors():
@@ -43,6 +43,8 @@ def test_host_calls_need_no_gpu_and_report_errors():
     assert L.b200_reg_name() == b"B200"
     assert L.b200_status_string(-4) == b"unsupported"
     assert L.b200_row_bytes(12, 5120) == 2880 and L.b200_row_bytes(14, 5120) == 4200
+    # KV-cache rows: q8_0 / q4_0 codes + f16 scales, padded to 16 bytes
+    assert L.b200_kv_row_bytes(8, 128) == 144 and L.b200_kv_row_bytes(2, 128) == 80 and L.b200_kv_row_bytes(1, 128) == 256
     assert L.b200_device_row_bytes(14, 5120) == 4208 and L.b200_device_row_bytes(12, 5120) == 2880
     assert L.b200_mul_mat_scratch_bytes(1, 256) == 768
     assert L.b200_dev_supports_op(1, 12, 0) == 1 and L.b200_dev_supports_op(1, 8, 0) == 0

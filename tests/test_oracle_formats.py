@@ -216,3 +216,30 @@ def test_moe_route():
         assert list(ids[t]) == order
         np.testing.assert_allclose(w[t], p[t, order] / p[t, order].sum(), rtol=1e-5)
     np.testing.assert_allclose(w.sum(-1), 1.0, rtol=1e-6)
+
+
+# ---- KV-cache row formats (ggml q8_0 / q4_0) ------------------------------------------------------
+@pytest.fixture(scope="module")
+def kv_gold():
+    return np.load(os.path.join(GOLD, "kv_rows.npz"))
+
+
+@pytest.mark.parametrize("name, ty", [("q8_0", orc.TYPE_Q8_0), ("q4_0", orc.TYPE_Q4_0)])
+def test_kv_row_quantisers_match_golden(kv_gold, name, ty):
+    blocks = orc.kv_quantize(ty, kv_gold["x"])
+    np.testing.assert_array_equal(blocks, kv_gold[name])
+    np.testing.assert_array_equal(orc.kv_dequantize(ty, kv_gold[name]), kv_gold[name + "_f32"])
+
+
+def test_kv_round_trip_is_decode_rounded_to_f16(kv_gold):
+    x = kv_gold["x"]
+    for name, ty in (("q8_0", orc.TYPE_Q8_0), ("q4_0", orc.TYPE_Q4_0)):
+        got = orc.kv_round_trip(ty, x)
+        np.testing.assert_array_equal(got, kv_gold[name + "_f32"].astype(np.float16).view(np.uint16))
+    np.testing.assert_array_equal(orc.kv_round_trip(orc.TYPE_F16, x), x.astype(np.float16).view(np.uint16))
+    # the quantisation error stays inside the formats' bounds: about half a step of amax / 127 (plus the f16 rounding of d), one step of amax / 8
+    amax = np.abs(x).reshape(-1, 4, 32).max(-1, keepdims=True)
+    e8 = np.abs(kv_gold["q8_0_f32"] - x).reshape(-1, 4, 32)
+    e4 = np.abs(kv_gold["q4_0_f32"] - x).reshape(-1, 4, 32)
+    assert (e8 <= amax / 127 * 0.57 + 1e-6).all()
+    assert (e4 <= amax / 8 * 1.01 + 1e-6).all()

@@ -68,3 +68,22 @@ def test_moe_forward_runs_and_is_finite():
     h, logits = m.forward(tokens=toks)
     assert np.isfinite(logits).all() and np.isfinite(h).all()
     assert logits.shape == (5, 512)
+
+
+def test_quantised_kv_cache_changes_little_and_keeps_prefill_equal_to_decode():
+    """q8_0 K / q4_0 V (what mesh-llm launches 5-50 GB models with) perturbs the logits slightly
+    and, like the f16 cache, gives the same result token by token as in one batch."""
+    kw = dict(DENSE, head_dim=128, n_embd=512)
+    toks = np.arange(1, 13, dtype=np.int32)
+    ref = orc.Model(**kw)
+    ref.generate(3)
+    want = ref.forward(tokens=toks)[1]
+    m = orc.Model(**kw, kv_type_k=orc.TYPE_Q8_0, kv_type_v=orc.TYPE_Q4_0)
+    m.generate(3)
+    got = m.forward(tokens=toks)[1]
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert 0 < err < 0.3  # random weights: no trained redundancy to absorb the 4-bit V rows
+    m2 = orc.Model(**kw, kv_type_k=orc.TYPE_Q8_0, kv_type_v=orc.TYPE_Q4_0)
+    m2.generate(3)
+    rows = [m2.forward(tokens=toks[i:i + 1], pos0=i)[1][0] for i in range(len(toks))]
+    np.testing.assert_allclose(np.stack(rows), got, rtol=0, atol=1e-6)
