@@ -258,6 +258,8 @@ def main():
     ap.add_argument("--micro-iters", type=int, default=20)
     ap.add_argument("--balance", action="store_true", help="N > 1: split layers by weight bytes (the last stage, which "
                     "holds the output head, gets fewer layers) instead of equal layer counts")
+    ap.add_argument("--handoff", default="peer", choices=["peer", "nccl"], help="N > 1: how a decode activation reaches the "
+                    "next stage: the library's peer-memory kernels, or torch.distributed send/recv")
     ap.add_argument("--kv", default="f16", choices=["f16", "q8_0-q4_0", "q4_0-q4_0", "auto"],
                     help="KV-cache row types (K-V); auto = the pair mesh-llm starts a model of this size with")
     ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")

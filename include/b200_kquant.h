@@ -374,6 +374,32 @@ B200_API b200_status b200_gguf_write_expert_shard(const b200_gguf *g, const int3
                                                   int32_t n_ids, const char *dst_path,
                                                   uint64_t *bytes_written);
 
+/* ---- stage-boundary hand-off through peer memory -----------------------------------------------
+ * Replaces the activation transfer between two stages (third_party/llama.cpp/patches/0002 lines
+ * 544-622: device -> host -> TCP -> host -> device; direct push lines 624-735) for stages on GPUs
+ * of one box.  The receiver creates an endpoint: a ring of n_slots landing slots in its own HBM.
+ * The sender maps it (handoff_open with the 64-byte handle exported by the receiver's process, or
+ * handoff_open_local inside one process) and sends payload number seqno = 0, 1, 2, ... : one
+ * kernel writes the payload over NVLink and publishes the number.  The receiver's handoff_wait is
+ * one kernel that acquires payload seqno and copies it to dst (dst null: *slot is the payload in
+ * place; call handoff_release(seqno) after its readers).  Waits are bounded by limit_ns (0 = 5 s):
+ * when one runs out, nothing is copied and handoff_status (call it after synchronising the stream)
+ * returns 1 on the sender's mapping (no free slot) or 2 on the endpoint (payload not arrived); the
+ * calls that follow on that object then give up at once.  Sizes are multiples of 4 bytes.        */
+typedef struct b200_handoff b200_handoff;
+B200_API b200_status b200_handoff_create(size_t slot_bytes, int32_t n_slots, b200_handoff **out);
+B200_API b200_status b200_handoff_export(const b200_handoff *endpoint, void *handle64);
+B200_API b200_status b200_handoff_open(const void *handle64, size_t slot_bytes, int32_t n_slots,
+                                       b200_handoff **out);
+B200_API b200_status b200_handoff_open_local(const b200_handoff *endpoint, b200_handoff **out);
+B200_API b200_status b200_handoff_send(b200_handoff *remote, const void *src, size_t bytes,
+                                       uint64_t seqno, uint64_t limit_ns, void *stream);
+B200_API b200_status b200_handoff_wait(b200_handoff *endpoint, void *dst, size_t bytes, uint64_t seqno,
+                                       uint64_t limit_ns, const void **slot, void *stream);
+B200_API b200_status b200_handoff_release(b200_handoff *endpoint, uint64_t seqno, void *stream);
+B200_API b200_status b200_handoff_status(b200_handoff *h, int32_t *status);
+B200_API void b200_handoff_free(b200_handoff *h);
+
 /* ---- worker front end: the ggml RPC wire protocol (version 4.1) served from this backend ------
  * What mesh-llm spawns as `rpc-server -d DEV -p PORT --gguf PATH` (mesh-llm/src/inference/launch.rs:
  * 887-933).  Commands and packed messages as in third_party/llama.cpp/patches/0002 lines 1042-1146

@@ -125,6 +125,15 @@ SIGNATURES = {
     "b200_cpy_f32_f16": (i32, [vp, i64, vp, vp]),
     "b200_attention": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, vp, vp, sz, vp]),
     "b200_attention_scratch_bytes": (sz, [i64, i64, i64, i64]),
+    "b200_handoff_create": (i32, [sz, i32, C.POINTER(vp)]),
+    "b200_handoff_export": (i32, [vp, vp]),
+    "b200_handoff_open": (i32, [vp, sz, i32, C.POINTER(vp)]),
+    "b200_handoff_open_local": (i32, [vp, C.POINTER(vp)]),
+    "b200_handoff_send": (i32, [vp, vp, sz, u64, u64, vp]),
+    "b200_handoff_wait": (i32, [vp, vp, sz, u64, u64, C.POINTER(vp), vp]),
+    "b200_handoff_release": (i32, [vp, u64, vp]),
+    "b200_handoff_status": (i32, [vp, C.POINTER(i32)]),
+    "b200_handoff_free": (None, [vp]),
     "b200_kv_row_bytes": (sz, [u32, i64]),
     "b200_kv_types_for_model_bytes": (None, [u64, C.POINTER(u32), C.POINTER(u32)]),
     "b200_kv_store": (i32, [vp, vp, vp, i64, i64, i64, C.c_float, i32, u32, u32, vp, vp, vp]),

@@ -96,6 +96,63 @@ class Transport:
             self.wait_slot(k)
 
 
+class PeerTransport:
+    """Transport's interface with the moves done by kernels of libb200kq.so: the sender writes the
+    payload into the receiving stage's landing ring through the NVLink peer mapping and publishes its
+    number; the receiver's kernel acquires it and copies it to the stage's input (handoff.py).  No
+    rendezvous and no host involvement per token; buffers are reused in stream order, so wait_slot
+    has nothing to wait for.  Endpoints: every stage but the first receives hidden states, the first
+    receives the greedy tokens of the last."""
+
+    def __init__(self, dist, rank, world, hidden_bytes, n_slots=16):
+        from .handoff import Endpoint, Sender
+
+        self.rank, self.world = rank, world
+        self.rx_h = Endpoint(hidden_bytes, n_slots) if rank > 0 else None
+        self.rx_t = Endpoint(16, n_slots) if rank == 0 and world > 1 else None
+        mine = {"h": self.rx_h.handle() if self.rx_h else None, "t": self.rx_t.handle() if self.rx_t else None}
+        handles = [None] * world
+        dist.all_gather_object(handles, mine)
+        self.tx_h = Sender.open(handles[rank + 1]["h"], hidden_bytes, n_slots) if rank < world - 1 else None
+        self.tx_t = Sender.open(handles[0]["t"], 16, n_slots) if rank == world - 1 and world > 1 else None
+
+    def wait_slot(self, key):
+        pass
+
+    def send_hidden(self, t, slot):
+        self.tx_h.send(t)
+
+    def recv_hidden(self, t):
+        self.rx_h.wait(t)
+
+    def send_token(self, t, slot):
+        self.tx_t.send(t)
+
+    def recv_token(self, t):
+        self.rx_t.wait(t)
+
+    def drain(self):
+        pass
+
+    def check(self):
+        """after the stream has been synchronised: raises if any bounded wait gave up"""
+        for o in (self.rx_h, self.rx_t, self.tx_h, self.tx_t):
+            if o is not None:
+                o.raise_on_timeout()
+
+    def close_senders(self):
+        """unmap the peers' rings; every rank does this (and a barrier) before any ring is freed"""
+        for o in (self.tx_h, self.tx_t):
+            if o is not None:
+                o.close()
+
+    def close(self):
+        self.close_senders()
+        for o in (self.rx_h, self.rx_t):
+            if o is not None:
+                o.close()
+
+
 def run_decode(stage_step, sched, rank, steps, transport, hidden_in, hidden_out, token_in, token_out,
                first_tokens, on_token=None, on_input=None):
     """Generic pipelined greedy decode.
@@ -167,12 +224,24 @@ def bench_pipeline(args, w, metric, rank, world, local):
     n_seq = world
     steps, warm = args.steps, max(3, args.warmup)
     n_ctx = w["prefill"] + 2 * (steps + warm) + 72
+    ids, names = {"f16": 1, "q4_0": 2, "q8_0": 8}, {1: "f16", 2: "q4_0", 8: "q8_0"}
+    kv = getattr(args, "kv", "f16")
+    if kv == "auto":  # the pair mesh-llm starts a model file of this size with
+        from bench import step_gemv_bytes
+        from .ops import kv_types_for_model_bytes
+
+        kt, vt = kv_types_for_model_bytes(step_gemv_bytes(w, 0, w["n_layer"], True) + w["n_vocab"] * w["n_embd"] * 0.5625)
+    else:
+        kt, vt = [ids[t] for t in (kv + "-" + kv).split("-")[:2]]
     st = Stage(**model, layer_begin=lo, layer_end=hi, has_embd=int(rank == 0), has_output=int(rank == world - 1),
-               n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local)
+               n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
     st.generate(20251125)
     tr = Transport(dist, rank, world, pg_fwd, pg_tok)
     sched = Schedule(world, n_seq)
     h = w["n_embd"]
+    # decode hand-off: peer-memory kernels unless --handoff nccl asks for send/recv; prefill ubatches (MBs) use send/recv
+    peer = getattr(args, "handoff", "peer") == "peer"
+    tr_dec = PeerTransport(dist, rank, world, h * 4) if peer else tr
     rng = np.random.default_rng(1234)
     prompts = torch.from_numpy(rng.integers(0, w["n_vocab"], (n_seq, w["prefill"])).astype(np.int32)).to(dev)
     hid_big = torch.empty((512, h), dtype=torch.float32, device=dev)
@@ -226,7 +295,7 @@ def bench_pipeline(args, w, metric, rank, world, local):
         token.copy_(h_tok, non_blocking=True)
 
     def decode(k, base, first_tokens, e2e=False):
-        run_decode(make_step(base), sched, rank, k, tr, hid1_in, hid1_out, tok1, tok_out, first_tokens,
+        run_decode(make_step(base), sched, rank, k, tr_dec, hid1_in, hid1_out, tok1, tok_out, first_tokens,
                    on_token=(lambda s_, k_, t_: via_host(t_)) if (e2e and last) else None,
                    on_input=via_host if (e2e and rank == 0) else None)
 
@@ -266,6 +335,8 @@ def bench_pipeline(args, w, metric, rank, world, local):
     te = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     clocks = sampler.stop(t0, t1) if rank == 0 else None
+    if peer:
+        tr_dec.check()
 
     if rank == 0:
         total = steps * n_seq
@@ -277,14 +348,20 @@ def bench_pipeline(args, w, metric, rank, world, local):
                        "workload": f"{w['name']} ({w['n_layer']} layers) split into {world} contiguous layer ranges, "
                                    f"one per GPU; {n_seq} sequences in flight, decode batch 1 per stage at context "
                                    f"{w['prefill']}+; f32 [1 x {h}] activation handed to the next stage over NVLink",
-                       "sequences_in_flight": n_seq,
+                       "sequences_in_flight": n_seq, "kv_cache": names[kt] + "-" + names[vt],
                        "l2": "each stage streams its weights every tick (>> 126 MB L2), no flush needed"},
             "e2e": {"value": total / (float(te.item()) * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n_seq,
                     "d2h_bytes_per_step": 4 * n_seq},
             "gpu_launches": int(launches.item()), "clocks": clocks,
             "prefill_tok_s": None if args.no_prefill else n_seq * w["prefill"] / (float(t_prefill.item()) * 1e-3),
-            "handoff": "torch.distributed send/recv (NCCL P2P over NVLink)",
+            "handoff": "peer-memory landing ring written by the sending stage's kernel over NVLink (prefill ubatches: "
+                       "torch.distributed send/recv)" if peer else "torch.distributed send/recv (NCCL P2P over NVLink)",
         }))
+    if peer:
+        tr_dec.close_senders()
+    dist.barrier()
+    if peer:
+        tr_dec.close()
     dist.destroy_process_group()
 
 
