@@ -260,6 +260,8 @@ def main():
                     "holds the output head, gets fewer layers) instead of equal layer counts")
     ap.add_argument("--handoff", default="peer", choices=["peer", "nccl"], help="N > 1: how a decode activation reaches the "
                     "next stage: the library's peer-memory kernels, or torch.distributed send/recv")
+    ap.add_argument("--handoff-latency", action="store_true", help="N = 2: round trips of one [1 x n_embd] f32 row between "
+                    "the two GPUs, peer-memory hand-off against send/recv; one line with the one-way latencies")
     ap.add_argument("--kv", default="f16", choices=["f16", "q8_0-q4_0", "q4_0-q4_0", "auto"],
                     help="KV-cache row types (K-V); auto = the pair mesh-llm starts a model of this size with")
     ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")
@@ -287,6 +289,8 @@ def main():
         args.gpus = world
     if world > 1:
         from mesh_llm_b200 import pipeline
+        if args.handoff_latency:
+            return pipeline.bench_handoff_latency(args, w, rank, world, local)
         if w.get("n_expert", 0):
             return pipeline.bench_expert_replicas(args, w, METRIC, rank, world, local)
         return pipeline.bench_pipeline(args, w, METRIC, rank, world, local)

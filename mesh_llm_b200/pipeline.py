@@ -365,6 +365,76 @@ def bench_pipeline(args, w, metric, rank, world, local):
     dist.destroy_process_group()
 
 
+def bench_handoff_latency(args, w, rank, world, local):
+    """One [1 x n_embd] f32 row bounced between ranks 0 and 1 `iters` times inside one stream on each side,
+    no host synchronisation in between: half the round trip is the one-way cost of a hand-off as a stage
+    sees it (launch of the send, the link, the wait).  Measured for the peer-memory kernels and for
+    torch.distributed send / recv; rank 0 prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    h = w["n_embd"]
+    x = torch.randn(1, h, device=dev)
+    y = torch.empty_like(x)
+    iters = max(200, args.steps * 8)
+    out = {}
+    if rank < 2:
+        from .handoff import Endpoint, Sender
+
+        rx = Endpoint(h * 4, 16)
+    else:
+        rx = None
+    handles = [None] * world
+    dist.all_gather_object(handles, rx.handle() if rx else None)
+    tx = Sender.open(handles[1 - rank], h * 4, 16) if rank < 2 else None
+
+    def bounce_peer(n):
+        for _ in range(n):
+            if rank == 0:
+                tx.send(x)
+                rx.wait(y)
+            elif rank == 1:
+                rx.wait(y)
+                tx.send(y)
+
+    def bounce_nccl(n):
+        for _ in range(n):
+            if rank == 0:
+                dist.send(x, 1)
+                dist.recv(y, 1)
+            elif rank == 1:
+                dist.recv(y, 0)
+                dist.send(y, 0)
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn in (("peer", bounce_peer), ("nccl", bounce_nccl)):
+        fn(20)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        fn(iters)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name + "_one_way_us"] = e0.elapsed_time(e1) * 1e3 / iters / 2
+        if rank == 0 and name == "peer":
+            assert torch.equal(x, y), "the row did not come back bit for bit"
+    if rank < 2:
+        rx.raise_on_timeout()
+        tx.raise_on_timeout()
+        tx.close()
+    dist.barrier()
+    if rx:
+        rx.close()
+    if rank == 0:
+        print(json.dumps({"handoff_latency": out, "payload_bytes": h * 4, "round_trips": iters, "n_gpus": world,
+                          "method": "CUDA events on rank 0 around the whole loop, no host synchronisation inside"}))
+    dist.destroy_process_group()
+
+
 def bench_expert_replicas(args, w, metric, rank, world, local):
     """bench.py body for an MoE model at N > 1: N independent replicas, rank r holding the trunk and
     experts [r*E/N, (r+1)*E/N) with the router rows of those experts (the layout the reference's
