@@ -235,6 +235,17 @@ struct KqActPrep {
     int32_t do_norm;
 };
 
+// one phase of a fused chain of decode matmuls: y = W . prep(x) (+ residual / SwiGLU of a gate-up pair)
+struct KqFusedPhase {
+    KqGemvSeg segs[2];
+    int32_t nseg;
+    int64_t K;
+    const float *residual;
+    int32_t swiglu;
+    KqActPrep prep;
+};
+b200_status kq_launch_gemv_fused(const KqFusedPhase *ph, int n_phase, int M, cudaStream_t st);
+
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
                            int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st,

@@ -494,13 +494,62 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
     }
 }
 
-template <uint32_t TYPE, int M>
-__global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM) gemv_block_kernel(const StreamParams p) {
+// ---- several dependent matmuls in one launch ------------------------------------------------------
+// A decode layer is a chain of matrix-vector products, each needing the whole output of the one
+// before.  As separate launches every link costs the tail of one kernel (the last warps finishing,
+// the fix-up), the hand-over and the head of the next (its first copies queueing) with HBM idle in
+// between.  The fused kernel runs the links as phases of one persistent grid: a warp that has
+// finished its share of phase i at once starts the weight stream of its share of phase i + 1 into
+// its own ring (weights depend on nothing), and only then joins the grid-wide barrier after which
+// the activations of phase i + 1 can be read.  Shared memory has one layout for all phases
+// (activation area of the longest row, then a fixed byte range per warp for its ring), so the early
+// copies of one warp never touch what another warp still reads.
+struct FusedCtx {
+    int act_bytes;   // activation area at the start of shared memory (all phases)
+    int ring_bytes;  // ring range of one warp
+    int phase;       // 0 = first phase (waits for the previous kernel), else waits for the grid
+    unsigned target; // arrivals the barrier before this phase has to see
+};
+__device__ unsigned int g_fused_bar[2]; // arrivals at the phase barriers, CTAs that have left; both return to 0
+
+// All threads of the CTA.  The barrier doubles as the arrival for the phase that ends: everything the CTA
+// wrote is made visible before it counts itself in.  Bounded like every other wait of the library.
+__device__ __forceinline__ void fused_grid_sync(unsigned target, volatile int *s_abort) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&g_fused_bar[0], 1u);
+        const uint64_t t0 = kq_globaltimer_ns();
+        while (true) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&g_fused_bar[0]) : "memory");
+            if (v >= target || *s_abort) break;
+            if (kq_globaltimer_ns() - t0 > KQ_WAIT_LIMIT_NS) {
+                *s_abort = 1;
+                atomicExch(&g_stream_error, 3);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+}
+
+// activations written earlier in the same launch by other SMs are read through L2
+template <bool FUSED>
+__device__ __forceinline__ float4 ld_act4(const float *p) {
+    return FUSED ? __ldcg(reinterpret_cast<const float4 *>(p)) : *reinterpret_cast<const float4 *>(p);
+}
+template <bool FUSED>
+__device__ __forceinline__ float ld_act1(const float *p) {
+    return FUSED ? __ldcg(p) : *p;
+}
+
+template <uint32_t TYPE, int M, bool FUSED>
+__device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem, int &s_abort, const FusedCtx &fx,
+                                            uint32_t (&uses)[4]) {
     using F = Fmt<TYPE>;
     constexpr int WARPS = F::WARPS;
-    KQ_PDL_TRIGGER();
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ int s_abort;
 #ifdef KQ_GEMV_TRACE
     __shared__ unsigned int s_trace;
     if (threadIdx.x == 0) {
@@ -523,13 +572,17 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     // 8-token kernel: tokens 32 bytes apart modulo 128, so that the B-fragment loads of the eight
     // token lanes of a warp fall on different banks
     const int act_tok = act_q + act_s + act_d + (M > 2 ? 32 : 0);
-    uint8_t *ring = smem + M * act_tok + (size_t)warp * p.ns * F::SLOT;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + M * act_tok + (size_t)WARPS * p.ns * F::SLOT) + warp * p.ns;
-    if (threadIdx.x == 0) s_abort = 0;
+    const int ns = FUSED ? min(4, fx.ring_bytes / F::SLOT) : p.ns; // ring depth
+    uint8_t *ring = FUSED ? smem + fx.act_bytes + (size_t)warp * fx.ring_bytes : smem + M * act_tok + (size_t)warp * ns * F::SLOT;
+    uint64_t *bars = FUSED ? reinterpret_cast<uint64_t *>(smem + fx.act_bytes + (size_t)WARPS * fx.ring_bytes) + warp * 4
+                           : reinterpret_cast<uint64_t *>(smem + M * act_tok + (size_t)WARPS * ns * F::SLOT) + warp * ns;
+    if (!FUSED && threadIdx.x == 0) s_abort = 0;
     // the ring and its barriers are private to the warp: set them up and start the weight stream
-    // before anything that depends on the previous kernel
-    if (lane == 0)
-        for (int s = 0; s < p.ns; s++) mbar_init(smem_u32(&bars[s]), 1);
+    // before anything that depends on the previous kernel.  Later phases of a fused launch keep the
+    // barriers of the first one (all four, whatever the ring depth of a phase) and continue their
+    // parity: uses[s] counts how often barrier s has completed so far.
+    if (lane == 0 && !(FUSED && fx.phase > 0))
+        for (int s = 0; s < (FUSED ? 4 : ns); s++) mbar_init(smem_u32(&bars[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncwarp();
     const int unit = blockIdx.x * WARPS + warp, n_units = gridDim.x * WARPS;
@@ -543,7 +596,7 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     // full (all warps of all SMs fill their rings at the same moment), so the remaining slots are
     // posted only after the loads of the activations have been issued: those loads then complete
     // behind the posting instead of after it.
-    const int pre = min(count, p.ns);
+    const int pre = min(count, ns);
     if (pre > 0) iss.post(p, lane, ring_addr, bar_addr);
     bool rest_posted = false;
     auto post_rest = [&]() {
@@ -553,7 +606,14 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
         }
     };
     TRACE_MARK(1);
-    KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
+    if (FUSED && fx.phase > 0) fused_grid_sync(fx.target, &s_abort); // the phase before this one is complete everywhere
+    else KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
+    if (FUSED && s_abort) {
+        // a wait of this CTA gave up: take no further part, but let the copies already posted land first
+        for (int j = 0; j < pre; j++) kq_mbar_wait(bar_addr + j * 8, uses[j] & 1, KQ_WAIT_LIMIT_NS);
+        for (int j = 0; j < pre; j++) uses[j]++;
+        return;
+    }
     TRACE_MARK(2);
     if (p.x) {
         // Every CTA prepares the activations for itself: RMSNorm with the sum of squares in double,
@@ -569,7 +629,7 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
             if (p.do_norm && !in_regs) { // long rows: statistics in a pass of their own
                 double ss = 0.0;
                 for (int i = threadIdx.x * 4; i < p.K; i += WARPS * 128) {
-                    const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+                    const float4 v = ld_act4<FUSED>(xr + i);
                     ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
                 }
 #pragma unroll
@@ -592,8 +652,8 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
                     wa[i] = wb[i] = make_float4(1.f, 1.f, 1.f, 1.f);
                     if (b < nb) {
                         const int o = b * 256 + lane * 8;
-                        va[i] = *reinterpret_cast<const float4 *>(xr + o);
-                        vb[i] = *reinterpret_cast<const float4 *>(xr + o + 4);
+                        va[i] = ld_act4<FUSED>(xr + o);
+                        vb[i] = ld_act4<FUSED>(xr + o + 4);
                         if (p.do_norm && p.norm_w) {
                             wa[i] = *reinterpret_cast<const float4 *>(p.norm_w + o);
                             wb[i] = *reinterpret_cast<const float4 *>(p.norm_w + o + 4);
@@ -718,8 +778,8 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     for (int m = 0; m < M; m++) acc[m] = 0.f;
     int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
     for (int j = 0; j < count; j++) {
-        const int slot = j % p.ns;
-        wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), &s_abort);
+        const int slot = j % ns;
+        wait_slot(bar_addr + slot * 8, (uint32_t)(((FUSED ? uses[slot] : 0u) + j / ns) & 1), &s_abort);
 #ifdef KQ_GEMV_TRACE
         if (j == 0) TRACE_MARK(4);
 #endif
@@ -733,7 +793,7 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
         }
         // the slot has been read by every lane: hand it back to the copy engine for unit j + ns
         __syncwarp();
-        if (j + p.ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
+        if (j + ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
         const bool last_slice = ks == p.nsteps - 1, last_unit = j == count - 1;
         if (last_slice || last_unit) {
             // row totals: the LPR lanes of a row add up; afterwards the row's first lane has it
@@ -821,7 +881,7 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
                         for (int m = 0; m < M; m++) {
                             float x = v[m];
                             if (sg.bias) x += sg.bias[row];
-                            if (p.residual) x += p.residual[(int64_t)m * sg.ldy + row];
+                            if (p.residual) x += ld_act1<FUSED>(p.residual + (int64_t)m * sg.ldy + row);
                             sg.y[(int64_t)m * sg.ldy + row] = x;
                         }
                     }
@@ -833,6 +893,10 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
             rg++;
         }
     }
+    if (FUSED)
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++)
+            if (sl < ns && count > sl) uses[sl] += (uint32_t)((count - sl + ns - 1) / ns);
 #ifdef KQ_GEMV_TRACE
     TRACE_MARK(5);
     if (lane == 0 && s_trace < 32768u) {
@@ -842,17 +906,57 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
 #endif
 }
 
+template <uint32_t TYPE, int M>
+__global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM) gemv_block_kernel(const StreamParams p) {
+    KQ_PDL_TRIGGER();
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_abort;
+    const FusedCtx none = {0, 0, 0, 0u};
+    uint32_t uses[4] = {0u, 0u, 0u, 0u};
+    stream_body<TYPE, M, false>(p, smem, s_abort, none, uses);
+}
+
+struct FusedParams {
+    StreamParams ph[3];
+    uint32_t type[3];
+    int32_t n_phase, act_bytes, ring_bytes;
+};
+
+template <int M>
+__global__ void __launch_bounds__(KQ_GEMV_WARPS * 32, 1) gemv_fused_kernel(const __grid_constant__ FusedParams fp) {
+    KQ_PDL_TRIGGER();
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    uint32_t uses[4] = {0u, 0u, 0u, 0u}; // completions of this warp's ring barriers so far
+    for (int ph = 0; ph < fp.n_phase; ph++) {
+        const FusedCtx fx = {fp.act_bytes, fp.ring_bytes, ph, (unsigned)ph * gridDim.x};
+        if (fp.type[ph] == B200_TYPE_Q4_K) stream_body<B200_TYPE_Q4_K, M, true>(fp.ph[ph], smem, s_abort, fx, uses);
+        else stream_body<B200_TYPE_Q6_K, M, true>(fp.ph[ph], smem, s_abort, fx, uses);
+    }
+    // the CTA that leaves last returns the barrier words to zero for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(&g_fused_bar[1], 1u);
+        if (prev == gridDim.x - 1) {
+            g_fused_bar[0] = 0u;
+            __threadfence();
+            g_fused_bar[1] = 0u;
+        }
+    }
+}
+
 int env_int2(const char *name, int dflt) {
     const char *v = getenv(name);
     return v ? atoi(v) : dflt;
 }
 
-template <uint32_t TYPE, int M>
-b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
-                         int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st,
-                         int m_actual = M) {
+template <uint32_t TYPE>
+void fill_params(StreamParams &p, const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
+                 int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep) {
     using F = Fmt<TYPE>;
-    StreamParams p = {};
+    p = StreamParams{};
     const int rows_per_rg = swiglu_pairs ? F::ROWS / 2 : F::ROWS;
     int tot = 0;
     for (int i = 0; i < nseg; i++) {
@@ -876,6 +980,21 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
         p.eps = prep->eps;
         p.do_norm = prep->do_norm;
     }
+}
+
+// bytes of one token's staged activations (codes, sums, scales) for rows of nb blocks
+inline int act_tok_bytes(uint32_t type, int nb, int M) {
+    const int sums = type == B200_TYPE_Q4_K ? 16 : 32;
+    return ((nb * ACT_BLK + 127) & ~127) + ((nb * sums + 127) & ~127) + ((nb * 4 + 127) & ~127) + (M > 2 ? 32 : 0);
+}
+
+template <uint32_t TYPE, int M>
+b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
+                         int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st,
+                         int m_actual = M) {
+    using F = Fmt<TYPE>;
+    StreamParams p;
+    fill_params<TYPE>(p, segs, nseg, q, d, bs, K, residual, swiglu_pairs, prep);
     const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
     const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) +
                         (M > 2 ? 32 : 0);
@@ -907,7 +1026,61 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     return B200_OK;
 }
 
+template <int M>
+b200_status launch_fused(const FusedParams &fp, size_t smem, cudaStream_t st) {
+    static bool attr_done[16];
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16 || !attr_done[dev]) {
+        KQ_CUDA(cudaFuncSetAttribute(gemv_fused_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        if (dev >= 0 && dev < 16) attr_done[dev] = true;
+    }
+    // one CTA per SM, all resident together: the phases meet at grid-wide barriers
+    kq_launch(gemv_fused_kernel<M>, kq_sm_count(), KQ_GEMV_WARPS * 32, smem, st, fp);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 } // namespace
+
+// Up to three dependent matmuls (each with the fused activation preparation) as phases of one
+// launch.  Returns B200_ERR_UNSUPPORTED when the shapes do not fit; nothing has been launched then.
+b200_status kq_launch_gemv_fused(const KqFusedPhase *ph, int n_phase, int M, cudaStream_t st) {
+    if (n_phase < 2 || n_phase > 3 || M < 1 || M > 2) return B200_ERR_UNSUPPORTED;
+    if (kq_sm_count() * KQ_GEMV_WARPS > MAX_UNITS) return B200_ERR_UNSUPPORTED;
+    FusedParams fp = {};
+    fp.n_phase = n_phase;
+    int act = 0;
+    for (int i = 0; i < n_phase; i++) {
+        const KqFusedPhase &f = ph[i];
+        if (f.nseg < 1 || f.nseg > 2 || f.K % 256 != 0 || !f.prep.x || ((uintptr_t)f.prep.x & 15) != 0) return B200_ERR_UNSUPPORTED;
+        if (f.swiglu && f.nseg != 2) return B200_ERR_UNSUPPORTED;
+        const uint32_t type = f.segs[0].type;
+        if (type != B200_TYPE_Q4_K && type != B200_TYPE_Q6_K) return B200_ERR_UNSUPPORTED;
+        for (int j = 0; j < f.nseg; j++)
+            if (f.segs[j].type != type || ((uintptr_t)f.segs[j].W & 15) != 0) return B200_ERR_UNSUPPORTED;
+        fp.type[i] = type;
+        if (type == B200_TYPE_Q4_K)
+            fill_params<B200_TYPE_Q4_K>(fp.ph[i], f.segs, f.nseg, nullptr, nullptr, nullptr, f.K, f.residual, f.swiglu, &f.prep);
+        else
+            fill_params<B200_TYPE_Q6_K>(fp.ph[i], f.segs, f.nseg, nullptr, nullptr, nullptr, f.K, f.residual, f.swiglu, &f.prep);
+        fp.ph[i].m_actual = M;
+        const int a = M * act_tok_bytes(type, (int)(f.K / 256), M);
+        if (a > act) act = a;
+    }
+    fp.act_bytes = (act + 127) & ~127;
+    // every warp gets the same byte range for its ring in all phases: two Q4_K units, which also holds one Q6_K unit
+    const int cap = 216 * 1024 - fp.act_bytes - KQ_GEMV_WARPS * 4 * 8;
+    int ring = cap / KQ_GEMV_WARPS;
+    const int want = 2 * Fmt<B200_TYPE_Q4_K>::SLOT;
+    if (ring > want) ring = want;
+    ring &= ~127;
+    if (ring < Fmt<B200_TYPE_Q6_K>::SLOT) return B200_ERR_UNSUPPORTED;
+    fp.ring_bytes = ring;
+    const size_t smem = (size_t)fp.act_bytes + (size_t)KQ_GEMV_WARPS * ring + (size_t)KQ_GEMV_WARPS * 4 * 8;
+    return M == 1 ? launch_fused<1>(fp, smem, st) : launch_fused<2>(fp, smem, st);
+}
 
 #ifdef KQ_GEMV_TRACE
 extern "C" __attribute__((visibility("default"))) int kq_gemv_trace_fetch(unsigned long long *out, int max_rec) {

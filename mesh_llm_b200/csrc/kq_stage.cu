@@ -9,6 +9,8 @@
 #include "kq_common.cuh"
 #include "kq_kvq.cuh"
 
+#include <stdlib.h>
+
 #include <map>
 #include <string>
 #include <vector>
@@ -270,7 +272,47 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             ATTN_(kq_attention(st->q, kc, vc, n_seq, T, pos_dev, pos0, c.n_head, c.n_head_kv, hd, seq_stride,
                                st->att, st->att_scratch, st->att_scratch_bytes, force_splits, kvt, s));
         }
-        if (fuse) {
+        float *xout = (last_layer && !c.has_output && hidden_out) ? hidden_out : st->x;
+        bool ffn_done = false, wo_done = false; // what has already gone out as part of a fused launch
+        if (fuse && c.n_expert == 0 && (classes & CLS_GEMV)) {
+            // attention output, gate / up with SwiGLU and down as three phases of one launch
+            KqFusedPhase ph[3] = {};
+            ph[0].segs[0] = {(const uint8_t *)L.wo->dev, L.wo->type, h, st->x, nullptr, h, 0};
+            ph[0].nseg = 1;
+            ph[0].K = nq;
+            ph[0].residual = xin;
+            ph[0].prep = {st->att, nullptr, 0.f, 0};
+            ph[1].segs[0] = {(const uint8_t *)L.gate->dev, L.gate->type, c.n_ff, st->g, nullptr, c.n_ff, 0};
+            ph[1].segs[1] = {(const uint8_t *)L.up->dev, L.up->type, c.n_ff, st->g, nullptr, c.n_ff, 0};
+            ph[1].nseg = 2;
+            ph[1].K = h;
+            ph[1].swiglu = 1;
+            ph[1].prep = {st->x, L.ffn_norm, c.rms_eps, 1};
+            ph[2].segs[0] = {(const uint8_t *)L.down->dev, L.down->type, h, xout, nullptr, h, 0};
+            ph[2].nseg = 1;
+            ph[2].K = c.n_ff;
+            ph[2].residual = st->x;
+            ph[2].prep = {st->g, nullptr, 0.f, 0};
+            static int mode = -1; // B200_GEMV_FUSED: 0 separate launches, 2 gate / up + down in one launch, 3 all three
+            if (mode < 0) {
+                const char *v = getenv("B200_GEMV_FUSED");
+                mode = v ? atoi(v) : 0;
+            }
+            b200_status frc = B200_ERR_UNSUPPORTED;
+            if (mode >= 3) {
+                frc = kq_launch_gemv_fused(ph, 3, rows, s);
+            } else if (mode == 2) {
+                KqGemvSeg so = {(const uint8_t *)L.wo->dev, L.wo->type, h, st->x, nullptr, h, 0};
+                KqActPrep pr = {st->att, nullptr, 0.f, 0};
+                KQ_TRY(kq_launch_gemv(&so, 1, st->aq, st->ad, st->abs16, rows, nq, xin, 0, nullptr, s, &pr));
+                frc = kq_launch_gemv_fused(ph + 1, 2, rows, s);
+                if (frc == B200_ERR_UNSUPPORTED) wo_done = true;
+            }
+            if (frc == B200_OK) ffn_done = true;
+            else if (frc != B200_ERR_UNSUPPORTED) return frc;
+        }
+        if (ffn_done || wo_done) {
+        } else if (fuse) {
             KqGemvSeg so = {(const uint8_t *)L.wo->dev, L.wo->type, h, st->x, nullptr, h, 0};
             KqActPrep pr = {st->att, nullptr, 0.f, 0};
             GEMV_(kq_launch_gemv(&so, 1, st->aq, st->ad, st->abs16, rows, nq, xin, 0, nullptr, s, &pr));
@@ -279,8 +321,8 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             GEMV_(mm(st, L.wo, rows, st->x, nullptr, xin, s)); // x = xin + Wo.att
         }
         // ---- feed-forward block
-        float *xout = (last_layer && !c.has_output && hidden_out) ? hidden_out : st->x;
-        if (c.n_expert > 0) {
+        if (ffn_done) {
+        } else if (c.n_expert > 0) {
             const int E = c.n_expert, ku = c.n_expert_used, fe = c.n_ff_exp, pairs = rows * ku;
             OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, st->xn, st->aq, st->ad, st->abs16, s));
             if (classes & CLS_OTHER) {

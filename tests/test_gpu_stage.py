@@ -330,3 +330,21 @@ def test_stage_rejects_bad_calls():
         st.forward(tokens=torch.zeros(9, dtype=torch.int32, device="cuda"))  # > n_ubatch
     with pytest.raises(B200Error):
         st.forward(tokens=toks, pos0=95)  # runs past n_ctx
+
+
+@pytest.mark.parametrize("mode", ["2", "3"])
+def test_layer_parity_with_the_matmuls_of_a_layer_fused_into_one_launch(mode):
+    """B200_GEMV_FUSED=2 / 3 runs gate-up + down (2) or attention output + gate-up + down (3) as phases of
+    one persistent launch with grid-wide barriers in between (off by default).  The switch is read once
+    per process, so the layer-parity test above is run again in a child process with it set."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, B200_GEMV_FUSED=mode)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", __file__, "-k",
+                        "test_every_layer_output_matches_given_the_same_input and not moe"],
+                       env=env, capture_output=True, text=True, timeout=600,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "2 passed" in r.stdout
