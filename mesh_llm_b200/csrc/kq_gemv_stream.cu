@@ -514,11 +514,17 @@ __device__ unsigned int g_fused_bar[2]; // arrivals at the phase barriers, CTAs 
 
 // All threads of the CTA.  The barrier doubles as the arrival for the phase that ends: everything the CTA
 // wrote is made visible before it counts itself in.  Bounded like every other wait of the library.
-__device__ __forceinline__ void fused_grid_sync(unsigned target, volatile int *s_abort) {
+// The barrier comes in two halves so that the copies of the next phase can be posted between them: the
+// fence of the arrival would otherwise have to sit behind those copies.
+__device__ __forceinline__ void fused_grid_arrive() {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(&g_fused_bar[0], 1u);
+    }
+}
+__device__ __forceinline__ void fused_grid_wait(unsigned target, volatile int *s_abort) {
+    if (threadIdx.x == 0) {
         const uint64_t t0 = kq_globaltimer_ns();
         while (true) {
             unsigned v;
@@ -572,6 +578,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
     // 8-token kernel: tokens 32 bytes apart modulo 128, so that the B-fragment loads of the eight
     // token lanes of a warp fall on different banks
     const int act_tok = act_q + act_s + act_d + (M > 2 ? 32 : 0);
+    if (FUSED && fx.phase > 0) fused_grid_arrive(); // everything this CTA wrote in the phase before is published
     const int ns = FUSED ? min(4, fx.ring_bytes / F::SLOT) : p.ns; // ring depth
     uint8_t *ring = FUSED ? smem + fx.act_bytes + (size_t)warp * fx.ring_bytes : smem + M * act_tok + (size_t)warp * ns * F::SLOT;
     uint64_t *bars = FUSED ? reinterpret_cast<uint64_t *>(smem + fx.act_bytes + (size_t)WARPS * fx.ring_bytes) + warp * 4
@@ -606,7 +613,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         }
     };
     TRACE_MARK(1);
-    if (FUSED && fx.phase > 0) fused_grid_sync(fx.target, &s_abort); // the phase before this one is complete everywhere
+    if (FUSED && fx.phase > 0) fused_grid_wait(fx.target, &s_abort); // the phase before this one is complete everywhere
     else KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
     if (FUSED && s_abort) {
         // a wait of this CTA gave up: take no further part, but let the copies already posted land first

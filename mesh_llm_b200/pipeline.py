@@ -241,7 +241,20 @@ def bench_pipeline(args, w, metric, rank, world, local):
     h = w["n_embd"]
     # decode hand-off: peer-memory kernels unless --handoff nccl asks for send/recv; prefill ubatches (MBs) use send/recv
     peer = getattr(args, "handoff", "peer") == "peer"
-    tr_dec = PeerTransport(dist, rank, world, h * 4) if peer else tr
+    tr_dec = tr
+    if peer:
+        # every rank must end up on the same transport: if mapping a neighbour's ring fails anywhere, all use send / recv
+        try:
+            tr_dec = PeerTransport(dist, rank, world, h * 4)
+            ok = torch.ones(1, device=dev)
+        except Exception as e:  # noqa: BLE001 - reported, then the collective below decides for everybody
+            print(f"[rank {rank}] peer-memory hand-off unavailable ({e}); using send / recv", flush=True)
+            ok = torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            if tr_dec is not tr:
+                tr_dec.close()
+            tr_dec, peer = tr, False
     rng = np.random.default_rng(1234)
     prompts = torch.from_numpy(rng.integers(0, w["n_vocab"], (n_seq, w["prefill"])).astype(np.int32)).to(dev)
     hid_big = torch.empty((512, h), dtype=torch.float32, device=dev)
