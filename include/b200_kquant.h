@@ -158,6 +158,16 @@ B200_API b200_status b200_backend_synchronize(b200_backend *be);
 B200_API void *b200_backend_stream(b200_backend *be);
 
 /* ---- direct kernel entry points (device pointers) -------------------------------------------
+ * ORDERING RULE for everything below that launches a matmul (b200_mul_mat, b200_mul_mat_q8,
+ * b200_mul_mat_static, b200_stage_forward, b200_backend_graph_compute): per device, such calls must
+ * be ordered on the GPU -- issued to one stream, or to streams the caller has ordered with events.
+ * The decode kernels combine partial sums through small per-device arrays inside the library (and the
+ * prefill GEMM keeps a per-device staging buffer); two matmul launches that overlap on one GPU would
+ * read each other's entries and return wrong numbers without any error.  This is the reference's own
+ * calling pattern: one decode thread per llama-server, and in rpc-server every backend call behind
+ * one mutex (patches/0002 lines 320-337).  Calls may come from different host threads as long as
+ * they do not overlap.  Activation pointers (x, q) must be 16-byte aligned.
+ *
  * Weight matrices passed to these are in DEVICE layout: Q4_K rows are the GGUF bytes
  * unchanged; Q6_K rows are repacked (b200_repack_q6k) into groups of 8 blocks, each group
  * [ql | qh | scales | d] with chunk-major ql / qh planes, 1680 bytes, so that a row slice is one
@@ -243,8 +253,15 @@ B200_API b200_status b200_attention_kv(const float *q, const void *k_cache, cons
 B200_API b200_status b200_get_rows(uint32_t type, const void *W, const int32_t *ids, int64_t T,
                                    int64_t K, float *y, void *stream);
 B200_API b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void *stream);
+/* Router of the expert layer (build_moe_ffn, third_party/llama.cpp/patches/0003 lines 82-108):
+ * softmax over the E logits of a token, the k largest selected (ties to the lower index), their
+ * probabilities renormalised to sum 1.  The masked form adds the reference's expert mask before the
+ * selection: mask (device, one byte per expert, 1 = allowed, NULL = none) gives a masked expert the
+ * selection value -inf, the weights still come from the unmasked probabilities.                  */
 B200_API b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k,
                                     int32_t *ids, float *w, void *stream);
+B200_API b200_status b200_moe_route_masked(const float *logits, int64_t T, int64_t E, int64_t k,
+                                           const uint8_t *mask, int32_t *ids, float *w, void *stream);
 /* Statistics of the output distribution per row of logits [T][n], computed on the device: what the
  * reference's server derives on the CPU from the full-vocabulary softmax after the prefill and
  * after every generated token when its mesh hooks are on (third_party/llama.cpp/patches/0005:
@@ -314,6 +331,11 @@ B200_API b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, in
 B200_API int64_t b200_stage_tensor_count(b200_stage *st);
 B200_API b200_status b200_stage_tensor_info(b200_stage *st, int64_t i, char *name, size_t name_cap,
                                             uint32_t *type, int64_t ne[3]);
+/* Expert mask of a mixture-of-experts stage: llama_model_set_expert_mask (patches/0003 lines 44-48 and
+ * 159-181).  mask (host): n_mask bytes, nonzero = expert allowed; NULL clears the mask.  Returns
+ * B200_ERR_INVALID when n_mask is not the stage's expert count (the reference returns -1) or the
+ * stage is dense.  Takes effect from the next forward call, captured decode graphs included.    */
+B200_API b200_status b200_stage_set_expert_mask(b200_stage *st, const uint8_t *mask, int32_t n_mask);
 B200_API b200_status b200_stage_synchronize(b200_stage *st);
 B200_API int64_t b200_stage_kernel_launches(b200_stage *st); /* launches issued so far        */
 

@@ -141,6 +141,7 @@ SIGNATURES = {
     "b200_get_rows": (i32, [u32, vp, vp, i64, i64, vp, vp]),
     "b200_argmax": (i32, [vp, i64, i64, vp, vp]),
     "b200_moe_route": (i32, [vp, i64, i64, i64, vp, vp, vp]),
+    "b200_moe_route_masked": (i32, [vp, i64, i64, i64, vp, vp, vp, vp]),
     "b200_logit_signals_scratch_bytes": (sz, [i64]),
     "b200_logit_signals": (i32, [vp, i64, i64, vp, vp, vp, vp, sz, vp]),
     "b200_stage_create": (i32, [C.POINTER(StageConfig), C.POINTER(vp)]),
@@ -169,6 +170,7 @@ SIGNATURES = {
     "b200_moe_assign": (i32, [vp, i32, i32, i32, i32, i32, i32, vp, i32, C.POINTER(i32), C.POINTER(i32),
                               C.POINTER(i32)]),
     "b200_gguf_write_expert_shard": (i32, [vp, vp, i32, C.c_char_p, C.POINTER(u64)]),
+    "b200_stage_set_expert_mask": (i32, [vp, vp, i32]),
     "b200_stage_synchronize": (i32, [vp]),
     "b200_stage_kernel_launches": (i64, [vp]),
 }

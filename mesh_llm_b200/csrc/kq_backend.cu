@@ -64,9 +64,25 @@ inline size_t device_bytes(const b200_tensor *t) {
     return (size_t)(kq_device_row_bytes(t->type, t->ne[0]) * nrows(t));
 }
 
+// The four extents arrive as 32-bit words from the wire; their product has to stay far inside int64
+// (and inside any buffer this library can allocate) for the byte counts below to mean anything.
+inline bool extents_ok(const b200_tensor *t) {
+    uint64_t n = 1;
+    for (int i = 0; i < 4; i++) {
+        if (t->ne[i] == 0) return true; // an empty tensor: every product is 0
+        n *= (uint64_t)t->ne[i];
+        if (n > (1ull << 46)) return false;
+    }
+    return true;
+}
+
 // tensor [data, data + device_bytes) must lie inside its buffer
 b200_status check_tensor(const b200_tensor *t) {
     KQ_REQUIRE(t, "null tensor");
+    if (!extents_ok(t)) {
+        kq_set_error("tensor %.64s: extents %u x %u x %u x %u overflow", t->name, t->ne[0], t->ne[1], t->ne[2], t->ne[3]);
+        return B200_ERR_BOUNDS;
+    }
     const b200_buffer *buf = (const b200_buffer *)(uintptr_t)t->buffer;
     KQ_REQUIRE(buf && buf->base, "tensor %.64s has no buffer", t->name);
     const uint64_t lo = (uint64_t)(uintptr_t)buf->base, hi = lo + buf->size;
@@ -141,6 +157,20 @@ b200_status window_check(b200_buffer *buf, const b200_tensor *t, const void *hos
     const size_t total = gguf_bytes(t);
     if (offset > total || size > total - offset) {
         kq_set_error("tensor %.64s: window [%zu, +%zu) exceeds %zu bytes", t->name, offset, size, total);
+        return B200_ERR_BOUNDS;
+    }
+    return B200_OK;
+}
+
+// the node's own tensor must have the type the kernel writes and room for every element it writes
+b200_status out_holds(const b200_tensor *t, uint32_t type, int64_t n_elems) {
+    if (t->type != type) {
+        kq_set_error("graph_compute: node %.64s: output type %u, the op writes type %u", t->name, t->type, type);
+        return B200_ERR_INVALID;
+    }
+    if (nelements(t) < n_elems) {
+        kq_set_error("graph_compute: node %.64s: output holds %lld elements, the op writes %lld", t->name,
+                     (long long)nelements(t), (long long)n_elems);
         return B200_ERR_BOUNDS;
     }
     return B200_OK;
@@ -360,7 +390,8 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             const int64_t n_used = c->ne[0], T = c->ne[1];
             KQ_REQUIRE(b->ne[0] == K && b->ne[2] == T && (b->ne[1] == n_used || b->ne[1] == 1),
                        "MUL_MAT_ID %.64s: x must be [K, n_used|1, T]", t->name);
-            KQ_REQUIRE(t->ne[0] == N && t->ne[1] == n_used && t->ne[2] == T, "MUL_MAT_ID %.64s: bad output shape", t->name);
+            KQ_REQUIRE(t->ne[0] == N && t->ne[1] == n_used && t->ne[2] == T && t->type == B200_TYPE_F32,
+                       "MUL_MAT_ID %.64s: bad output shape", t->name);
             (void)E;
             const int64_t xrows = b->ne[1] * T;
             KQ_TRY(ensure_scratch(be, b200_mul_mat_scratch_bytes(xrows, K)));
@@ -377,6 +408,7 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             break;
         }
         case B200_OP_RMS_NORM:
+            KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(a)));
             KQ_TRY(kq_rms_norm((const float *)pa, nullptr, nrows(a), a->ne[0], f32_param(t, 0), y, nullptr, nullptr,
                                nullptr, s));
             break;
@@ -385,6 +417,7 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             KQ_REQUIRE(b && b->type == B200_TYPE_F32 && b->ne[0] == a->ne[0], "%.64s: operand shapes", t->name);
             const int64_t total = nelements(a), nbe = nelements(b);
             KQ_REQUIRE(nbe == total || nbe == a->ne[0], "%.64s: src1 must match or be one row", t->name);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, total));
             if (t->op == B200_OP_MUL)
                 kq_launch(mul_rows_kernel, (unsigned)kq_div_up(total, 256), 256, 0, s, (const float *)pa, (const float *)pb,
                                                                                total, a->ne[0], nbe, y);
@@ -398,6 +431,7 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
         case B200_OP_ROPE: {
             KQ_REQUIRE(b && b->ne[0] == a->ne[2], "ROPE %.64s: one position per token", t->name);
             KQ_REQUIRE(t->op_params[0] == (int32_t)a->ne[0], "ROPE %.64s: partial rotation is not supported", t->name);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(a)));
             if (t->data != a->data)
                 KQ_CUDA(cudaMemcpyAsync(y, pa, (size_t)nelements(a) * 4, cudaMemcpyDeviceToDevice, s));
             KQ_TRY(b200_rope(y, (const int32_t *)pb, a->ne[2], a->ne[1], a->ne[0], f32_param(t, 2),
@@ -405,14 +439,17 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             break;
         }
         case B200_OP_SWIGLU:
-            KQ_REQUIRE(b && nelements(b) == nelements(a), "SWIGLU %.64s: shapes", t->name);
+            KQ_REQUIRE(b && b->type == B200_TYPE_F32 && nelements(b) == nelements(a), "SWIGLU %.64s: shapes", t->name);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(a)));
             KQ_TRY(b200_swiglu((const float *)pa, (const float *)pb, nelements(a), y, s));
             break;
         case B200_OP_GET_ROWS:
             KQ_REQUIRE(b, "GET_ROWS %.64s: ids", t->name);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(b) * (int64_t)a->ne[0]));
             KQ_TRY(b200_get_rows(a->type, pa, (const int32_t *)pb, nelements(b), a->ne[0], y, s));
             break;
         case B200_OP_CPY:
+            if (t->type == B200_TYPE_F16 || t->type == B200_TYPE_F32) KQ_TRY(out_holds(t, t->type, nelements(a)));
             if (t->type == B200_TYPE_F16)
                 KQ_TRY(b200_cpy_f32_f16((const float *)pa, nelements(a), (uint16_t *)y, s));
             else if (t->type == B200_TYPE_F32)
@@ -426,6 +463,10 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             KQ_REQUIRE(b && c && c->type == B200_TYPE_F16, "ATTN %.64s: K and V caches", t->name);
             const int hd = a->ne[0], n_head = a->ne[1], T = a->ne[2], n_kv = b->ne[1];
             const int pos0 = t->op_params[1];
+            KQ_REQUIRE(b->ne[0] == a->ne[0] && c->ne[0] == a->ne[0] && c->ne[1] == b->ne[1] && c->ne[2] == b->ne[2],
+                       "ATTN %.64s: K and V caches must be [head_dim, n_kv, n_ctx] with q's head_dim", t->name);
+            KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "ATTN %.64s: %d query heads over %d KV heads", t->name, n_head, n_kv);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(a)));
             KQ_REQUIRE(pos0 >= 0 && (int64_t)pos0 + T <= (int64_t)b->ne[2], "ATTN %.64s: positions exceed the cache", t->name);
             const size_t need = b200_attention_scratch_bytes(std::min(T, 64), n_head, hd, b->ne[2]);
             KQ_TRY(ensure_scratch(be, need));
@@ -435,10 +476,15 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
         }
         case B200_OP_MOE_ROUTE:
             KQ_REQUIRE(b && b->type == B200_TYPE_I32, "MOE_ROUTE %.64s: src1 receives the ids", t->name);
+            KQ_REQUIRE(t->op_params[0] >= 1 && (uint32_t)t->op_params[0] <= a->ne[0], "MOE_ROUTE %.64s: k = %d of %u experts",
+                       t->name, t->op_params[0], a->ne[0]);
+            KQ_TRY(out_holds(t, B200_TYPE_F32, (int64_t)t->op_params[0] * nrows(a)));
+            KQ_TRY(out_holds(b, B200_TYPE_I32, (int64_t)t->op_params[0] * nrows(a)));
             KQ_TRY(b200_moe_route((const float *)pa, a->ne[1], a->ne[0], t->op_params[0],
                                   (int32_t *)(uintptr_t)b->data, y, s));
             break;
         case B200_OP_ARGMAX:
+            KQ_TRY(out_holds(t, B200_TYPE_I32, nrows(a)));
             KQ_TRY(b200_argmax((const float *)pa, nrows(a), a->ne[0], (int32_t *)y, s));
             break;
         default:

@@ -24,6 +24,8 @@
 // returns.
 #include "kq_common.cuh"
 
+#include <mutex>
+
 #include <cuda.h> // CUtensorMap and the encode entry point's types; the driver is reached through the runtime
 #include <string.h>
 
@@ -567,6 +569,10 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
     KQ_REQUIRE(((uintptr_t)W & 15) == 0 && ((uintptr_t)q & 15) == 0, "gemm: operands must be 16-byte aligned");
     // Per-device scratch for the re-tiled activations, grown on demand and kept; launches that share
     // it are ordered by using one stream per device at a time, as the stage engine and the backend do.
+    // Host threads may call for different devices at the same time: the table and its growth are
+    // guarded, the launches themselves are not serialised.
+    static std::mutex scratch_mu;
+    std::unique_lock<std::mutex> scratch_lock(scratch_mu);
     static uint4 *tiled[KQ_MAX_DEVICES];
     static size_t tiled_cap[KQ_MAX_DEVICES];
     static bool attr[KQ_MAX_DEVICES];
@@ -586,18 +592,20 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
         KQ_CUDA(cudaMalloc(&tiled[dev], need));
         tiled_cap[dev] = need;
     }
+    uint4 *const tiled_dev = tiled[dev];
+    if (!attr[dev]) {
+        KQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        attr[dev] = true;
+    }
+    scratch_lock.unlock();
     const int64_t n_piece = (int64_t)need / 16;
-    kq_launch(retile_act_kernel, dim3((unsigned)kq_div_up(n_piece, 256)), 256, 0, st, q, tiled[dev], (int)M, (int)K, n_piece);
+    kq_launch(retile_act_kernel, dim3((unsigned)kq_div_up(n_piece, 256)), 256, 0, st, q, tiled_dev, (int)M, (int)K, n_piece);
     KQ_COUNT_LAUNCH();
-    GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled[dev]), d, bs, y, bias, residual,
+    GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled_dev), d, bs, y, bias, residual,
                     (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type};
     // two CTAs per SM: each holds 256 of the 512 TMEM columns and under half of the shared memory
     const int smem = SMEM_TOTAL;
     static_assert(SMEM_TOTAL <= 112 * 1024, "two tiles must fit the shared memory of an SM");
-    if (!attr[dev]) {
-        KQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr[dev] = true;
-    }
     CUtensorMap wmap;
     memset(&wmap, 0, sizeof(wmap));
     if (type == B200_TYPE_Q4_K) {

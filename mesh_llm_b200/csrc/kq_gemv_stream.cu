@@ -1101,10 +1101,19 @@ extern "C" __attribute__((visibility("default"))) int kq_gemv_trace_fetch(unsign
     return (int)n;
 }
 #endif
+// Callers synchronise the device first.  After a wait gave up, a producer that was merely late may
+// still have left flagged entries in the fix-up scratch (or arrivals at the phase barrier) that the
+// next launch would take for its own: everything is returned to zero before the error is reported.
 int kq_stream_error_fetch() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
+    if (v) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_partials) == cudaSuccess) cudaMemset(p, 0, sizeof(g_partials));
+        if (cudaGetSymbolAddress(&p, g_partials8) == cudaSuccess) cudaMemset(p, 0, sizeof(g_partials8));
+        if (cudaGetSymbolAddress(&p, g_fused_bar) == cudaSuccess) cudaMemset(p, 0, sizeof(g_fused_bar));
+        cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
+    }
     return v;
 }
 

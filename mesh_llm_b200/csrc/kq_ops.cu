@@ -356,15 +356,18 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *x, int64_t n,
     }
 }
 
-// router: one warp per token; E <= 256, k <= 32
+// router: one warp per token; E <= 256, k <= 32.  probs = softmax over all experts; the choice is made
+// on probs + mask (0 for an allowed expert, -inf for a masked one: third_party/llama.cpp/patches/0003
+// lines 82-108), ties to the lower index; the weights are the unmasked probs of the chosen experts,
+// renormalised.  mask: one byte per expert (1 = allowed) or null.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int64_t T, int E, int k,
-                                                        int32_t *ids, float *w) {
+                                                        const uint8_t *mask, int32_t *ids, float *w) {
     KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= T) return;
     const float *lr = logits + t * E;
-    float v[8];
+    float v[8], sel[8];
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -376,35 +379,41 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int
     float den = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;
-        if (v[i] > 0.f) den += v[i];
+        v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : 0.f;
+        den += v[i];
     }
     den = kq_warp_sum(den);
+    // selection value: the prob of an allowed expert (>= 0), -1 for a masked one (all equal, below every
+    // allowed one, as -inf is), -2 once taken, -3 outside the table
 #pragma unroll
-    for (int i = 0; i < 8; i++)
-        if (v[i] >= 0.f) v[i] = v[i] / den;
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        v[i] = v[i] / den;
+        sel[i] = e >= E ? -3.f : ((mask && !mask[e]) ? -1.f : v[i]);
+    }
     float wsum = 0.f, mine = 0.f;
     int myid = 0;
     for (int s = 0; s < k; s++) {
-        float best = -1.f;
+        float best = -4.f, bp = 0.f;
         int be = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const int e = lane + 32 * i;
-            if (v[i] > best || (v[i] == best && e < be)) { best = v[i]; be = e; }
+            if (sel[i] > best || (sel[i] == best && e < be)) { best = sel[i]; be = e; bp = v[i]; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+            const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; bp = op; }
         }
-        wsum += best;
-        if (lane == s) { mine = best; myid = be; }
+        wsum += bp;
+        if (lane == s) { mine = bp; myid = be; }
         if ((be & 31) == lane) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
-                if (i == (be >> 5)) v[i] = -2.f; // taken
+                if (i == (be >> 5)) sel[i] = -2.f; // taken
         }
     }
     if (lane < k) {
@@ -607,14 +616,20 @@ b200_status b200_argmax(const float *x, int64_t T, int64_t n, int32_t *idx, void
     return B200_OK;
 }
 
-b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w,
-                           void *stream) {
+b200_status b200_moe_route_masked(const float *logits, int64_t T, int64_t E, int64_t k, const uint8_t *mask,
+                                  int32_t *ids, float *w, void *stream) {
+    KQ_REQUIRE(logits && ids && w && T >= 1, "moe_route: null argument");
     KQ_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= 32 && k <= E, "moe_route: E <= 256, k <= 32");
     kq_launch(moe_route_kernel, (unsigned)kq_div_up(T, 4), 128, 0, (cudaStream_t)stream, logits, T, (int)E, (int)k,
-                                                                                ids, w);
+                                                                                mask, ids, w);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
+}
+
+b200_status b200_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w,
+                           void *stream) {
+    return b200_moe_route_masked(logits, T, E, k, nullptr, ids, w, stream);
 }
 
 } // extern "C"

@@ -270,10 +270,10 @@ bool handle(b200_rpc_server *s, int fd, uint8_t cmd, std::vector<uint8_t> &in) {
         {
             std::lock_guard<std::mutex> lock(s->backend_mutex);
             if (!s->live(q.src.buffer) || !s->live(q.dst.buffer)) return false;
-            uint64_t n = 1;
-            for (int d = 0; d < 4; d++) n *= q.src.ne[d];
-            const size_t bytes = b200_buft_alloc_size(q.src.type, q.src.ne);
-            (void)n;
+            // the tensor's exact byte count (the allocation size is rounded up and would be refused)
+            const uint64_t rows = (uint64_t)q.src.ne[1] * q.src.ne[2] * q.src.ne[3];
+            const size_t bytes = q.src.type == B200_TYPE_I32 ? (size_t)(rows * q.src.ne[0] * 4)
+                                                             : (size_t)(rows * (uint64_t)b200_row_bytes(q.src.type, q.src.ne[0]));
             r = b200_buffer_cpy_tensor(&q.src, &q.dst, 0, bytes) == 1 ? 1 : 0;
         }
         return send_rsp(fd, &r, 1);

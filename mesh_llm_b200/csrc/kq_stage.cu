@@ -139,6 +139,7 @@ struct b200_stage {
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr,
           *u = nullptr, *last = nullptr, *logits_int = nullptr, *att_scratch = nullptr, *rl = nullptr,
           *rw = nullptr, *hp = nullptr, *yp = nullptr;
+    uint8_t *expert_mask = nullptr; // one byte per expert, 1 = allowed (all ones when no mask is set)
     int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
     size_t att_scratch_bytes = 0;
     void *scan_scratch = nullptr; // slices and counters of the vocabulary scan
@@ -331,7 +332,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             KQ_COUNT_LAUNCH();
             KQ_LAUNCH_CHECK();
             }
-            OTHER_(b200_moe_route(st->rl, rows, E, ku, st->rid, st->rw, s));
+            OTHER_(b200_moe_route_masked(st->rl, rows, E, ku, st->expert_mask, st->rid, st->rw, s));
             // gate/up of the selected experts with fused SwiGLU, one (token, slot) pair per grid row
             const int64_t gstride = kq_device_row_bytes(L.gate_e->type, h) * fe;
             const int64_t dstride = kq_device_row_bytes(L.down_e->type, fe) * h;
@@ -571,6 +572,8 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
         A((void **)&st->rid, pairs * 4);
         A((void **)&st->hp, pairs * c.n_ff_exp * 4);
         A((void **)&st->yp, pairs * h * 4);
+        A((void **)&st->expert_mask, 256);
+        if (rc == B200_OK && cudaMemset(st->expert_mask, 1, 256) != cudaSuccess) rc = B200_ERR_CUDA;
     }
     if (rc == B200_OK && cudaStreamCreateWithFlags(&st->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
         kq_set_error("stage: cudaStreamCreate failed");
@@ -856,6 +859,21 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
     KQ_CUDA(e);
     *ms_per_step = ms / iters;
     if (launches_per_step) *launches_per_step = per_step;
+    return B200_OK;
+}
+
+b200_status b200_stage_set_expert_mask(b200_stage *st, const uint8_t *mask, int32_t n_mask) {
+    KQ_REQUIRE(st, "stage_set_expert_mask: null stage");
+    KQ_REQUIRE(st->c.n_expert > 0, "stage_set_expert_mask: the stage has no experts");
+    KQ_REQUIRE(!mask || n_mask == st->c.n_expert, "stage_set_expert_mask: %d entries for %d experts", n_mask,
+               st->c.n_expert);
+    KqDevGuard dev_guard(st->c.device);
+    // The router always reads the stage's mask array (a captured decode graph holds its address);
+    // "no mask" is all ones.  The copy is ordered after everything already queued on the device.
+    uint8_t host[256];
+    for (int i = 0; i < 256; i++) host[i] = (!mask || i >= n_mask) ? 1 : (mask[i] ? 1 : 0);
+    KQ_CUDA(cudaDeviceSynchronize());
+    KQ_CUDA(cudaMemcpy(st->expert_mask, host, 256, cudaMemcpyHostToDevice));
     return B200_OK;
 }
 

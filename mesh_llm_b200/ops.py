@@ -207,10 +207,14 @@ def logit_signals(logits, chosen=None):
                 top_id=sig[:, 8:13].contiguous().view(torch.int32), argmax=am)
 
 
-def moe_route(logits, k):
+def moe_route(logits, k, mask=None):
     logits = _dev(logits).contiguous().float()
     T, E = logits.shape
     ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
     w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
-    check(lib().b200_moe_route(ptr(logits), T, E, k, ptr(ids), ptr(w), cur_stream()))
+    if mask is not None:  # uint8 device tensor, one entry per expert, nonzero = allowed
+        mask = (_dev(mask) != 0).to(torch.uint8).contiguous()
+        if mask.numel() != E:
+            raise ValueError("expert mask needs one entry per expert")
+    check(lib().b200_moe_route_masked(ptr(logits), T, E, k, ptr(mask), ptr(ids), ptr(w), cur_stream()))
     return ids, w

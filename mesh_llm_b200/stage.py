@@ -109,5 +109,14 @@ class Stage:
                                        ptr(next_tokens), cur_stream()))
         return hidden_out, logits, next_tokens
 
+    def set_expert_mask(self, mask):
+        """mask: one entry per expert (nonzero = allowed) or None to clear it; as the reference's
+        llama_model_set_expert_mask, a mask of the wrong length is refused"""
+        if mask is None:
+            check(lib().b200_stage_set_expert_mask(self.h, None, 0))
+            return
+        m = np.ascontiguousarray(np.asarray(mask) != 0, dtype=np.uint8)
+        check(lib().b200_stage_set_expert_mask(self.h, m.ctypes.data, m.size))
+
     def synchronize(self):
         check(lib().b200_stage_synchronize(self.h))

@@ -77,6 +77,9 @@ def lib():
         L.orc_kv_round_trip.argtypes = [i32, vp, i64, vp]
         L.orc_argmax.argtypes = [vp, i64, i64, vp]
         L.orc_moe_route.argtypes = [vp, i64, i64, i64, vp, vp]
+        L.orc_moe_route_masked.argtypes = [vp, i64, i64, i64, vp, vp, vp]
+        L.orc_model_set_expert_mask.argtypes = [vp, vp, i32]
+        L.orc_model_set_expert_mask.restype = i32
         L.orc_model_create.argtypes = [C.POINTER(Config)]
         L.orc_model_create.restype = vp
         L.orc_model_free.argtypes = [vp]
@@ -247,12 +250,18 @@ def argmax(x):
     return idx
 
 
-def moe_route(logits, k):
+def moe_route(logits, k, mask=None):
+    """mask: one entry per expert, nonzero = allowed (the reference's expert mask); None = all"""
     logits = _c(logits, np.float32)
     T, E = logits.shape
     ids = np.empty((T, k), np.int32)
     w = np.empty((T, k), np.float32)
-    lib().orc_moe_route(_p(logits), T, E, k, _p(ids), _p(w))
+    if mask is None:
+        lib().orc_moe_route(_p(logits), T, E, k, _p(ids), _p(w))
+    else:
+        mask = _c(np.asarray(mask) != 0, np.uint8)
+        assert mask.size == E
+        lib().orc_moe_route_masked(_p(logits), T, E, k, _p(mask), _p(ids), _p(w))
     return ids, w
 
 
@@ -304,6 +313,13 @@ class Model:
         data = _c(data, np.uint8).reshape(-1)
         if not lib().orc_model_set_tensor(self.h, name.encode(), type_, _p(data), data.size):
             raise ValueError(f"set_tensor({name}) rejected")
+
+    def set_expert_mask(self, mask):
+        """mask: one entry per expert (nonzero = allowed) or None to clear; -> 0, or -1 on a wrong length"""
+        if mask is None:
+            return lib().orc_model_set_expert_mask(self.h, None, 0)
+        mask = _c(np.asarray(mask) != 0, np.uint8)
+        return lib().orc_model_set_expert_mask(self.h, _p(mask), mask.size)
 
     def forward(self, tokens=None, hidden_in=None, pos0=0, seq=0, want_logits=True):
         c = self.cfg

@@ -631,7 +631,15 @@ void orc_argmax(const float *x, int64_t T, int64_t n, int32_t *idx) {
     }
 }
 
-void orc_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w) {
+/* Router of build_moe_ffn (third_party/llama.cpp/patches/0003-moe-add-expert-analysis-and-split-
+ * tools.patch lines 82-108): probs = softmax over all experts; selection_probs = probs + mask, the
+ * mask being 0 for an allowed expert and -inf for a masked one (lines 44-48 and 159-181: one bool per
+ * expert, set on the model); top-k by selection_probs; the weights are the *unmasked* probs of the
+ * selected experts, renormalised to sum 1.  Ties go to the lower expert index.  mask == NULL: all
+ * experts allowed.  If fewer than k experts are allowed, masked ones fill the remaining slots in
+ * index order (all their selection values are equal). */
+void orc_moe_route_masked(const float *logits, int64_t T, int64_t E, int64_t k, const uint8_t *mask,
+                          int32_t *ids, float *w) {
     float *p = (float *)malloc(sizeof(float) * (size_t)E);
     for (int64_t t = 0; t < T; t++) {
         const float *l = logits + t * E;
@@ -647,12 +655,17 @@ void orc_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t
         float wsum = 0.f;
         for (int64_t s = 0; s < k; s++) {
             int64_t best = -1;
+            float best_sel = 0.f;
             for (int64_t e = 0; e < E; e++) {
                 int taken = 0;
                 for (int64_t u = 0; u < s; u++)
                     if (ids[t * k + u] == e) taken = 1;
                 if (taken) continue;
-                if (best < 0 || p[e] > p[best]) best = e;
+                const float sel = (mask && !mask[e]) ? -INFINITY : p[e];
+                if (best < 0 || sel > best_sel) {
+                    best = e;
+                    best_sel = sel;
+                }
             }
             ids[t * k + s] = (int32_t)best;
             w[t * k + s] = p[best];
@@ -661,6 +674,10 @@ void orc_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t
         for (int64_t s = 0; s < k; s++) w[t * k + s] /= wsum;
     }
     free(p);
+}
+
+void orc_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w) {
+    orc_moe_route_masked(logits, T, E, k, NULL, ids, w);
 }
 
 /* ---------------------------------------------------------------- whole stage */
@@ -677,6 +694,7 @@ struct orc_model {
     int n_tensors;
     orc_tensor *t;
     uint16_t *kc, *vc; /* [layer_local][seq][ctx][n_kv][hd] */
+    uint8_t *expert_mask; /* one byte per expert (1 = allowed) or NULL: llama_model_set_expert_mask */
 };
 
 static orc_tensor *add_tensor(orc_model *m, const char *name, int type, int64_t ne0, int64_t ne1,
@@ -754,7 +772,22 @@ void orc_model_free(orc_model *m) {
     free(m->t);
     free(m->kc);
     free(m->vc);
+    free(m->expert_mask);
     free(m);
+}
+
+/* llama_model_set_expert_mask (patches/0003 lines 159-181): NULL clears; a mask whose length is not
+ * the model's expert count is refused with -1. */
+int orc_model_set_expert_mask(orc_model *m, const uint8_t *mask, int32_t n_mask) {
+    if (!mask) {
+        free(m->expert_mask);
+        m->expert_mask = NULL;
+        return 0;
+    }
+    if (n_mask != m->c.n_expert) return -1;
+    if (!m->expert_mask) m->expert_mask = (uint8_t *)malloc((size_t)n_mask);
+    for (int i = 0; i < n_mask; i++) m->expert_mask[i] = mask[i] ? 1 : 0;
+    return 0;
 }
 
 int orc_model_n_tensors(orc_model *m) { return m->n_tensors; }
@@ -933,7 +966,7 @@ int orc_model_forward(orc_model *m, int32_t seq, const int32_t *tokens, const fl
                     for (int64_t i = 0; i < h; i++) acc += wr[e * h + i] * xn[t * h + i];
                     rl[t * E + e] = acc;
                 }
-            orc_moe_route(rl, T, E, ku, ids, rw);
+            orc_moe_route_masked(rl, T, E, ku, m->expert_mask, ids, rw);
             orc_tensor *ge = layer_tensor(m, l, "ffn_gate_exps.weight");
             orc_tensor *ue = layer_tensor(m, l, "ffn_up_exps.weight");
             orc_tensor *de = layer_tensor(m, l, "ffn_down_exps.weight");

@@ -89,6 +89,9 @@ void orc_get_rows(int type, const uint8_t *W, const int32_t *ids, int64_t T, int
 void orc_argmax(const float *x, int64_t T, int64_t n, int32_t *idx);
 /* router: softmax over E logits, top-k (ties -> lower id), weights renormalised to sum 1     */
 void orc_moe_route(const float *logits, int64_t T, int64_t E, int64_t k, int32_t *ids, float *w);
+/* the same with the reference's expert mask (one byte per expert, 1 = allowed; NULL = none) */
+void orc_moe_route_masked(const float *logits, int64_t T, int64_t E, int64_t k, const uint8_t *mask,
+                          int32_t *ids, float *w);
 
 /* ---- whole stage ------------------------------------------------------------------------- */
 typedef struct {
@@ -118,6 +121,9 @@ int orc_model_get_tensor(orc_model *m, const char *name, int32_t *type, const vo
                          int64_t *nbytes, int64_t ne[3]);
 int orc_model_set_tensor(orc_model *m, const char *name, int32_t type, const void *data,
                          int64_t nbytes);
+/* expert mask of a mixture-of-experts model: one byte per expert (1 = allowed), NULL clears;
+ * returns -1 when n_mask is not the model's expert count, else 0                            */
+int orc_model_set_expert_mask(orc_model *m, const uint8_t *mask, int32_t n_mask);
 int orc_model_n_tensors(orc_model *m);
 const char *orc_model_tensor_name(orc_model *m, int i);
 /* run T tokens of sequence `seq` starting at position pos0.  First stage takes tokens, other

@@ -94,6 +94,9 @@ class Client:
     def get_tensor(self, tensor, offset, size):
         return self.call(GET_TENSOR, bytes(tensor) + struct.pack("<QQ", offset, size))
 
+    def copy_tensor(self, src, dst):
+        return self.call(COPY_TENSOR, bytes(src) + bytes(dst))[0]
+
     def register_peer(self, peer_id, endpoint):
         ep = endpoint.encode()[:127]
         return self.call(REGISTER_PEER, struct.pack("<I128s", peer_id, ep))[0]

@@ -249,3 +249,80 @@ def test_graph_compute_mul_mat_id_matches_per_expert_oracle():
             assert np.abs(got[t, s] - ref).max() <= 1e-3 * np.abs(ref).max()
     lib().b200_backend_free(be)
     buf.free()
+
+
+def test_graph_compute_rejects_outputs_too_small_for_what_the_op_writes():
+    """A graph that arrives over the wire may name a destination smaller than the op's result.  Every op
+    checks the node's own shape and type before it launches: the call answers out-of-bounds (or invalid
+    for a wrong type), launches nothing for that node, and the bytes after the small tensor stay as
+    they were."""
+    from mesh_llm_b200.capi import Tensor, lib
+
+    h, T = 512, 6
+    buf = Buf(0, 1 << 22)
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((T, h)).astype(np.float32)
+    t_x = buf.tensor(F32, (h, T), "x")
+    t_pos = buf.tensor(I32, (T,), "pos")
+    t_ids = buf.tensor(I32, (T,), "ids")
+    buf.set(t_x, x)
+    buf.set(t_pos, np.arange(T, dtype=np.int32))
+    buf.set(t_ids, np.zeros(T, np.int32))
+    small = buf.tensor(F32, (h, 1), "small")       # one row where T rows would be written
+    guard = buf.tensor(F32, (h, T), "guard")       # sits right behind it in the buffer
+    sentinel = np.full((T, h), 7.25, np.float32)
+    buf.set(guard, sentinel)
+    be = C.c_void_p()
+    assert lib().b200_backend_init(0, C.byref(be)) == 0
+
+    def run(op, type_, srcs, params=(), ne=None):
+        t = Tensor()
+        C.memmove(C.byref(t), C.byref(small), C.sizeof(Tensor))
+        t.id = 990000 + run.n
+        run.n += 1
+        t.type = type_
+        if ne:
+            for i in range(4):
+                t.ne[i] = (list(ne) + [1] * 4)[i]
+        t.op = OP[op]
+        for i, s in enumerate(srcs):
+            t.src[i] = s.id
+        for i, p in enumerate(params):
+            t.op_params[i] = p
+        table = (Tensor * (len(srcs) + 1))(*srcs, t)
+        return lib().b200_backend_graph_compute(be, (C.c_uint64 * 1)(t.id), 1, table, len(srcs) + 1)
+
+    run.n = 0
+    launches_before = lib().b200_backend_synchronize(be)
+    assert launches_before == 0
+    assert run("RMS_NORM", F32, [t_x], [_f32bits(1e-6)]) == -5
+    assert run("ADD", F32, [t_x, t_x]) == -5
+    assert run("MUL", F32, [t_x, t_x]) == -5
+    assert run("SWIGLU", F32, [t_x, t_x]) == -5
+    assert run("CPY", F32, [t_x]) == -5
+    assert run("CPY", F16, [t_x]) == -5
+    assert run("GET_ROWS", F32, [t_x, t_ids]) == -5
+    assert run("ARGMAX", I32, [t_x], ne=(1,)) == -5
+    assert run("ARGMAX", F32, [t_x], ne=(T,)) == -1          # the op writes i32
+    q = buf.tensor(F32, (128, 4, T), "q")
+    kc = buf.tensor(F16, (128, 2, 16), "kc")
+    vc = buf.tensor(F16, (128, 2, 16), "vc")
+    vbad = buf.tensor(F16, (64, 2, 16), "vbad")
+    assert run("ROPE", F32, [q, t_pos], [128, 2, _f32bits(1e6)]) == -5
+    assert run("ATTN", F32, [q, kc, vc], [_f32bits(0.088), 0]) == -5
+    full_ne = (128, 4, T)
+    assert run("ATTN", F32, [q, kc, vbad], [_f32bits(0.088), 0], ne=full_ne) == -1  # V of another head_dim
+    logits = buf.tensor(F32, (8, T), "logits")
+    idsout = buf.tensor(I32, (2, T), "idsout")
+    assert run("MOE_ROUTE", F32, [logits, idsout], [2], ne=(2, 1)) == -5
+    assert run("MOE_ROUTE", F32, [logits, idsout], [9], ne=(9, T)) == -1       # k above the expert count
+    # extents whose product does not fit are refused before any size is computed from them
+    huge = Tensor()
+    C.memmove(C.byref(huge), C.byref(small), C.sizeof(Tensor))
+    for i in range(4):
+        huge.ne[i] = 0xFFFFFFFF
+    assert lib().b200_buffer_init_tensor(buf.h, C.byref(huge)) == -5
+    assert lib().b200_backend_synchronize(be) == 0
+    np.testing.assert_array_equal(buf.get(guard, T * h * 4, dtype=np.float32).reshape(T, h), sentinel)
+    lib().b200_backend_free(be)
+    buf.free()

@@ -258,3 +258,22 @@ def test_argmax_and_router(ops):
         rid, rw = orc.moe_route(logits, k)
         np.testing.assert_array_equal(ids.cpu().numpy(), rid)
         assert rel_err(w.cpu().numpy(), rw) <= 1e-5
+
+
+def test_router_with_the_expert_mask(ops):
+    """probs -> + mask (0 / -inf) -> top-k, weights from the unmasked probs
+    (third_party/llama.cpp/patches/0003 lines 82-108): ids exact, weights to f32 rounding; a mask that
+    leaves fewer than k experts lets masked ones fill the last slots in index order."""
+    import torch
+
+    rng = np.random.default_rng(16)
+    for E, k, n_allowed in ((128, 8, 16), (128, 8, 72), (16, 8, 8), (16, 4, 2), (8, 2, 8)):
+        logits = rng.standard_normal((33, E)).astype(np.float32)
+        mask = np.zeros(E, np.uint8)
+        mask[rng.permutation(E)[:n_allowed]] = 1
+        ids, w = ops.moe_route(torch.from_numpy(logits).cuda(), k, mask=torch.from_numpy(mask).cuda())
+        rid, rw = orc.moe_route(logits, k, mask)
+        np.testing.assert_array_equal(ids.cpu().numpy(), rid)
+        assert rel_err(w.cpu().numpy(), rw) <= 1e-5
+        if n_allowed >= k:
+            assert mask[ids.cpu().numpy()].all()

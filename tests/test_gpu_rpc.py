@@ -199,3 +199,53 @@ def test_spawned_worker_executable():
         proc.terminate()
         assert proc.wait(timeout=20) == 0
     assert subprocess.run([exe, "-d", "CUDA0", "-p", str(port)], capture_output=True).returncode == 2  # unknown device name
+
+
+def test_copy_tensor_of_a_size_that_is_no_multiple_of_256():
+    """COPY_TENSOR copies the tensor's own byte count: 100 floats, read back exactly."""
+    with Server() as s:
+        c = Client(s.port)
+        h, _ = c.alloc_buffer(0, 1 << 16)
+        base = c.buffer_get_base(h)
+        src = make_tensor(h, base, (100,), name="src")
+        dst = make_tensor(h, base + 4096, (100,), name="dst")
+        data = np.random.default_rng(31).standard_normal(100).astype(np.float32)
+        c.set_tensor(src, 0, data.tobytes())
+        assert c.buffer_clear(h, 0)
+        c.set_tensor(src, 0, data.tobytes())
+        assert c.copy_tensor(src, dst) == 1
+        got = np.frombuffer(c.get_tensor(dst, 0, 400), np.float32)
+        np.testing.assert_array_equal(got, data)
+        # the bytes behind the destination were not touched
+        tail = make_tensor(h, base + 4096 + 400, (64,), name="tail")
+        assert not np.frombuffer(c.get_tensor(tail, 0, 256), np.uint8).any()
+        assert c.free_buffer(h)
+        c.close()
+
+
+def test_graph_with_a_too_small_destination_over_the_wire_writes_nothing():
+    """GRAPH_COMPUTE has no response; a node whose destination cannot hold the op's result is refused
+    by the backend before anything is launched: the server drops the connection and the memory behind
+    the destination is unchanged."""
+    with Server() as s:
+        c = Client(s.port)
+        h, _ = c.alloc_buffer(0, 1 << 20)
+        base = c.buffer_get_base(h)
+        T, n = 8, 512
+        x = np.random.default_rng(32).standard_normal((T, n)).astype(np.float32)
+        tx = make_tensor(h, base, (n, T), name="x", id_=21)
+        small = make_tensor(h, base + 65536, (n, 1), name="small", id_=22, op=3, src=(21,))  # RMS_NORM of 8 rows into 1
+        small.op_params[0] = int(np.float32(1e-6).view(np.int32))
+        guard = make_tensor(h, base + 65536 + n * 4, (n, T - 1), name="guard", id_=23)
+        c.set_tensor(tx, 0, x.tobytes())
+        sentinel = np.full((T - 1, n), 3.5, np.float32)
+        c.set_tensor(guard, 0, sentinel.tobytes())
+        c.graph_compute(0, [22], [tx, small])
+        with pytest.raises((ConnectionError, OSError)):  # a failed command ends the connection, as in the reference
+            c.get_tensor(guard, 0, 16)
+        c.close()
+        c2 = Client(s.port)  # buffers belong to the server, not to the connection
+        got = np.frombuffer(c2.get_tensor(guard, 0, sentinel.nbytes), np.float32).reshape(T - 1, n)
+        np.testing.assert_array_equal(got, sentinel)
+        assert c2.free_buffer(h)
+        c2.close()

@@ -310,6 +310,46 @@ def test_device_generated_weights_round_trip_through_the_oracle():
     assert kl_top1(lg.cpu().numpy(), ref)[0] < 1e-4 and rel_err(lg.cpu().numpy(), ref) < 5e-2
 
 
+def test_expert_mask_on_a_stage_follows_the_oracle_and_can_be_cleared():
+    """llama_model_set_expert_mask on a mixture-of-experts stage: with half of the experts masked the
+    logits follow the oracle under the same mask (prefill and the captured decode graph), differ from
+    the unmasked run, return to it when the mask is cleared, and a mask of the wrong length is refused."""
+    import torch
+    from mesh_llm_b200.capi import B200Error
+
+    m, st = make_pair(MOE, 17, n_ubatch=32)
+    toks = np.random.default_rng(6).integers(0, 1024, 12).astype(np.int32)
+    td = torch.from_numpy(toks).cuda()
+    _, base, nxt = st.forward(tokens=td, all_logits=True)
+    base = base.cpu().numpy()
+    _, dec_base, _ = st.forward(tokens=nxt[-1:].clone(), pos0=12)
+    dec_base = dec_base.cpu().numpy()
+    mask = np.zeros(16, np.uint8)
+    mask[[0, 3, 4, 7, 9, 10, 13, 15]] = 1
+    assert m.set_expert_mask(mask[:5]) == -1
+    with pytest.raises(B200Error):
+        st.set_expert_mask(mask[:5])
+    assert m.set_expert_mask(mask) == 0
+    st.set_expert_mask(mask)
+    _, ref = m.forward(tokens=toks)
+    _, got, nx2 = st.forward(tokens=td, all_logits=True)
+    got = got.cpu().numpy()
+    assert kl_top1(got, ref)[0] < 1e-4 and rel_err(got, ref) < 5e-2
+    assert np.abs(got - base).max() > 1e-3 * np.abs(base).max()
+    tok = nx2[-1:].clone()
+    _, lref = m.forward(tokens=tok.cpu().numpy(), pos0=12)
+    _, lg, _ = st.forward(tokens=tok, pos0=12)  # the decode graph captured before the mask was set
+    assert kl_top1(lg.cpu().numpy(), lref)[0] < 1e-4
+    st.set_expert_mask(None)
+    _, again, nx3 = st.forward(tokens=td, all_logits=True)
+    assert np.array_equal(again.cpu().numpy(), base)
+    _, dec_again, _ = st.forward(tokens=nx3[-1:].clone(), pos0=12)
+    assert np.array_equal(dec_again.cpu().numpy(), dec_base)
+    dense, dst = make_pair(DENSE, 11, n_ubatch=8)
+    with pytest.raises(B200Error):
+        dst.set_expert_mask(np.ones(16, np.uint8))
+
+
 def test_stage_rejects_bad_calls():
     import torch
     from mesh_llm_b200.capi import B200Error

@@ -87,3 +87,23 @@ def test_quantised_kv_cache_changes_little_and_keeps_prefill_equal_to_decode():
     m2.generate(3)
     rows = [m2.forward(tokens=toks[i:i + 1], pos0=i)[1][0] for i in range(len(toks))]
     np.testing.assert_allclose(np.stack(rows), got, rtol=0, atol=1e-6)
+
+
+def test_oracle_expert_mask_equals_routing_without_the_masked_experts():
+    """selection_probs = probs + (0 | -inf), weights from the unmasked probs renormalised over the
+    selection (third_party/llama.cpp/patches/0003 lines 82-108): with at least k experts allowed that
+    is the routing of the same logits with the masked experts' logits at -inf."""
+    rng = np.random.default_rng(3)
+    for E, k in ((128, 8), (16, 4)):
+        logits = rng.standard_normal((21, E)).astype(np.float32)
+        mask = np.zeros(E, np.uint8)
+        mask[rng.permutation(E)[: E // 2]] = 1
+        ids, w = orc.moe_route(logits, k, mask)
+        cut = logits.copy()
+        cut[:, mask == 0] = -np.inf
+        ids2, w2 = orc.moe_route(cut, k)
+        assert np.array_equal(ids, ids2) and np.abs(w - w2).max() < 1e-6
+        assert mask[ids].all() and np.allclose(w.sum(-1), 1, atol=1e-6)
+    m = orc.Model(n_layer=1, n_embd=256, n_head=2, n_head_kv=1, head_dim=128, n_ff=0, n_vocab=256, n_ctx=8,
+                  n_expert=8, n_expert_used=2, n_ff_exp=256)
+    assert m.set_expert_mask(np.ones(7)) == -1 and m.set_expert_mask(np.ones(8)) == 0 and m.set_expert_mask(None) == 0
