@@ -336,6 +336,10 @@ B200_API b200_status b200_stage_tensor_info(b200_stage *st, int64_t i, char *nam
  * B200_ERR_INVALID when n_mask is not the stage's expert count (the reference returns -1) or the
  * stage is dense.  Takes effect from the next forward call, captured decode graphs included.    */
 B200_API b200_status b200_stage_set_expert_mask(b200_stage *st, const uint8_t *mask, int32_t n_mask);
+/* Diagnostics: copies the first n_floats of one of the stage's activation buffers, as the last forward
+ * call (of the stage's last layer) left it, to host memory.  which: "q", "k", "v" (projections; q and
+ * k after RoPE when T > 1), "att" (attention output), "g" (SwiGLU output), "x" (residual stream).     */
+B200_API b200_status b200_stage_peek(b200_stage *st, const char *which, float *host_out, size_t n_floats);
 B200_API b200_status b200_stage_synchronize(b200_stage *st);
 B200_API int64_t b200_stage_kernel_launches(b200_stage *st); /* launches issued so far        */
 

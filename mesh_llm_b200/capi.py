@@ -171,6 +171,7 @@ SIGNATURES = {
                               C.POINTER(i32)]),
     "b200_gguf_write_expert_shard": (i32, [vp, vp, i32, C.c_char_p, C.POINTER(u64)]),
     "b200_stage_set_expert_mask": (i32, [vp, vp, i32]),
+    "b200_stage_peek": (i32, [vp, C.c_char_p, vp, C.c_size_t]),
     "b200_stage_synchronize": (i32, [vp]),
     "b200_stage_kernel_launches": (i64, [vp]),
 }

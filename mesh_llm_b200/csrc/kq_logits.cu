@@ -220,8 +220,13 @@ b200_status b200_logit_signals(const float *logits, int64_t T, int64_t n, const 
     int n_slice = (int)kq_div_up(n, 4096);
     if (n_slice > SLICES_MAX) n_slice = SLICES_MAX;
     if (n_slice < 1) n_slice = 1;
-    SlicePart *parts = (SlicePart *)scratch;
-    int *counters = (int *)((uint8_t *)scratch + (((size_t)T * SLICES_MAX * sizeof(SlicePart) + 255) & ~(size_t)255));
+    // Layout of the scratch: the per-row counters first, then the slice records.  Where the records
+    // start depends on the size of the scratch only, never on this call's T: calls with different row
+    // counts that share one scratch (a prefill with all rows, then decode steps with one) must find the
+    // counters, which every launch leaves at zero, in the same place.
+    const size_t rows_cap = (scratch_bytes - 256) / ((size_t)SLICES_MAX * sizeof(SlicePart) + sizeof(int));
+    int *counters = (int *)scratch;
+    SlicePart *parts = (SlicePart *)((uint8_t *)scratch + ((rows_cap * sizeof(int) + 255) & ~(size_t)255));
     kq_launch(logit_scan_kernel, dim3((unsigned)n_slice, (unsigned)T), NT, 0, (cudaStream_t)stream, logits, n, n_slice,
               chosen, parts, counters, signals, argmax_out);
     KQ_COUNT_LAUNCH();

@@ -862,6 +862,27 @@ b200_status b200_stage_profile_decode(b200_stage *st, int32_t n_seq, int32_t pos
     return B200_OK;
 }
 
+b200_status b200_stage_peek(b200_stage *st, const char *which, float *host_out, size_t n_floats) {
+    KQ_REQUIRE(st && which && host_out, "stage_peek: null argument");
+    const b200_stage_config &c = st->c;
+    const size_t R = (size_t)st->rows_max, nq = (size_t)c.n_head * c.head_dim, nkv = (size_t)c.n_head_kv * c.head_dim;
+    const float *src = nullptr;
+    size_t cap = 0;
+    const std::string w(which);
+    if (w == "x") { src = st->x; cap = R * c.n_embd; }
+    else if (w == "q") { src = st->q; cap = R * nq; }
+    else if (w == "k") { src = st->k; cap = R * nkv; }
+    else if (w == "v") { src = st->v; cap = R * nkv; }
+    else if (w == "att") { src = st->att; cap = R * nq; }
+    else if (w == "g") { src = st->g; cap = R * (size_t)(c.n_expert > 0 ? 0 : c.n_ff); }
+    KQ_REQUIRE(src, "stage_peek: no buffer named %s (x, q, k, v, att, g)", which);
+    KQ_REQUIRE(n_floats <= cap, "stage_peek: %s holds %zu floats, asked for %zu", which, cap, n_floats);
+    KqDevGuard dev_guard(c.device);
+    KQ_CUDA(cudaDeviceSynchronize());
+    KQ_CUDA(cudaMemcpy(host_out, src, n_floats * 4, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
 b200_status b200_stage_set_expert_mask(b200_stage *st, const uint8_t *mask, int32_t n_mask) {
     KQ_REQUIRE(st, "stage_set_expert_mask: null stage");
     KQ_REQUIRE(st->c.n_expert > 0, "stage_set_expert_mask: the stage has no experts");

@@ -118,5 +118,11 @@ class Stage:
         m = np.ascontiguousarray(np.asarray(mask) != 0, dtype=np.uint8)
         check(lib().b200_stage_set_expert_mask(self.h, m.ctypes.data, m.size))
 
+    def peek(self, which, shape):
+        """diagnostics: an internal activation buffer ("q", "k", "v", "att", "g", "x") after the last forward"""
+        out = np.empty(shape, np.float32)
+        check(lib().b200_stage_peek(self.h, which.encode(), out.ctypes.data, out.size))
+        return out
+
     def synchronize(self):
         check(lib().b200_stage_synchronize(self.h))

@@ -350,6 +350,25 @@ def test_expert_mask_on_a_stage_follows_the_oracle_and_can_be_cleared():
         dst.set_expert_mask(np.ones(16, np.uint8))
 
 
+def test_greedy_token_after_calls_with_different_row_counts():
+    """The vocabulary scan keeps per-row counters in the stage's scratch; a prefill that asks for all
+    rows and the one-row decode steps after it share that scratch and must both leave a token."""
+    import torch
+
+    m, st = make_pair(DENSE, 19, n_ubatch=32)
+    toks = torch.from_numpy(np.random.default_rng(8).integers(0, 2048, 19).astype(np.int32)).cuda()
+    _, lg, nxt = st.forward(tokens=toks, all_logits=True)
+    assert np.array_equal(nxt.cpu().numpy(), lg.cpu().numpy().argmax(-1))
+    tok = nxt[-1:].clone()
+    for step in range(3):
+        nx = torch.full((1,), -7, dtype=torch.int32, device="cuda")
+        _, lg1, _ = st.forward(tokens=tok, pos0=19 + step, all_logits=True, next_tokens=nx)
+        assert int(nx.item()) == int(lg1.cpu().numpy()[0].argmax())
+        tok = nx.clone()
+    _, lg, nxt = st.forward(tokens=toks[:7], all_logits=True)  # and back to several rows
+    assert np.array_equal(nxt.cpu().numpy(), lg.cpu().numpy().argmax(-1))
+
+
 def test_stage_rejects_bad_calls():
     import torch
     from mesh_llm_b200.capi import B200Error
