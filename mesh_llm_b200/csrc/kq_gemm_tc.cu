@@ -33,7 +33,8 @@ namespace {
 
 constexpr int TM = 128, TN = 64, NTHREADS = 256, NCOL = TN / 2; // NCOL: result columns per thread
 constexpr int LBO_A = TM * 16;      // bytes between consecutive 16-byte K chunks of the token operand
-constexpr int LBO_B = TN * 16;      // ... of a weight plane
+constexpr int LBO_B = 2 * TN * 16;  // ... of the weight operand: the hi plane's rows, then the lo plane's (one tile of 2 TN rows)
+constexpr int LBO_BMIN = TN * 16;   // ... of the f16 min operand
 constexpr int SBO = 128;            // bytes between consecutive groups of 8 rows
 constexpr int A_BYTES = TM * 256;   // int8 token slab: 128 rows x 256 K bytes
 constexpr int B_BYTES = TN * 256;   // one int8 weight plane
@@ -72,7 +73,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 
 // canonical K-major, no swizzle: 16-byte chunk kc of row r
 __device__ __forceinline__ uint32_t op_off_a(int r, int kc) { return kc * LBO_A + (r >> 3) * SBO + (r & 7) * 16; }
+// weight operand: rows 0 .. TN-1 of the tile are the hi plane, rows TN .. 2 TN-1 the lo plane
 __device__ __forceinline__ uint32_t op_off_b(int r, int kc) { return kc * LBO_B + (r >> 3) * SBO + (r & 7) * 16; }
+__device__ __forceinline__ uint32_t op_off_bmin(int r, int kc) { return kc * LBO_BMIN + (r >> 3) * SBO + (r & 7) * 16; }
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo) {
     uint64_t d = 0;
@@ -83,9 +86,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo) {
     return d;               // layout type 0: no swizzle
 }
 
-// kind::i8: D s32, A s8, B s8 or u8, both K-major, M = 128, N = 128
+// kind::i8: D s32, A s8, B s8 or u8, both K-major, M = 128, N = 2 TN (both planes in one instruction)
 __device__ __forceinline__ uint32_t idesc_i8(bool b_signed) {
-    return (2u << 4) | (1u << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+    return (2u << 4) | (1u << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)((2 * TN) >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 }
 // kind::f16: D f32, A f16, B f16
 __device__ __forceinline__ uint32_t idesc_f16() {
@@ -119,6 +122,32 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b,
                  : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), \
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])     \
                  : "memory")
+
+// Packed f32 pairs: sm_100 issues mul / fma on two floats per instruction (same IEEE results as the
+// scalar forms), which halves the floating-point instructions of the epilogue.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t a, uint32_t b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
 
 // Four 4-bit codes (one per byte of nib4) times the sub-block scale, split into the planes
 // hi = (sc*q) >> 8 and lo = (sc*q) & 255.  Two 16-bit lanes per multiply; the products' low and high
@@ -182,12 +211,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
     const int chalf = warp >> 2;            // columns [NCOL*chalf, NCOL*chalf + NCOL)
     const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
-    float yacc[NCOL]; // running f32 result of this thread's token row x its weight columns
+    uint64_t yacc[NCOL / 2]; // running f32 result of this thread's token row x its weight columns, as f32 pairs
 #pragma unroll
-    for (int i = 0; i < NCOL; i++) yacc[i] = 0.f;
+    for (int i = 0; i < NCOL / 2; i++) yacc[i] = 0ull;
 
     const uint32_t a_base = smem_u32(smem + SMEM_A), bhi_base = smem_u32(smem + SMEM_BHI),
-                   blo_base = smem_u32(smem + SMEM_BLO), amin_base = smem_u32(smem + SMEM_AMIN),
+                   amin_base = smem_u32(smem + SMEM_AMIN),
                    bmin_base = smem_u32(smem + SMEM_BMIN);
     const bool q4 = p.type == B200_TYPE_Q4_K;
     const int64_t wstride = kq_device_row_bytes(p.type, p.K);
@@ -311,8 +340,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                         mh[2 * j] = v;
                         mh[2 * j + 1] = v;
                     }
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_b(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_b(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_bmin(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_bmin(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
                 }
                 uint4 hi_l, lo_l, hi_h, lo_h;
                 q4_planes(w.x & 0x0F0F0F0Fu, sc0, hi_l.x, lo_l.x);
@@ -323,15 +352,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                 q4_planes((w.y >> 4) & 0x0F0F0F0Fu, sc1, hi_h.y, lo_h.y);
                 q4_planes((w.z >> 4) & 0x0F0F0F0Fu, sc1, hi_h.z, lo_h.z);
                 q4_planes((w.w >> 4) & 0x0F0F0F0Fu, sc1, hi_h.w, lo_h.w);
-                const uint32_t o_l = op_off_b(r, 4 * g + h), o_h = op_off_b(r, 4 * g + 2 + h);
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o_l) = hi_l;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BLO + o_l) = lo_l;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o_h) = hi_h;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BLO + o_h) = lo_h;
+                const int kc_l = 4 * g + h, kc_h = 4 * g + 2 + h;
+                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc_l)) = hi_l;
+                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc_l)) = lo_l;
+                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc_h)) = hi_h;
+                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc_h)) = lo_h;
             }
         } else {
             // Q6_K: one task per (row, qh chunk j): 4 scale groups of 16 elements, w' = sc * (q - 32)
-            // split as hi * 64 + lo with lo in 0..63 (unsigned plane) and hi in -64..64 (signed plane)
+            // split as hi * 64 + lo with lo in 0..63 and hi in -64..63 (both planes signed)
 #pragma unroll
             for (int t = 0; t < WT6; t++) {
                 const int wt = warp + t * (NTHREADS / 32), r = 8 * wt + (lane & 7), j = lane >> 3;
@@ -363,9 +392,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                         hi4[wd] = hi;
                         lo4[wd] = lo;
                     }
-                    const uint32_t o = op_off_b(r, 8 * hh + 2 * q + c1);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BHI + o) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BLO + o) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                    const int kc = 8 * hh + 2 * q + c1;
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                    *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
                 }
             }
         }
@@ -389,14 +418,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (a_ok && !s_abort) {
-                const uint32_t id_hi = idesc_i8(true), id_lo = idesc_i8(false); // the low plane is unsigned
+                // Q4_K planes are unsigned (hi 0..3, lo 0..255), Q6_K planes signed (hi -64..63, lo 0..63)
+                const uint32_t id_main = idesc_i8(!q4);
 #pragma unroll
-                for (int s = 0; s < 8; s++) { // K = 32 per instruction: chunks 2s, 2s+1
-                    const uint64_t ad = make_desc(a_base + 2 * s * LBO_A, LBO_A);
-                    mma_i8(tmem + COL_HI, ad, make_desc(bhi_base + 2 * s * LBO_B, LBO_B), id_hi, s > 0);
-                    mma_i8(tmem + COL_LO, ad, make_desc(blo_base + 2 * s * LBO_B, LBO_B), id_lo, s > 0);
-                }
-                if (q4) mma_f16(tmem + COL_MIN, make_desc(amin_base, LBO_A), make_desc(bmin_base, LBO_B), idesc_f16(), 0);
+                for (int s = 0; s < 8; s++) // K = 32 per instruction: chunks 2s, 2s+1; N = hi rows | lo rows
+                    mma_i8(tmem + COL_HI, make_desc(a_base + 2 * s * LBO_A, LBO_A), make_desc(bhi_base + 2 * s * LBO_B, LBO_B),
+                           id_main, s > 0);
+                if (q4) mma_f16(tmem + COL_MIN, make_desc(amin_base, LBO_A), make_desc(bmin_base, LBO_BMIN), idesc_f16(), 0);
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a)
                          : "memory");
@@ -428,6 +456,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
         // ---- epilogue of the super-block: y += d_a * (d_w * (R*hi + lo) - dmin * min) ------------
         if (!failed) {
             const float da = da_s[row];
+            const uint64_t da2 = pack2(da, da);
             const int R = q4 ? 256 : 64;
 #pragma unroll
             for (int c = 0; c < NCOL; c += 16) {
@@ -439,16 +468,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i4 = 0; i4 < 16; i4 += 4) {
-                    const float4 dw4 = *reinterpret_cast<const float4 *>(&dw_s[col + i4]);
-                    const float4 dm4 = *reinterpret_cast<const float4 *>(&dmin_s[col + i4]);
-                    const float dwv[4] = {dw4.x, dw4.y, dw4.z, dw4.w}, dmv[4] = {dm4.x, dm4.y, dm4.z, dm4.w};
+                    // t = dw * main - dmin * min (one rounding each for the product and the fused subtract),
+                    // y = fma(da, t, y): the arithmetic of the scalar form, two columns per instruction
+                    const ulonglong2 dw4 = *reinterpret_cast<const ulonglong2 *>(&dw_s[col + i4]);
+                    const ulonglong2 dm4 = *reinterpret_cast<const ulonglong2 *>(&dmin_s[col + i4]);
+                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x ^ 0x8000000080000000ull, dm4.y ^ 0x8000000080000000ull};
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int i = i4 + k;
-                        const int main_i = R * (int)hi[i] + (int)lo[i];
-                        float t = dwv[k] * (float)main_i;
-                        if (q4) t -= dmv[k] * __uint_as_float(mn[i]);
-                        yacc[c + i] = fmaf(da, t, yacc[c + i]);
+                    for (int k = 0; k < 2; k++) {
+                        const int i = i4 + 2 * k;
+                        const float f0 = (float)(R * (int)hi[i] + (int)lo[i]), f1 = (float)(R * (int)hi[i + 1] + (int)lo[i + 1]);
+                        uint64_t t = mul2(dwp[k], pack2(f0, f1));
+                        if (q4) t = fma2(dmp[k], pack2u(mn[i], mn[i + 1]), t);
+                        yacc[(c + i) / 2] = fma2(da2, t, yacc[(c + i) / 2]);
                     }
                 }
             }
@@ -477,7 +508,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
             const int col = chalf * NCOL + c;
             if (n0 + col < p.N) {
                 const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
-                float v = yacc[c];
+                float v, v_odd;
+                unpack2(yacc[c / 2], v, v_odd);
+                if (c & 1) v = v_odd;
                 if (p.bias) v += p.bias[n0 + col];
                 if (p.residual) v += p.residual[o];
                 p.y[o] = v;
