@@ -195,6 +195,16 @@ B200_API b200_status b200_mul_mat_q8(uint32_t type, const void *W, const int8_t 
                                      const int16_t *bsum16, int64_t M, int64_t N, int64_t K,
                                      float *y, const float *bias, const float *residual,
                                      void *stream);
+/* MUL_MAT_ID of the ggml op surface (build_moe_ffn's expert matmuls, third_party/llama.cpp/patches/0003
+ * lines 82-108): W holds E expert matrices [N x K] one after the other (device layout); pair p of the
+ * n_pairs (token, slot) pairs uses expert ids[p] (device i32) on activation row p / (n_pairs / n_x_rows)
+ * of x [n_x_rows][K] and writes y[p][N].  With more than 8 pairs the pairs are gathered per expert (a
+ * stable counting sort on the device) and every expert's rows go through the tensor-core GEMM in one
+ * grouped launch; with fewer, one streamed matrix-vector product per pair.  E <= 256.               */
+B200_API size_t b200_mul_mat_id_scratch_bytes(int64_t n_x_rows, int64_t n_pairs, int64_t K, int64_t E);
+B200_API b200_status b200_mul_mat_id(uint32_t type, const void *W, int64_t E, const float *x, int64_t n_x_rows,
+                                     const int32_t *ids, int64_t n_pairs, int64_t N, int64_t K, float *y,
+                                     void *scratch, size_t scratch_bytes, void *stream);
 /* The same contraction as b200_mul_mat for callers that must not allocate and have no scratch
  * to lend (no counterpart in the reference; an addition of this library).  Meant for a stage whose
  * device memory was budgeted in full before it started, for a decode loop that cannot afford

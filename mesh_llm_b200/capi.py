@@ -140,6 +140,8 @@ SIGNATURES = {
     "b200_attention_kv": (i32, [vp, vp, vp, u32, u32, i64, i64, i64, i64, i64, vp, vp, sz, vp]),
     "b200_get_rows": (i32, [u32, vp, vp, i64, i64, vp, vp]),
     "b200_argmax": (i32, [vp, i64, i64, vp, vp]),
+    "b200_mul_mat_id_scratch_bytes": (sz, [i64, i64, i64, i64]),
+    "b200_mul_mat_id": (i32, [u32, vp, i64, vp, i64, vp, i64, i64, i64, vp, vp, sz, vp]),
     "b200_moe_route": (i32, [vp, i64, i64, i64, vp, vp, vp]),
     "b200_moe_route_masked": (i32, [vp, i64, i64, i64, vp, vp, vp, vp]),
     "b200_logit_signals_scratch_bytes": (sz, [i64]),

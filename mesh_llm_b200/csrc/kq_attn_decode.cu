@@ -51,8 +51,8 @@ __device__ __forceinline__ uint8_t *sw_elem(uint8_t *base, int row, int dim) {
 template <int HD, int G>
 __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                                                               const __grid_constant__ CUtensorMap vmap,
-                                                              const float *__restrict__ q, const float *__restrict__ k_new,
-                                                              const float *__restrict__ v_new, __half *kc, __half *vc,
+                                                              const float *q, const float *k_new,
+                                                              const float *v_new, __half *kc, __half *vc,
                                                               const int32_t *pos_dev, int pos_val, int n_head, int n_kv,
                                                               int64_t seq_stride, int n_split, float scale, int neox,
                                                               RopeTab tab, float *out, float *part_o, float *part_ml,

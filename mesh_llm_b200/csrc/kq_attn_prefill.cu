@@ -37,10 +37,10 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t 
 }
 
 template <int G>
-__global__ void __launch_bounds__(G * 32) attn_prefill_kernel(const float *__restrict__ q, const __half *__restrict__ kc,
-                                                               const __half *__restrict__ vc, int T, const int32_t *pos0_dev,
+__global__ void __launch_bounds__(G * 32) attn_prefill_kernel(const float *q, const __half *kc,
+                                                               const __half *vc, int T, const int32_t *pos0_dev,
                                                                int pos0, int n_head, int n_kv, int64_t seq_stride,
-                                                               float scale_log2, float *__restrict__ out, KqKvTypes kvt) {
+                                                               float scale_log2, float *out, KqKvTypes kvt) {
     KQ_PDL_ENTER();
     extern __shared__ __align__(128) uint8_t sm[]; // K tiles [2], then V tiles [2]
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, kh = blockIdx.y, seq = blockIdx.z;

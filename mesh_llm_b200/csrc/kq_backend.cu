@@ -392,19 +392,13 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
                        "MUL_MAT_ID %.64s: x must be [K, n_used|1, T]", t->name);
             KQ_REQUIRE(t->ne[0] == N && t->ne[1] == n_used && t->ne[2] == T && t->type == B200_TYPE_F32,
                        "MUL_MAT_ID %.64s: bad output shape", t->name);
-            (void)E;
-            const int64_t xrows = b->ne[1] * T;
-            KQ_TRY(ensure_scratch(be, b200_mul_mat_scratch_bytes(xrows, K)));
-            auto up = [](size_t v) { return (v + 255) / 256 * 256; };
-            int8_t *q = (int8_t *)be->scratch;
-            float *d = (float *)((char *)be->scratch + up((size_t)(xrows * K)));
-            int16_t *bs = (int16_t *)((char *)d + up((size_t)(xrows * K / 256 * 4)));
-            KQ_TRY(b200_quantize_act((const float *)pb, xrows, K, q, d, bs, s));
-            KqGemvSeg sg = {(const uint8_t *)pa, a->type, (int32_t)N, y, nullptr, (int32_t)N,
-                            kq_device_row_bytes(a->type, K) * N};
-            KqGemvIndirect ind = {(const int32_t *)(uintptr_t)c->data, (int32_t)(n_used * T),
-                                  (int32_t)(b->ne[1] == 1 ? n_used : 1)};
-            KQ_TRY(kq_launch_gemv(&sg, 1, q, d, bs, 1, K, nullptr, 0, &ind, s));
+            KQ_REQUIRE(E >= 1 && E <= 256, "MUL_MAT_ID %.64s: at most 256 experts", t->name);
+            const int64_t xrows = b->ne[1] * T, pairs = n_used * T;
+            const size_t need = b200_mul_mat_id_scratch_bytes(xrows, pairs, K, E);
+            KQ_TRY(ensure_scratch(be, need));
+            // more than 8 pairs: gathered per expert and run through the tensor-core GEMM in one grouped launch
+            KQ_TRY(b200_mul_mat_id(a->type, pa, E, (const float *)pb, xrows, (const int32_t *)(uintptr_t)c->data, pairs, N, K, y,
+                                   be->scratch, be->scratch_bytes, s));
             break;
         }
         case B200_OP_RMS_NORM:

@@ -171,4 +171,40 @@ b200_status b200_mul_mat(uint32_t type, const void *W, const float *x, int64_t M
     return b200_mul_mat_q8(type, W, q, d, bs, M, N, K, y, nullptr, nullptr, stream);
 }
 
+size_t b200_mul_mat_id_scratch_bytes(int64_t n_x_rows, int64_t n_pairs, int64_t K, int64_t E) {
+    return b200_mul_mat_scratch_bytes(n_x_rows, K) + ((kq_moe_sort_scratch_bytes(n_pairs, E) + 255) / 256) * 256;
+}
+
+b200_status b200_mul_mat_id(uint32_t type, const void *W, int64_t E, const float *x, int64_t n_x_rows, const int32_t *ids,
+                            int64_t n_pairs, int64_t N, int64_t K, float *y, void *scratch, size_t scratch_bytes,
+                            void *stream) {
+    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "mul_mat_id: weight type %u", type);
+    KQ_REQUIRE(W && x && ids && y && scratch, "mul_mat_id: null pointer");
+    KQ_REQUIRE(E >= 1 && E <= 256 && N >= 1 && K >= 256 && K % 256 == 0, "mul_mat_id: bad shape E=%lld N=%lld K=%lld",
+               (long long)E, (long long)N, (long long)K);
+    KQ_REQUIRE(n_x_rows >= 1 && n_pairs >= n_x_rows && n_pairs % n_x_rows == 0,
+               "mul_mat_id: %lld pairs over %lld activation rows", (long long)n_pairs, (long long)n_x_rows);
+    KQ_REQUIRE(((uintptr_t)scratch & 255) == 0 && scratch_bytes >= b200_mul_mat_id_scratch_bytes(n_x_rows, n_pairs, K, E),
+               "mul_mat_id: scratch must be 256-byte aligned and hold %zu bytes", b200_mul_mat_id_scratch_bytes(n_x_rows, n_pairs, K, E));
+    cudaStream_t st = (cudaStream_t)stream;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    int8_t *q = (int8_t *)scratch;
+    float *d = (float *)((char *)scratch + up((size_t)(n_x_rows * K)));
+    int16_t *bs = (int16_t *)((char *)d + up((size_t)(n_x_rows * K / 256 * 4)));
+    int32_t *sorted = (int32_t *)((char *)scratch + b200_mul_mat_scratch_bytes(n_x_rows, K));
+    b200_status rc = b200_quantize_act(x, n_x_rows, K, q, d, bs, stream);
+    if (rc != B200_OK) return rc;
+    const int act_div = (int)(n_pairs / n_x_rows);
+    const int64_t estride = kq_device_row_bytes(type, K) * N;
+    if (n_pairs > 8) { // many pairs: gathered per expert, one grouped launch of the tensor-core kernel
+        rc = kq_moe_sort(ids, n_pairs, E, sorted, kq_moe_sort_scratch_bytes(n_pairs, E), st);
+        if (rc != B200_OK) return rc;
+        rc = kq_launch_gemm_grouped(type, (const uint8_t *)W, estride, q, d, bs, act_div, n_pairs, E, N, K, y, sorted, st);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+    }
+    KqGemvSeg sg = {(const uint8_t *)W, type, (int32_t)N, y, nullptr, (int32_t)N, estride};
+    KqGemvIndirect ind = {ids, (int32_t)n_pairs, (int32_t)act_div};
+    return kq_launch_gemv(&sg, 1, q, d, bs, 1, K, nullptr, 0, &ind, st);
+}
+
 } // extern "C"

@@ -120,7 +120,10 @@ static inline __host__ __device__ KqQ6Addr kq_q6_addr(int nb, int blk) {
 // step is a chain of some 700 short kernels, so taking the launch latency off the critical path
 // is worth about as much as a faster kernel.  Kernels may do work that does not depend on earlier
 // kernels (prefetching weights) before KQ_PDL_WAIT(); they must not read activations or write
-// anything before it.
+// anything before it.  For the same reason no kernel parameter that points at data another kernel of
+// the stream produces is declared `const T *__restrict__`: the compiler may treat loads through such
+// a pointer as invariant and move them above the wait (a load placed right behind the wait was seen
+// to return the predecessor's stale value).
 extern int g_kq_pdl;
 #ifdef __CUDACC__
 #define KQ_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
@@ -255,6 +258,13 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
                                   const KqActPrep *prep, cudaStream_t st);
 b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y, int8_t *q,
                         float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride);
+// MUL_MAT_ID over many tokens: stable expert-major order of the (token, slot) pairs, then one grouped
+// launch of the tensor-core GEMM per expert-packed matrix (y[pair][N] = W[expert(pair)] . x[pair / act_div])
+size_t kq_moe_sort_scratch_bytes(int64_t n_pairs, int64_t E);
+b200_status kq_moe_sort(const int32_t *ids, int64_t n_pairs, int64_t E, int32_t *scratch, size_t scratch_bytes, cudaStream_t st);
+b200_status kq_launch_gemm_grouped(uint32_t type, const uint8_t *W, int64_t expert_stride, const int8_t *q, const float *d,
+                                   const int16_t *bs, int act_div, int64_t n_pairs, int64_t E, int64_t N, int64_t K, float *y,
+                                   const int32_t *sorted, cudaStream_t st);
 int kq_stream_error_fetch(); // 0 ok; nonzero = a bounded device-side wait gave up since the last call
 int kq_gemm_error_fetch();
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,

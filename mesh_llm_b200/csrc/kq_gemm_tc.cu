@@ -67,6 +67,12 @@ struct GemmParams {
     const float *bias, *residual;
     int32_t M, N, K, nb;
     uint32_t type;
+    // grouped (per-expert) mode, MUL_MAT_ID: token tile blockIdx.y belongs to expert tile_expert[y]; its
+    // rows are the gathered (token, slot) pairs row_src[y * 128 + r] (-1 = padding), whose activations
+    // are those of row row_src / act_div and whose result goes to row row_src of y.  Null: dense mode.
+    const int32_t *row_src, *tile_expert, *n_tiles;
+    int32_t act_div;
+    int64_t expert_stride; // bytes between consecutive expert matrices
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -161,7 +167,7 @@ __device__ __forceinline__ void q4_planes(uint32_t nib4, uint32_t sc, uint32_t &
 
 // Q8 codes [M][K] -> [M/128][K/16][128 rows][16 bytes]: one super-block of a 128-token tile becomes a
 // contiguous 32 KB run already in the operand layout; rows past M are zero.
-__global__ void __launch_bounds__(256) retile_act_kernel(const int8_t *__restrict__ q, uint4 *__restrict__ out, int M, int K,
+__global__ void __launch_bounds__(256) retile_act_kernel(const int8_t *q, uint4 *out, int M, int K,
                                                          int64_t n_piece) {
     KQ_PDL_ENTER();
     const int kcs = K / 16;
@@ -171,6 +177,24 @@ __global__ void __launch_bounds__(256) retile_act_kernel(const int8_t *__restric
         const int kc = (int)(t % kcs), mt = (int)(t / kcs);
         const int m = mt * TM + r;
         out[i] = m < M ? *reinterpret_cast<const uint4 *>(q + (int64_t)m * K + kc * 16) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// The same for gathered rows: tile t, row r takes the codes of activation row row_src[t * 128 + r] / act_div
+// (zeros where row_src is negative: padding behind an expert's last pair).  Tiles past *n_tiles are skipped.
+__global__ void __launch_bounds__(256) retile_gather_kernel(const int8_t *q, uint4 *out,
+                                                            const int32_t *row_src, const int32_t *n_tiles,
+                                                            int act_div, int K, int64_t n_piece) {
+    KQ_PDL_ENTER();
+    const int kcs = K / 16;
+    const int64_t live = (int64_t)(*n_tiles) * kcs * TM;
+    if (live < n_piece) n_piece = live;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_piece; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i % TM);
+        const int64_t t = i / TM;
+        const int kc = (int)(t % kcs), mt = (int)(t / kcs);
+        const int src = row_src[mt * TM + r];
+        out[i] = src >= 0 ? *reinterpret_cast<const uint4 *>(q + (int64_t)(src / act_div) * K + kc * 16) : make_uint4(0, 0, 0, 0);
     }
 }
 
@@ -184,6 +208,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    const bool grouped = p.row_src != nullptr;
+    if (grouped && (int)blockIdx.y >= *p.n_tiles) return; // the grid is sized for the worst case
+    const int expert = grouped ? p.tile_expert[blockIdx.y] : 0;
     float *da_s = reinterpret_cast<float *>(smem + SMEM_SCAL);
     float *dw_s = da_s + TM, *dmin_s = dw_s + TN;
     const uint32_t mbar_a = smem_u32(&mbar);
@@ -234,6 +261,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
     float pf_da = 0.f;
     int4 pf_bs0 = make_int4(0, 0, 0, 0), pf_bs1 = make_int4(0, 0, 0, 0);
 
+    // activation row of this thread's token duty (threads 0 .. TM-1), -1 past the end / for padding
+    int src_act = -1;
+    if (tid < TM) {
+        if (grouped) {
+            const int sr = p.row_src[m0 + tid];
+            src_act = sr >= 0 ? sr / p.act_div : -1;
+        } else if (m0 + tid < p.M) {
+            src_act = m0 + tid;
+        }
+    }
+    const uint8_t *const Wb = p.W + (int64_t)expert * p.expert_stride;
     auto issue_raw = [&](int b) { // one tiled TMA box: 64 rows x 144 bytes; rows past N arrive as zeros
         if (q4 && warp == 1 && lane == 0) {
             const uint32_t bar = smem_u32(&full_raw[b & 1]);
@@ -241,7 +279,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                              smem_u32(smem + SMEM_RAW + (b & 1) * RAW_BYTES)),
-                         "l"(&wmap), "r"(b * KQ_Q4K_BYTES), "r"(n0), "r"(bar)
+                         "l"(&wmap), "r"(b * KQ_Q4K_BYTES), "r"(n0 + expert * p.N), "r"(bar)
                          : "memory");
         }
     };
@@ -258,11 +296,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
     };
     auto prefetch = [&](int b) { // per-token scalars and (Q6_K) the weight pieces, into registers
         if (tid < TM) {
-            const int r = tid;
-            const bool in = m0 + r < p.M;
-            pf_da = in ? p.ad[(int64_t)(m0 + r) * p.nb + b] : 0.f;
+            const bool in = src_act >= 0;
+            pf_da = in ? p.ad[(int64_t)src_act * p.nb + b] : 0.f;
             if (q4) {
-                const int4 *bsp = reinterpret_cast<const int4 *>(p.abs16 + ((int64_t)(m0 + r) * p.nb + b) * 16);
+                const int4 *bsp = reinterpret_cast<const int4 *>(p.abs16 + ((int64_t)src_act * p.nb + b) * 16);
                 pf_bs0 = in ? bsp[0] : make_int4(0, 0, 0, 0);
                 pf_bs1 = in ? bsp[1] : make_int4(0, 0, 0, 0);
             }
@@ -277,7 +314,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                 p6_sc[t] = 0;
                 p6_d[t] = 0.f;
                 if (n0 + r < p.N) {
-                    const uint8_t *rowp = p.W + (int64_t)(n0 + r) * wstride;
+                    const uint8_t *rowp = Wb + (int64_t)(n0 + r) * wstride;
                     p6_h[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.qh + j * qa.cs));
                     p6_a[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1) * qa.cs));
                     p6_b[t] = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1 + 2) * qa.cs));
@@ -502,12 +539,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
         kq_mbar_wait(smem_u32(&full_a), (uint32_t)(last_a & 1), 5 * KQ_WAIT_LIMIT_NS);
     }
     // ---- write the tile -------------------------------------------------------------------------
-    if (!failed && m0 + row < p.M) {
+    const int out_row = grouped ? p.row_src[m0 + row] : (m0 + row < p.M ? m0 + row : -1);
+    if (!failed && out_row >= 0) {
 #pragma unroll
         for (int c = 0; c < NCOL; c++) {
             const int col = chalf * NCOL + c;
             if (n0 + col < p.N) {
-                const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
+                const int64_t o = (int64_t)out_row * p.N + n0 + col;
                 float v, v_odd;
                 unpack2(yacc[c / 2], v, v_odd);
                 if (c & 1) v = v_odd;
@@ -521,6 +559,74 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
     __syncthreads();
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+// ---- expert-major order of the (token, slot) pairs of a routed batch (MUL_MAT_ID with many tokens) ----
+// A stable counting sort by expert: the pairs of expert e, in pair order, become the rows of that
+// expert's token tiles; every expert starts on a tile boundary, the rows behind its last pair are
+// padding (-1).  One CTA of 8 warps; warp w walks a contiguous range of the pairs 32 at a time, so the
+// order inside an expert is the pair order whatever the timing.  Output: n_tiles, the expert of each
+// tile, and for each tile row the pair it holds.
+constexpr int SORT_WARPS = 8, SORT_MAX_E = 256;
+__global__ void __launch_bounds__(SORT_WARPS * 32) moe_sort_kernel(const int32_t *ids, int n_pairs, int E,
+                                                                   int32_t *n_tiles_out, int32_t *tile_expert, int32_t *row_src) {
+    KQ_PDL_ENTER();
+    __shared__ int cnt[SORT_WARPS][SORT_MAX_E]; // pass 1: pairs of expert e in warp w's range; then the range's offset inside the expert
+    __shared__ int tile_start[SORT_MAX_E];
+    __shared__ int s_tiles;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < SORT_WARPS * SORT_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
+    __syncthreads();
+    const int chunk = ((n_pairs + SORT_WARPS - 1) / SORT_WARPS + 31) & ~31;
+    const int begin = min(n_pairs, warp * chunk), end = min(n_pairs, begin + chunk);
+    for (int i = begin; i < end; i += 32) {
+        const int pr = i + lane;
+        int e = pr < end ? ids[pr] : -1;
+        if (e < 0 || e >= E) e = -1; // not an expert of this table: the pair is dropped
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == __ffs(same) - 1) cnt[warp][e] += __popc(same);
+        __syncwarp();
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < E) {
+        int run = 0;
+        for (int w = 0; w < SORT_WARPS; w++) {
+            const int c = cnt[w][threadIdx.x];
+            cnt[w][threadIdx.x] = run;
+            run += c;
+        }
+        tile_start[threadIdx.x] = run; // the expert's pair count, for the moment
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < E; e++) {
+            const int nt = (tile_start[e] + TM - 1) / TM;
+            tile_start[e] = t;
+            for (int k = 0; k < nt; k++) tile_expert[t + k] = e;
+            t += nt;
+        }
+        s_tiles = t;
+        *n_tiles_out = t;
+    }
+    __syncthreads();
+    const int live = s_tiles * TM;
+    for (int i = threadIdx.x; i < live; i += blockDim.x) row_src[i] = -1;
+    __syncthreads();
+    for (int i = begin; i < end; i += 32) {
+        const int pr = i + lane;
+        int e = pr < end ? ids[pr] : -1;
+        if (e < 0 || e >= E) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int leader = __ffs(same) - 1;
+        int base = 0;
+        if (e >= 0 && lane == leader) base = cnt[warp][e];
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (e >= 0) row_src[tile_start[e] * TM + base + __popc(same & ((1u << lane) - 1u))] = pr;
+        __syncwarp();
+        if (e >= 0 && lane == leader) cnt[warp][e] = base + __popc(same);
+        __syncwarp();
+    }
 }
 
 } // namespace
@@ -594,26 +700,16 @@ b200_status kq_tmap_encode(void *map128, int elem_bytes, int rank, const void *b
     return B200_OK;
 }
 
-b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, const float *d, const int16_t *bs,
-                              int64_t M, int64_t N, int64_t K, float *y, const float *bias, const float *residual,
-                              cudaStream_t st) {
-    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "gemm: weight type %u", type);
-    KQ_REQUIRE(K % 256 == 0 && M > 0 && N > 0, "gemm: bad shape");
-    KQ_REQUIRE(((uintptr_t)W & 15) == 0 && ((uintptr_t)q & 15) == 0, "gemm: operands must be 16-byte aligned");
-    // Per-device scratch for the re-tiled activations, grown on demand and kept; launches that share
-    // it are ordered by using one stream per device at a time, as the stage engine and the backend do.
-    // Host threads may call for different devices at the same time: the table and its growth are
-    // guarded, the launches themselves are not serialised.
+// Per-device scratch for the re-tiled activations, grown on demand and kept; launches that share
+// it are ordered by using one stream per device at a time, as the stage engine and the backend do.
+// Host threads may call for different devices at the same time: the table and its growth are
+// guarded, the launches themselves are not serialised.
+static b200_status kq_gemm_scratch(int dev, size_t need, cudaStream_t st, uint4 **out) {
     static std::mutex scratch_mu;
-    std::unique_lock<std::mutex> scratch_lock(scratch_mu);
+    std::lock_guard<std::mutex> scratch_lock(scratch_mu);
     static uint4 *tiled[KQ_MAX_DEVICES];
     static size_t tiled_cap[KQ_MAX_DEVICES];
     static bool attr[KQ_MAX_DEVICES];
-    int dev = 0;
-    KQ_CUDA(cudaGetDevice(&dev));
-    KQ_REQUIRE(dev >= 0 && dev < KQ_MAX_DEVICES, "gemm: device %d out of range", dev);
-    const int64_t m_tiles = kq_div_up(M, TM);
-    const size_t need = (size_t)m_tiles * TM * K;
     if (need > tiled_cap[dev]) {
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         KQ_CUDA(cudaStreamIsCapturing(st, &cs));
@@ -625,17 +721,35 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
         KQ_CUDA(cudaMalloc(&tiled[dev], need));
         tiled_cap[dev] = need;
     }
-    uint4 *const tiled_dev = tiled[dev];
     if (!attr[dev]) {
         KQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
         attr[dev] = true;
     }
-    scratch_lock.unlock();
+    *out = tiled[dev];
+    return B200_OK;
+}
+
+b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, const float *d, const int16_t *bs,
+                              int64_t M, int64_t N, int64_t K, float *y, const float *bias, const float *residual,
+                              cudaStream_t st) {
+    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "gemm: weight type %u", type);
+    KQ_REQUIRE(K % 256 == 0 && M > 0 && N > 0, "gemm: bad shape");
+    KQ_REQUIRE(((uintptr_t)W & 15) == 0 && ((uintptr_t)q & 15) == 0, "gemm: operands must be 16-byte aligned");
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    KQ_REQUIRE(dev >= 0 && dev < KQ_MAX_DEVICES, "gemm: device %d out of range", dev);
+    const int64_t m_tiles = kq_div_up(M, TM);
+    const size_t need = (size_t)m_tiles * TM * K;
+    uint4 *tiled_dev = nullptr;
+    {
+        const b200_status rc = kq_gemm_scratch(dev, need, st, &tiled_dev);
+        if (rc != B200_OK) return rc;
+    }
     const int64_t n_piece = (int64_t)need / 16;
     kq_launch(retile_act_kernel, dim3((unsigned)kq_div_up(n_piece, 256)), 256, 0, st, q, tiled_dev, (int)M, (int)K, n_piece);
     KQ_COUNT_LAUNCH();
     GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled_dev), d, bs, y, bias, residual,
-                    (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type};
+                    (int32_t)M, (int32_t)N, (int32_t)K, (int32_t)(K / 256), type, nullptr, nullptr, nullptr, 1, 0};
     // two CTAs per SM: each holds 256 of the 512 TMEM columns and under half of the shared memory
     const int smem = SMEM_TOTAL;
     static_assert(SMEM_TOTAL <= 112 * 1024, "two tiles must fit the shared memory of an SM");
@@ -647,6 +761,65 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
     }
     dim3 grid((unsigned)kq_div_up(N, TN), (unsigned)kq_div_up(M, TM));
     kq_launch(gemm_tc_kernel, grid, NTHREADS, smem, st, p, wmap);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// ---- MUL_MAT_ID over many tokens: pairs gathered per expert, one grouped launch of the tensor-core kernel ----
+// Scratch of the sort, in int32 words: [0] number of live tiles, [1 .. 1 + max_tiles) expert per tile,
+// [1 + max_tiles ..) pair per tile row; max_tiles = ceil(n_pairs / 128) + n_expert bounds sum_e ceil(c_e / 128).
+static inline int64_t moe_max_tiles(int64_t n_pairs, int64_t E) { return kq_div_up(n_pairs, TM) + E; }
+
+size_t kq_moe_sort_scratch_bytes(int64_t n_pairs, int64_t E) {
+    const int64_t mt = moe_max_tiles(n_pairs, E);
+    return (size_t)(1 + mt + mt * TM + 64) * sizeof(int32_t);
+}
+
+b200_status kq_moe_sort(const int32_t *ids, int64_t n_pairs, int64_t E, int32_t *scratch, size_t scratch_bytes, cudaStream_t st) {
+    KQ_REQUIRE(ids && scratch && n_pairs >= 1 && E >= 1 && E <= SORT_MAX_E, "moe_sort: n_pairs >= 1, 1 <= experts <= %d", SORT_MAX_E);
+    KQ_REQUIRE(scratch_bytes >= kq_moe_sort_scratch_bytes(n_pairs, E), "moe_sort: scratch of %zu bytes, %zu needed", scratch_bytes,
+               kq_moe_sort_scratch_bytes(n_pairs, E));
+    const int64_t mt = moe_max_tiles(n_pairs, E);
+    kq_launch(moe_sort_kernel, 1, SORT_WARPS * 32, 0, st, ids, (int)n_pairs, (int)E, scratch, scratch + 1, scratch + 1 + mt);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// y[pair][N] = W[expert of the pair] . x[pair / act_div]: q / d / bs are the quantised activations of the
+// n_pairs / act_div source rows, sorted = the scratch kq_moe_sort left for these pairs.
+b200_status kq_launch_gemm_grouped(uint32_t type, const uint8_t *W, int64_t expert_stride, const int8_t *q, const float *d,
+                                   const int16_t *bs, int act_div, int64_t n_pairs, int64_t E, int64_t N, int64_t K, float *y,
+                                   const int32_t *sorted, cudaStream_t st) {
+    KQ_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "grouped gemm: weight type %u", type);
+    KQ_REQUIRE(K % 256 == 0 && n_pairs > 0 && N > 0 && act_div >= 1, "grouped gemm: bad shape");
+    if (N % TN != 0) return B200_ERR_UNSUPPORTED; // an expert's last row tile would run into the next expert's rows
+    KQ_REQUIRE(((uintptr_t)W & 15) == 0 && ((uintptr_t)q & 15) == 0 && expert_stride % 16 == 0, "grouped gemm: operands must be 16-byte aligned");
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    KQ_REQUIRE(dev >= 0 && dev < KQ_MAX_DEVICES, "gemm: device %d out of range", dev);
+    const int64_t mt = moe_max_tiles(n_pairs, E);
+    uint4 *tiled_dev = nullptr;
+    b200_status rc = kq_gemm_scratch(dev, (size_t)mt * TM * K, st, &tiled_dev);
+    if (rc != B200_OK) return rc;
+    const int64_t n_piece = mt * TM * K / 16;
+    const int64_t blocks = kq_div_up(n_piece, 256);
+    kq_launch(retile_gather_kernel, dim3((unsigned)(blocks > 65535 * 16 ? 65535 * 16 : blocks)), 256, 0, st, q, tiled_dev,
+              sorted + 1 + mt, sorted, act_div, (int)K, n_piece);
+    KQ_COUNT_LAUNCH();
+    GemmParams p = {W, reinterpret_cast<const int8_t *>(tiled_dev), d, bs, y, nullptr, nullptr,
+                    (int32_t)(mt * TM), (int32_t)N, (int32_t)K, (int32_t)(K / 256), type,
+                    sorted + 1 + mt, sorted + 1, sorted, (int32_t)act_div, expert_stride};
+    CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    if (type == B200_TYPE_Q4_K) {
+        KQ_REQUIRE(expert_stride == kq_device_row_bytes(type, K) * N, "grouped gemm: expert matrices must be contiguous");
+        rc = make_weight_map(&wmap, W, N * E, kq_device_row_bytes(type, K));
+        if (rc != B200_OK) return rc;
+    }
+    dim3 grid((unsigned)(N / TN), (unsigned)mt);
+    kq_launch(gemm_tc_kernel, grid, NTHREADS, SMEM_TOTAL, st, p, wmap);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;

@@ -62,7 +62,7 @@ __device__ __forceinline__ void st_release_sys(uint64_t *p, uint64_t v) {
 }
 
 // One CTA.  ring / flags / consumed belong to the receiver (peer memory when it is another GPU).
-__global__ void __launch_bounds__(256) handoff_send_kernel(const uint4 *__restrict__ src, size_t bytes, uint8_t *ring,
+__global__ void __launch_bounds__(256) handoff_send_kernel(const uint4 *src, size_t bytes, uint8_t *ring,
                                                             size_t slot_stride, uint64_t *flags, const uint64_t *consumed,
                                                             uint64_t *known, int *err, uint64_t seqno, int n_slots,
                                                             uint64_t limit_ns) {
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) handoff_send_kernel(const uint4 *__restri
 }
 
 // One CTA on the receiver.  dst may be null: the caller then reads the slot in place.
-__global__ void __launch_bounds__(256) handoff_wait_kernel(uint4 *__restrict__ dst, size_t bytes, const uint8_t *ring,
+__global__ void __launch_bounds__(256) handoff_wait_kernel(uint4 *dst, size_t bytes, const uint8_t *ring,
                                                             size_t slot_stride, const uint64_t *flags, uint64_t *consumed,
                                                             int *err, uint64_t seqno, int n_slots, uint64_t limit_ns) {
     KQ_PDL_WAIT(); // dst may still be read by the kernels before this one

@@ -78,7 +78,7 @@ __device__ void block_topk(float (&tv)[TOPK], int (&ti)[TOPK], float *out_v, int
     }
 }
 
-__global__ void __launch_bounds__(NT) logit_scan_kernel(const float *__restrict__ x, int64_t n, int n_slice,
+__global__ void __launch_bounds__(NT) logit_scan_kernel(const float *x, int64_t n, int n_slice,
                                                         const int32_t *chosen, SlicePart *parts, int *counters,
                                                         b200_logit_signals_t *sig, int32_t *argmax_out) {
     KQ_PDL_ENTER();

@@ -87,9 +87,9 @@ __global__ void rope_store_kernel(float *q, const float *k, const float *v, cons
 // scores one position against all G heads (K row read once), the tile's probabilities go through
 // shared memory, and each lane accumulates 4 of the 128 output dims for all G heads.
 template <int HD, int G>
-__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q,
-                                                        const __half *__restrict__ kc,
-                                                        const __half *__restrict__ vc, int T,
+__global__ void __launch_bounds__(128) attention_kernel(const float *q,
+                                                        const __half *kc,
+                                                        const __half *vc, int T,
                                                         const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int64_t seq_stride,
                                                         int n_split, float scale, float *out,
                                                         float *part_o, float *part_ml) {

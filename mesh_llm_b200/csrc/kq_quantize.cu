@@ -29,7 +29,7 @@ __device__ __forceinline__ void quantize_block_warp(const float (&v)[8], int lan
     if (lane == 0) *d_out = d;
 }
 
-__global__ void __launch_bounds__(128) quantize_act_kernel(const float *__restrict__ x, int64_t nblocks,
+__global__ void __launch_bounds__(128) quantize_act_kernel(const float *x, int64_t nblocks,
                                                            int8_t *q, float *d, int16_t *bs) {
     KQ_PDL_ENTER();
     const int lane = threadIdx.x & 31;
@@ -43,8 +43,8 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float *__restri
 
 // RMSNorm (x * rsqrt(mean(x^2) + eps) * w) with optional f32 output and optional Q8 output.
 // One CTA of 256 threads per row; h is a multiple of 256 when q != null.
-__global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x,
-                                                       const float *__restrict__ w, int h, float eps,
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float *x,
+                                                       const float *w, int h, float eps,
                                                        float *y, int8_t *q, float *d, int16_t *bs,
                                                        int64_t x_row_stride) {
     KQ_PDL_ENTER();
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
 }
 
 // ---- Q6_K repack: GGUF block-interleaved rows <-> device rows [ql | qh | scales | d | pad] ------
-__global__ void repack_q6k_kernel(const uint16_t *__restrict__ src, uint16_t *__restrict__ dst,
+__global__ void repack_q6k_kernel(const uint16_t *src, uint16_t *dst,
                                   int64_t n_rows, int nb, int64_t dst_row_u16, int inverse) {
     KQ_PDL_ENTER();
     const int64_t per_row = (int64_t)nb * 105;

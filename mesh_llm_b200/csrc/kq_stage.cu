@@ -138,7 +138,9 @@ struct b200_stage {
     int rows_max = 0;
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr,
           *u = nullptr, *last = nullptr, *logits_int = nullptr, *att_scratch = nullptr, *rl = nullptr,
-          *rw = nullptr, *hp = nullptr, *yp = nullptr;
+          *rw = nullptr, *hp = nullptr, *hp2 = nullptr, *yp = nullptr;
+    int32_t *moe_sorted = nullptr; // expert-major order of the routed pairs of a batch
+    size_t moe_sorted_bytes = 0;
     uint8_t *expert_mask = nullptr; // one byte per expert, 1 = allowed (all ones when no mask is set)
     int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
     size_t att_scratch_bytes = 0;
@@ -340,12 +342,33 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
                 {(const uint8_t *)L.gate_e->dev, L.gate_e->type, fe, st->hp, nullptr, fe, gstride},
                 {(const uint8_t *)L.up_e->dev, L.up_e->type, fe, st->hp, nullptr, fe, gstride},
             };
+            // Many tokens: the pairs are gathered per expert and each expert-packed matrix is one grouped
+            // launch of the tensor-core GEMM (build_moe_ffn's MUL_MAT_ID); few tokens: one indirect GEMV
+            // row per pair.  B200_MOE_GROUPED=0 keeps the second form for every batch size.
+            static int grouped_on = -1;
+            if (grouped_on < 0) {
+                const char *v = getenv("B200_MOE_GROUPED");
+                grouped_on = !(v && v[0] == '0');
+            }
+            bool grouped = grouped_on && rows > 8 && fe % 64 == 0 && h % 64 == 0 && classes == CLS_ALL;
+            if (grouped) {
+                KQ_TRY(kq_moe_sort(st->rid, pairs, E, st->moe_sorted, st->moe_sorted_bytes, s));
+                KQ_TRY(kq_launch_gemm_grouped(L.gate_e->type, (const uint8_t *)L.gate_e->dev, gstride, st->aq, st->ad, st->abs16, ku,
+                                              pairs, E, fe, h, st->hp, st->moe_sorted, s));
+                KQ_TRY(kq_launch_gemm_grouped(L.up_e->type, (const uint8_t *)L.up_e->dev, gstride, st->aq, st->ad, st->abs16, ku,
+                                              pairs, E, fe, h, st->hp2, st->moe_sorted, s));
+                KQ_TRY(b200_swiglu(st->hp, st->hp2, (int64_t)pairs * fe, st->hp, s));
+                KQ_TRY(b200_quantize_act(st->hp, pairs, fe, st->aq, st->ad, st->abs16, s));
+                KQ_TRY(kq_launch_gemm_grouped(L.down_e->type, (const uint8_t *)L.down_e->dev, dstride, st->aq, st->ad, st->abs16, 1,
+                                              pairs, E, h, fe, st->yp, st->moe_sorted, s));
+            } else {
             KqGemvIndirect ind = {st->rid, pairs, ku};
             GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, 1, h, nullptr, 1, &ind, s));
             OTHER_(b200_quantize_act(st->hp, pairs, fe, st->aq, st->ad, st->abs16, s));
             KqGemvSeg dn = {(const uint8_t *)L.down_e->dev, L.down_e->type, h, st->yp, nullptr, h, dstride};
             KqGemvIndirect ind2 = {st->rid, pairs, 1};
             GEMV_(kq_launch_gemv(&dn, 1, st->aq, st->ad, st->abs16, 1, fe, nullptr, 0, &ind2, s));
+            }
             if (classes & CLS_OTHER) {
             kq_launch(moe_combine_kernel, (unsigned)kq_div_up((int64_t)rows * h, 256), 256, 0, s, 
                 st->yp, st->rw, st->x, rows, ku, h, xout);
@@ -571,6 +594,9 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
         A((void **)&st->rw, pairs * 4);
         A((void **)&st->rid, pairs * 4);
         A((void **)&st->hp, pairs * c.n_ff_exp * 4);
+        A((void **)&st->hp2, R > 8 ? pairs * c.n_ff_exp * 4 : 0);
+        st->moe_sorted_bytes = kq_moe_sort_scratch_bytes(pairs, c.n_expert);
+        A((void **)&st->moe_sorted, st->moe_sorted_bytes);
         A((void **)&st->yp, pairs * h * 4);
         A((void **)&st->expert_mask, 256);
         if (rc == B200_OK && cudaMemset(st->expert_mask, 1, 256) != cudaSuccess) rc = B200_ERR_CUDA;
@@ -875,6 +901,10 @@ b200_status b200_stage_peek(b200_stage *st, const char *which, float *host_out, 
     else if (w == "v") { src = st->v; cap = R * nkv; }
     else if (w == "att") { src = st->att; cap = R * nq; }
     else if (w == "g") { src = st->g; cap = R * (size_t)(c.n_expert > 0 ? 0 : c.n_ff); }
+    else if (w == "hp") { src = st->hp; cap = R * (size_t)c.n_expert_used * c.n_ff_exp; }
+    else if (w == "yp") { src = st->yp; cap = R * (size_t)c.n_expert_used * c.n_embd; }
+    else if (w == "sorted") { src = (const float *)st->moe_sorted; cap = st->moe_sorted_bytes / 4; }
+    else if (w == "rid") { src = (const float *)st->rid; cap = R * (size_t)c.n_expert_used; }
     KQ_REQUIRE(src, "stage_peek: no buffer named %s (x, q, k, v, att, g)", which);
     KQ_REQUIRE(n_floats <= cap, "stage_peek: %s holds %zu floats, asked for %zu", which, cap, n_floats);
     KqDevGuard dev_guard(c.device);

@@ -207,6 +207,20 @@ def logit_signals(logits, chosen=None):
                 top_id=sig[:, 8:13].contiguous().view(torch.int32), argmax=am)
 
 
+def mul_mat_id(type_, W, n_expert, x, ids, N, K):
+    """MUL_MAT_ID: W [n_expert * N, row bytes] device layout, x [rows, K] f32, ids [n_pairs] int32 (n_pairs a
+    multiple of rows: pair p uses row p // (n_pairs // rows)) -> y [n_pairs, N]"""
+    x = _dev(x).contiguous().float().reshape(-1, K)
+    ids = _dev(ids).contiguous().to(torch.int32).reshape(-1)
+    rows, pairs = x.shape[0], ids.numel()
+    need = lib().b200_mul_mat_id_scratch_bytes(rows, pairs, K, n_expert)
+    scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    y = torch.empty((pairs, N), dtype=torch.float32, device=x.device)
+    check(lib().b200_mul_mat_id(type_, ptr(W), n_expert, ptr(x), rows, ptr(ids), pairs, N, K, ptr(y), ptr(scratch), need,
+                                cur_stream()))
+    return y
+
+
 def moe_route(logits, k, mask=None):
     logits = _dev(logits).contiguous().float()
     T, E = logits.shape

