@@ -16,6 +16,8 @@
 // on one stream); two kernels that wait on one another are never put on the same GPU.
 #include "kq_common.cuh"
 
+#include <algorithm>
+
 #include <string.h>
 
 namespace {
@@ -99,6 +101,41 @@ __global__ void __launch_bounds__(256) handoff_send_kernel(const uint4 *src, siz
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) st_release_sys(flags + slot, seqno + 1);
+}
+
+// Large payloads (a prefill micro-batch: megabytes) go out as three launches on the sender's stream:
+// reserve (one thread waits for the slot to be free), copy (a grid of CTAs stores the payload into the
+// peer's slot), publish (system-scope fence, then the payload's number).  The copy kernel has finished,
+// and with it all its stores, before the publishing kernel starts.
+__global__ void handoff_reserve_kernel(const uint64_t *consumed, uint64_t *known, int *err, uint64_t seqno, int n_slots,
+                                       uint64_t limit_ns) {
+    KQ_PDL_WAIT();
+    int ok = *reinterpret_cast<volatile int *>(err) == 0;
+    if (ok && seqno >= *known + (uint64_t)n_slots) {
+        const uint64_t t0 = kq_globaltimer_ns();
+        uint64_t c = ld_acquire_sys(consumed);
+        while (seqno >= c + (uint64_t)n_slots) {
+            if (kq_globaltimer_ns() - t0 > limit_ns) {
+                ok = 0;
+                break;
+            }
+            __nanosleep(200);
+            c = ld_acquire_sys(consumed);
+        }
+        *known = c;
+    }
+    if (!ok) atomicCAS(err, 0, 1); // no free slot in time
+}
+__global__ void __launch_bounds__(256) handoff_copy_kernel(const uint4 *src, uint4 *dst, size_t n16, const int *err) {
+    KQ_PDL_WAIT(); // src is the output of the kernels before; the reservation precedes this kernel
+    if (*reinterpret_cast<const volatile int *>(err) != 0) return;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+__global__ void handoff_publish_kernel(uint64_t *flag, const int *err, uint64_t seqno) {
+    KQ_PDL_WAIT(); // every store of the copy kernel has been performed
+    if (*reinterpret_cast<const volatile int *>(err) != 0) return;
+    __threadfence_system();
+    st_release_sys(flag, seqno + 1);
 }
 
 // One CTA on the receiver.  dst may be null: the caller then reads the slot in place.
@@ -242,6 +279,24 @@ b200_status b200_handoff_send(b200_handoff *remote, const void *src, size_t byte
     KQ_REQUIRE(bytes > 0 && bytes % 4 == 0 && bytes <= remote->slot_bytes && ((uintptr_t)src & 3) == 0,
                "handoff_send: %zu bytes do not fit a slot of %zu (multiples of 4, 4-byte aligned)", bytes, remote->slot_bytes);
     uint8_t *b = remote->base;
+    if (bytes >= (256u << 10) && bytes % 16 == 0 && ((uintptr_t)src & 15) == 0) {
+        // a micro-batch: reserve, copy with a whole grid, publish
+        const uint64_t lim = limit_ns ? limit_ns : 5000000000ull;
+        const int slot = (int)(seqno % (uint64_t)remote->n_slots);
+        cudaStream_t st = (cudaStream_t)stream;
+        kq_launch(handoff_reserve_kernel, 1, 1, 0, st, (const uint64_t *)(b + remote->lay.ctrl_off), remote->known,
+                  remote->send_err, seqno, remote->n_slots, lim);
+        const size_t n16 = bytes / 16;
+        const unsigned grid = (unsigned)std::min<size_t>((n16 + 255) / 256, (size_t)kq_sm_count() * 4);
+        kq_launch(handoff_copy_kernel, grid, 256, 0, st, (const uint4 *)src, (uint4 *)(b + (size_t)slot * remote->lay.slot_stride), n16,
+                  (const int *)remote->send_err);
+        kq_launch(handoff_publish_kernel, 1, 1, 0, st, (uint64_t *)(b + remote->lay.flags_off) + slot, (const int *)remote->send_err, seqno);
+        KQ_COUNT_LAUNCH();
+        KQ_COUNT_LAUNCH();
+        KQ_COUNT_LAUNCH();
+        KQ_LAUNCH_CHECK();
+        return B200_OK;
+    }
     kq_launch(handoff_send_kernel, 1, 256, 0, (cudaStream_t)stream, (const uint4 *)src, bytes, b, remote->lay.slot_stride,
               (uint64_t *)(b + remote->lay.flags_off), (const uint64_t *)(b + remote->lay.ctrl_off), remote->known,
               remote->send_err, seqno, remote->n_slots, limit_ns ? limit_ns : 5000000000ull);

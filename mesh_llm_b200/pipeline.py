@@ -198,91 +198,158 @@ def run_decode(stage_step, sched, rank, steps, transport, hidden_in, hidden_out,
     transport.drain()
 
 
+class _RawDeviceFloats:
+    """lets torch view device memory it does not own (a landing slot of the hand-off ring)"""
+
+    def __init__(self, address, n_floats):
+        self.__cuda_array_interface__ = {"shape": (n_floats,), "typestr": "<f4", "data": (int(address), False), "version": 3}
+
+
+class PrefillPeerLink:
+    """Micro-batches of a prefill between neighbouring stages through peer memory: a ring of three
+    landing slots of [512 x n_embd] f32 in the receiver's HBM.  The sender's stream reserves a slot,
+    copies with a whole grid over NVLink and publishes; the receiver's stream acquires the slot, runs
+    its layers on it in place and releases it.  Nobody waits on the host, so micro-batch u + 1 is
+    computed while u crosses and while the next stage works on u."""
+
+    def __init__(self, dist, rank, world, slot_bytes, n_slots=3):
+        from .handoff import Endpoint, Sender
+
+        self.rx = Endpoint(slot_bytes, n_slots) if rank > 0 else None
+        handles = [None] * world
+        dist.all_gather_object(handles, self.rx.handle() if self.rx else None)
+        self.tx = Sender.open(handles[rank + 1], slot_bytes, n_slots) if rank < world - 1 else None
+
+    def send(self, t):
+        self.tx.send(t)
+
+    def recv_in_place(self, rows, h, device):
+        """-> (tensor [rows, h] over the landing slot, payload number to release after use)"""
+        import torch
+
+        addr, seqno = self.rx.wait_in_place(rows * h * 4)
+        return torch.as_tensor(_RawDeviceFloats(addr, rows * h), device=device).view(rows, h), seqno
+
+    def release(self, seqno):
+        self.rx.release(seqno)
+
+    def check(self):
+        for o in (self.rx, self.tx):
+            if o is not None:
+                o.raise_on_timeout()
+
+    def close_senders(self):
+        if self.tx is not None:
+            self.tx.close()
+
+    def close(self):
+        self.close_senders()
+        if self.rx is not None:
+            self.rx.close()
+
+
 # ------------------------------------------------------------------------------------------------
-def bench_pipeline(args, w, metric, rank, world, local):
-    """bench.py body for N > 1: N stages, N sequences in flight, value = all tokens / max time."""
+MODEL_KEYS = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
+              "rope_neox", "rope_theta", "rms_eps")
+
+
+def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=True):
+    """One dense workload over `world` stages: prefill, pipelined decode with `world` sequences in flight
+    (device-timed and end to end), one sequence alone through all stages, the slowest stage's GEMV-only
+    replay, and a replay of sequence 0 on a single stage holding the whole model (rank 0) whose tokens
+    must equal the pipeline's.  Returns the measurements on every rank."""
+    import ctypes as C
+
     import torch
     import torch.distributed as dist
 
+    from bench import ClockSampler, gemv_bytes, hbm_peak, matmuls, step_gemv_bytes
+
+    from .capi import check, lib
     from .stage import Stage
 
-    torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    pg_fwd = dist.new_group(backend="nccl")
-    pg_tok = dist.new_group(backend="nccl")
-    model_keys = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "qkv_bias",
-                  "rope_neox", "rope_theta", "rms_eps")
-    model = {k: w[k] for k in model_keys}
+    model = {k: w[k] for k in MODEL_KEYS}
     head_cost = 0.0
     if getattr(args, "balance", False):  # the output head in units of an average layer's weight bytes
-        from bench import gemv_bytes, matmuls
-
         layer_b = sum(gemv_bytes(N, K, ty) for l in (0, 1) for (N, K, ty) in matmuls(w, l)) / 2
         head_cost = gemv_bytes(w["n_vocab"], w["n_embd"], 14) / layer_b
     lo, hi = layer_range(w["n_layer"], world, rank, head_cost)
     n_seq = world
-    steps, warm = args.steps, max(3, args.warmup)
-    n_ctx = w["prefill"] + 2 * (steps + warm) + 72
+    n_ctx = w["prefill"] + 3 * (steps + warm) + 72
     ids, names = {"f16": 1, "q4_0": 2, "q8_0": 8}, {1: "f16", 2: "q4_0", 8: "q8_0"}
     kv = getattr(args, "kv", "f16")
     if kv == "auto":  # the pair mesh-llm starts a model file of this size with
-        from bench import step_gemv_bytes
         from .ops import kv_types_for_model_bytes
 
         kt, vt = kv_types_for_model_bytes(step_gemv_bytes(w, 0, w["n_layer"], True) + w["n_vocab"] * w["n_embd"] * 0.5625)
     else:
         kt, vt = [ids[t] for t in (kv + "-" + kv).split("-")[:2]]
-    st = Stage(**model, layer_begin=lo, layer_end=hi, has_embd=int(rank == 0), has_output=int(rank == world - 1),
+    last = rank == world - 1
+    st = Stage(**model, layer_begin=lo, layer_end=hi, has_embd=int(rank == 0), has_output=int(last),
                n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
     st.generate(20251125)
     tr = Transport(dist, rank, world, pg_fwd, pg_tok)
     sched = Schedule(world, n_seq)
     h = w["n_embd"]
-    # decode hand-off: peer-memory kernels unless --handoff nccl asks for send/recv; prefill ubatches (MBs) use send/recv
+    # hand-off: peer-memory kernels unless --handoff nccl asks for send / recv
     peer = getattr(args, "handoff", "peer") == "peer"
-    tr_dec = tr
+    tr_dec, big = tr, None
     if peer:
         # every rank must end up on the same transport: if mapping a neighbour's ring fails anywhere, all use send / recv
         try:
             tr_dec = PeerTransport(dist, rank, world, h * 4)
+            big = PrefillPeerLink(dist, rank, world, 512 * h * 4)
             ok = torch.ones(1, device=dev)
         except Exception as e:  # noqa: BLE001 - reported, then the collective below decides for everybody
             print(f"[rank {rank}] peer-memory hand-off unavailable ({e}); using send / recv", flush=True)
             ok = torch.zeros(1, device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if ok.item() == 0:
-            if tr_dec is not tr:
-                tr_dec.close()
-            tr_dec, peer = tr, False
+            for o in (tr_dec if tr_dec is not tr else None, big):
+                if o is not None:
+                    o.close()
+            tr_dec, big, peer = tr, None, False
     rng = np.random.default_rng(1234)
     prompts = torch.from_numpy(rng.integers(0, w["n_vocab"], (n_seq, w["prefill"])).astype(np.int32)).to(dev)
     hid_big = torch.empty((512, h), dtype=torch.float32, device=dev)
-    hid_out = torch.empty((512, h), dtype=torch.float32, device=dev)
+    hid_out = [torch.empty((512, h), dtype=torch.float32, device=dev) for _ in range(2)]
     first = torch.zeros(n_seq, dtype=torch.int32, device=dev)
     tok1 = torch.zeros(1, dtype=torch.int32, device=dev)
-    logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev) if rank == world - 1 else None
-    last = rank == world - 1
+    logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev) if last else None
 
-    # ---- prefill: every sequence's prompt flows through the stages in ubatches of 512
+    # ---- prefill: every sequence's prompt flows through the stages in micro-batches of 512
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     if not args.no_prefill:
+        u = 0
         for s in range(n_seq):
             for p0 in range(0, w["prefill"], 512):
                 T = min(512, w["prefill"] - p0)
-                hin = None
+                hin, held = None, None
                 if rank > 0:
-                    tr.recv_hidden(hid_big[:T])
-                    hin = hid_big[:T]
+                    if big is not None:
+                        hin, held = big.recv_in_place(T, h, dev)
+                    else:
+                        tr.recv_hidden(hid_big[:T])
+                        hin = hid_big[:T]
+                out = hid_out[u & 1][:T]
+                if big is None and not last:
+                    tr.wait_slot(("h", u & 1))  # the send posted from this buffer two micro-batches ago
                 st.forward(tokens=prompts[s, p0:p0 + T] if rank == 0 else None, hidden_in=hin, n_seq=1, T=T,
-                           pos0=p0, seq0=s, hidden_out=None if last else hid_out[:T], logits=logits,
+                           pos0=p0, seq0=s, hidden_out=None if last else out, logits=logits,
                            next_tokens=first[s:s + 1] if last else None)
+                if held is not None:
+                    big.release(held)
                 if not last:
-                    tr.send_hidden(hid_out[:T], 0)
-                    tr.wait_slot(("h", 0))
+                    if big is not None:
+                        big.send(out)
+                    else:
+                        tr.send_hidden(out, u & 1)
+                u += 1
+        tr.drain()
     e1.record()
     torch.cuda.synchronize()
     t_prefill = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -293,6 +360,7 @@ def bench_pipeline(args, w, metric, rank, world, local):
     hid1_in = torch.empty((1, h), dtype=torch.float32, device=dev)
     hid1_out = [torch.empty((1, h), dtype=torch.float32, device=dev) for _ in range(2)]
     tok_out = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(2)]
+    seq0_tokens = []  # last stage: the greedy tokens of sequence 0, in the order they were produced
 
     def make_step(base):
         def stage_step(seq, step, token, hidden_in, out):
@@ -307,75 +375,180 @@ def bench_pipeline(args, w, metric, rank, world, local):
         torch.cuda.current_stream().synchronize()
         token.copy_(h_tok, non_blocking=True)
 
-    def decode(k, base, first_tokens, e2e=False):
-        run_decode(make_step(base), sched, rank, k, tr_dec, hid1_in, hid1_out, tok1, tok_out, first_tokens,
-                   on_token=(lambda s_, k_, t_: via_host(t_)) if (e2e and last) else None,
+    def keep(seq, step, token):
+        if seq == 0:
+            seq0_tokens.append(token.clone())
+
+    def decode(k, base, first_tokens, e2e=False, sch=None, record=False):
+        def on_token(s_, k_, t_):
+            if record:
+                keep(s_, k_, t_)
+            if e2e:
+                via_host(t_)
+        run_decode(make_step(base), sch or sched, rank, k, tr_dec, hid1_in, hid1_out, tok1, tok_out, first_tokens,
+                   on_token=on_token if (last and (e2e or record)) else None,
                    on_input=via_host if (e2e and rank == 0) else None)
 
-    decode(warm, pos_base, first)
+    def timed(fn):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    decode(warm, pos_base, first, record=True)
     torch.cuda.synchronize()
     dist.barrier()
     launches0 = st.kernel_launches()
-    from bench import ClockSampler
-
-    sampler = ClockSampler(local)
-    if rank == 0:
+    sampler = ClockSampler(local) if (full and rank == 0) else None
+    if sampler:
         sampler.start()
         time.sleep(0.3)
-    dist.barrier()
-    torch.cuda.synchronize()
     t0 = time.time()
-    e0.record()
-    decode(steps, pos_base + warm, first)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
+    ms = timed(lambda: decode(steps, pos_base + warm, first, record=True))
     t1 = time.time()
-    tt = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms = float(tt.item())
     launches = torch.tensor([st.kernel_launches() - launches0], device=dev, dtype=torch.int64)
     dist.all_reduce(launches)
-
     # ---- end to end: result token crosses to the host and back every step
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0.record()
-    decode(steps, pos_base + warm + steps, first, e2e=True)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    te = timed(lambda: decode(steps, pos_base + warm + steps, first, e2e=True))
+    clocks = sampler.stop(t0, t1) if sampler else None
+    # ---- one sequence alone through all stages: the latency-bound batch-1 figure
+    k1 = max(4, steps // 2)
+    t_single = timed(lambda: decode(k1, pos_base + warm + 2 * steps, first, sch=Schedule(world, 1)))
     if peer:
         tr_dec.check()
+        big.check()
 
-    if rank == 0:
-        total = steps * n_seq
-        print(json.dumps({
-            "metric": metric, "value": total / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
-            "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine", "data": "synthetic",
-            "config": {"split": "weighted by bytes (output head counted)" if head_cost > 0 else "equal layer counts",
-                       "workload": f"{w['name']} ({w['n_layer']} layers) split into {world} contiguous layer ranges, "
-                                   f"one per GPU; {n_seq} sequences in flight, decode batch 1 per stage at context "
-                                   f"{w['prefill']}+; f32 [1 x {h}] activation handed to the next stage over NVLink",
-                       "sequences_in_flight": n_seq, "kv_cache": names[kt] + "-" + names[vt],
-                       "l2": "each stage streams its weights every tick (>> 126 MB L2), no flush needed"},
-            "e2e": {"value": total / (float(te.item()) * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * n_seq,
-                    "d2h_bytes_per_step": 4 * n_seq},
-            "gpu_launches": int(launches.item()), "clocks": clocks,
-            "prefill_tok_s": None if args.no_prefill else n_seq * w["prefill"] / (float(t_prefill.item()) * 1e-3),
-            "handoff": "peer-memory landing ring written by the sending stage's kernel over NVLink (prefill ubatches: "
-                       "torch.distributed send/recv)" if peer else "torch.distributed send/recv (NCCL P2P over NVLink)",
-        }))
+    # ---- this stage's GEMV launches alone; the slowest stage bounds the pipeline
+    ms_gemv, n_gemv = C.c_float(), C.c_int64()
+    check(lib().b200_stage_profile_decode(st.h, 1, pos_base, 1, 10, C.byref(ms_gemv), C.byref(n_gemv)))
+    peak, peak_source = hbm_peak()
+    algo = step_gemv_bytes(w, lo, hi, last, 1)
+    mine = torch.tensor([ms_gemv.value, algo, float(n_gemv.value)], device=dev, dtype=torch.float64)
+    allr = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allr, mine)
+    per_stage = [(float(t[0]), float(t[1]), int(t[2])) for t in allr]
+    slow = max(range(world), key=lambda r: per_stage[r][0])
+    s_ms, s_algo, s_n = per_stage[slow]
+    roofline = {
+        "bound": "hbm", "achieved": s_algo / (s_ms * 1e-3) / 1e9, "peak": peak, "peak_source": peak_source, "unit": "GB/s",
+        "frac": s_algo / (s_ms * 1e-3) / 1e9 / peak, "stage": slow,
+        "per_stage_frac": [a / (m * 1e-3) / 1e9 / peak for (m, a, _) in per_stage],
+        "traffic": None, "kernel": "gemv_block_kernel (Q4_K/Q6_K x Q8 decode GEMV), the slowest stage's launches of one step",
+        "launches_per_step": s_n, "algorithmic_bytes_per_launch": s_algo / max(1, s_n),
+        "avg_launch_us": s_ms * 1e3 / max(1, s_n), "gemv_ms_per_step": s_ms,
+    }
+
+    # ---- outputs must match: sequence 0 replayed on one stage holding the whole model
+    n_tok = warm + steps
+    toks = torch.stack(seq0_tokens).reshape(-1).to(torch.int32) if last else torch.zeros(n_tok, dtype=torch.int32, device=dev)
+    dist.broadcast(toks, world - 1)
+    match = torch.ones(1, device=dev)
     if peer:
         tr_dec.close_senders()
+        big.close_senders()
     dist.barrier()
     if peer:
         tr_dec.close()
+        big.close()
+    st.close()
+    del st
+    torch.cuda.empty_cache()
+    if rank == 0 and not getattr(args, "no_match", False):
+        one = Stage(**model, n_ctx=n_ctx, n_seq=1, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
+        one.generate(20251125)
+        lg = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev)
+        t_ = torch.zeros(1, dtype=torch.int32, device=dev)
+        for p0 in range(0, w["prefill"], 512):
+            T = min(512, w["prefill"] - p0)
+            one.forward(tokens=prompts[0, p0:p0 + T], n_seq=1, T=T, pos0=p0, logits=lg, next_tokens=t_)
+        got = []
+        ok = bool(int(t_.item()) == int(first[0].item()))
+        for (k, base) in ((warm, pos_base), (steps, pos_base + warm)):
+            cur = first[0:1].clone()
+            for i in range(k):
+                nx = torch.zeros(1, dtype=torch.int32, device=dev)
+                one.forward(tokens=cur, n_seq=1, T=1, pos0=base + i, logits=lg, next_tokens=nx)
+                got.append(nx)
+                cur = nx
+        got = torch.cat(got)
+        ok = ok and bool(torch.equal(got, toks))
+        match.fill_(1.0 if ok else 0.0)
+        one.close()
+    dist.broadcast(match, 0)
+    total = steps * n_seq
+    return {
+        "value": total / (ms * 1e-3), "ms_per_step": ms / steps, "e2e_value": total / (te * 1e-3),
+        "gpu_launches": int(launches.item()), "clocks": clocks, "n_seq": n_seq,
+        "prefill_tok_s": None if args.no_prefill else n_seq * w["prefill"] / (float(t_prefill.item()) * 1e-3),
+        "single_sequence_tok_s": k1 / (t_single * 1e-3),
+        "tokens_match_single_stage": None if getattr(args, "no_match", False) else bool(match.item() == 1.0),
+        "tokens_compared": 1 + n_tok, "roofline": roofline, "kv_cache": names[kt] + "-" + names[vt], "peer": peer,
+        "split": "weighted by bytes (output head counted)" if head_cost > 0 else "equal layer counts",
+    }
+
+
+def bench_pipeline(args, w, metric, rank, world, local):
+    """bench.py body for N > 1: N stages, N sequences in flight, value = all tokens / max time."""
+    import torch
+    import torch.distributed as dist
+
+    from bench import WORKLOADS, cpu_decode_sample
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    pg_fwd = dist.new_group(backend="nccl")
+    pg_tok = dist.new_group(backend="nccl")
+    steps, warm = args.steps, max(3, args.warmup)
+    r = run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=True)
+    extra = {}
+    if not getattr(args, "no_extras", False) and args.workload == "cfg2" and not args.layers:
+        # the 70B shape over the same N stages, in the same run
+        w3 = dict(WORKLOADS["cfg3"])
+        r3 = run_pipeline(args, w3, rank, world, local, pg_fwd, pg_tok, max(8, min(steps, 16)), 3, full=False)
+        extra = {"cfg3_decode_tok_s": r3["value"], "cfg3_e2e_tok_s": r3["e2e_value"],
+                 "cfg3_single_sequence_tok_s": r3["single_sequence_tok_s"], "cfg3_prefill_tok_s": r3["prefill_tok_s"],
+                 "cfg3_tokens_match_single_stage": r3["tokens_match_single_stage"],
+                 "cfg3_gemv_frac_of_hbm_peak": r3["roofline"]["frac"],
+                 "cfg3_workload": f"{w3['name']} ({w3['n_layer']} layers) over {world} stages, {world} sequences in flight, "
+                                  f"prefill {w3['prefill']}, decode at context {w3['prefill']}+"}
+    cpu = None
+    if rank == 0 and not args.no_cpu:
+        v, cores, sample = cpu_decode_sample(w)
+        cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+    h = w["n_embd"]
+    bad = r["tokens_match_single_stage"] is False or extra.get("cfg3_tokens_match_single_stage") is False
+    if rank == 0:
+        out = {
+            "metric": metric, "value": r["value"], "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int4/6 -> int32, f32 combine", "data": "synthetic",
+            "config": {"split": r["split"],
+                       "workload": f"{w['name']} ({w['n_layer']} layers) split into {world} contiguous layer ranges, "
+                                   f"one per GPU; {r['n_seq']} sequences in flight, decode batch 1 per stage at context "
+                                   f"{w['prefill']}+; f32 [1 x {h}] activation handed to the next stage over NVLink",
+                       "sequences_in_flight": r["n_seq"], "kv_cache": r["kv_cache"],
+                       "l2": "each stage streams its weights every tick (>> 126 MB L2), no flush needed"},
+            "e2e": {"value": r["e2e_value"], "unit": "tok/s", "h2d_bytes_per_step": 4 * r["n_seq"],
+                    "d2h_bytes_per_step": 4 * r["n_seq"]},
+            "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "roofline": r["roofline"], "cpu_baseline": cpu,
+            "prefill_tok_s": r["prefill_tok_s"], "single_sequence_tok_s": r["single_sequence_tok_s"],
+            "tokens_match_single_stage": r["tokens_match_single_stage"], "tokens_compared": r["tokens_compared"],
+            "handoff": "peer-memory landing rings written by the sending stage's kernels over NVLink (decode rows and "
+                       "prefill micro-batches)" if r["peer"] else "torch.distributed send/recv (NCCL P2P over NVLink)",
+        }
+        out.update(extra)
+        print(json.dumps(out), flush=True)
+    dist.barrier()
     dist.destroy_process_group()
+    if bad:
+        raise SystemExit("the pipeline's tokens differ from the single stage's")
 
 
 def bench_handoff_latency(args, w, rank, world, local):

@@ -185,3 +185,26 @@ def test_bad_arguments_are_refused():
         tx.send(torch.zeros(128, device="cuda"))  # 512 bytes into 256-byte slots
     with pytest.raises(B200Error):
         ep.wait(torch.zeros(128, device="cuda"))
+
+
+def test_micro_batches_cross_in_place_through_a_three_slot_ring():
+    """What the pipelined prefill does at a stage boundary: payloads of megabytes (reserve, grid-wide copy,
+    publish on the sender's stream), read in place by the receiver through a tensor view of the landing
+    slot and released afterwards; five payloads through three slots."""
+    import torch
+    from mesh_llm_b200.handoff import Endpoint
+    from mesh_llm_b200.pipeline import _RawDeviceFloats
+
+    rows, h = 256, 1024  # 1 MB
+    ep = Endpoint(rows * h * 4, n_slots=3)
+    tx = ep.local_sender()
+    for i in range(5):
+        src = torch.randn(rows, h, device="cuda") + i
+        tx.send(src, limit_ns=50 * MS)
+        addr, seq = ep.wait_in_place(rows * h * 4, limit_ns=50 * MS)
+        view = torch.as_tensor(_RawDeviceFloats(addr, rows * h), device="cuda").view(rows, h)
+        got = view.clone()  # the stage's kernels would read the slot here
+        ep.release(seq)
+        torch.cuda.synchronize()
+        assert torch.equal(got, src), i
+    assert ep.status() == 0 and tx.status() == 0
