@@ -83,6 +83,9 @@ struct StreamParams {
     int32_t rg_end[3];
     int32_t nseg, n_rg, nb, K, nsteps, swiglu;
     int32_t ns; // ring depth per warp
+    // a launch that serves two matrix types at once gives each its own range of CTAs [cta0, cta0 + n_cta)
+    // (n_cta == 0: the whole grid); the fix-up scratch is indexed by the warp's number in the whole grid
+    int32_t cta0, n_cta;
     int32_t m_actual; // tokens really present (the 8-token kernel pads the rest with zeros)
     const int8_t *aq;
     const float *ad;
@@ -592,7 +595,8 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         for (int s = 0; s < (FUSED ? 4 : ns); s++) mbar_init(smem_u32(&bars[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncwarp();
-    const int unit = blockIdx.x * WARPS + warp, n_units = gridDim.x * WARPS;
+    const int unit = ((int)blockIdx.x - p.cta0) * WARPS + warp, n_units = (p.n_cta ? p.n_cta : (int)gridDim.x) * WARPS;
+    const int pbase = p.cta0 * WARPS; // this launch part's first line of the fix-up scratch
     const int64_t total = (int64_t)p.n_rg * p.nsteps;
     const int64_t begin = total * unit / n_units, end = total * (unit + 1) / n_units;
     const int count = (int)(end - begin);
@@ -819,7 +823,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                 if (t == 0)
 #pragma unroll
                     for (int m = 0; m < M; m++)
-                        *(volatile unsigned long long *)&g_partials[unit][rs * M + m] =
+                        *(volatile unsigned long long *)&g_partials[pbase + unit][rs * M + m] =
                             (unsigned long long)__float_as_uint(v[m]) | (1ull << 32);
             } else {
                 if (!last_slice) {
@@ -841,7 +845,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                         for (int m = 0; m < M; m++) {
                             got[m] = 0.f;
                             if (mine) {
-                                volatile unsigned long long *e = &g_partials[u2][rs * M + m];
+                                volatile unsigned long long *e = &g_partials[pbase + u2][rs * M + m];
                                 unsigned long long w = 0;
                                 bool ok = false;
                                 const uint64_t t0 = kq_globaltimer_ns();
@@ -921,6 +925,20 @@ __global__ void __launch_bounds__(Fmt<TYPE>::WARPS * 32, Fmt<TYPE>::CTAS_PER_SM)
     const FusedCtx none = {0, 0, 0, 0u};
     uint32_t uses[4] = {0u, 0u, 0u, 0u};
     stream_body<TYPE, M, false>(p, smem, s_abort, none, uses);
+}
+
+// One launch for a projection whose matrices are of both types (Q4_K attn_q / attn_k with a Q6_K attn_v):
+// the first p4.n_cta CTAs stream the Q4_K rows, the rest the Q6_K rows, each part dealt over its own CTAs
+// in proportion to its bytes, so both finish together and the second launch with its fixed cost is gone.
+template <int M>
+__global__ void __launch_bounds__(KQ_GEMV_WARPS * 32, 1) gemv_mixed_kernel(const StreamParams p4, const StreamParams p6) {
+    KQ_PDL_TRIGGER();
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_abort;
+    const FusedCtx none = {0, 0, 0, 0u};
+    uint32_t uses[4] = {0u, 0u, 0u, 0u};
+    if ((int)blockIdx.x < p4.n_cta) stream_body<B200_TYPE_Q4_K, M, false>(p4, smem, s_abort, none, uses);
+    else stream_body<B200_TYPE_Q6_K, M, false>(p6, smem, s_abort, none, uses);
 }
 
 struct FusedParams {
@@ -1028,6 +1046,66 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
         if (dev >= 0 && dev < 16) attr_done[dev] = true;
     }
     kq_launch(gemv_block_kernel<TYPE, M>, grid, WARPS * 32, smem, st, p);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// ring depth and shared-memory bytes of one launch part; false when the row does not fit
+template <uint32_t TYPE, int M>
+bool plan_part(StreamParams &p, size_t &smem) {
+    using F = Fmt<TYPE>;
+    const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
+    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) + (M > 2 ? 32 : 0);
+    int cap = F::SMEM_CAP;
+    if (M * act_tok + F::WARPS * F::SLOT + 1024 > cap) cap = 216 * 1024;
+    int ns = (cap - M * act_tok - F::WARPS * 8 * 8) / (F::WARPS * F::SLOT);
+    if (ns > 4) ns = 4;
+    if (ns < 1) return false;
+    p.ns = ns;
+    smem = (size_t)M * act_tok + (size_t)F::WARPS * ns * F::SLOT + (size_t)F::WARPS * ns * 8;
+    return smem <= 226 * 1024;
+}
+
+template <int M>
+b200_status launch_mixed(const KqGemvSeg *s4, int n4, const KqGemvSeg *s6, int n6, const int8_t *q, const float *d,
+                         const int16_t *bs, int64_t K, const KqActPrep *prep, cudaStream_t st) {
+    StreamParams p4, p6;
+    fill_params<B200_TYPE_Q4_K>(p4, s4, n4, q, d, bs, K, nullptr, 0, prep);
+    fill_params<B200_TYPE_Q6_K>(p6, s6, n6, q, d, bs, K, nullptr, 0, prep);
+    p4.m_actual = p6.m_actual = M;
+    size_t sm4 = 0, sm6 = 0;
+    if (!plan_part<B200_TYPE_Q4_K, M>(p4, sm4) || !plan_part<B200_TYPE_Q6_K, M>(p6, sm6)) return B200_ERR_UNSUPPORTED;
+    int total = kq_sm_count();
+    if (total * KQ_GEMV_WARPS > MAX_UNITS) total = MAX_UNITS / KQ_GEMV_WARPS;
+    double b4 = 0, b6 = 0;
+    for (int i = 0; i < n4; i++) b4 += (double)s4[i].n_rows * kq_device_row_bytes(B200_TYPE_Q4_K, K);
+    for (int i = 0; i < n6; i++) b6 += (double)s6[i].n_rows * kq_device_row_bytes(B200_TYPE_Q6_K, K);
+    // a Q6_K CTA needs longer for its bytes than a Q4_K CTA (larger units, more arithmetic per weight, and at
+    // these sizes a warp holds one or two units): its bytes count more when the CTAs are divided
+    static int w6_pct = -1;
+    if (w6_pct < 0) w6_pct = env_int2("B200_GEMV_MIX_W6", 225);
+    b6 *= w6_pct / 100.0;
+    int c6 = (int)(total * b6 / (b4 + b6) + 0.5);
+    if (c6 < 1) c6 = 1;
+    if (c6 > total - 1) c6 = total - 1;
+    int c4 = total - c6;
+    const int64_t want4 = kq_div_up((int64_t)p4.n_rg * p4.nsteps, KQ_GEMV_WARPS), want6 = kq_div_up((int64_t)p6.n_rg * p6.nsteps, KQ_GEMV_WARPS);
+    if (want4 < c4) c4 = (int)(want4 < 1 ? 1 : want4);
+    if (want6 < c6) c6 = (int)(want6 < 1 ? 1 : want6);
+    p4.cta0 = 0;
+    p4.n_cta = c4;
+    p6.cta0 = c4;
+    p6.n_cta = c6;
+    const size_t smem = sm4 > sm6 ? sm4 : sm6;
+    static bool attr_done[16];
+    int dev = 0;
+    KQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16 || !attr_done[dev]) {
+        KQ_CUDA(cudaFuncSetAttribute(gemv_mixed_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        if (dev >= 0 && dev < 16) attr_done[dev] = true;
+    }
+    kq_launch(gemv_mixed_kernel<M>, c4 + c6, KQ_GEMV_WARPS * 32, smem, st, p4, p6);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;
@@ -1157,6 +1235,17 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
     }
     if (!(prep && prep->x) && ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0)) return B200_ERR_UNSUPPORTED;
     if (prep && prep->x && ((uintptr_t)prep->x & 15) != 0) return B200_ERR_UNSUPPORTED;
+    if (!swiglu_pairs && !residual && env_int2("B200_GEMV_MIXED", 1)) {
+        // matrices of both types in one projection: one launch with the CTAs divided between the types
+        KqGemvSeg s4[3], s6[3];
+        int n4 = 0, n6 = 0;
+        for (int i = 0; i < nseg; i++) (segs[i].type == B200_TYPE_Q4_K ? s4[n4++] : s6[n6++]) = segs[i];
+        if (n4 > 0 && n6 > 0) {
+            const b200_status rc = M == 1 ? launch_mixed<1>(s4, n4, s6, n6, q, d, bs, K, prep, st)
+                                          : launch_mixed<2>(s4, n4, s6, n6, q, d, bs, K, prep, st);
+            if (rc != B200_ERR_UNSUPPORTED) return rc;
+        }
+    }
     for (uint32_t type : {(uint32_t)B200_TYPE_Q4_K, (uint32_t)B200_TYPE_Q6_K}) {
         KqGemvSeg sel[3];
         int n = 0;
