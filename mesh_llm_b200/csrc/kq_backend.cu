@@ -313,7 +313,7 @@ b200_status b200_backend_synchronize(b200_backend *be) {
     KQ_REQUIRE(be, "backend_synchronize: null backend");
     DevGuard g(be->dev);
     KQ_CUDA(cudaStreamSynchronize(be->stream));
-    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
+    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4) | (kq_attn_tc_error_fetch() << 8);
     if (werr) {
         kq_set_error("backend_synchronize: a bounded device-side wait gave up (code %d)", werr);
         return B200_ERR_TIMEOUT;

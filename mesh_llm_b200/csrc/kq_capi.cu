@@ -54,7 +54,7 @@ const char *b200_status_string(b200_status s) {
 
 b200_status b200_check_device_waits(void) {
     KQ_CUDA(cudaDeviceSynchronize());
-    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
+    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4) | (kq_attn_tc_error_fetch() << 8);
     if (werr) {
         kq_set_error("a bounded device-side wait gave up (code 0x%x)", werr);
         return B200_ERR_TIMEOUT;

@@ -267,6 +267,7 @@ b200_status kq_launch_gemm_grouped(uint32_t type, const uint8_t *W, int64_t expe
                                    const int32_t *sorted, cudaStream_t st);
 int kq_stream_error_fetch(); // 0 ok; nonzero = a bounded device-side wait gave up since the last call
 int kq_gemm_error_fetch();
+int kq_attn_tc_error_fetch();
 b200_status kq_launch_gemm(uint32_t type, const uint8_t *W, const int8_t *q, const float *d,
                            const int16_t *bs, int64_t M, int64_t N, int64_t K, float *y,
                            const float *bias, const float *residual, cudaStream_t st);

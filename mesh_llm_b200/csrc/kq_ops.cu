@@ -8,6 +8,9 @@
 #include <math.h>
 #include <stdlib.h>
 
+b200_status kq_attention_prefill_tc(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
+                                    const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd, int64_t seq_stride,
+                                    float *out, cudaStream_t st);
 b200_status kq_attention_prefill_mma(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                                      const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd, int64_t seq_stride,
                                      float *out, KqKvTypes kvt, cudaStream_t st);
@@ -476,6 +479,16 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
     if (use_mma < 0) {
         const char *v = getenv("B200_ATTN_MMA");
         use_mma = !(v && v[0] == '0');
+    }
+    // f16 caches, head_dim 128: the tcgen05 kernel (B200_ATTN_TC=0 keeps the mma.sync kernel)
+    static int use_tc = -1;
+    if (use_tc < 0) {
+        const char *v = getenv("B200_ATTN_TC");
+        use_tc = !(v && v[0] == '0');
+    }
+    if (use_mma && use_tc && T >= 32 && force_splits <= 0) {
+        const b200_status rc = kq_attention_prefill_tc(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, st);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
     }
     if (use_mma && T >= 32 && force_splits <= 0) {
         const b200_status rc = kq_attention_prefill_mma(q, kc, vc, n_seq, T, pos0_dev, pos0, n_head, n_kv, hd, seq_stride, out, kvt, st);

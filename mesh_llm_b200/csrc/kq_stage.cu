@@ -932,7 +932,7 @@ b200_status b200_stage_synchronize(b200_stage *st) {
     KQ_REQUIRE(st, "stage_synchronize: null stage");
     KqDevGuard dev_guard(st->c.device);
     KQ_CUDA(cudaDeviceSynchronize());
-    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4);
+    const int werr = kq_stream_error_fetch() | (kq_gemm_error_fetch() << 4) | (kq_attn_tc_error_fetch() << 8);
     if (werr) {
         kq_set_error("stage_synchronize: a bounded device-side wait gave up (code %d)", werr);
         return B200_ERR_TIMEOUT;
