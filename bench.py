@@ -322,6 +322,7 @@ def main():
         v, cores, sample = cpu_decode_sample(w)
         out["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
     if not args.no_extras and args.workload == "cfg2" and not args.layers:
+        out["prefill_gemm_roofline"] = prefill_gemm_roofline()
         # the other configurations of the benchmark list, in the same run on the same GPU
         k = max(8, min(args.steps, 24))
         r3 = bench_single(args, dict(WORKLOADS["cfg3"]), local, full=False, steps=k)
@@ -491,6 +492,24 @@ def bench_single(args, w, local, full=True, steps=None):
         "workload": f"{w['name']} ({w['n_layer']} layers), prefill {w['prefill']}, decode batch 1 at context {w['prefill']}+, "
                     f"one stage on one GPU, {steps} steps",
     }
+
+
+def prefill_gemm_roofline():
+    """The prefill GEMM against a tensor-core ceiling measured in the same run: the useful int8 rate
+    (2 M N K per launch) of the 32B shape's FFN matmuls at M = 2048, and a bare loop of the kernel's own
+    tcgen05.mma kind::i8 instruction on all SMs (b200_probe_int8_mma).  Every useful product costs two MMAs
+    (the K-quant sub-block scale is folded into the weight, which then needs two int8 planes), so the
+    issued rate is twice the useful one."""
+    from mesh_llm_b200 import ops
+
+    peak, _ = ops.probe_int8_mma(65536, 5)
+    rows = {}
+    for (N, K, t) in ((27648, 5120, "q4_k"), (5120, 27648, "q4_k"), (5120, 27648, "q6_k")):
+        rows[f"{t}_{N}x{K}_m2048"] = micro_one(N, K, 2048, t, 4)["TOPps"]
+    best = max(rows.values())
+    return {"bound": "tensor", "achieved": best, "achieved_issued": 2 * best, "peak": peak,
+            "peak_source": "measured in this run: bare tcgen05.mma.kind::i8 loop, M 128 x N 256 x K 32, one CTA per SM",
+            "unit": "TOP/s", "frac": best / peak, "frac_issued": 2 * best / peak, "useful_TOPps": rows}
 
 
 def hbm_peak():

@@ -68,9 +68,11 @@ enum {
                             [2]=theta (f32 bits)                                                 */
     B200_OP_SWIGLU,      /* silu(src0) * src1                                                     */
     B200_OP_GET_ROWS,    /* src0 = table (Q4_K/Q6_K/F32), src1 = ids i32                          */
-    B200_OP_CPY,         /* f32 -> f32 / f16 copy (KV-cache write)                                */
+    B200_OP_CPY,         /* f32 -> f32 / f16 / q8_0 / q4_0 (KV-cache write; quantised rows in ggml's
+                            34 / 18-byte blocks)                                                  */
     B200_OP_ATTN,        /* fused causal attention (FLASH_ATTN_EXT): src0 = q [hd, n_head, T],
-                            src1 = K cache f16 [hd, n_kv, n_ctx], src2 = V cache likewise;
+                            src1 = K cache [hd, n_kv, n_ctx] of type f16, q8_0 or q4_0 (ggml block
+                            layout, read in place; quantised: hd = 128), src2 = V cache likewise;
                             op_params[0] = scale (f32 bits), [1] = pos0                          */
     B200_OP_MOE_ROUTE,   /* softmax + top-k + renormalise: src0 = logits [E, T];
                             op_params[0] = k; output = weights f32 [k, T]; ids written to src1   */
@@ -222,6 +224,12 @@ B200_API b200_status b200_mul_mat_id(uint32_t type, const void *W, int64_t E, co
 #define B200_MUL_MAT_STATIC_MAX_K 32768
 B200_API b200_status b200_mul_mat_static(uint32_t type, const void *W, const float *x, int64_t M,
                                          int64_t N, int64_t K, float *y, void *stream);
+/* Measurement aid with no counterpart in the reference: times a bare loop of the prefill GEMM's
+ * tensor-core instruction (tcgen05.mma kind::i8, M 128 x N 256 x K 32, operands resting in shared
+ * memory, no loads and no epilogue) on every SM of the current device and returns the int8 rate
+ * in TOP/s (best of `repeats` launches of `n_mma` instructions per SM) -- the measured ceiling
+ * the GEMM's useful rate is reported against.  Synchronises the device.                         */
+B200_API b200_status b200_probe_int8_mma(int32_t n_mma, int32_t repeats, double *tops_out, double *ms_out);
 /* exact per-block integer sums [M][N][K/256] (parity instrumentation; summ may be NULL)        */
 B200_API b200_status b200_block_sums(uint32_t type, const void *W, const int8_t *q,
                                      const int16_t *bsum16, int64_t M, int64_t N, int64_t K,

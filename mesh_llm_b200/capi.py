@@ -116,6 +116,7 @@ SIGNATURES = {
     "b200_mul_mat": (i32, [u32, vp, vp, i64, i64, i64, vp, vp, sz, vp]),
     "b200_mul_mat_q8": (i32, [u32, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, vp]),
     "b200_mul_mat_static": (i32, [u32, vp, vp, i64, i64, i64, vp, vp]),
+    "b200_probe_int8_mma": (i32, [i32, i32, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200_block_sums": (i32, [u32, vp, vp, vp, i64, i64, i64, vp, vp, vp]),
     "b200_rms_norm": (i32, [vp, vp, i64, i64, C.c_float, vp, vp]),
     "b200_rope": (i32, [vp, vp, i64, i64, i64, C.c_float, i32, vp]),

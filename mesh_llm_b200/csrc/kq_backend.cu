@@ -51,6 +51,33 @@ __global__ void add_bcast_kernel(const float *a, const float *b, int64_t total, 
     if (i < total) y[i] = a[i] + b[nb_elems == total ? i : i % n];
 }
 
+// CPY f32 -> q8_0 / q4_0: how llama.cpp writes a quantised KV cache.  One warp per block of 32 values,
+// ggml's block layout at the destination.
+__global__ void cpy_f32_kvq_kernel(const float *x, int64_t n_blocks, int type, uint8_t *dst) {
+    KQ_PDL_ENTER();
+    const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= n_blocks) return; // whole warps leave together
+    const int lane = threadIdx.x & 31;
+    kq_kv_store_ggml_block(type, x[blk * 32 + lane], dst + blk * (type == KQ_KV_Q8_0 ? 34 : 18), lane);
+}
+
+// A quantised cache tensor in ggml's block layout -> this library's row layout (codes of a row's blocks,
+// then their scales; 16-byte aligned rows, which the attention kernels fetch as TMA boxes).  Bytes are
+// moved, never changed.  One thread per block of a row.
+__global__ void kvq_ggml_to_rows_kernel(const uint8_t *src, int64_t n_rows, int hd, int type, uint8_t *dst) {
+    KQ_PDL_ENTER();
+    const int nb = hd / 32, cb = type == KQ_KV_Q8_0 ? 32 : 16;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * nb) return;
+    const int64_t r = i / nb;
+    const int b = (int)(i % nb);
+    const uint16_t *in = reinterpret_cast<const uint16_t *>(src + (r * nb + b) * (cb + 2));
+    uint8_t *row = dst + r * kq_kv_row_bytes(type, hd);
+    reinterpret_cast<uint16_t *>(row + nb * cb)[b] = in[0];
+    uint16_t *codes = reinterpret_cast<uint16_t *>(row + b * cb);
+    for (int k = 0; k < cb / 2; k++) codes[k] = in[1 + k];
+}
+
 inline int64_t nelements(const b200_tensor *t) {
     return (int64_t)t->ne[0] * t->ne[1] * t->ne[2] * t->ne[3];
 }
@@ -95,6 +122,10 @@ b200_status check_tensor(const b200_tensor *t) {
     if (t->type == B200_TYPE_Q4_K || t->type == B200_TYPE_Q6_K) {
         KQ_REQUIRE(t->ne[0] % 256 == 0, "tensor %.64s: ne[0] must be a multiple of 256", t->name);
         KQ_REQUIRE((t->data & 15) == 0, "tensor %.64s: quantised data must be 16-byte aligned", t->name);
+    }
+    if (t->type == B200_TYPE_Q4_0 || t->type == B200_TYPE_Q8_0) {
+        KQ_REQUIRE(t->ne[0] % 32 == 0, "tensor %.64s: ne[0] must be a multiple of 32", t->name);
+        KQ_REQUIRE((t->data & 1) == 0, "tensor %.64s: q4_0 / q8_0 blocks must be 2-byte aligned", t->name);
     }
     return B200_OK;
 }
@@ -448,13 +479,22 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
                 KQ_TRY(b200_cpy_f32_f16((const float *)pa, nelements(a), (uint16_t *)y, s));
             else if (t->type == B200_TYPE_F32)
                 KQ_CUDA(cudaMemcpyAsync(y, pa, (size_t)nelements(a) * 4, cudaMemcpyDeviceToDevice, s));
-            else {
+            else if (t->type == B200_TYPE_Q8_0 || t->type == B200_TYPE_Q4_0) { // a quantised KV cache being written
+                KQ_REQUIRE(a->type == B200_TYPE_F32 && a->ne[0] % 32 == 0, "CPY %.64s: f32 rows of whole blocks", t->name);
+                KQ_TRY(out_holds(t, t->type, nelements(a)));
+                const int64_t n_blocks = nelements(a) / 32;
+                if (n_blocks > 0) {
+                    KQ_CUDA(kq_launch(cpy_f32_kvq_kernel, dim3((unsigned)kq_div_up(n_blocks, 8)), dim3(256), 0, s, (const float *)pa,
+                                     n_blocks, (int)t->type, (uint8_t *)y));
+                }
+            } else {
                 kq_set_error("CPY %.64s: destination type %u", t->name, t->type);
                 return B200_ERR_UNSUPPORTED;
             }
             break;
         case B200_OP_ATTN: {
-            KQ_REQUIRE(b && c && c->type == B200_TYPE_F16, "ATTN %.64s: K and V caches", t->name);
+            KQ_REQUIRE(b && c && kq_kv_type_ok((int)b->type) && kq_kv_type_ok((int)c->type),
+                       "ATTN %.64s: K and V caches of type f16, q8_0 or q4_0", t->name);
             const int hd = a->ne[0], n_head = a->ne[1], T = a->ne[2], n_kv = b->ne[1];
             const int pos0 = t->op_params[1];
             KQ_REQUIRE(b->ne[0] == a->ne[0] && c->ne[0] == a->ne[0] && c->ne[1] == b->ne[1] && c->ne[2] == b->ne[2],
@@ -462,10 +502,32 @@ b200_status b200_backend_graph_compute(b200_backend *be, const uint64_t *node_id
             KQ_REQUIRE(n_kv > 0 && n_head % n_kv == 0, "ATTN %.64s: %d query heads over %d KV heads", t->name, n_head, n_kv);
             KQ_TRY(out_holds(t, B200_TYPE_F32, nelements(a)));
             KQ_REQUIRE(pos0 >= 0 && (int64_t)pos0 + T <= (int64_t)b->ne[2], "ATTN %.64s: positions exceed the cache", t->name);
-            const size_t need = b200_attention_scratch_bytes(std::min(T, 64), n_head, hd, b->ne[2]);
-            KQ_TRY(ensure_scratch(be, need));
-            KQ_TRY(kq_attention((const float *)pa, (const uint16_t *)pb, (const uint16_t *)(uintptr_t)c->data, 1, T,
-                                nullptr, pos0, n_head, n_kv, hd, 0, y, (float *)be->scratch, be->scratch_bytes, 0, KqKvTypes(), s));
+            KqKvTypes kvt;
+            kvt.k = (int)b->type;
+            kvt.v = (int)c->type;
+            KQ_REQUIRE(!kvt.quantised() || hd == 128, "ATTN %.64s: quantised caches need head_dim 128", t->name);
+            // A quantised cache arrives in ggml's block layout (34 / 18-byte blocks, 2-byte aligned).  The rows
+            // in use are re-laid into the scratch in this library's 16-byte-aligned row layout -- a move of
+            // bytes -- and attended to there; the cache tensor itself is only read.
+            const int64_t rows = (int64_t)(pos0 + T) * n_kv;
+            const size_t kq_bytes = kvt.k != KQ_KV_F16 ? (size_t)rows * kq_kv_row_bytes(kvt.k, hd) : 0;
+            const size_t vq_bytes = kvt.v != KQ_KV_F16 ? (size_t)rows * kq_kv_row_bytes(kvt.v, hd) : 0;
+            const size_t att = (b200_attention_scratch_bytes(std::min(T, 64), n_head, hd, b->ne[2]) + 255) & ~(size_t)255;
+            KQ_TRY(ensure_scratch(be, att + kq_bytes + vq_bytes));
+            const uint8_t *kp = (const uint8_t *)pb, *vp = (const uint8_t *)(uintptr_t)c->data;
+            uint8_t *stage = (uint8_t *)be->scratch + att;
+            if (kq_bytes) {
+                KQ_CUDA(kq_launch(kvq_ggml_to_rows_kernel, dim3((unsigned)kq_div_up(rows * (hd / 32), 256)), dim3(256), 0, s, kp,
+                                 rows, hd, kvt.k, stage));
+                kp = stage;
+            }
+            if (vq_bytes) {
+                KQ_CUDA(kq_launch(kvq_ggml_to_rows_kernel, dim3((unsigned)kq_div_up(rows * (hd / 32), 256)), dim3(256), 0, s, vp,
+                                 rows, hd, kvt.v, stage + kq_bytes));
+                vp = stage + kq_bytes;
+            }
+            KQ_TRY(kq_attention((const float *)pa, (const uint16_t *)kp, (const uint16_t *)vp, 1, T, nullptr, pos0, n_head, n_kv,
+                                hd, 0, y, (float *)be->scratch, att, 0, kvt, s));
             break;
         }
         case B200_OP_MOE_ROUTE:

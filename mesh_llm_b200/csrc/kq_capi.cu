@@ -114,7 +114,8 @@ int32_t b200_dev_supports_op(uint32_t op, uint32_t t0, uint32_t t1) {
     case B200_OP_ARGMAX: return t0 == B200_TYPE_F32;
     case B200_OP_ROPE: return t0 == B200_TYPE_F32 && t1 == B200_TYPE_I32;
     case B200_OP_CPY: return t0 == B200_TYPE_F32;
-    case B200_OP_ATTN: return t0 == B200_TYPE_F32 && t1 == B200_TYPE_F16;
+    case B200_OP_ATTN: // K cache (src1; V may differ): f16, or ggml's q8_0 / q4_0 blocks
+        return t0 == B200_TYPE_F32 && (t1 == B200_TYPE_F16 || t1 == B200_TYPE_Q8_0 || t1 == B200_TYPE_Q4_0);
     default: return 0;
     }
 }

@@ -71,6 +71,8 @@ static inline __host__ __device__ int64_t kq_row_bytes(uint32_t type, int64_t k)
     case B200_TYPE_F16: return k * 2;
     case B200_TYPE_Q4_K: return k / KQ_QK * KQ_Q4K_BYTES;
     case B200_TYPE_Q6_K: return k / KQ_QK * KQ_Q6K_BYTES;
+    case B200_TYPE_Q4_0: return k / 32 * 18; // ggml block_q4_0: f16 d, 16 bytes of nibbles
+    case B200_TYPE_Q8_0: return k / 32 * 34; // ggml block_q8_0: f16 d, 32 int8
     default: return 0;
     }
 }

@@ -29,20 +29,18 @@ __host__ __device__ inline int kq_kv_row_bytes(int type, int hd) {
 }
 
 #ifdef __CUDACC__
-// One warp stores block `blk` of a row (lane = value within the block, x = that value) and returns
-// the f16 value the cache will decode it to.  Multiplications, the addition and the divisions are
-// the individually rounded IEEE operations of the scalar definition (no fused multiply-add).
-__device__ __forceinline__ __half kq_kv_store_block(int type, float x, uint8_t *row, int hd, int blk, int lane) {
+// One warp quantises a block of 32 values (lane = value within the block, x = that value): q is the
+// lane's code (q8_0: -127 .. 127; q4_0: 0 .. 15), dh the block's f16 scale; returns the f16 value the
+// cache will decode the lane's code to.  Multiplications, the addition and the divisions are the
+// individually rounded IEEE operations of the scalar definition (no fused multiply-add).
+__device__ __forceinline__ __half kq_kv_block_codes(int type, float x, int &q, __half &dh) {
     const float ax = fabsf(x);
     const float amax = kq_warp_max(ax);
-    __half *scales = reinterpret_cast<__half *>(row + kq_kv_codes_bytes(type, hd));
     if (type == KQ_KV_Q8_0) {
         const float d = __fdiv_rn(amax, 127.f);
         const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
-        const int q = (int)roundf(__fmul_rn(x, id));
-        const __half dh = __float2half_rn(d);
-        row[blk * 32 + lane] = (uint8_t)(int8_t)q;
-        if (lane == 0) scales[blk] = dh;
+        q = (int)roundf(__fmul_rn(x, id));
+        dh = __float2half_rn(d);
         return __float2half_rn(__fmul_rn((float)q, __half2float(dh)));
     }
     // q4_0: the first value of largest magnitude sets the scale, with its sign
@@ -51,13 +49,41 @@ __device__ __forceinline__ __half kq_kv_store_block(int type, float x, uint8_t *
     const float mx = amax == 0.f ? 0.f : first;
     const float d = __fdiv_rn(mx, -8.f);
     const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
-    int q = (int)__fadd_rn(__fmul_rn(x, id), 8.5f); // truncation, values in [0.5, 16.5]
+    q = (int)__fadd_rn(__fmul_rn(x, id), 8.5f); // truncation, values in [0.5, 16.5]
     q = min(q, 15);
-    const __half dh = __float2half_rn(d);
-    const int hi = __shfl_down_sync(0xffffffffu, q, 16);
-    if (lane < 16) row[blk * 16 + lane] = (uint8_t)(q | (hi << 4));
-    if (lane == 0) scales[blk] = dh;
+    dh = __float2half_rn(d);
     return __float2half_rn(__fmul_rn((float)(q - 8), __half2float(dh)));
+}
+
+// ... and stores it as block `blk` of a row in the device layout (codes of all blocks, then the scales)
+__device__ __forceinline__ __half kq_kv_store_block(int type, float x, uint8_t *row, int hd, int blk, int lane) {
+    int q;
+    __half dh;
+    const __half back = kq_kv_block_codes(type, x, q, dh);
+    __half *scales = reinterpret_cast<__half *>(row + kq_kv_codes_bytes(type, hd));
+    if (type == KQ_KV_Q8_0) {
+        row[blk * 32 + lane] = (uint8_t)(int8_t)q;
+    } else {
+        const int hi = __shfl_down_sync(0xffffffffu, q, 16);
+        if (lane < 16) row[blk * 16 + lane] = (uint8_t)(q | (hi << 4));
+    }
+    if (lane == 0) scales[blk] = dh;
+    return back;
+}
+
+// ... or as a block of ggml's own layout (block_q8_0: f16 d, int8 qs[32], 34 bytes; block_q4_0: f16 d,
+// uint8 qs[16] with value j in the low and value j + 16 in the high nibble of byte j, 18 bytes)
+__device__ __forceinline__ void kq_kv_store_ggml_block(int type, float x, uint8_t *block, int lane) {
+    int q;
+    __half dh;
+    kq_kv_block_codes(type, x, q, dh);
+    if (type == KQ_KV_Q8_0) {
+        block[2 + lane] = (uint8_t)(int8_t)q;
+    } else {
+        const int hi = __shfl_down_sync(0xffffffffu, q, 16);
+        if (lane < 16) block[2 + lane] = (uint8_t)(q | (hi << 4));
+    }
+    if (lane == 0) *reinterpret_cast<__half *>(block) = dh; // blocks are 2-byte aligned
 }
 
 __device__ __forceinline__ uint32_t kq_kv_h2(float a, float b) {

@@ -81,6 +81,15 @@ def mul_mat_q8(type_, W, q, d, bs, N, K, bias=None, residual=None, out=None):
     return y
 
 
+def probe_int8_mma(n_mma=65536, repeats=5):
+    """(TOP/s, ms) of a bare tcgen05.mma kind::i8 loop on every SM of the current device"""
+    import ctypes as C
+
+    tops, ms = C.c_double(0.0), C.c_double(0.0)
+    check(lib().b200_probe_int8_mma(n_mma, repeats, C.byref(tops), C.byref(ms)))
+    return tops.value, ms.value
+
+
 def block_sums(type_, W, q, bs, N, K):
     M = q.shape[0]
     sumi = torch.empty((M, N, K // 256), dtype=torch.int32, device=q.device)

@@ -326,3 +326,62 @@ def test_graph_compute_rejects_outputs_too_small_for_what_the_op_writes():
     np.testing.assert_array_equal(buf.get(guard, T * h * 4, dtype=np.float32).reshape(T, h), sentinel)
     lib().b200_backend_free(be)
     buf.free()
+
+
+Q4_0, Q8_0 = 2, 8
+
+
+@pytest.mark.parametrize("kt, vt", [(Q8_0, Q4_0), (Q4_0, Q4_0), (F16, Q8_0)], ids=["q8_0-q4_0", "q4_0-q4_0", "f16-q8_0"])
+@pytest.mark.parametrize("T, pos0", [(1, 77), (40, 0), (70, 58)])
+def test_graph_attention_over_a_quantised_cache_in_ggml_block_layout(kt, vt, T, pos0):
+    """The caches mesh-llm starts large models with (mesh-llm/src/inference/launch.rs:568-591), as llama.cpp
+    holds them: tensors of type q8_0 / q4_0 in ggml's 34 / 18-byte blocks.  A CPY node quantises f32 rows
+    into such a tensor (the bytes must be the pinned CPU quantiser's), and ATTN reads K and V from them in
+    place; the result is compared with the oracle's attention over the f16 decode of the same bytes."""
+    from mesh_llm_b200.capi import Tensor, check, lib
+
+    rng = np.random.default_rng(100 * T + pos0)
+    hd, n_head, n_kv = 128, 8, 2
+    L = pos0 + T
+    buf = Buf(0, 1 << 24)
+    k = (rng.standard_normal((L, n_kv, hd)) * rng.uniform(0.05, 2.0, (L, n_kv, 1))).astype(np.float32)
+    v = (rng.standard_normal((L, n_kv, hd)) * rng.uniform(0.05, 4.0, (L, n_kv, 1))).astype(np.float32)
+    q = rng.standard_normal((T, n_head, hd)).astype(np.float32)
+    t_k, t_v, t_q = buf.tensor(F32, (hd, n_kv, L), "k"), buf.tensor(F32, (hd, n_kv, L), "v"), buf.tensor(F32, (hd, n_head, T), "q")
+    for t, d in ((t_k, k), (t_v, v), (t_q, q)):
+        buf.set(t, d)
+
+    def node(op, type_, ne, srcs, name, params=()):
+        t = buf.tensor(type_, ne, name)
+        t.op = OP[op]
+        for i, s in enumerate(srcs):
+            t.src[i] = s.id
+        for i, p in enumerate(params):
+            t.op_params[i] = p
+        return t
+
+    c_k = node("CPY", kt, (hd, n_kv, L + 5), [t_k], "cache_k")
+    c_v = node("CPY", vt, (hd, n_kv, L + 5), [t_v], "cache_v")
+    att = node("ATTN", F32, (hd, n_head, T), [t_q, c_k, c_v], "att", [_f32bits(hd ** -0.5), pos0])
+    nodes = [c_k, c_v, att]
+    table = (Tensor * 6)(t_k, t_v, t_q, *nodes)
+    be = C.c_void_p()
+    check(lib().b200_backend_init(0, C.byref(be)))
+    check(lib().b200_backend_graph_compute(be, (C.c_uint64 * 3)(*[n.id for n in nodes]), 3, table, 6))
+
+    def as_f16(t, type_, src):
+        if type_ == F16:
+            got = buf.get(t, L * n_kv * hd * 2, dtype=np.uint16).reshape(L, n_kv, hd)
+            np.testing.assert_array_equal(got, orc.f32_to_f16(src))
+            return got
+        bb = 34 if type_ == Q8_0 else 18
+        blocks = buf.get(t, L * n_kv * 4 * bb).reshape(L, n_kv, 4 * bb)
+        np.testing.assert_array_equal(blocks, orc.kv_quantize(type_, src))  # the pinned quantiser's bytes
+        return orc.kv_dequantize(type_, blocks).astype(np.float16).view(np.uint16)
+
+    kc, vc = as_f16(c_k, kt, k), as_f16(c_v, vt, v)
+    got = buf.get(att, T * n_head * hd * 4, dtype=np.float32).reshape(T, n_head, hd)
+    ref = orc.attention(q * np.float32(1.0), kc, vc, pos0)
+    assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
+    lib().b200_backend_free(be)
+    buf.free()

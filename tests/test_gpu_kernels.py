@@ -303,3 +303,11 @@ def test_mul_mat_id_matches_the_oracle_pair_by_pair(ops, ty, E, N, K, rows, k):
             for s_ in range(k):
                 ref = orc.mul_mat(ty, Wr[ids[t, s_]], x[t:t + 1], N, K)[0]
                 assert rel_err(y[t, s_], ref) <= REL, (rep, t, s_)
+
+
+def test_int8_tensor_probe_returns_a_plausible_rate(ops):
+    """the bare tcgen05.mma kind::i8 loop: between a fifth of and a little above the nominal 4.5 POP/s"""
+    tops, ms = ops.probe_int8_mma(16384, 3)
+    assert 900.0 < tops < 6000.0 and ms > 0, (tops, ms)
+    with pytest.raises(Exception):
+        ops.probe_int8_mma(4, 1)
