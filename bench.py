@@ -234,6 +234,36 @@ def run_micro(args):
     print(json.dumps(micro_one(int(N), int(K), int(M), tname, args.micro_iters)))
 
 
+def run_micro_attn(args):
+    """--micro-attn n_head,n_kv,pos0,T: the prefill attention kernel alone (f16 cache, head_dim 128), timed
+    with CUDA events; TFLOP/s counts 4 * head_dim flops per (query, visible key, head).  Also the command
+    the committed ncu capture of that kernel was taken with."""
+    import torch
+    from mesh_llm_b200 import ops
+
+    nh, nkv, pos0, T = (int(v) for v in args.micro_attn.split(","))
+    hd = 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    kc = torch.randn(pos0 + T, nkv, hd, device="cuda", generator=g).half()
+    vc = torch.randn(pos0 + T, nkv, hd, device="cuda", generator=g).half()
+    q = torch.randn(T, nh, hd, device="cuda", generator=g)
+    for _ in range(3):
+        ops.attention(q, kc, vc, pos0)
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.micro_iters):
+            ops.attention(q, kc, vc, pos0)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / args.micro_iters)
+    pairs = T * pos0 + T * (T + 1) // 2
+    print(json.dumps({"micro_attn": args.micro_attn, "us_per_launch": best * 1e3,
+                      "TFLOPps": 4.0 * hd * nh * pairs / (best * 1e-3) / 1e12}))
+
+
 SWEEP_SHAPES = ((5120, 27648), (27648, 5120), (8192, 28672), (28672, 8192), (151936, 2048))
 SWEEP_M = (1, 8, 64, 512, 4096)
 
@@ -261,6 +291,7 @@ def main():
     ap.add_argument("--micro", default="", help="isolated quantised matmul instead of the model: 'N,K,M,type' "
                     "(type q4_k|q6_k); prints one line with us per launch and GB/s (M<=8) or TOP/s")
     ap.add_argument("--micro-iters", type=int, default=20)
+    ap.add_argument("--micro-attn", default="", help="the prefill attention kernel alone: 'n_head,n_kv,pos0,T'")
     ap.add_argument("--balance", action="store_true", help="N > 1: split layers by weight bytes (the last stage, which "
                     "holds the output head, gets fewer layers) instead of equal layer counts")
     ap.add_argument("--handoff", default="peer", choices=["peer", "nccl"], help="N > 1: how a decode activation reaches the "
@@ -275,6 +306,8 @@ def main():
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)
+    if args.micro_attn:
+        return run_micro_attn(args)
     if args.sweep:
         return run_sweep(args)
     w = dict(WORKLOADS[args.workload])
@@ -455,7 +488,7 @@ def bench_single(args, w, local, full=True, steps=None):
         # largest cfg2 matrices gave (1.02 Q4_K, 1.04 Q6_K; profiles/gemv_block_kernel_*.md)
         "traffic": NCU_TRAFFIC_RATIO * algo / max(1, n_gemv.value),
         "traffic_source": "derived: algorithmic bytes x %.2f, the DRAM / algorithmic ratio ncu measured on isolated cfg2 "
-                          "launches at M = 1 (profiles/gemv_block_kernel_q4k_27648x5120_m1.md)" % NCU_TRAFFIC_RATIO,
+                          "launches at M = 1 (profiles/gemv_block_kernel_m1.md)" % NCU_TRAFFIC_RATIO,
         "kernel": "gemv_block_kernel (Q4_K/Q6_K x Q8 decode GEMV)",
         "launches_per_step": int(n_gemv.value), "algorithmic_bytes_per_launch": algo / max(1, n_gemv.value),
         "avg_launch_us": ms_gemv.value * 1e3 / max(1, n_gemv.value),

@@ -211,6 +211,32 @@ __device__ __forceinline__ int kq_act_code(float x, float id) {
     int v = __float2int_rn(__fmul_rn(x, id));
     return max(-127, min(127, v));
 }
+
+// The quantiser applied to one block by one warp (b200_quantize_act and every fused form of it).
+// One warp per 256-element block.  Lane l owns elements 8l .. 8l+7 (values in v[8]).
+__device__ __forceinline__ void kq_quantize_block_warp(const float (&v)[8], int lane, int8_t *qb,
+                                                    float *d_out, int16_t *bs_out) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    amax = kq_warp_max(amax);
+    const float d = kq_act_scale(amax), id = kq_act_inv(d);
+    int c[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        c[i] = kq_act_code(v[i], id);
+        s += c[i];
+    }
+    uint2 pk;
+    pk.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) |
+           ((uint32_t)(c[3] & 0xFF) << 24);
+    pk.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) |
+           ((uint32_t)(c[7] & 0xFF) << 24);
+    *reinterpret_cast<uint2 *>(qb + lane * 8) = pk;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    if ((lane & 1) == 0) bs_out[lane >> 1] = (int16_t)s;
+    if (lane == 0) *d_out = d;
+}
 #endif
 
 // ---- internal launchers shared between translation units -----------------------------------

@@ -3,6 +3,7 @@
 // All of them are bandwidth-trivial next to the weight stream; they are written to cost few
 // launches and to read the KV cache once per group of query heads.
 #include "kq_common.cuh"
+#include "kq_route.cuh"
 #include "kq_kvq.cuh"
 
 #include <math.h>
@@ -369,60 +370,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *logits, int
     const int lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= T) return;
-    const float *lr = logits + t * E;
-    float v[8], sel[8];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int e = lane + 32 * i;
-        v[i] = e < E ? lr[e] : -INFINITY;
-        mx = fmaxf(mx, v[i]);
-    }
-    mx = kq_warp_max(mx);
-    float den = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : 0.f;
-        den += v[i];
-    }
-    den = kq_warp_sum(den);
-    // selection value: the prob of an allowed expert (>= 0), -1 for a masked one (all equal, below every
-    // allowed one, as -inf is), -2 once taken, -3 outside the table
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int e = lane + 32 * i;
-        v[i] = v[i] / den;
-        sel[i] = e >= E ? -3.f : ((mask && !mask[e]) ? -1.f : v[i]);
-    }
-    float wsum = 0.f, mine = 0.f;
-    int myid = 0;
-    for (int s = 0; s < k; s++) {
-        float best = -4.f, bp = 0.f;
-        int be = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int e = lane + 32 * i;
-            if (sel[i] > best || (sel[i] == best && e < be)) { best = sel[i]; be = e; bp = v[i]; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            const float op = __shfl_xor_sync(0xffffffffu, bp, o);
-            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; bp = op; }
-        }
-        wsum += bp;
-        if (lane == s) { mine = bp; myid = be; }
-        if ((be & 31) == lane) {
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                if (i == (be >> 5)) sel[i] = -2.f; // taken
-        }
-    }
-    if (lane < k) {
-        ids[t * k + lane] = myid;
-        w[t * k + lane] = mine / wsum;
-    }
+    kq_route_warp(logits + t * E, E, k, mask, ids + t * k, w + t * k, lane);
 }
 
 template <int HD>

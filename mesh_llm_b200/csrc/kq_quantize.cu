@@ -4,31 +4,6 @@
 
 namespace {
 
-// One warp per 256-element block.  Lane l owns elements 8l .. 8l+7 (values in v[8]).
-__device__ __forceinline__ void quantize_block_warp(const float (&v)[8], int lane, int8_t *qb,
-                                                    float *d_out, int16_t *bs_out) {
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-    amax = kq_warp_max(amax);
-    const float d = kq_act_scale(amax), id = kq_act_inv(d);
-    int c[8], s = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        c[i] = kq_act_code(v[i], id);
-        s += c[i];
-    }
-    uint2 pk;
-    pk.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) |
-           ((uint32_t)(c[3] & 0xFF) << 24);
-    pk.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) |
-           ((uint32_t)(c[7] & 0xFF) << 24);
-    *reinterpret_cast<uint2 *>(qb + lane * 8) = pk;
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    if ((lane & 1) == 0) bs_out[lane >> 1] = (int16_t)s;
-    if (lane == 0) *d_out = d;
-}
-
 __global__ void __launch_bounds__(128) quantize_act_kernel(const float *x, int64_t nblocks,
                                                            int8_t *q, float *d, int16_t *bs) {
     KQ_PDL_ENTER();
@@ -38,7 +13,7 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float *x, int64
     const float4 *xp = reinterpret_cast<const float4 *>(x + blk * 256 + lane * 8);
     const float4 a = xp[0], b = xp[1];
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    quantize_block_warp(v, lane, q + blk * 256, d + blk, bs + blk * 16);
+    kq_quantize_block_warp(v, lane, q + blk * 256, d + blk, bs + blk * 16);
 }
 
 // RMSNorm (x * rsqrt(mean(x^2) + eps) * w) with optional f32 output and optional Q8 output.
@@ -85,7 +60,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x,
                 *reinterpret_cast<float4 *>(yo + 4) = make_float4(v[4], v[5], v[6], v[7]);
             }
             const int64_t gb = (int64_t)row * nb + b;
-            quantize_block_warp(v, lane, q + gb * 256, d + gb, bs + gb * 16);
+            kq_quantize_block_warp(v, lane, q + gb * 256, d + gb, bs + gb * 16);
         }
     } else {
         for (int i = tid; i < h; i += 256) y[(int64_t)row * h + i] = xr[i] * scale * (w ? w[i] : 1.0f);
