@@ -68,9 +68,18 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const float *x, c
         const float4 *wr = reinterpret_cast<const float4 *>(Wr + (int64_t)e * h);
         const float4 *xv = reinterpret_cast<const float4 *>(xn);
         float acc = 0.f;
-        for (int i = lane; i < h / 4; i += 32) {
-            const float4 a = __ldg(wr + i), b = xv[i];
-            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        const int n4 = h / 4;
+        for (int i0 = lane; i0 < n4; i0 += 32 * 8) { // eight loads in flight per lane; the sum keeps its order
+            float4 a[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i0 + 32 * j < n4) a[j] = __ldg(wr + i0 + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i0 + 32 * j < n4) {
+                    const float4 b = xv[i0 + 32 * j];
+                    acc += a[j].x * b.x + a[j].y * b.y + a[j].z * b.z + a[j].w * b.w;
+                }
         }
         acc = kq_warp_sum(acc);
         if (lane == 0) rl[(int64_t)row * E + e] = acc;
@@ -87,10 +96,101 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const float *x, c
     }
 }
 
-constexpr int DOWN_ROWS = 16; // output rows per CTA: two per warp
+constexpr int DOWN_ROWS = 8; // output rows per CTA: one per warp
+
+// the lane's share of one block of one (row, slot): requested early, consumed after the prologue
+template <uint32_t TYPE>
+struct LaneBlock;
+template <>
+struct LaneBlock<B200_TYPE_Q4_K> {
+    uint4 hdr, w;
+    __device__ __forceinline__ void load(const uint8_t *rowp, int nb, int blk, int c) {
+        const uint8_t *b = rowp + (int64_t)blk * KQ_Q4K_BYTES;
+        hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        w = kq_ld_stream(b + 16 + 16 * c);
+    }
+    __device__ __forceinline__ float dot(const int8_t *aq, float da, const int16_t *s16blk, int c, float acc) const {
+        const int e_lo = 64 * (c >> 1) + 16 * (c & 1);
+        const Q4Scales sc = q4k_lane_scales(hdr, c);
+        const int4 alo = *reinterpret_cast<const int4 *>(aq + e_lo);
+        const int4 ahi = *reinterpret_cast<const int4 *>(aq + e_lo + 32);
+        const int16_t *s16 = s16blk + (e_lo >> 4);
+        int isum, msum;
+        q4k_lane_ints(w, sc, alo, ahi, s16[0], s16[2], isum, msum);
+        acc = fmaf(sc.d * da, (float)isum, acc);
+        return fmaf(-(sc.dmin * da), (float)msum, acc);
+    }
+};
+template <>
+struct LaneBlock<B200_TYPE_Q6_K> {
+    uint4 ql, qh;
+    int scl, sch;
+    float dw;
+    __device__ __forceinline__ void load(const uint8_t *rowp, int nb, int blk, int c) {
+        const int hh = c >> 2, cc = c & 3;
+        const KqQ6Addr qa = kq_q6_addr(nb, blk);
+        ql = kq_ld_stream(rowp + qa.ql + qa.cs * c);
+        qh = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.qh + qa.cs * (2 * hh + (cc & 1))));
+        const int8_t *scp = reinterpret_cast<const int8_t *>(rowp + qa.sc);
+        scl = scp[8 * hh + cc];
+        sch = scp[8 * hh + 4 + cc];
+        dw = kq_h2f(*reinterpret_cast<const uint16_t *>(rowp + qa.d));
+    }
+    __device__ __forceinline__ float dot(const int8_t *aq, float da, const int16_t *s16blk, int c, float acc) const {
+        const int hh = c >> 2, cc = c & 3;
+        const int e_lo = 128 * hh + 16 * cc;
+        const int4 alo = *reinterpret_cast<const int4 *>(aq + e_lo);
+        const int4 ahi = *reinterpret_cast<const int4 *>(aq + e_lo + 64);
+        const int16_t *s16 = s16blk + (e_lo >> 4);
+        const int isum = q6k_lane_ints(ql, qh, cc, scl, sch, alo, ahi, s16[0], s16[4]);
+        return fmaf(dw * da, (float)isum, acc);
+    }
+};
+
+// gate and up rows of the experts chosen for each (token, slot) pair, SwiGLU applied: one warp per output
+// element (its gate row and its up row), all of the rows' blocks requested at once.  grid (fe / 4, pairs).
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(128) moe_gate_up_kernel(const uint8_t *Wg, const uint8_t *Wu, int64_t expert_stride,
+                                                          const int8_t *aq, const float *ad, const int16_t *abs16,
+                                                          const int32_t *ids, int ku, int K, int fe, float *hp) {
+    KQ_PDL_ENTER();
+    const int pair = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * 4 + warp;
+    if (j >= fe) return; // the whole warp
+    const int nb = K / 256, sub = lane >> 3, c = lane & 7;
+    const int64_t stride = kq_device_row_bytes(TYPE, K);
+    const int64_t off = (int64_t)ids[pair] * expert_stride + (int64_t)j * stride;
+    const int arow = pair / ku;
+    const int8_t *a_row = aq + (int64_t)arow * K;
+    const float *d_row = ad + (int64_t)arow * nb;
+    const int16_t *s_row = abs16 + (int64_t)arow * nb * 16;
+    float g = 0.f, u = 0.f;
+    for (int it0 = 0; it0 * 4 < nb; it0 += 2) { // two steps of four blocks in flight for each of the two rows
+        LaneBlock<TYPE> lg[2], lu[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int blk = (it0 + i) * 4 + sub;
+            if (blk < nb) {
+                lg[i].load(Wg + off, nb, blk, c);
+                lu[i].load(Wu + off, nb, blk, c);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int blk = (it0 + i) * 4 + sub;
+            if (blk < nb) {
+                g = lg[i].dot(a_row + blk * 256, d_row[blk], s_row + blk * 16, c, g);
+                u = lu[i].dot(a_row + blk * 256, d_row[blk], s_row + blk * 16, c, u);
+            }
+        }
+    }
+    g = kq_warp_sum(g);
+    u = kq_warp_sum(u);
+    if (lane == 0) hp[(int64_t)pair * fe + j] = (g / (1.0f + expf(-g))) * u;
+}
 
 template <uint32_t TYPE>
-__global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint8_t *W, int64_t expert_stride, const float *hp,
+__global__ void __launch_bounds__(256, 2) moe_down_combine_kernel(const uint8_t *W, int64_t expert_stride, const float *hp,
                                                                const int32_t *ids, const float *wts, const float *res, int ku,
                                                                int h, int fe, float *out) {
     KQ_PDL_ENTER();
@@ -100,6 +200,22 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint8_t *W,
     int8_t *aq = reinterpret_cast<int8_t *>(sm);                                   // [ku][fe]
     float *ad = reinterpret_cast<float *>(sm + (size_t)ku * fe);                   // [ku][nb]
     int16_t *abs16 = reinterpret_cast<int16_t *>(sm + (size_t)ku * fe + (((size_t)nblk * 4 + 15) & ~(size_t)15)); // [ku][nb][16]
+    const int sub = lane >> 3, c = lane & 7;
+    const int64_t stride = kq_device_row_bytes(TYPE, fe);
+    const int n = blockIdx.x * DOWN_ROWS + warp; // this warp's output row
+    const bool row_on = n < h;
+    // the first four blocks of every slot's row are requested before anything else: they fly while the
+    // prologue quantises the activations
+    const uint8_t *rowp[8];
+    LaneBlock<TYPE> lb[8];
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+        rowp[s] = nullptr;
+        if (s < ku && row_on) rowp[s] = W + (int64_t)ids[(int64_t)t * ku + s] * expert_stride + (int64_t)n * stride;
+    }
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+        if (s < ku && row_on && sub < nb) lb[s].load(rowp[s], nb, sub, c);
     // the token's pairs are consecutive rows of hp: its ku * nb blocks are one run
     const float *hrow = hp + (int64_t)t * ku * fe;
     for (int b = warp; b < nblk; b += 8) {
@@ -109,98 +225,33 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint8_t *W,
         kq_quantize_block_warp(v, lane, aq + b * 256, ad + b, abs16 + b * 16);
     }
     __syncthreads();
-    const int sub = lane >> 3, c = lane & 7;
-    const int64_t stride = kq_device_row_bytes(TYPE, fe);
-    for (int rr = 0; rr < 2; rr++) {
-        const int n = blockIdx.x * DOWN_ROWS + warp * 2 + rr;
-        if (n >= h) break; // the whole warp
-        float acc[8];
+    if (!row_on) return; // the whole warp
+    float acc[8];
 #pragma unroll
-        for (int s = 0; s < 8; s++) acc[s] = 0.f;
-        for (int it = 0; it * 4 < nb; it++) {
-            const int blk = it * 4 + sub;
-            const bool on = blk < nb;
+    for (int s = 0; s < 8; s++) acc[s] = 0.f;
+    for (int it = 0; it * 4 < nb; it++) {
+        const int blk = it * 4 + sub;
+        if (it > 0) {
 #pragma unroll
-            for (int s0 = 0; s0 < 8; s0 += 4) { // four slots' weights in flight at a time
-                if (s0 >= ku) break;
-                if (TYPE == B200_TYPE_Q4_K) {
-                    uint4 hdr[4], w[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        hdr[j] = w[j] = make_uint4(0, 0, 0, 0);
-                        if (on && s0 + j < ku) {
-                            const uint8_t *b = W + (int64_t)ids[(int64_t)t * ku + s0 + j] * expert_stride + (int64_t)n * stride +
-                                               (int64_t)blk * KQ_Q4K_BYTES;
-                            hdr[j] = __ldg(reinterpret_cast<const uint4 *>(b));
-                            w[j] = kq_ld_stream(b + 16 + 16 * c);
-                        }
-                    }
-                    const int e_lo = 64 * (c >> 1) + 16 * (c & 1);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        if (on && s0 + j < ku) {
-                            const int s = s0 + j;
-                            const Q4Scales sc = q4k_lane_scales(hdr[j], c);
-                            const int8_t *a = aq + s * fe + blk * 256 + e_lo;
-                            const int4 alo = *reinterpret_cast<const int4 *>(a);
-                            const int4 ahi = *reinterpret_cast<const int4 *>(a + 32);
-                            const float da = ad[s * nb + blk];
-                            const int16_t *s16 = abs16 + (s * nb + blk) * 16 + (e_lo >> 4);
-                            int isum, msum;
-                            q4k_lane_ints(w[j], sc, alo, ahi, s16[0], s16[2], isum, msum);
-                            acc[s] = fmaf(sc.d * da, (float)isum, acc[s]);
-                            acc[s] = fmaf(-(sc.dmin * da), (float)msum, acc[s]);
-                        }
-                    }
-                } else {
-                    const int hh = c >> 2, cc = c & 3;
-                    const int e_lo = 128 * hh + 16 * cc;
-                    uint4 ql[4], qh[4];
-                    int scl[4], sch[4];
-                    float dw[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        ql[j] = qh[j] = make_uint4(0, 0, 0, 0);
-                        scl[j] = sch[j] = 0;
-                        dw[j] = 0.f;
-                        if (on && s0 + j < ku) {
-                            const uint8_t *rp = W + (int64_t)ids[(int64_t)t * ku + s0 + j] * expert_stride + (int64_t)n * stride;
-                            const KqQ6Addr qa = kq_q6_addr(nb, blk);
-                            ql[j] = kq_ld_stream(rp + qa.ql + qa.cs * c);
-                            qh[j] = __ldg(reinterpret_cast<const uint4 *>(rp + qa.qh + qa.cs * (2 * hh + (cc & 1))));
-                            const int8_t *scp = reinterpret_cast<const int8_t *>(rp + qa.sc);
-                            scl[j] = scp[8 * hh + cc];
-                            sch[j] = scp[8 * hh + 4 + cc];
-                            dw[j] = kq_h2f(*reinterpret_cast<const uint16_t *>(rp + qa.d));
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        if (on && s0 + j < ku) {
-                            const int s = s0 + j;
-                            const int8_t *a = aq + s * fe + blk * 256 + e_lo;
-                            const int4 alo = *reinterpret_cast<const int4 *>(a);
-                            const int4 ahi = *reinterpret_cast<const int4 *>(a + 64);
-                            const float da = ad[s * nb + blk];
-                            const int16_t *s16 = abs16 + (s * nb + blk) * 16 + (e_lo >> 4);
-                            const int isum = q6k_lane_ints(ql[j], qh[j], cc, scl[j], sch[j], alo, ahi, s16[0], s16[4]);
-                            acc[s] = fmaf(dw[j] * da, (float)isum, acc[s]);
-                        }
-                    }
-                }
-            }
+            for (int s = 0; s < 8; s++)
+                if (s < ku && blk < nb) lb[s].load(rowp[s], nb, blk, c);
         }
-        // per slot the full dot product first, then the weighted sum in slot order on top of the residual
-        float y = 0.f;
+        if (blk < nb) {
 #pragma unroll
-        for (int s = 0; s < 8; s++) {
-            if (s < ku) {
-                const float v = kq_warp_sum(acc[s]);
-                y += wts[(int64_t)t * ku + s] * v;
-            }
+            for (int s = 0; s < 8; s++)
+                if (s < ku) acc[s] = lb[s].dot(aq + s * fe + blk * 256, ad[s * nb + blk], abs16 + (s * nb + blk) * 16, c, acc[s]);
         }
-        if (lane == 0) out[(int64_t)t * h + n] = res[(int64_t)t * h + n] + y;
     }
+    // per slot the full dot product first, then the weighted sum in slot order on top of the residual
+    float y = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+        if (s < ku) {
+            const float v = kq_warp_sum(acc[s]);
+            y += wts[(int64_t)t * ku + s] * v;
+        }
+    }
+    if (lane == 0) out[(int64_t)t * h + n] = res[(int64_t)t * h + n] + y;
 }
 
 } // namespace
@@ -233,6 +284,21 @@ b200_status kq_moe_down_combine(uint32_t type, const uint8_t *W, int64_t expert_
     else
         KQ_CUDA(kq_launch(moe_down_combine_kernel<B200_TYPE_Q6_K>, grid, dim3(256), smem, st, W, expert_stride, hp, ids, wts, res, ku, h,
                           fe, out));
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// hp[pair] = swiglu(Wg[ids[pair]] . a, Wu[ids[pair]] . a) with a = the Q8 activations of token pair / ku
+b200_status kq_moe_gate_up(uint32_t type, const uint8_t *Wg, const uint8_t *Wu, int64_t expert_stride, const int8_t *aq,
+                           const float *ad, const int16_t *abs16, const int32_t *ids, int pairs, int ku, int K, int fe, float *hp,
+                           cudaStream_t st) {
+    if (pairs < 1 || pairs > 65535 || ku < 1 || K % 256 != 0 || (type != B200_TYPE_Q4_K && type != B200_TYPE_Q6_K)) return B200_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)kq_div_up(fe, 4), pairs);
+    if (type == B200_TYPE_Q4_K)
+        KQ_CUDA(kq_launch(moe_gate_up_kernel<B200_TYPE_Q4_K>, grid, dim3(128), 0, st, Wg, Wu, expert_stride, aq, ad, abs16, ids, ku, K, fe, hp));
+    else
+        KQ_CUDA(kq_launch(moe_gate_up_kernel<B200_TYPE_Q6_K>, grid, dim3(128), 0, st, Wg, Wu, expert_stride, aq, ad, abs16, ids, ku, K, fe, hp));
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;

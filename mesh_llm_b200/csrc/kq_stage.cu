@@ -19,6 +19,15 @@ b200_status kq_synth_weights(uint32_t type, void *W, int64_t n_rows, int64_t K, 
                              float sigma, cudaStream_t st);
 b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y,
                         int8_t *q, float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride = 0);
+b200_status kq_moe_router_fused(const float *x, const float *norm_w, float eps, const float *router_w, int rows, int E, int h,
+                                int k, const uint8_t *mask, float *rl, int32_t *ids, float *wts, int8_t *q, float *d,
+                                int16_t *bs, unsigned int *counters, cudaStream_t st);
+b200_status kq_moe_gate_up(uint32_t type, const uint8_t *Wg, const uint8_t *Wu, int64_t expert_stride, const int8_t *aq,
+                           const float *ad, const int16_t *abs16, const int32_t *ids, int pairs, int ku, int K, int fe, float *hp,
+                           cudaStream_t st);
+b200_status kq_moe_down_combine(uint32_t type, const uint8_t *W, int64_t expert_stride, const float *hp, const int32_t *ids,
+                                const float *wts, const float *res, int rows, int ku, int h, int fe, float *out,
+                                cudaStream_t st);
 b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc, int n_seq, int T,
                          const int32_t *pos0_dev, int pos0, int n_head, int n_kv, int hd,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
@@ -143,6 +152,7 @@ struct b200_stage {
     size_t moe_sorted_bytes = 0;
     uint8_t *expert_mask = nullptr; // one byte per expert, 1 = allowed (all ones when no mask is set)
     int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
+    unsigned int *moe_counters = nullptr; // one word per token row, zero between launches (moe_router_fused_kernel)
     size_t att_scratch_bytes = 0;
     void *scan_scratch = nullptr; // slices and counters of the vocabulary scan
     size_t scan_scratch_bytes = 0;
@@ -327,6 +337,23 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
         if (ffn_done) {
         } else if (c.n_expert > 0) {
             const int E = c.n_expert, ku = c.n_expert_used, fe = c.n_ff_exp, pairs = rows * ku;
+            // Few tokens (a decode step): norm, Q8, router logits and routing are one launch, and the down
+            // matmul quantises its own input and leaves the weighted sum on the residual (kq_moe_decode.cu).
+            // B200_MOE_FUSED=0 keeps the separate launches.
+            static int moe_fused_on = -1;
+            if (moe_fused_on < 0) {
+                const char *v = getenv("B200_MOE_FUSED");
+                moe_fused_on = !(v && v[0] == '0');
+            }
+            bool fused_small = moe_fused_on && rows <= 8 && classes == CLS_ALL && ku <= 8 && fe % 256 == 0 && h % 256 == 0;
+            if (fused_small) {
+                const b200_status rs = kq_moe_router_fused(st->x, L.ffn_norm, c.rms_eps, L.router, (int)rows, (int)E, (int)h, (int)ku,
+                                                           st->expert_mask, st->rl, st->rid, st->rw, st->aq, st->ad, st->abs16,
+                                                           st->moe_counters, s);
+                if (rs == B200_ERR_UNSUPPORTED) fused_small = false;
+                else KQ_TRY(rs);
+            }
+            if (!fused_small) {
             OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, st->xn, st->aq, st->ad, st->abs16, s));
             if (classes & CLS_OTHER) {
             kq_launch(router_logits_kernel, (unsigned)kq_div_up((int64_t)rows * E, 4), 128, 0, s, L.router, st->xn,
@@ -335,6 +362,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             KQ_LAUNCH_CHECK();
             }
             OTHER_(b200_moe_route_masked(st->rl, rows, E, ku, st->expert_mask, st->rid, st->rw, s));
+            }
             // gate/up of the selected experts with fused SwiGLU, one (token, slot) pair per grid row
             const int64_t gstride = kq_device_row_bytes(L.gate_e->type, h) * fe;
             const int64_t dstride = kq_device_row_bytes(L.down_e->type, fe) * h;
@@ -363,13 +391,26 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
                                               pairs, E, h, fe, st->yp, st->moe_sorted, s));
             } else {
             KqGemvIndirect ind = {st->rid, pairs, ku};
-            GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, 1, h, nullptr, 1, &ind, s));
+            b200_status rg = B200_ERR_UNSUPPORTED;
+            if (fused_small && L.gate_e->type == L.up_e->type)
+                rg = kq_moe_gate_up(L.gate_e->type, (const uint8_t *)L.gate_e->dev, (const uint8_t *)L.up_e->dev, gstride, st->aq,
+                                    st->ad, st->abs16, st->rid, (int)pairs, (int)ku, (int)h, (int)fe, st->hp, s);
+            if (rg == B200_ERR_UNSUPPORTED) GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, 1, h, nullptr, 1, &ind, s));
+            else KQ_TRY(rg);
+            if (fused_small) {
+                const b200_status rs = kq_moe_down_combine(L.down_e->type, (const uint8_t *)L.down_e->dev, dstride, st->hp, st->rid,
+                                                           st->rw, st->x, (int)rows, (int)ku, (int)h, (int)fe, xout, s);
+                if (rs == B200_ERR_UNSUPPORTED) fused_small = false;
+                else KQ_TRY(rs);
+            }
+            if (!fused_small) {
             OTHER_(b200_quantize_act(st->hp, pairs, fe, st->aq, st->ad, st->abs16, s));
             KqGemvSeg dn = {(const uint8_t *)L.down_e->dev, L.down_e->type, h, st->yp, nullptr, h, dstride};
             KqGemvIndirect ind2 = {st->rid, pairs, 1};
             GEMV_(kq_launch_gemv(&dn, 1, st->aq, st->ad, st->abs16, 1, fe, nullptr, 0, &ind2, s));
             }
-            if (classes & CLS_OTHER) {
+            }
+            if (!fused_small && (classes & CLS_OTHER)) {
             kq_launch(moe_combine_kernel, (unsigned)kq_div_up((int64_t)rows * h, 256), 256, 0, s, 
                 st->yp, st->rw, st->x, rows, ku, h, xout);
             KQ_COUNT_LAUNCH();
@@ -600,6 +641,8 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
         A((void **)&st->yp, pairs * h * 4);
         A((void **)&st->expert_mask, 256);
         if (rc == B200_OK && cudaMemset(st->expert_mask, 1, 256) != cudaSuccess) rc = B200_ERR_CUDA;
+        A((void **)&st->moe_counters, 256);
+        if (rc == B200_OK && cudaMemset(st->moe_counters, 0, 256) != cudaSuccess) rc = B200_ERR_CUDA;
     }
     if (rc == B200_OK && cudaStreamCreateWithFlags(&st->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
         kq_set_error("stage: cudaStreamCreate failed");
