@@ -8,7 +8,7 @@
 
 __device__ __forceinline__ void kq_route_warp(const float *lr, int E, int k, const uint8_t *mask, int32_t *ids, float *w,
                                               int lane) {
-    float v[8], sel[8];
+    float v[8];
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -24,37 +24,37 @@ __device__ __forceinline__ void kq_route_warp(const float *lr, int E, int k, con
         den += v[i];
     }
     den = kq_warp_sum(den);
-    // selection value: the prob of an allowed expert (>= 0), -1 for a masked one (all equal, below every
-    // allowed one, as -inf is), -2 once taken, -3 outside the table
+    // selection key, larger = preferred: the prob of an allowed expert as its bit pattern (probs are not
+    // negative, so the patterns order as the values do) + 4; 3 for a masked expert (all equal, below every
+    // allowed one, as -inf is); 2 once taken; 1 outside the table
+    uint32_t key[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int e = lane + 32 * i;
         v[i] = v[i] / den;
-        sel[i] = e >= E ? -3.f : ((mask && !mask[e]) ? -1.f : v[i]);
+        key[i] = e >= E ? 1u : ((mask && !mask[e]) ? 3u : __float_as_uint(v[i]) + 4u);
     }
     float wsum = 0.f, mine = 0.f;
     int myid = 0;
     for (int s = 0; s < k; s++) {
-        float best = -4.f, bp = 0.f;
-        int be = 0x7fffffff;
+        uint32_t bk = key[0];
+        int bi = 0;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int e = lane + 32 * i;
-            if (sel[i] > best || (sel[i] == best && e < be)) { best = sel[i]; be = e; bp = v[i]; }
-        }
+        for (int i = 1; i < 8; i++)
+            if (key[i] > bk) { bk = key[i]; bi = i; } // ties inside a lane: the lower expert
+        const uint32_t top = __reduce_max_sync(0xffffffffu, bk);
+        const int be = (int)__reduce_min_sync(0xffffffffu, bk == top ? (uint32_t)(lane + 32 * bi) : 0xffffffffu); // ties: the lower expert
+        float pv = v[0];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            const float op = __shfl_xor_sync(0xffffffffu, bp, o);
-            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; bp = op; }
-        }
+        for (int i = 1; i < 8; i++)
+            if (i == (be >> 5)) pv = v[i];
+        const float bp = __shfl_sync(0xffffffffu, pv, be & 31);
         wsum += bp;
         if (lane == s) { mine = bp; myid = be; }
         if ((be & 31) == lane) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
-                if (i == (be >> 5)) sel[i] = -2.f; // taken
+                if (i == (be >> 5)) key[i] = 2u; // taken
         }
     }
     if (lane < k) {
