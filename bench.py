@@ -123,13 +123,30 @@ _CPU_OPERANDS = {}
 
 
 # ------------------------------------------------------------------------------------------------
+def host_threads():
+    """threads the CPU legs may really use: the cores this process is allowed on, cut to the container's CPU
+    quota when there is one (more OpenMP threads than that only fight each other)"""
+    n = os.cpu_count() or 1
+    try:
+        n = min(n, len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()[:2]
+        if quota != "max":
+            n = min(n, max(1, int(int(quota) / int(period))))
+    except Exception:
+        pass
+    return max(1, n)
+
+
 def cpu_decode_sample(w, threads=None, reps=2):
     """times the CPU oracle on one layer of each parity (+ the LM head) at M = 1 and extrapolates
     to the full depth.  Returns (tok/s, cores, description)."""
     from oracle import binding as orc
 
     # all host cores, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its workers)
-    orc.lib().orc_set_threads(threads or os.cpu_count() or 1)
+    orc.lib().orc_set_threads(threads or host_threads())
     cores = orc.lib().orc_get_threads()
     shapes = {}
     for layer in (0, 1):
@@ -569,7 +586,7 @@ def cfg1_timed_cpu_leg(local, n_decode=128):
     n_ctx = w["prefill"] + n_decode + 8
     st = Stage(**model, n_ctx=n_ctx, n_seq=1, n_ubatch=512, device=local)
     st.generate(20251125)
-    orc.lib().orc_set_threads(os.cpu_count() or 1)
+    orc.lib().orc_set_threads(host_threads())
     cores = orc.lib().orc_get_threads()
     m = orc.Model(**model, n_ctx=n_ctx)
     for n in m.tensor_names():  # the device-generated weights, read back in GGUF layout
