@@ -425,15 +425,21 @@ def bench_single(args, w, local, full=True, steps=None):
     nxt = torch.zeros(1, dtype=torch.int32, device=dev)
     logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev)
     if not args.no_prefill:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for p0 in range(0, w["prefill"], 512):
-            chunk = prompt[p0:p0 + 512]
-            st.forward(tokens=chunk, n_seq=1, T=chunk.numel(), pos0=p0, logits=logits, next_tokens=nxt)
-        e1.record()
-        torch.cuda.synchronize()
-        prefill_tok_s = w["prefill"] / (e0.elapsed_time(e1) * 1e-3)
+        # the prompt goes through twice: the first pass is the warm-up (first launches, scratch growth), the
+        # second, which rewrites the same cache rows with the same values, is the timed one
+        for timed in (False, True):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for p0 in range(0, w["prefill"], 512):
+                chunk = prompt[p0:p0 + 512]
+                st.forward(tokens=chunk, n_seq=1, T=chunk.numel(), pos0=p0, logits=logits, next_tokens=nxt)
+            e1.record()
+            torch.cuda.synchronize()
+            if timed:
+                prefill_tok_s = w["prefill"] / (e0.elapsed_time(e1) * 1e-3)
+            elif os.environ.get("B200_BENCH_VERBOSE"):
+                print(f"[bench] warm-up prefill pass: {w['prefill'] / (e0.elapsed_time(e1) * 1e-3):.0f} tok/s", file=sys.stderr)
     pos = w["prefill"]
 
     # ---- decode, device resident: the stage feeds itself its own greedy token

@@ -24,7 +24,9 @@
 // returns.
 #include "kq_common.cuh"
 
+#include <algorithm>
 #include <mutex>
+#include <stdlib.h>
 
 #include <cuda.h> // CUtensorMap and the encode entry point's types; the driver is reached through the runtime
 #include <string.h>
@@ -163,6 +165,86 @@ __device__ __forceinline__ void q4_planes(uint32_t nib4, uint32_t sc, uint32_t &
     const uint32_t p13 = ((nib4 >> 8) & 0x000F000Fu) * sc; // codes 1 and 3: bytes [lo1 hi1 lo3 hi3]
     lo = __byte_perm(p02, p13, 0x6240);
     hi = __byte_perm(p02, p13, 0x7351);
+}
+
+// ---- weights of one super-block -> the two int8 planes (and the f16 min operand, the f32 block scales) ----
+// Q4_K, one task per (row r of the tile, 16-byte chunk c of the block's quants): hdr = the block's first 16
+// bytes, w = chunk c.  Chunk c gives K chunks 4g+h (low nibbles, sub-block 2g) and 4g+2+h (high, 2g+1).
+__device__ __forceinline__ void unpack_q4_task(const uint4 &hdr, const uint4 &w, int r, int c, uint8_t *bhi, float *dw_s,
+                                               float *dmin_s, uint8_t *bmin) {
+    const int g = c >> 1, h = c & 1;
+    const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+    const uint32_t scw = g < 2 ? sc_lo : sc_hi;
+    const uint32_t sc0 = (scw >> (8 * ((2 * g) & 3))) & 0xFF, sc1 = (scw >> (8 * ((2 * g + 1) & 3))) & 0xFF;
+    if (c == 0) {
+        const uint32_t m_lo = hdr.z & 0x3F3F3F3Fu, m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        dw_s[r] = dd.x;
+        dmin_s[r] = dd.y;
+        __half mh[16]; // m_j against both sums of 16 of sub-block j
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t mw = j < 4 ? m_lo : m_hi;
+            const __half v = __int2half_rn((int)((mw >> (8 * (j & 3))) & 0xFF));
+            mh[2 * j] = v;
+            mh[2 * j + 1] = v;
+        }
+        *reinterpret_cast<uint4 *>(bmin + op_off_bmin(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
+        *reinterpret_cast<uint4 *>(bmin + op_off_bmin(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
+    }
+    uint4 hi_l, lo_l, hi_h, lo_h;
+    q4_planes(w.x & 0x0F0F0F0Fu, sc0, hi_l.x, lo_l.x);
+    q4_planes(w.y & 0x0F0F0F0Fu, sc0, hi_l.y, lo_l.y);
+    q4_planes(w.z & 0x0F0F0F0Fu, sc0, hi_l.z, lo_l.z);
+    q4_planes(w.w & 0x0F0F0F0Fu, sc0, hi_l.w, lo_l.w);
+    q4_planes((w.x >> 4) & 0x0F0F0F0Fu, sc1, hi_h.x, lo_h.x);
+    q4_planes((w.y >> 4) & 0x0F0F0F0Fu, sc1, hi_h.y, lo_h.y);
+    q4_planes((w.z >> 4) & 0x0F0F0F0Fu, sc1, hi_h.z, lo_h.z);
+    q4_planes((w.w >> 4) & 0x0F0F0F0Fu, sc1, hi_h.w, lo_h.w);
+    const int kc_l = 4 * g + h, kc_h = 4 * g + 2 + h;
+    *reinterpret_cast<uint4 *>(bhi + op_off_b(r, kc_l)) = hi_l;
+    *reinterpret_cast<uint4 *>(bhi + op_off_b(TN + r, kc_l)) = lo_l;
+    *reinterpret_cast<uint4 *>(bhi + op_off_b(r, kc_h)) = hi_h;
+    *reinterpret_cast<uint4 *>(bhi + op_off_b(TN + r, kc_h)) = lo_h;
+}
+
+// Q6_K, one task per (row r, qh chunk j): qh4 = the chunk of 2-bit highs, qa4 / qb4 its two chunks of low
+// nibbles, sc4 = the four int8 scales of its scale groups, dwv = the block's f32 scale.  4 scale groups of 16
+// elements, w' = sc * (q - 32) split as hi * 64 + lo with lo in 0..63 and hi in -64..63 (both planes signed).
+__device__ __forceinline__ void unpack_q6_task(const uint4 &qh4, const uint4 &qa4, const uint4 &qb4, uint32_t sc4, float dwv,
+                                               int r, int j, uint8_t *bhi, float *dw_s, float *dmin_s) {
+    const int hh = j >> 1, c1 = j & 1;
+    const uint32_t hw[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+    const uint32_t aw[4] = {qa4.x, qa4.y, qa4.z, qa4.w};
+    const uint32_t bw[4] = {qb4.x, qb4.y, qb4.z, qb4.w};
+    if (j == 0) {
+        dw_s[r] = dwv;
+        dmin_s[r] = 0.f;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; q++) { // bit pair q of the qh bytes: elements 128hh + 32q + 16c1 + i
+        const int scq = (int)(int8_t)((sc4 >> (8 * q)) & 0xFF);
+        uint32_t hi4[4], lo4[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            const uint32_t nib = (q & 1) ? bw[wd] : aw[wd];
+            const uint32_t l4 = (q & 2) ? (nib >> 4) & 0x0F0F0F0Fu : nib & 0x0F0F0F0Fu;
+            const uint32_t h2 = (hw[wd] >> (2 * q)) & 0x03030303u;
+            const uint32_t code = l4 | (h2 << 4); // 4 codes 0..63
+            uint32_t hi = 0, lo = 0;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int wv = scq * ((int)((code >> (8 * k)) & 0xFF) - 32);
+                hi |= (uint32_t)((wv >> 6) & 0xFF) << (8 * k);
+                lo |= (uint32_t)(wv & 63) << (8 * k);
+            }
+            hi4[wd] = hi;
+            lo4[wd] = lo;
+        }
+        const int kc = 8 * hh + 2 * q + c1;
+        *reinterpret_cast<uint4 *>(bhi + op_off_b(r, kc)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+        *reinterpret_cast<uint4 *>(bhi + op_off_b(TN + r, kc)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+    }
 }
 
 // Q8 codes [M][K] -> [M/128][K/16][128 rows][16 bytes]: one super-block of a 128-token tile becomes a
@@ -358,42 +440,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
 #pragma unroll
             for (int t = 0; t < WT4; t++) {
                 const int wt = warp + t * (NTHREADS / 32), r = 8 * (wt >> 1) + (lane & 7), c = 4 * (wt & 1) + (lane >> 3);
-                const int g = c >> 1, h = c & 1;
                 const uint8_t *blk = smem + SMEM_RAW + (b & 1) * RAW_BYTES + r * KQ_Q4K_BYTES;
                 const uint4 hdr = *reinterpret_cast<const uint4 *>(blk), w = *reinterpret_cast<const uint4 *>(blk + 16 + 16 * c);
-                const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-                const uint32_t scw = g < 2 ? sc_lo : sc_hi;
-                const uint32_t sc0 = (scw >> (8 * ((2 * g) & 3))) & 0xFF, sc1 = (scw >> (8 * ((2 * g + 1) & 3))) & 0xFF;
-                if (c == 0) {
-                    const uint32_t m_lo = hdr.z & 0x3F3F3F3Fu, m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-                    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-                    dw_s[r] = dd.x;
-                    dmin_s[r] = dd.y;
-                    __half mh[16]; // m_j against both sums of 16 of sub-block j
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint32_t mw = j < 4 ? m_lo : m_hi;
-                        const __half v = __int2half_rn((int)((mw >> (8 * (j & 3))) & 0xFF));
-                        mh[2 * j] = v;
-                        mh[2 * j + 1] = v;
-                    }
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_bmin(r, 0)) = *reinterpret_cast<uint4 *>(&mh[0]);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BMIN + op_off_bmin(r, 1)) = *reinterpret_cast<uint4 *>(&mh[8]);
-                }
-                uint4 hi_l, lo_l, hi_h, lo_h;
-                q4_planes(w.x & 0x0F0F0F0Fu, sc0, hi_l.x, lo_l.x);
-                q4_planes(w.y & 0x0F0F0F0Fu, sc0, hi_l.y, lo_l.y);
-                q4_planes(w.z & 0x0F0F0F0Fu, sc0, hi_l.z, lo_l.z);
-                q4_planes(w.w & 0x0F0F0F0Fu, sc0, hi_l.w, lo_l.w);
-                q4_planes((w.x >> 4) & 0x0F0F0F0Fu, sc1, hi_h.x, lo_h.x);
-                q4_planes((w.y >> 4) & 0x0F0F0F0Fu, sc1, hi_h.y, lo_h.y);
-                q4_planes((w.z >> 4) & 0x0F0F0F0Fu, sc1, hi_h.z, lo_h.z);
-                q4_planes((w.w >> 4) & 0x0F0F0F0Fu, sc1, hi_h.w, lo_h.w);
-                const int kc_l = 4 * g + h, kc_h = 4 * g + 2 + h;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc_l)) = hi_l;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc_l)) = lo_l;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc_h)) = hi_h;
-                *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc_h)) = lo_h;
+                unpack_q4_task(hdr, w, r, c, smem + SMEM_BHI, dw_s, dmin_s, smem + SMEM_BMIN);
             }
         } else {
             // Q6_K: one task per (row, qh chunk j): 4 scale groups of 16 elements, w' = sc * (q - 32)
@@ -401,38 +450,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
 #pragma unroll
             for (int t = 0; t < WT6; t++) {
                 const int wt = warp + t * (NTHREADS / 32), r = 8 * wt + (lane & 7), j = lane >> 3;
-                const int hh = j >> 1, c1 = j & 1;
-                const uint32_t hw[4] = {p6_h[t].x, p6_h[t].y, p6_h[t].z, p6_h[t].w};
-                const uint32_t aw[4] = {p6_a[t].x, p6_a[t].y, p6_a[t].z, p6_a[t].w};
-                const uint32_t bw[4] = {p6_b[t].x, p6_b[t].y, p6_b[t].z, p6_b[t].w};
-                if (j == 0) {
-                    dw_s[r] = p6_d[t];
-                    dmin_s[r] = 0.f;
-                }
-#pragma unroll
-                for (int q = 0; q < 4; q++) { // bit pair q of the qh bytes: elements 128hh + 32q + 16c1 + i
-                    const int scq = (int)(int8_t)((p6_sc[t] >> (8 * q)) & 0xFF);
-                    uint32_t hi4[4], lo4[4];
-#pragma unroll
-                    for (int wd = 0; wd < 4; wd++) {
-                        const uint32_t nib = (q & 1) ? bw[wd] : aw[wd];
-                        const uint32_t l4 = (q & 2) ? (nib >> 4) & 0x0F0F0F0Fu : nib & 0x0F0F0F0Fu;
-                        const uint32_t h2 = (hw[wd] >> (2 * q)) & 0x03030303u;
-                        const uint32_t code = l4 | (h2 << 4); // 4 codes 0..63
-                        uint32_t hi = 0, lo = 0;
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const int wv = scq * ((int)((code >> (8 * k)) & 0xFF) - 32);
-                            hi |= (uint32_t)((wv >> 6) & 0xFF) << (8 * k);
-                            lo |= (uint32_t)(wv & 63) << (8 * k);
-                        }
-                        hi4[wd] = hi;
-                        lo4[wd] = lo;
-                    }
-                    const int kc = 8 * hh + 2 * q + c1;
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(r, kc)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                    *reinterpret_cast<uint4 *>(smem + SMEM_BHI + op_off_b(TN + r, kc)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
-                }
+                unpack_q6_task(p6_h[t], p6_a[t], p6_b[t], p6_sc[t], p6_d[t], r, j, smem + SMEM_BHI, dw_s, dmin_s);
             }
         }
         PROF_T(t_1);
@@ -546,6 +564,297 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
             const int col = chalf * NCOL + c;
             if (n0 + col < p.N) {
                 const int64_t o = (int64_t)out_row * p.N + n0 + col;
+                float v, v_odd;
+                unpack2(yacc[c / 2], v, v_odd);
+                if (c & 1) v = v_odd;
+                if (p.bias) v += p.bias[n0 + col];
+                if (p.residual) v += p.residual[o];
+                p.y[o] = v;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+// ====================================================================================================
+// Pre-unpacked planes: the form for two or more 128-token tiles.
+// gemm_tc_kernel unpacks a weight tile once per token tile.  With several token tiles the unpacked operand
+// is built once instead -- unpack_planes_kernel writes, for every (64-row tile, super-block), the image the
+// tensor core reads: [hi | lo planes 32 KB | f16 min operand 2 KB | d_w 64 f32 | d_min 64 f32] -- and
+// gemm_planes_kernel brings an image in with one bulk copy per super-block and does no CUDA-core work before
+// its MMAs.  The token side is prepared alike (retile_act_img_kernel: [codes 32 KB | f16 sums-of-16 operand
+// 4 KB] per token tile and super-block).  Token tiles of one weight tile are neighbours in the grid, so an
+// image is fetched from HBM once and served from L2 to the other token tiles.  The arithmetic, operand
+// layouts, MMAs and epilogue are those of gemm_tc_kernel: results are bit-identical.
+// ====================================================================================================
+constexpr int IMG_BMIN = 2 * B_BYTES;               // offsets inside a weight image
+constexpr int IMG_DW = IMG_BMIN + BMIN_BYTES;
+constexpr int IMG_DMIN = IMG_DW + TN * 4;
+constexpr int IMG_BYTES = IMG_DMIN + TN * 4;        // 35328
+constexpr int AIMG_AMIN = A_BYTES;                  // offset of the f16 operand inside a token image
+constexpr int AIMG_BYTES = A_BYTES + AMIN_BYTES;    // 36864
+constexpr int PL_SMEM_A = 0, PL_SMEM_B = AIMG_BYTES, PL_SMEM_TOTAL = AIMG_BYTES + 2 * IMG_BYTES + 64;
+static_assert(IMG_BYTES % 16 == 0 && AIMG_BYTES % 1024 == 0, "bulk copies move multiples of 16 bytes to aligned places");
+static_assert(PL_SMEM_TOTAL <= 112 * 1024, "two CTAs per SM");
+
+// grid (super-blocks, weight tiles); one image per CTA, staged in shared memory and written with one bulk store
+__global__ void __launch_bounds__(NTHREADS) unpack_planes_kernel(uint32_t type, const uint8_t *W, int N, int nb, uint8_t *img) {
+    KQ_PDL_ENTER();
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x, nt = blockIdx.y, n0 = nt * TN;
+    float *dw_s = reinterpret_cast<float *>(smem + IMG_DW), *dmin_s = reinterpret_cast<float *>(smem + IMG_DMIN);
+    const int64_t wstride = kq_device_row_bytes(type, (int64_t)nb * 256);
+    if (type == B200_TYPE_Q4_K) {
+        constexpr int WT4 = TN * 8 / NTHREADS;
+#pragma unroll
+        for (int t = 0; t < WT4; t++) {
+            const int wt = warp + t * (NTHREADS / 32), r = 8 * (wt >> 1) + (lane & 7), c = 4 * (wt & 1) + (lane >> 3);
+            uint4 hdr = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0); // rows past N: zero blocks
+            if (n0 + r < N) {
+                const uint8_t *blk = W + (int64_t)(n0 + r) * wstride + (int64_t)b * KQ_Q4K_BYTES;
+                hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+                w = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 16 * c));
+            }
+            unpack_q4_task(hdr, w, r, c, smem, dw_s, dmin_s, smem + IMG_BMIN);
+        }
+    } else {
+        constexpr int WT6 = TN * 4 / NTHREADS;
+        const KqQ6Addr qa = kq_q6_addr(nb, b);
+        for (int i = tid; i < BMIN_BYTES / 16; i += NTHREADS) reinterpret_cast<uint4 *>(smem + IMG_BMIN)[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int t = 0; t < WT6; t++) {
+            const int wt = warp + t * (NTHREADS / 32), r = 8 * wt + (lane & 7), j = lane >> 3;
+            const int hh = j >> 1, c1 = j & 1;
+            uint4 h4 = make_uint4(0, 0, 0, 0), a4 = h4, b4 = h4;
+            uint32_t sc = 0;
+            float dv = 0.f;
+            if (n0 + r < N) {
+                const uint8_t *rowp = W + (int64_t)(n0 + r) * wstride;
+                h4 = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.qh + j * qa.cs));
+                a4 = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1) * qa.cs));
+                b4 = __ldg(reinterpret_cast<const uint4 *>(rowp + qa.ql + (4 * hh + c1 + 2) * qa.cs));
+                const uint8_t *scp = rowp + qa.sc + 8 * hh + c1; // scale groups 8hh + 2q + c1
+                sc = (uint32_t)scp[0] | ((uint32_t)scp[2] << 8) | ((uint32_t)scp[4] << 16) | ((uint32_t)scp[6] << 24);
+                dv = kq_h2f(*reinterpret_cast<const uint16_t *>(rowp + qa.d));
+            }
+            unpack_q6_task(h4, a4, b4, sc, dv, r, j, smem, dw_s, dmin_s);
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+        uint8_t *dst = img + ((int64_t)nt * nb + b) * IMG_BYTES;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(smem)), "r"(IMG_BYTES)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // the store has left shared memory and is complete
+    }
+}
+
+// Q8 codes and sums of 16 -> token images: (token tile mt, super-block b) at (mt * nb + b) * AIMG_BYTES.
+// One thread per 16-byte piece: pieces 0..15 of a row are its code chunks, 16 and 17 its sums as f16.
+__global__ void __launch_bounds__(256) retile_act_img_kernel(const int8_t *q, const int16_t *bs, uint8_t *out, int M, int K,
+                                                             int64_t n_piece) {
+    KQ_PDL_ENTER();
+    const int nb = K / 256;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_piece; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i % TM);
+        int64_t t = i / TM;
+        const int j = (int)(t % 18);
+        t /= 18;
+        const int b = (int)(t % nb), mt = (int)(t / nb);
+        const int m = mt * TM + r;
+        uint8_t *rec = out + ((int64_t)mt * nb + b) * AIMG_BYTES;
+        if (j < 16) {
+            const uint4 v = m < M ? *reinterpret_cast<const uint4 *>(q + (int64_t)m * K + b * 256 + j * 16) : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(rec + op_off_a(r, j)) = v;
+        } else { // sums of 16 as f16 (|sum| <= 2032: exact)
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < M) {
+                const int4 s8 = *reinterpret_cast<const int4 *>(bs + ((int64_t)m * nb + b) * 16 + 8 * (j - 16));
+                const int16_t *s16 = reinterpret_cast<const int16_t *>(&s8);
+                __half h[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) h[k] = __int2half_rn((int)s16[k]);
+                v = *reinterpret_cast<uint4 *>(&h[0]);
+            }
+            *reinterpret_cast<uint4 *>(rec + AIMG_AMIN + op_off_a(r, j - 16)) = v;
+        }
+    }
+}
+
+struct PlanesParams {
+    const uint8_t *bimg; // weight images, [weight tile][super-block]
+    const uint8_t *aimg; // token images, [token tile][super-block]
+    const float *ad;     // Q8 block scales [M][nb]
+    float *y;
+    const float *bias, *residual;
+    int32_t M, N, nb;
+    uint32_t type;
+};
+
+// grid (token tiles, weight tiles): the token tiles of one weight tile run side by side
+__global__ void __launch_bounds__(NTHREADS, 2) gemm_planes_kernel(const PlanesParams p) {
+    KQ_PDL_ENTER();
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t mbar;      // the MMAs of a super-block have completed
+    __shared__ uint64_t full_b[2]; // a weight image has landed
+    __shared__ uint64_t full_a;    // the token image has landed
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mt = blockIdx.x, nt = blockIdx.y, m0 = mt * TM, n0 = nt * TN;
+    const uint32_t mbar_a = smem_u32(&mbar);
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_a), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_b[0])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_b[1])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_a)), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const int row = (warp & 3) * 32 + lane; // token row of the tile = TMEM lane
+    const int chalf = warp >> 2;            // columns [NCOL*chalf, NCOL*chalf + NCOL)
+    const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    uint64_t yacc[NCOL / 2];
+#pragma unroll
+    for (int i = 0; i < NCOL / 2; i++) yacc[i] = 0ull;
+    const bool q4 = p.type == B200_TYPE_Q4_K;
+    const int nb = p.nb;
+    const uint8_t *bsrc = p.bimg + (int64_t)nt * nb * IMG_BYTES, *asrc = p.aimg + (int64_t)mt * nb * AIMG_BYTES;
+    const uint32_t a_base = smem_u32(smem + PL_SMEM_A), amin_base = a_base + AIMG_AMIN;
+    auto issue_b = [&](int b) { // the whole weight image of super-block b: one contiguous run
+        if (warp == 1 && lane == 0) {
+            const uint32_t bar = smem_u32(&full_b[b & 1]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(IMG_BYTES) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             smem_u32(smem + PL_SMEM_B + (b & 1) * IMG_BYTES)),
+                         "l"(bsrc + (int64_t)b * IMG_BYTES), "r"(IMG_BYTES), "r"(bar)
+                         : "memory");
+        }
+    };
+    auto issue_a = [&](int b) {
+        if (warp == 1 && lane == 0) {
+            const uint32_t bar = smem_u32(&full_a);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(AIMG_BYTES) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(a_base),
+                         "l"(asrc + (int64_t)b * AIMG_BYTES), "r"(AIMG_BYTES), "r"(bar)
+                         : "memory");
+        }
+    };
+    const bool row_in = m0 + row < p.M;
+    const float *ad_row = p.ad + (int64_t)(row_in ? m0 + row : 0) * nb;
+    issue_b(0);
+    issue_a(0);
+    if (nb > 1) issue_b(1);
+    float pf_da = row_in ? ad_row[0] : 0.f;
+    int last_b = nb > 1 ? 1 : 0, last_a = 0; // newest images handed to the copy engine
+    uint32_t phase = 0;
+    bool failed = false;
+    for (int b = 0; b < nb && !failed; b++) {
+        const uint8_t *img = smem + PL_SMEM_B + (b & 1) * IMG_BYTES;
+        if (warp == 0) {
+            if (lane == 0) {
+                bool ok = kq_mbar_wait(smem_u32(&full_a), (uint32_t)(b & 1), 5 * KQ_WAIT_LIMIT_NS);
+                ok = ok && kq_mbar_wait(smem_u32(&full_b[b & 1]), (uint32_t)((b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+                if (!ok) {
+                    s_abort = 1;
+                    atomicExch(&g_gemm_error, 4);
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (ok && !s_abort) {
+                    const uint32_t id_main = idesc_i8(!q4), bhi_base = smem_u32(img);
+#pragma unroll
+                    for (int s = 0; s < 8; s++) // K = 32 per instruction: chunks 2s, 2s+1; N = hi rows | lo rows
+                        mma_i8(tmem + COL_HI, make_desc(a_base + 2 * s * LBO_A, LBO_A), make_desc(bhi_base + 2 * s * LBO_B, LBO_B),
+                               id_main, s > 0);
+                    if (q4) mma_f16(tmem + COL_MIN, make_desc(amin_base, LBO_A), make_desc(bhi_base + IMG_BMIN, LBO_BMIN), idesc_f16(), 0);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a) : "memory");
+            }
+            __syncwarp();
+        }
+        const float da = pf_da;
+        if (b + 1 < nb) pf_da = row_in ? ad_row[b + 1] : 0.f;
+        {
+            const bool ok = s_abort ? false : kq_mbar_wait(mbar_a, phase, 5 * KQ_WAIT_LIMIT_NS);
+            if (!ok) {
+                s_abort = 1;
+                atomicExch(&g_gemm_error, 1);
+            }
+            phase ^= 1;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // every thread observes the image's own barrier (complete by now) before it reads the block scales
+        if (!s_abort && !kq_mbar_wait(smem_u32(&full_b[b & 1]), (uint32_t)((b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS)) s_abort = 1;
+        if (s_abort) failed = true;
+        if (!failed && b + 1 < nb) { // the token image has been read
+            issue_a(b + 1);
+            last_a = b + 1;
+        }
+        if (!failed) { // y += d_a * (d_w * (R*hi + lo) - dmin * min), as in gemm_tc_kernel
+            const float *dw_s = reinterpret_cast<const float *>(img + IMG_DW), *dmin_s = reinterpret_cast<const float *>(img + IMG_DMIN);
+            const uint64_t da2 = pack2(da, da);
+            const int R = q4 ? 256 : 64;
+#pragma unroll
+            for (int c = 0; c < NCOL; c += 16) {
+                const uint32_t col = chalf * NCOL + c;
+                uint32_t hi[16], lo[16], mn[16];
+                TMEM_LD16(tlane + COL_HI + col, hi);
+                TMEM_LD16(tlane + COL_LO + col, lo);
+                if (q4) TMEM_LD16(tlane + COL_MIN + col, mn);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i4 = 0; i4 < 16; i4 += 4) {
+                    const ulonglong2 dw4 = *reinterpret_cast<const ulonglong2 *>(&dw_s[col + i4]);
+                    const ulonglong2 dm4 = *reinterpret_cast<const ulonglong2 *>(&dmin_s[col + i4]);
+                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x ^ 0x8000000080000000ull, dm4.y ^ 0x8000000080000000ull};
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        const int i = i4 + 2 * k;
+                        const float f0 = (float)(R * (int)hi[i] + (int)lo[i]), f1 = (float)(R * (int)hi[i + 1] + (int)lo[i + 1]);
+                        uint64_t t = mul2(dwp[k], pack2(f0, f1));
+                        if (q4) t = fma2(dmp[k], pack2u(mn[i], mn[i + 1]), t);
+                        yacc[(c + i) / 2] = fma2(da2, t, yacc[(c + i) / 2]);
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads(); // the accumulators and this image's buffer are free again
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!s_abort && b + 2 < nb) {
+            issue_b(b + 2);
+            last_b = b + 2;
+        }
+    }
+    if (failed || s_abort) { // never leave with bulk copies still writing this CTA's shared memory
+        kq_mbar_wait(smem_u32(&full_b[last_b & 1]), (uint32_t)((last_b >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+        if (last_b > 0) kq_mbar_wait(smem_u32(&full_b[(last_b - 1) & 1]), (uint32_t)(((last_b - 1) >> 1) & 1), 5 * KQ_WAIT_LIMIT_NS);
+        kq_mbar_wait(smem_u32(&full_a), (uint32_t)(last_a & 1), 5 * KQ_WAIT_LIMIT_NS);
+        failed = true;
+    }
+    if (!failed && row_in) {
+#pragma unroll
+        for (int c = 0; c < NCOL; c++) {
+            const int col = chalf * NCOL + c;
+            if (n0 + col < p.N) {
+                const int64_t o = (int64_t)(m0 + row) * p.N + n0 + col;
                 float v, v_odd;
                 unpack2(yacc[c / 2], v, v_odd);
                 if (c & 1) v = v_odd;
@@ -729,6 +1038,71 @@ static b200_status kq_gemm_scratch(int dev, size_t need, cudaStream_t st, uint4 
     return B200_OK;
 }
 
+// scratch of the planes form: weight images and token images of one matmul, per device, grown on demand
+static b200_status kq_gemm_planes_scratch(int dev, size_t need_b, size_t need_a, cudaStream_t st, uint8_t **bimg, uint8_t **aimg) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    static uint8_t *buf[KQ_MAX_DEVICES][2];
+    static size_t cap[KQ_MAX_DEVICES][2];
+    static bool attr[KQ_MAX_DEVICES];
+    const size_t need[2] = {need_b, need_a};
+    for (int i = 0; i < 2; i++) {
+        if (need[i] <= cap[dev][i]) continue;
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        KQ_CUDA(cudaStreamIsCapturing(st, &cs));
+        KQ_REQUIRE(cs == cudaStreamCaptureStatusNone, "gemm: operand scratch cannot grow during stream capture");
+        KQ_CUDA(cudaDeviceSynchronize());
+        if (buf[dev][i]) KQ_CUDA(cudaFree(buf[dev][i]));
+        buf[dev][i] = nullptr;
+        cap[dev][i] = 0;
+        if (cudaMalloc(&buf[dev][i], need[i]) != cudaSuccess) {
+            cudaGetLastError();
+            return B200_ERR_UNSUPPORTED; // no room for the images: the caller takes the form that needs none
+        }
+        cap[dev][i] = need[i];
+    }
+    if (!attr[dev]) {
+        KQ_CUDA(cudaFuncSetAttribute(gemm_planes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PL_SMEM_TOTAL));
+        attr[dev] = true;
+    }
+    *bimg = buf[dev][0];
+    *aimg = buf[dev][1];
+    return B200_OK;
+}
+
+static int planes_min_m() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMM_PLANES_MIN_M"); // 0 switches the form off
+        v = e ? atoi(e) : 3 * TM; // measured: from three token tiles on the images pay for themselves
+        if (v <= 0) v = 1 << 30;
+    }
+    return v;
+}
+
+// the form with pre-unpacked operands; B200_ERR_UNSUPPORTED (nothing launched) when it does not apply
+static b200_status launch_gemm_planes(uint32_t type, const uint8_t *W, const int8_t *q, const float *d, const int16_t *bs, int64_t M,
+                                      int64_t N, int64_t K, float *y, const float *bias, const float *residual, int dev,
+                                      cudaStream_t st) {
+    const int64_t m_tiles = kq_div_up(M, TM), n_tiles = kq_div_up(N, TN), nb = K / 256;
+    if (M < planes_min_m() || n_tiles > 65535 || m_tiles > 0x7fffffff / 2) return B200_ERR_UNSUPPORTED;
+    uint8_t *bimg = nullptr, *aimg = nullptr;
+    const b200_status rs = kq_gemm_planes_scratch(dev, (size_t)n_tiles * nb * IMG_BYTES, (size_t)m_tiles * nb * AIMG_BYTES, st, &bimg, &aimg);
+    if (rs != B200_OK) return rs;
+    KQ_CUDA(kq_launch(unpack_planes_kernel, dim3((unsigned)nb, (unsigned)n_tiles), dim3(NTHREADS), (size_t)IMG_BYTES, st, type, W, (int)N,
+                      (int)nb, bimg));
+    KQ_COUNT_LAUNCH();
+    const int64_t n_piece = m_tiles * nb * 18 * TM;
+    KQ_CUDA(kq_launch(retile_act_img_kernel, dim3((unsigned)std::min<int64_t>(kq_div_up(n_piece, 256), 1 << 20)), dim3(256), 0, st, q, bs,
+                      aimg, (int)M, (int)K, n_piece));
+    KQ_COUNT_LAUNCH();
+    PlanesParams p = {bimg, aimg, d, y, bias, residual, (int32_t)M, (int32_t)N, (int32_t)nb, type};
+    KQ_CUDA(kq_launch(gemm_planes_kernel, dim3((unsigned)m_tiles, (unsigned)n_tiles), dim3(NTHREADS), (size_t)PL_SMEM_TOTAL, st, p));
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, const float *d, const int16_t *bs,
                               int64_t M, int64_t N, int64_t K, float *y, const float *bias, const float *residual,
                               cudaStream_t st) {
@@ -738,6 +1112,10 @@ b200_status kq_launch_gemm_tc(uint32_t type, const uint8_t *W, const int8_t *q, 
     int dev = 0;
     KQ_CUDA(cudaGetDevice(&dev));
     KQ_REQUIRE(dev >= 0 && dev < KQ_MAX_DEVICES, "gemm: device %d out of range", dev);
+    {
+        const b200_status rp = launch_gemm_planes(type, W, q, d, bs, M, N, K, y, bias, residual, dev, st);
+        if (rp != B200_ERR_UNSUPPORTED) return rp;
+    }
     const int64_t m_tiles = kq_div_up(M, TM);
     const size_t need = (size_t)m_tiles * TM * K;
     uint4 *tiled_dev = nullptr;

@@ -10,7 +10,7 @@ accumulation), and it must equal the CPU oracle's int32 block sums bit for bit.
 
 Token counts select the kernels: M = 1, 2 the streaming decode GEMV (gemv_block_kernel<type, 1|2>),
 M = 3..8 its mma.m16n8k32 batch form (Q4_K) or the dp4a kernel (Q6_K), M > 8 the tcgen05 prefill
-GEMM with its two-plane recombination.
+GEMM with its two-plane recombination (from 384 tokens on in its form with pre-unpacked operand images).
 """
 import numpy as np
 import pytest
@@ -62,7 +62,7 @@ CASES = [(256, 256), (100, 512), (264, 512), (64, 2048)]
 
 
 @pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K], ids=["q4_k", "q6_k"])
-@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 130])
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 130, 390])
 @pytest.mark.parametrize("N,K", CASES)
 def test_matmul_output_is_the_integer_sum(ops, ty, M, N, K):
     import torch
@@ -81,7 +81,7 @@ def test_matmul_output_is_the_integer_sum(ops, ty, M, N, K):
     assert np.array_equal(y, want.astype(np.float32))
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 130])
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 130, 390])
 @pytest.mark.parametrize("N,K", CASES)
 def test_q4k_min_term_is_the_integer_sum(ops, M, N, K):
     """d = 0, dmin = 1: the output is minus sum_blocks sum_j m_j sum_i a_ij"""
