@@ -364,8 +364,8 @@ def main():
                    "sequences_in_flight": 1, "kv_cache": r["kv_cache"]},
         "e2e": {"value": r["e2e_value"], "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "roofline": r["roofline"], "cpu_baseline": None,
-        "prefill_tok_s": r["prefill_tok_s"], "decode_batch8_tok_s": r["decode_batch8_tok_s"],
-        "single_sequence_tok_s": r["value"],
+        "prefill_tok_s": r["prefill_tok_s"], "prefill_ubatch2048_tok_s": r["prefill_ub2048_tok_s"],
+        "decode_batch8_tok_s": r["decode_batch8_tok_s"], "single_sequence_tok_s": r["value"],
         "decode_weight_stream_frac_of_hbm_peak": r["weight_stream_frac"],
     }
     if not args.no_cpu:
@@ -378,10 +378,12 @@ def main():
         r3 = bench_single(args, dict(WORKLOADS["cfg3"]), local, full=False, steps=k)
         out.update({"cfg3_decode_tok_s": r3["value"], "cfg3_e2e_tok_s": r3["e2e_value"],
                     "cfg3_single_sequence_tok_s": r3["value"], "cfg3_prefill_tok_s": r3["prefill_tok_s"],
+                    "cfg3_prefill_ubatch2048_tok_s": r3["prefill_ub2048_tok_s"],
                     "cfg3_gemv_frac_of_hbm_peak": r3["roofline"]["frac"], "cfg3_workload": r3["workload"]})
         r4 = bench_single(args, dict(WORKLOADS["cfg4"]), local, full=False, steps=k)
         out.update({"cfg4_decode_tok_s": r4["value"], "cfg4_e2e_tok_s": r4["e2e_value"],
-                    "cfg4_prefill_tok_s": r4["prefill_tok_s"], "cfg4_decode_batch8_tok_s": r4["decode_batch8_tok_s"],
+                    "cfg4_prefill_tok_s": r4["prefill_tok_s"], "cfg4_prefill_ubatch2048_tok_s": r4["prefill_ub2048_tok_s"],
+                    "cfg4_decode_batch8_tok_s": r4["decode_batch8_tok_s"],
                     "cfg4_active_bytes_frac_of_hbm_peak": r4["weight_stream_frac_active"], "cfg4_workload": r4["workload"]})
         if not args.no_cpu:
             out["cfg1_gpu_vs_cpu"] = cfg1_timed_cpu_leg(local)
@@ -407,13 +409,14 @@ def bench_single(args, w, local, full=True, steps=None):
     n_seq = 8
     ids, names = {"f16": 1, "q4_0": 2, "q8_0": 8}, {1: "f16", 2: "q4_0", 8: "q8_0"}
     kt, vt = (1, 1) if args.kv == "auto" else [ids[t] for t in (args.kv + "-" + args.kv).split("-")[:2]]
-    st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
+    UB = 2048  # largest micro-batch the stage is sized for (the reference uses 512, and 2048 for vision models)
+    st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=UB, device=local, kv_type_k=kt, kv_type_v=vt)
     weight_bytes = st.weight_bytes()
     if args.kv == "auto" and ops.kv_types_for_model_bytes(weight_bytes) != (kt, vt):
         # the pair mesh-llm starts a model file of this size with
         kt, vt = ops.kv_types_for_model_bytes(weight_bytes)
         st.close()
-        st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
+        st = Stage(**model, n_ctx=n_ctx, n_seq=n_seq, n_ubatch=UB, device=local, kv_type_k=kt, kv_type_v=vt)
     st.generate(20251125)
     kv_label = names[kt] + "-" + names[vt]
     dev = torch.device("cuda", local)
@@ -421,25 +424,30 @@ def bench_single(args, w, local, full=True, steps=None):
 
     # ---- prefill: prompt of `prefill` uniform-random tokens in ubatches of 512 (sequence 0)
     prompt = torch.from_numpy(rng.integers(0, w["n_vocab"], w["prefill"]).astype(np.int32)).to(dev)
-    prefill_tok_s = None
+    prefill_tok_s = prefill_ub2048 = None
     nxt = torch.zeros(1, dtype=torch.int32, device=dev)
     logits = torch.empty((1, w["n_vocab"]), dtype=torch.float32, device=dev)
     if not args.no_prefill:
         # the prompt goes through twice: the first pass is the warm-up (first launches, scratch growth), the
         # second, which rewrites the same cache rows with the same values, is the timed one
-        for timed in (False, True):
+        # micro-batches of 2048 first (llama-server's --ubatch-size for vision models, launch.rs:1501-1503), then
+        # the default 512, whose cache rows the decode steps continue from
+        for ub, timed in ((UB, False), (UB, True), (512, False), (512, True)):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            for p0 in range(0, w["prefill"], 512):
-                chunk = prompt[p0:p0 + 512]
+            for p0 in range(0, w["prefill"], ub):
+                chunk = prompt[p0:p0 + ub]
                 st.forward(tokens=chunk, n_seq=1, T=chunk.numel(), pos0=p0, logits=logits, next_tokens=nxt)
             e1.record()
             torch.cuda.synchronize()
-            if timed:
-                prefill_tok_s = w["prefill"] / (e0.elapsed_time(e1) * 1e-3)
+            rate = w["prefill"] / (e0.elapsed_time(e1) * 1e-3)
+            if timed and ub == 512:
+                prefill_tok_s = rate
+            elif timed:
+                prefill_ub2048 = rate
             elif os.environ.get("B200_BENCH_VERBOSE"):
-                print(f"[bench] warm-up prefill pass: {w['prefill'] / (e0.elapsed_time(e1) * 1e-3):.0f} tok/s", file=sys.stderr)
+                print(f"[bench] warm-up prefill pass, micro-batch {ub}: {rate:.0f} tok/s", file=sys.stderr)
     pos = w["prefill"]
 
     # ---- decode, device resident: the stage feeds itself its own greedy token
@@ -541,7 +549,7 @@ def bench_single(args, w, local, full=True, steps=None):
     active = step_gemv_bytes(w, 0, w["n_layer"], True, 1)  # bytes one token touches (experts: the selected ones)
     return {
         "value": value, "ms_per_step": ms / steps, "e2e_value": e2e_value, "gpu_launches": int(gpu_launches),
-        "prefill_tok_s": prefill_tok_s, "decode_batch8_tok_s": b8, "roofline": roofline, "clocks": clocks,
+        "prefill_tok_s": prefill_tok_s, "prefill_ub2048_tok_s": prefill_ub2048, "decode_batch8_tok_s": b8, "roofline": roofline, "clocks": clocks,
         "weight_bytes": weight_bytes, "kv_cache": kv_label,
         "weight_stream_frac": None if w.get("n_expert", 0) else (weight_bytes / (ms / steps * 1e-3) / 1e9) / peak,
         "weight_stream_frac_active": (active / (ms / steps * 1e-3) / 1e9) / peak,
