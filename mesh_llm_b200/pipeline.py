@@ -508,22 +508,32 @@ def bench_pipeline(args, w, metric, rank, world, local):
     steps, warm = args.steps, max(3, args.warmup)
     r = run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=True)
     extra = {}
+    if not getattr(args, "no_extras", False) and not getattr(args, "balance", False) and not args.layers:
+        # the same workload with the layers split by weight bytes (the last stage also holds the output head)
+        import copy
+
+        args_b = copy.copy(args)
+        args_b.balance = True
+        rb = run_pipeline(args_b, w, rank, world, local, pg_fwd, pg_tok, max(8, min(steps, 16)), 3, full=False)
+        extra.update({"balanced_split_decode_tok_s": rb["value"], "balanced_split_e2e_tok_s": rb["e2e_value"],
+                      "balanced_split": rb["split"], "balanced_split_tokens_match_single_stage": rb["tokens_match_single_stage"]})
     if not getattr(args, "no_extras", False) and args.workload == "cfg2" and not args.layers:
         # the 70B shape over the same N stages, in the same run
         w3 = dict(WORKLOADS["cfg3"])
         r3 = run_pipeline(args, w3, rank, world, local, pg_fwd, pg_tok, max(8, min(steps, 16)), 3, full=False)
-        extra = {"cfg3_decode_tok_s": r3["value"], "cfg3_e2e_tok_s": r3["e2e_value"],
+        extra.update({"cfg3_decode_tok_s": r3["value"], "cfg3_e2e_tok_s": r3["e2e_value"],
                  "cfg3_single_sequence_tok_s": r3["single_sequence_tok_s"], "cfg3_prefill_tok_s": r3["prefill_tok_s"],
                  "cfg3_tokens_match_single_stage": r3["tokens_match_single_stage"],
                  "cfg3_gemv_frac_of_hbm_peak": r3["roofline"]["frac"],
                  "cfg3_workload": f"{w3['name']} ({w3['n_layer']} layers) over {world} stages, {world} sequences in flight, "
-                                  f"prefill {w3['prefill']}, decode at context {w3['prefill']}+"}
+                                  f"prefill {w3['prefill']}, decode at context {w3['prefill']}+"})
     cpu = None
     if rank == 0 and not args.no_cpu:
         v, cores, sample = cpu_decode_sample(w)
         cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
     h = w["n_embd"]
-    bad = r["tokens_match_single_stage"] is False or extra.get("cfg3_tokens_match_single_stage") is False
+    bad = (r["tokens_match_single_stage"] is False or extra.get("cfg3_tokens_match_single_stage") is False or
+           extra.get("balanced_split_tokens_match_single_stage") is False)
     if rank == 0:
         out = {
             "metric": metric, "value": r["value"], "unit": "tok/s", "n_gpus": world, "steps": steps,
