@@ -60,29 +60,16 @@ def row_errs(got, ref):
     return np.abs(np.asarray(got, np.float64) - ref).max(-1) / np.abs(ref).max()
 
 
-def check_layer_rows(got, ref, what):
-    """Rows whose Q8 codes all agree with the oracle's match to ~1e-7.  Inside a layer the
-    activations are re-quantised twice (attention output, SwiGLU output); a value that sits within
-    an f32 rounding error of a .5 tie takes the neighbouring int8 code when the sum that produced
-    it was accumulated in another order (online softmax against two-pass, lane-partial sums against
-    a sequential loop), and that moves the whole output row by about amax / (127 rms sqrt(K)) --
-    a few 1e-3 at the toy widths used here, below 1e-3 at the widths of the real models.  So: the
-    typical row must be (near) exact, no row may be off by more than 1e-2, and rows beyond 1e-3
-    must be a minority."""
-    e = row_errs(got, ref)
-    flipped = e > 1e-3
-    assert np.median(e) <= 1e-5, (what, e)
-    assert e.max() <= 1e-2, (what, e)
-    assert flipped.sum() <= max(1, len(e) // 3), (what, e)
-    return e.max(), int(flipped.sum())
-
-
 @pytest.mark.parametrize("cfg", [DENSE, LLAMA, MOE], ids=["qwen2-dense", "llama-dense", "qwen3-moe"])
 def test_every_layer_output_matches_given_the_same_input(cfg):
-    """Layer-by-layer parity: each layer gets the oracle's own input for that layer (prefill of
-    19 tokens, then one decode step on the same KV cache).  Feeding identical inputs keeps the
-    comparison about one layer's arithmetic."""
-    import torch
+    """Layer-by-layer parity at the small widths, with the strict bound: each layer gets the oracle's own
+    input (prefill of 19 tokens, then one decode step on the same KV cache) and is compared segment by
+    segment -- every stretch between two re-quantisation points within 1e-3 of max |ref| on every row,
+    with the segment's input shared exactly -- and end to end for the rows whose Q8 codes equal the
+    oracle's (tests/test_gpu_real_widths.py does the same at the widths of the benchmark configurations;
+    tests/layer_oracle.py says why a single differing code moves a row by more than the bound)."""
+    from layer_oracle import LayerOracle
+    from test_gpu_real_widths import check_layer
 
     full = orc.Model(**cfg)
     full.generate(11)
@@ -92,22 +79,20 @@ def test_every_layer_output_matches_given_the_same_input(cfg):
     h_pre, h_dec = emb[:19], emb[19:]
     worst, flips = 0.0, 0
     for l in range(cfg["n_layer"]):
-        om, st = _load_range(cfg, full, l, l + 1, n_ubatch=32)
-        ref_pre, _ = om.forward(hidden_in=h_pre)
-        ref_dec, _ = om.forward(hidden_in=h_dec, pos0=19)
-        got_pre, _, _ = st.forward(hidden_in=torch.from_numpy(h_pre).cuda())
-        got_dec, _, _ = st.forward(hidden_in=torch.from_numpy(h_dec).cuda(), pos0=19)
-        for got, ref, what in ((got_pre, ref_pre, f"layer {l} prefill"), (got_dec, ref_dec, f"layer {l} decode")):
-            w, f = check_layer_rows(got.cpu().numpy(), ref, what)
-            worst, flips = max(worst, w), flips + f
-        h_pre, h_dec = ref_pre, ref_dec
+        _, st = _load_range(cfg, full, l, l + 1, n_ubatch=32)
+        L = LayerOracle(full, cfg, l)
+        h_pre, a, f, _ = check_layer("small", f"layer {l} prefill", cfg, L, st, h_pre, 0)
+        h_dec, a2, f2, _ = check_layer("small", f"layer {l} decode", cfg, L, st, h_dec, 19)
+        worst, flips = max(worst, a, a2), flips + f + f2
         st.close()
     # output head on the oracle's final hidden state: one quantiser (reproducible), so strict
     om, st = _load_range(cfg, full, cfg["n_layer"], cfg["n_layer"], out=True, n_ubatch=32)
     _, ref = om.forward(hidden_in=h_pre)
+    import torch
+
     _, lg, _ = st.forward(hidden_in=torch.from_numpy(h_pre).cuda(), all_logits=True)
     assert rel_err(lg.cpu().numpy(), ref) <= 1e-3
-    print(f"worst row error {worst:.2e}, rows with a flipped code {flips}")
+    print(f"worst segment row error {worst:.2e}, rows with a code other than the oracle's {flips}")
 
 
 @pytest.mark.parametrize("cfg", [DENSE, LLAMA, MOE], ids=["qwen2-dense", "llama-dense", "qwen3-moe"])
