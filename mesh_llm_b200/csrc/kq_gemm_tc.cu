@@ -982,7 +982,7 @@ b200_status make_weight_map(CUtensorMap *map, const uint8_t *W, int64_t N, int64
 } // namespace
 
 // Generic tiled tensor map for other kernels (the type lives in <cuda.h>; callers pass 128 bytes).
-// elem_bytes 1 or 2; swizzle128 selects the 128-byte swizzle (inner box extent <= 128 bytes).
+// elem_bytes 1, 2 or 8; swizzle128 selects the 128-byte swizzle (inner box extent <= 128 bytes).
 b200_status kq_tmap_encode(void *map128, int elem_bytes, int rank, const void *base, const uint64_t *dims,
                            const uint64_t *strides_bytes, const uint32_t *box, int swizzle128) {
     static EncodeTiledFn encode = nullptr;
@@ -1001,7 +1001,7 @@ b200_status kq_tmap_encode(void *map128, int elem_bytes, int rank, const void *b
         es[i] = 1;
         if (i + 1 < rank) sb[i] = strides_bytes[i];
     }
-    const CUresult rc = encode((CUtensorMap *)map128, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+    const CUresult rc = encode((CUtensorMap *)map128, elem_bytes == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT64 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
                                (cuuint32_t)rank, const_cast<void *>(base), d, sb, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
