@@ -25,12 +25,24 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const float *x, c
                                                                int E, int h, int k, const uint8_t *mask, float *rl,
                                                                int32_t *ids, float *wts, int8_t *q, float *d, int16_t *bs,
                                                                unsigned int *counters) {
-    KQ_PDL_ENTER();
+    KQ_PDL_TRIGGER();
     extern __shared__ __align__(16) float xn[]; // the normalised row
     __shared__ double part[8];
     __shared__ float s_scale;
     __shared__ int s_last;
     const int row = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // The router's weights do not depend on the kernel before: the first 2048 of this warp's first expert
+    // row are requested before the dependency wait and fly during the norm.
+    constexpr int PRE = 16;
+    float4 wpre[PRE];
+    const int e_first = blockIdx.x * 8 + warp, n4 = h / 4;
+    if (e_first < E) {
+        const float4 *wr = reinterpret_cast<const float4 *>(Wr + (int64_t)e_first * h);
+#pragma unroll
+        for (int j = 0; j < PRE; j++)
+            if (lane + 32 * j < n4) wpre[j] = __ldg(wr + lane + 32 * j);
+    }
+    KQ_PDL_WAIT();
     const float *xr = x + (int64_t)row * h;
     double ss = 0.0; // in double, so that the scale does not depend on the order of the reduction
     for (int i = tid * 4; i < h; i += 1024) {
@@ -64,12 +76,21 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const float *x, c
         }
     }
     __syncthreads();
-    for (int e = blockIdx.x * 8 + warp; e < E; e += gridDim.x * 8) { // one warp per expert
+    for (int e = e_first; e < E; e += gridDim.x * 8) { // one warp per expert
         const float4 *wr = reinterpret_cast<const float4 *>(Wr + (int64_t)e * h);
         const float4 *xv = reinterpret_cast<const float4 *>(xn);
         float acc = 0.f;
-        const int n4 = h / 4;
-        for (int i0 = lane; i0 < n4; i0 += 32 * 8) { // eight loads in flight per lane; the sum keeps its order
+        int i0 = lane;
+        if (e == e_first) { // the part requested ahead; the sum keeps its order
+#pragma unroll
+            for (int j = 0; j < PRE; j++)
+                if (lane + 32 * j < n4) {
+                    const float4 b = xv[lane + 32 * j];
+                    acc += wpre[j].x * b.x + wpre[j].y * b.y + wpre[j].z * b.z + wpre[j].w * b.w;
+                }
+            i0 = lane + 32 * PRE;
+        }
+        for (; i0 < n4; i0 += 32 * 8) { // eight loads in flight per lane
             float4 a[8];
 #pragma unroll
             for (int j = 0; j < 8; j++)
