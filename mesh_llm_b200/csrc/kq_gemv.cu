@@ -139,6 +139,9 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                             sch[r] = scp[8 * h + 4 + cc];
                             dw[r] = kq_h2f(*reinterpret_cast<const uint16_t *>(rp[r] + qa.d));
                         }
+                        uint32_t vl[R][4], vh[R][4]; // the six-bit codes, assembled once for all tokens
+#pragma unroll
+                        for (int r = 0; r < R; r++) q6k_lane_codes(ql[r], qh[r], cc, vl[r], vh[r]);
 #pragma unroll
                         for (int m = 0; m < M; m++) {
                             const int8_t *a = aq + (int64_t)m * p.K + blk * 256 + e_lo;
@@ -149,8 +152,7 @@ __global__ void __launch_bounds__(128) gemv_kernel(const GemvParams p) {
                             const int bl = s16[0], bh = s16[4];
 #pragma unroll
                             for (int r = 0; r < R; r++) {
-                                const int isum =
-                                    q6k_lane_ints(ql[r], qh[r], cc, scl[r], sch[r], alo, ahi, bl, bh);
+                                const int isum = q6k_lane_dot(vl[r], vh[r], scl[r], sch[r], alo, ahi, bl, bh);
                                 acc[r][m] = fmaf(dw[r] * da, (float)isum, acc[r][m]);
                             }
                         }

@@ -817,11 +817,14 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
     __syncthreads();
     TRACE_MARK(3);
     if (count <= 0) return;
-    if constexpr (M > 2) {
+    if constexpr (M > 2 && TYPE == B200_TYPE_Q4_K) {
         mma_units<TYPE, M>(p, smem, act_tok, act_q, act_s, ring, ring_addr, bar_addr, iss, count, begin, unit, n_units, total,
                            &s_abort);
         return;
     }
+    // Q6_K with 3 or 4 tokens takes the loop below: one lane per block against all staged tokens, the block
+    // decoded once; rows x tokens = 16 partial sums per unit is what a line of the fix-up scratch holds
+    static_assert(M <= 2 || TYPE == B200_TYPE_Q4_K || F::ROWS * M <= 16, "a unit's partial sums must fit one line of the fix-up scratch");
 
     float acc[M];
 #pragma unroll
@@ -916,7 +919,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                     for (int m = 0; m < M; m++) {
                         const float up = __shfl_down_sync(0xffffffffu, v[m], 16); // same row of the up matrix
                         const int row = row0 + rs;
-                        if (t == 0 && rs < F::ROWS / 2 && row < p.seg[0].n_rows) {
+                        if (t == 0 && rs < F::ROWS / 2 && row < p.seg[0].n_rows && (M <= 2 || m < p.m_actual)) {
                             float gt = v[m], ut = up;
                             if (p.seg[0].bias) gt += p.seg[0].bias[row];
                             if (p.seg[1].bias) ut += p.seg[1].bias[row];
@@ -929,6 +932,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                     if (row < sg.n_rows) {
 #pragma unroll
                         for (int m = 0; m < M; m++) {
+                            if (M > 2 && m >= p.m_actual) continue; // a padding token
                             float x = v[m];
                             if (sg.bias) x += sg.bias[row];
                             if (p.residual) x += ld_act1<FUSED>(p.residual + (int64_t)m * sg.ldy + row);
@@ -1281,9 +1285,32 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
         // It stages 8 tokens when they fit in shared memory next to the ring, else 4 at a time (the
         // matrix is then streamed once per group of 4 tokens).
         if ((prep && prep->x) || env_int2("B200_GEMV_MMA", 1) == 0) return B200_ERR_UNSUPPORTED;
-        for (int i = 0; i < nseg; i++)
-            if (segs[i].type != B200_TYPE_Q4_K || ((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;
+        bool all4 = true, all6 = true;
+        for (int i = 0; i < nseg; i++) {
+            if (((uintptr_t)segs[i].W & 15) != 0) return B200_ERR_UNSUPPORTED;
+            all4 = all4 && segs[i].type == B200_TYPE_Q4_K;
+            all6 = all6 && segs[i].type == B200_TYPE_Q6_K;
+        }
         if ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0) return B200_ERR_UNSUPPORTED;
+        if (all6 && !swiglu_pairs && env_int2("B200_GEMV_Q6_BATCH", 1)) {
+            // Q6_K: the streaming kernel's dp4a form with four tokens staged, the matrix streamed once per
+            // group of four
+            const int64_t nb6 = K / 256;
+            for (int m0 = 0; m0 < M; m0 += 4) {
+                KqGemvSeg sh[3];
+                for (int i = 0; i < nseg; i++) {
+                    sh[i] = segs[i];
+                    sh[i].y = segs[i].y + (int64_t)m0 * segs[i].ldy;
+                }
+                const int mc = M - m0 < 4 ? M - m0 : 4;
+                const b200_status rc = launch_block<B200_TYPE_Q6_K, 4>(sh, nseg, q + (int64_t)m0 * K, d + m0 * nb6, bs + m0 * nb6 * 16, K,
+                                                                       residual ? residual + (int64_t)m0 * segs[0].ldy : nullptr, 0,
+                                                                       nullptr, st, mc);
+                if (rc != B200_OK) return m0 == 0 ? rc : B200_ERR_INVALID;
+            }
+            return B200_OK;
+        }
+        if (!all4) return B200_ERR_UNSUPPORTED;
         if (M > 4) {
             const b200_status rc = launch_block<B200_TYPE_Q4_K, 8>(segs, nseg, q, d, bs, K, residual, swiglu_pairs, nullptr, st, M);
             if (rc != B200_ERR_UNSUPPORTED) return rc;

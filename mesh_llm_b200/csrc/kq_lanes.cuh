@@ -58,6 +58,32 @@ static __device__ __forceinline__ void q4k_lane_ints(const uint4 &w, const Q4Sca
 // ql = the lane's 16 low-nibble bytes (chunk c of 8, half h = c >> 2, cc = c & 3); qh = the 16
 // bytes of 2-bit highs that cover the same 16 positions; the lane's low nibbles are elements
 // 128h + 16cc .. +15 and its high nibbles elements 128h + 64 + 16cc .. +15.
+// the lane's 32 six-bit codes, assembled once per weight row: vl = four words of the low-nibble elements
+// (128h + 16cc .. +15), vh = four words of the high-nibble elements (128h + 64 + 16cc .. +15)
+static __device__ __forceinline__ void q6k_lane_codes(const uint4 &ql, const uint4 &qh, int cc, uint32_t (&vl)[4],
+                                                      uint32_t (&vh)[4]) {
+    const int s_lo = 2 * (cc >> 1), s_hi = 4 + s_lo;
+    const uint32_t w[4] = {ql.x, ql.y, ql.z, ql.w}, h[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        vl[i] = (w[i] & 0x0F0F0F0Fu) | (((h[i] >> s_lo) & 0x03030303u) << 4);
+        vh[i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | (((h[i] >> s_hi) & 0x03030303u) << 4);
+    }
+}
+// ... against one token's activations (the same integer as q6k_lane_ints)
+static __device__ __forceinline__ int q6k_lane_dot(const uint32_t (&vl)[4], const uint32_t (&vh)[4], int sc_lo, int sc_hi,
+                                                   const int4 &alo, const int4 &ahi, int bl, int bh) {
+    int dl = __dp4a((int)vl[0], alo.x, 0), dh = __dp4a((int)vh[0], ahi.x, 0);
+    dl = __dp4a((int)vl[1], alo.y, dl);
+    dh = __dp4a((int)vh[1], ahi.y, dh);
+    dl = __dp4a((int)vl[2], alo.z, dl);
+    dh = __dp4a((int)vh[2], ahi.z, dh);
+    dl = __dp4a((int)vl[3], alo.w, dl);
+    dh = __dp4a((int)vh[3], ahi.w, dh);
+    // codes are stored with +32 bias: sum (q-32) a = sum q a - 32 sum a
+    return sc_lo * (dl - 32 * bl) + sc_hi * (dh - 32 * bh);
+}
+
 static __device__ __forceinline__ int q6k_lane_ints(const uint4 &ql, const uint4 &qh, int cc, int sc_lo,
                                              int sc_hi, const int4 &alo, const int4 &ahi, int bl,
                                              int bh) {
