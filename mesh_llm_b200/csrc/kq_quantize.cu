@@ -16,6 +16,29 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float *x, int64
     kq_quantize_block_warp(v, lane, q + blk * 256, d + blk, bs + blk * 16);
 }
 
+// SwiGLU and the Q8 quantiser of its result in one pass (the input of the down projection in a prefill): one warp
+// per 256-element block, lane l on elements 8l .. 8l+7; y (f32, may alias g) is written when it is not null.
+// Same expression and same quantiser as the separate kernels, so codes and values are theirs.
+__global__ void __launch_bounds__(128) swiglu_quantize_kernel(const float *g, const float *u, int64_t nblocks, float *y, int8_t *q,
+                                                              float *d, int16_t *bs) {
+    KQ_PDL_ENTER();
+    const int lane = threadIdx.x & 31;
+    const int64_t blk = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (blk >= nblocks) return;
+    const int64_t o = blk * 256 + lane * 8;
+    const float4 g0 = *reinterpret_cast<const float4 *>(g + o), g1 = *reinterpret_cast<const float4 *>(g + o + 4);
+    const float4 u0 = *reinterpret_cast<const float4 *>(u + o), u1 = *reinterpret_cast<const float4 *>(u + o + 4);
+    const float a[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, b[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = (a[i] / (1.0f + expf(-a[i]))) * b[i];
+    if (y) {
+        *reinterpret_cast<float4 *>(y + o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(y + o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    kq_quantize_block_warp(v, lane, q + blk * 256, d + blk, bs + blk * 16);
+}
+
 // RMSNorm (x * rsqrt(mean(x^2) + eps) * w) with optional f32 output and optional Q8 output.
 // One CTA of 256 threads per row; h is a multiple of 256 when q != null.
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x,
@@ -239,6 +262,18 @@ b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, fl
     KQ_REQUIRE(!q || h % 256 == 0, "rms_norm: Q8 output needs h %% 256 == 0");
     KQ_REQUIRE(y || q, "rms_norm: no output");
     kq_launch(rms_norm_kernel, (unsigned)T, 256, 0, st, x, w, (int)h, eps, y, q, d, bs, x_row_stride ? x_row_stride : h);
+    KQ_COUNT_LAUNCH();
+    KQ_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// y = silu(g) * u for [M][K] and its Q8 form; K a multiple of 256, pointers 16-byte aligned; y may be null or alias g
+b200_status kq_swiglu_quantize(const float *g, const float *u, int64_t M, int64_t K, float *y, int8_t *q, float *d, int16_t *bs,
+                               cudaStream_t st) {
+    KQ_REQUIRE(M > 0 && K > 0 && K % 256 == 0, "swiglu_quantize: K must be a multiple of 256");
+    KQ_REQUIRE((((uintptr_t)g | (uintptr_t)u | (uintptr_t)y | (uintptr_t)q) & 15) == 0, "swiglu_quantize: alignment");
+    const int64_t nblocks = M * (K / 256);
+    kq_launch(swiglu_quantize_kernel, (unsigned)kq_div_up(nblocks, 4), 128, 0, st, g, u, nblocks, y, q, d, bs);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
     return B200_OK;

@@ -22,6 +22,8 @@ b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, fl
 b200_status kq_moe_router_fused(const float *x, const float *norm_w, float eps, const float *router_w, int rows, int E, int h,
                                 int k, const uint8_t *mask, float *rl, int32_t *ids, float *wts, int8_t *q, float *d,
                                 int16_t *bs, unsigned int *counters, cudaStream_t st);
+b200_status kq_swiglu_quantize(const float *g, const float *u, int64_t M, int64_t K, float *y, int8_t *q, float *d, int16_t *bs,
+                               cudaStream_t st);
 b200_status kq_moe_gate_up(uint32_t type, const uint8_t *Wg, const uint8_t *Wu, int64_t expert_stride, const int8_t *aq,
                            const float *ad, const int16_t *abs16, const int32_t *ids, int pairs, int ku, int K, int fe, float *hp,
                            cudaStream_t st);
@@ -385,8 +387,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
                                               pairs, E, fe, h, st->hp, st->moe_sorted, s));
                 KQ_TRY(kq_launch_gemm_grouped(L.up_e->type, (const uint8_t *)L.up_e->dev, gstride, st->aq, st->ad, st->abs16, ku,
                                               pairs, E, fe, h, st->hp2, st->moe_sorted, s));
-                KQ_TRY(b200_swiglu(st->hp, st->hp2, (int64_t)pairs * fe, st->hp, s));
-                KQ_TRY(b200_quantize_act(st->hp, pairs, fe, st->aq, st->ad, st->abs16, s));
+                KQ_TRY(kq_swiglu_quantize(st->hp, st->hp2, pairs, fe, st->hp, st->aq, st->ad, st->abs16, s));
                 KQ_TRY(kq_launch_gemm_grouped(L.down_e->type, (const uint8_t *)L.down_e->dev, dstride, st->aq, st->ad, st->abs16, 1,
                                               pairs, E, h, fe, st->yp, st->moe_sorted, s));
             } else {
@@ -429,14 +430,15 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             } else {
                 GEMV_(mm(st, L.gate, rows, st->g, nullptr, nullptr, s));
                 GEMV_(mm(st, L.up, rows, st->u, nullptr, nullptr, s));
-                OTHER_(b200_swiglu(st->g, st->u, (int64_t)rows * c.n_ff, st->g, s));
+                // SwiGLU and the Q8 form the down projection reads, in one pass
+                OTHER_(kq_swiglu_quantize(st->g, st->u, rows, c.n_ff, st->g, st->aq, st->ad, st->abs16, s));
             }
             if (fuse) {
                 KqGemvSeg sd = {(const uint8_t *)L.down->dev, L.down->type, h, xout, nullptr, h, 0};
                 KqActPrep pr = {st->g, nullptr, 0.f, 0};
                 GEMV_(kq_launch_gemv(&sd, 1, st->aq, st->ad, st->abs16, rows, c.n_ff, st->x, 0, nullptr, s, &pr));
             } else {
-                OTHER_(b200_quantize_act(st->g, rows, c.n_ff, st->aq, st->ad, st->abs16, s));
+                if (rows <= 8) OTHER_(b200_quantize_act(st->g, rows, c.n_ff, st->aq, st->ad, st->abs16, s));
                 GEMV_(mm(st, L.down, rows, xout, nullptr, st->x, s)); // x = x + Wdown.act
             }
         }
