@@ -180,7 +180,7 @@ __device__ __forceinline__ void unpack_q4_task(const uint4 &hdr, const uint4 &w,
         const uint32_t m_lo = hdr.z & 0x3F3F3F3Fu, m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
         const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
         dw_s[r] = dd.x;
-        dmin_s[r] = dd.y;
+        dmin_s[r] = -dd.y; // kept negated: the epilogue subtracts the min term with one fused multiply-add
         __half mh[16]; // m_j against both sums of 16 of sub-block j
 #pragma unroll
         for (int j = 0; j < 8; j++) {
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_tc_kernel(const GemmParams p
                     // y = fma(da, t, y): the arithmetic of the scalar form, two columns per instruction
                     const ulonglong2 dw4 = *reinterpret_cast<const ulonglong2 *>(&dw_s[col + i4]);
                     const ulonglong2 dm4 = *reinterpret_cast<const ulonglong2 *>(&dmin_s[col + i4]);
-                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x ^ 0x8000000080000000ull, dm4.y ^ 0x8000000080000000ull};
+                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x, dm4.y}; // -dmin
 #pragma unroll
                     for (int k = 0; k < 2; k++) {
                         const int i = i4 + 2 * k;
@@ -823,7 +823,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemm_planes_kernel(const PlanesPa
                 for (int i4 = 0; i4 < 16; i4 += 4) {
                     const ulonglong2 dw4 = *reinterpret_cast<const ulonglong2 *>(&dw_s[col + i4]);
                     const ulonglong2 dm4 = *reinterpret_cast<const ulonglong2 *>(&dmin_s[col + i4]);
-                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x ^ 0x8000000080000000ull, dm4.y ^ 0x8000000080000000ull};
+                    const uint64_t dwp[2] = {dw4.x, dw4.y}, dmp[2] = {dm4.x, dm4.y}; // -dmin
 #pragma unroll
                     for (int k = 0; k < 2; k++) {
                         const int i = i4 + 2 * k;
