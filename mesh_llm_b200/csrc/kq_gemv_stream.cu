@@ -91,6 +91,7 @@ struct StreamParams {
     // of one bulk copy per row.  use_tma == 0: the maps are unset and the rows are copied one by one.
     alignas(64) CUtensorMap map[3];
     int32_t use_tma;
+    int32_t pf_mode; // L2 prefetch before the dependency wait: 1 norm weights, 2 and the biases
     KqGemvSeg seg[3];
     int32_t rg_end[3];
     int32_t nseg, n_rg, nb, K, nsteps, swiglu;
@@ -655,6 +656,24 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
             rest_posted = true;
         }
     };
+    // The norm weights are read once per step, so they come from HBM; they do not depend on the kernel before.
+    // Each CTA pulls its share of their lines into L2 now (a line or two), so that after the wait all CTAs read
+    // them from L2.
+    if (!FUSED && p.pf_mode >= 1 && p.x && p.do_norm && p.norm_w && threadIdx.x == 0) {
+        const int lines = (p.K * 4 + 127) / 128;
+        for (int ln = blockIdx.x; ln < lines; ln += gridDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(p.norm_w) + (size_t)ln * 128));
+    }
+    // ... and so are the biases, which the last instructions of a row group would otherwise fetch from HBM
+    if (!FUSED && p.pf_mode >= 2 && threadIdx.x == 32) {
+        const int nsg = p.swiglu ? 2 : p.nseg;
+        for (int i = 0; i < nsg; i++) {
+            if (!p.seg[i].bias) continue;
+            const int lines = (p.seg[i].n_rows * 4 + 127) / 128;
+            for (int ln = blockIdx.x; ln < lines; ln += gridDim.x)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(p.seg[i].bias) + (size_t)ln * 128));
+        }
+    }
     TRACE_MARK(1);
     if (FUSED && fx.phase > 0) fused_grid_wait(fx.target, &s_abort); // the phase before this one is complete everywhere
     else KQ_PDL_WAIT(); // activations (and the output buffer) belong to earlier kernels up to here
@@ -1058,6 +1077,9 @@ b200_status make_maps(StreamParams &p, int nseg_all) {
     using F = Fmt<TYPE>;
     static int on = -1;
     if (on < 0) on = env_int2("B200_GEMV_TMA", 1);
+    static int pf = -1;
+    if (pf < 0) pf = env_int2("B200_GEMV_PREFETCH", 2);
+    p.pf_mode = pf;
     p.use_tma = 0;
     memset(p.map, 0, sizeof(p.map));
     const int box_rows = p.swiglu ? F::ROWS / 2 : F::ROWS;
