@@ -10,6 +10,7 @@
 
 #include <cuda.h> // CUtensorMap
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <map>
@@ -48,8 +49,34 @@ __device__ __forceinline__ uint8_t *sw_elem(uint8_t *base, int row, int dim) {
     return base + box * BOX_BYTES + sw_off(row, off >> 4) + (off & 15);
 }
 
-template <int HD, int G>
-__global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+constexpr int QH_PITCH = 128 * 2 + 16; // bytes per row of the f16 copy of q: eight rows fall on eight bank groups
+
+// MMA = false: 4 * G warps, warp (ti, g) serves query head g on rows ti*32 .. ti*32+31 of a chunk with scalar
+// FMAs (lane = row).  MMA = true (head_dim 128, G <= 8): eight warps, one per head for everything that is per
+// head; the first four compute: warp ti takes the same 32 rows for ALL
+// G heads on the tensor cores: S = Q K^T as mma.m16n8k16 with the heads as the 16 rows of the tile (K
+// fragments by ldmatrix out of the swizzled chunk), softmax on the accumulator fragments, and the values
+// as O^T = V^T P^T, for which the probabilities are already in the B-fragment layout and V comes in by
+// ldmatrix.trans -- dims are the rows of that product, so none of its tile is wasted.  q and the probabilities
+// enter as hi + lo pairs of f16 (two MMAs each), K and V are f16 as stored, accumulation is f32: the result
+// agrees with the f32 scalar form to rounding of the sums.
+template <int HD, int G, bool MMA>
+__global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                                                               const __grid_constant__ CUtensorMap vmap,
                                                               const float *q, const float *k_new,
                                                               const float *v_new, __half *kc, __half *vc,
@@ -58,7 +85,8 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
                                                               RopeTab tab, float *out, float *part_o, float *part_ml,
                                                               int *counters, KqKvTypes kvt) {
     KQ_PDL_TRIGGER();
-    constexpr int DPL = HD / 32, HALF = HD / 2, NBOX = HD / 64, NT = 128 * G;
+    constexpr int DPL = HD / 32, HALF = HD / 2, NBOX = HD / 64, NT = MMA ? 256 : 128 * G;
+    static_assert(!MMA || (HD == 128 && G <= 8), "the tensor-core form is built for head_dim 128 and up to 8 heads per KV head");
     extern __shared__ __align__(1024) uint8_t dsm_raw[];
     uint8_t *dsm = dsm_raw + ((1024u - (smem_u32(dsm_raw) & 1023u)) & 1023u); // swizzled boxes start on 1 KB
     uint8_t *k_s = dsm, *v_s = dsm + NBOX * BOX_BYTES;
@@ -68,6 +96,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     uint8_t *kraw_s = dsm + 2 * NBOX * BOX_BYTES + 4 * G * HD * (int)sizeof(float); // raw rows of a quantised chunk
     uint8_t *vraw_s = kraw_s + (kq ? ROWS_PER_CTA * k_row : 0);
     __shared__ float q_s[G][HD];
+    __shared__ __align__(16) uint8_t qh_s[MMA ? 2 * 16 * QH_PITCH : 16]; // MMA: q as f16 hi + lo parts, 16 rows each (rows >= G zero)
     __shared__ float p_s[4 * G][32];
     __shared__ float ml_s[4][G][2];
     __shared__ float w_s[G][64];
@@ -77,7 +106,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     __shared__ int s_last, s_abort;
     const int kh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = warp % G, ti = warp / G;
+    const int g = MMA ? 0 : warp % G, ti = MMA ? warp : warp / G;
     const int pos = pos_dev ? *pos_dev : pos_val; // written before this step started
     const int L = pos + 1;
     int chunk = (L + n_split - 1) / n_split;
@@ -95,9 +124,12 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     }
     __syncthreads();
 
-    float m = -INFINITY, l = 0.f, o[DPL];
+    float m = -INFINITY, l = 0.f, o[DPL]; // MMA: m and l belong to head lane / 4 (all four lanes of a quad hold them)
 #pragma unroll
     for (int i = 0; i < DPL; i++) o[i] = 0.f;
+    float oacc[MMA ? 8 : 1][4]; // MMA: O^T tiles: rows = dims 16 mt + lane/4 (+8), columns = heads 2 (lane%4), +1
+#pragma unroll
+    for (int i = 0; i < (MMA ? 8 : 1); i++) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
     uint32_t phase = 0;
     bool first = true;
     for (int cb = p_begin; cb < p_end || first; cb += ROWS_PER_CTA) {
@@ -134,16 +166,31 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
         }
         if (first) {
             KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
-            if (ti == 0)
-                for (int f = lane; f < HALF; f += 32) { // query head g, rotated and pre-scaled
+            if (MMA) {
+                for (int i = threadIdx.x; i < 2 * 16 * QH_PITCH / 16; i += NT) reinterpret_cast<uint4 *>(qh_s)[i] = make_uint4(0, 0, 0, 0);
+                __syncthreads();
+            }
+            for (int gg = MMA ? warp : g; gg < (MMA ? G : g + 1); gg += 8) {
+                if (!MMA && ti != 0) break;
+                for (int f = lane; f < HALF; f += 32) { // query head gg, rotated and pre-scaled
                     const float ang = (float)pos * tab.inv_freq[f];
                     const float c = cosf(ang), sn = sinf(ang);
                     const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
-                    const float *qv = q + ((int64_t)seq * n_head + kh * G + g) * HD;
+                    const float *qv = q + ((int64_t)seq * n_head + kh * G + gg) * HD;
                     const float a = qv[i0], b = qv[i1];
-                    q_s[g][i0] = (a * c - b * sn) * scale;
-                    q_s[g][i1] = (a * sn + b * c) * scale;
+                    const float r0 = (a * c - b * sn) * scale, r1 = (a * sn + b * c) * scale;
+                    if (MMA) { // q = hi + lo with both parts in f16: the products lose nothing of the f32 value that matters
+                        const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
+                        *reinterpret_cast<__half *>(qh_s + gg * QH_PITCH + i0 * 2) = h0;
+                        *reinterpret_cast<__half *>(qh_s + gg * QH_PITCH + i1 * 2) = h1;
+                        *reinterpret_cast<__half *>(qh_s + (16 + gg) * QH_PITCH + i0 * 2) = __float2half_rn(r0 - __half2float(h0));
+                        *reinterpret_cast<__half *>(qh_s + (16 + gg) * QH_PITCH + i1 * 2) = __float2half_rn(r1 - __half2float(h1));
+                    } else {
+                        q_s[gg][i0] = r0;
+                        q_s[gg][i1] = r1;
+                    }
                 }
+            }
             first = false;
         }
         if (ccnt == 0) break; // CTA-uniform: an empty slice only takes part in the combine below
@@ -232,9 +279,90 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
             }
         }
         __syncthreads();
-        // this warp's tile: rows ti*32 .. +31 of the chunk, lane = position
+        // this warp's tile: rows ti*32 .. +31 of the chunk
         const int cnt = max(0, min(32, ccnt - ti * 32));
-        if (cnt > 0) {
+        if constexpr (MMA) {
+            if (cnt > 0 && warp < 4) {
+                const int t4 = lane & 3, kb = ti * 32;
+                if (cnt < 32) { // rows of the tile past the context may hold anything: their values must not reach the MMA
+                    for (int i = lane; i < (32 - cnt) * 16; i += 32) {
+                        const int r = kb + cnt + (i >> 4), c = i & 15;
+                        *reinterpret_cast<uint4 *>(v_s + (c >> 3) * BOX_BYTES + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+                const uint32_t qh = smem_u32(qh_s), ks = smem_u32(k_s), vs = smem_u32(v_s);
+                float sacc[4][4];
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) { // 16 dims per step
+                    uint32_t qa[4], ql[4];
+                    const uint32_t qoff = ((lane & 7) + ((lane >> 3) & 1) * 8) * QH_PITCH + (16 * kk + (lane >> 4) * 8) * 2;
+                    ldsm_x4(qh + qoff, qa[0], qa[1], qa[2], qa[3]);
+                    ldsm_x4(qh + 16 * QH_PITCH + qoff, ql[0], ql[1], ql[2], ql[3]);
+#pragma unroll
+                    for (int np = 0; np < 2; np++) { // two key tiles of 8 per load
+                        const int key = kb + 8 * (2 * np + (lane >> 4)) + (lane & 7), c = 2 * kk + ((lane >> 3) & 1);
+                        uint32_t r0, r1, r2, r3;
+                        ldsm_x4(ks + (c >> 3) * BOX_BYTES + sw_off(key, c & 7), r0, r1, r2, r3);
+                        mma_f16(sacc[2 * np], qa, r0, r1);
+                        mma_f16(sacc[2 * np + 1], qa, r2, r3);
+                        mma_f16(sacc[2 * np], ql, r0, r1);
+                        mma_f16(sacc[2 * np + 1], ql, r2, r3);
+                    }
+                }
+                // softmax of head g4 over this tile's keys (this thread: keys 8 nt + 2 t4, +1)
+                float mt = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        if (8 * nt + 2 * t4 + j >= cnt) sacc[nt][j] = -INFINITY;
+                        mt = fmaxf(mt, sacc[nt][j]);
+                    }
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+                const float mn = fmaxf(m, mt); // cnt > 0: at least key 0 is finite
+                const float alpha = (m == -INFINITY) ? 0.f : expf(m - mn);
+                float rs = 0.f;
+                uint32_t pb[4], pl[4]; // probabilities as f16 pairs, hi and lo parts: the B fragments of O^T = V^T P^T
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) {
+                    const float p0 = expf(sacc[nt][0] - mn), p1 = expf(sacc[nt][1] - mn); // exp(-inf) = 0 for masked keys
+                    rs += p0 + p1;
+                    const __half2 hi = __floats2half2_rn(p0, p1);
+                    const float2 back = __half22float2(hi);
+                    pb[nt] = *reinterpret_cast<const uint32_t *>(&hi);
+                    pl[nt] = pack_h2(p0 - back.x, p1 - back.y);
+                }
+                rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+                rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+                l = l * alpha + rs;
+                m = mn;
+                // this thread's accumulator columns are heads 2 t4 and 2 t4 + 1: their factors sit in other quads
+                const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * t4) * 4), a1 = __shfl_sync(0xffffffffu, alpha, (2 * t4 + 1) * 4);
+#pragma unroll
+                for (int mt8 = 0; mt8 < 8; mt8++) {
+                    oacc[mt8][0] *= a0;
+                    oacc[mt8][1] *= a1;
+                    oacc[mt8][2] *= a0;
+                    oacc[mt8][3] *= a1;
+                }
+#pragma unroll
+                for (int ks2 = 0; ks2 < 2; ks2++) { // 16 keys per step
+                    const int key = kb + 16 * ks2 + ((lane >> 4) & 1) * 8 + (lane & 7);
+#pragma unroll
+                    for (int mt8 = 0; mt8 < 8; mt8++) { // 16 dims per tile
+                        const int c = 2 * mt8 + ((lane >> 3) & 1);
+                        uint32_t va[4];
+                        ldsm_x4_t(vs + (c >> 3) * BOX_BYTES + sw_off(key, c & 7), va[0], va[1], va[2], va[3]);
+                        mma_f16(oacc[mt8], va, pb[2 * ks2], pb[2 * ks2 + 1]);
+                        mma_f16(oacc[mt8], va, pl[2 * ks2], pl[2 * ks2 + 1]);
+                    }
+                }
+            }
+        } else if (cnt > 0) {
             const bool valid = lane < cnt;
             float sc = 0.f;
             if (valid) {
@@ -280,15 +408,34 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     }
 
     // combine the 4 tiles of each head inside the CTA (tile order)
+    if constexpr (MMA) {
+        const int g4 = lane >> 2, t4 = lane & 3;
+        if (warp < 4) {
 #pragma unroll
-    for (int i = 0; i < DPL; i++) o_s[ti][g][lane * DPL + i] = o[i];
-    if (lane == 0) {
-        ml_s[ti][g][0] = m;
-        ml_s[ti][g][1] = l;
+        for (int mt8 = 0; mt8 < 8; mt8++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int hh = 2 * t4 + (j & 1), dim = 16 * mt8 + g4 + (j >> 1) * 8;
+                if (hh < G) o_s[ti][hh][dim] = oacc[mt8][j];
+            }
+        if (t4 == 0 && g4 < G) {
+            ml_s[ti][g4][0] = m;
+            ml_s[ti][g4][1] = l;
+        }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o_s[ti][g][lane * DPL + i] = o[i];
+        if (lane == 0) {
+            ml_s[ti][g][0] = m;
+            ml_s[ti][g][1] = l;
+        }
     }
     __syncthreads();
+    // one warp per head from here on: warp g of the G * 4 (ti == 0), or the four warps taking heads in turn
+    for (int g = MMA ? warp : (ti == 0 ? warp % G : G); g < G; g += MMA ? 8 : G) {
     const int head = kh * G + g;
-    if (ti == 0) {
+    {
         float mm = -INFINITY;
         for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[w][g][0]);
         float acc[DPL], ll = 0.f;
@@ -314,6 +461,7 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
             }
         }
     }
+    }
     if (n_split == 1) return;
     // the CTA that finishes last combines the splits of its G heads (in split order) and re-arms
     // the counter for the next launch
@@ -327,7 +475,8 @@ __global__ void __launch_bounds__(128 * G) attn_decode_kernel(const __grid_const
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    if (ti == 0) {
+    for (int g = MMA ? warp : (ti == 0 ? warp % G : G); g < G; g += MMA ? 8 : G) {
+        const int head = kh * G + g;
         // splits were written by other SMs: read them through L2 (ld.cg); max / weights once per head
         for (int sp = lane; sp < n_split; sp += 32) {
             const int64_t e = (((int64_t)seq * n_head + head) * n_split + sp) * 2;
@@ -379,10 +528,25 @@ b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap,
     const size_t raw = (kvt.k != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.k, HD) : 0) +
                        (kvt.v != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.v, HD) : 0);
     const size_t smem = 2 * (HD / 64) * BOX_BYTES + (size_t)4 * G * HD * sizeof(float) + raw + 1024; // + room to align to 1 KB
+    // head_dim 128: the tensor-core form (eight warps per CTA); B200_ATTN_DECODE_MMA=0 keeps the scalar one
+    static int use_mma = -1;
+    if (use_mma < 0) {
+        const char *e = getenv("B200_ATTN_DECODE_MMA");
+        use_mma = !(e && e[0] == '0');
+    }
 #define KQ_AD(GG)                                                                                              \
+    if constexpr (HD == 128) {                                                                                 \
+        if (use_mma) {                                                                                         \
+            if (smem > 48 * 1024)                                                                              \
+                cudaFuncSetAttribute(attn_decode_kernel<HD, GG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            kq_launch(attn_decode_kernel<HD, GG, true>, grid, 256, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head,  \
+                      n_kv, seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);                 \
+            break;                                                                                             \
+        }                                                                                                      \
+    }                                                                                                          \
     if (smem > 48 * 1024)                                                                                      \
-        cudaFuncSetAttribute(attn_decode_kernel<HD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    kq_launch(attn_decode_kernel<HD, GG>, grid, 128 * GG, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, \
+        cudaFuncSetAttribute(attn_decode_kernel<HD, GG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    kq_launch(attn_decode_kernel<HD, GG, false>, grid, 128 * GG, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, \
               seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt)
     switch (G) {
     case 1: KQ_AD(1); break;

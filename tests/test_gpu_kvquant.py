@@ -167,9 +167,10 @@ def test_layer_outputs_with_a_quantised_cache(cfg, kt, vt):
 
     Batches go through the f16 tensor-core attention whatever the cache type; its 2-4e-4 error flips int8
     codes of the re-quantised attention output, which at these toy widths moves a row by 3-7e-3 (the f16
-    cache shows the same figures), so batch rows are held to 2e-2.  Decode steps compute in f32 over the
-    same cache bytes: they must be near exact unless a cache code sat on a boundary (see above), which
-    may touch a minority of them."""
+    cache shows the same figures), so batch rows are held to 2e-2.  Decode steps run their products on
+    mma.m16n8k16 too, but with q and the probabilities as hi + lo pairs of f16, i.e. to f32 accuracy over the
+    same cache bytes: they must be near exact unless a cache code sat on a boundary (see above), which may
+    touch a minority of them."""
     import torch
 
     full = orc.Model(**cfg)
@@ -198,7 +199,7 @@ def test_layer_outputs_with_a_quantised_cache(cfg, kt, vt):
         st.close()
     dec = np.array(dec)
     print(f"batch rows worst {batch_worst:.2e}; decode rows {np.array2string(dec, precision=1)}")
-    assert np.median(dec) <= 1e-4, dec
+    assert dec.max() <= 2e-2 and np.median(dec) <= 1e-4, dec
 
 
 def test_decode_equals_prefill_on_the_gpu_cache():
