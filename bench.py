@@ -317,6 +317,9 @@ def main():
                     "the two GPUs, peer-memory hand-off against send/recv; one line with the one-way latencies")
     ap.add_argument("--kv", default="f16", choices=["f16", "q8_0-q4_0", "q4_0-q4_0", "auto"],
                     help="KV-cache row types (K-V); auto = the pair mesh-llm starts a model of this size with")
+    ap.add_argument("--seqs-per-stage", type=int, default=2, help="N > 1: sequences in flight per stage (every stage still "
+                    "works on one sequence per tick at batch 1; with 1 the token's way back from the last stage to the "
+                    "first is on every tick's critical path, with 2 it is hidden)")
     ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the cfg3 / cfg4 / cfg1-against-CPU measurements "
                     "that follow the headline workload in the same run")
     ap.add_argument("--sweep", action="store_true", help="the isolated matmul sweep: all shapes x types x M")

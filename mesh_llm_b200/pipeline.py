@@ -158,8 +158,11 @@ def run_decode(stage_step, sched, rank, steps, transport, hidden_in, hidden_out,
     """Generic pipelined greedy decode.
 
     stage_step(seq, step, token_or_None, hidden_in_or_None, out) runs this rank's layers for one
-    token of `seq` and writes `out`: one of the two `hidden_out` buffers (not the last stage) or one
-    of the two `token_out` buffers (last stage).  `first_tokens[seq]` feeds step 0 on the first
+    token of `seq` and writes `out`: one of the `hidden_out` buffers (not the last stage) or one of
+    the `token_out` buffers (last stage), used in rotation.  Over a transport whose sends complete
+    only when received (send / recv), two hidden buffers are enough, and the last stage needs as many
+    token buffers as there are sequences: with more sequences than stages its tokens wait for the
+    first stage to come round to them.  `first_tokens[seq]` feeds step 0 on the first
     stage.  on_token(seq, step, token) is called on the last stage after each token, on_input(token)
     on the first stage before each token is consumed.
     """
@@ -170,7 +173,7 @@ def run_decode(stage_step, sched, rank, steps, transport, hidden_in, hidden_out,
         if w is None or w[1] >= steps:
             continue
         seq, step = w
-        slot = n & 1
+        slot = n % (len(token_out) if last else len(hidden_out))
         n += 1
         if last:
             transport.wait_slot(("t", slot))
@@ -254,7 +257,7 @@ MODEL_KEYS = ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n
 
 
 def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=True):
-    """One dense workload over `world` stages: prefill, pipelined decode with `world` sequences in flight
+    """One dense workload over `world` stages: prefill, pipelined decode with `seqs_per_stage * world` sequences in flight
     (device-timed and end to end), one sequence alone through all stages, the slowest stage's GEMV-only
     replay, and a replay of sequence 0 on a single stage holding the whole model (rank 0) whose tokens
     must equal the pipeline's.  Returns the measurements on every rank."""
@@ -275,8 +278,11 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
         layer_b = sum(gemv_bytes(N, K, ty) for l in (0, 1) for (N, K, ty) in matmuls(w, l)) / 2
         head_cost = gemv_bytes(w["n_vocab"], w["n_embd"], 14) / layer_b
     lo, hi = layer_range(w["n_layer"], world, rank, head_cost)
-    n_seq = world
-    n_ctx = w["prefill"] + 3 * (steps + warm) + 72
+    spp = max(1, int(getattr(args, "seqs_per_stage", 1)))
+    if getattr(args, "handoff", "peer") != "peer":
+        spp = 1  # rendezvous sends: a token that waits for its receiver would stall the last stage
+    n_seq = world * spp
+    n_ctx = w["prefill"] + 4 * (steps + warm) + 72
     ids, names = {"f16": 1, "q4_0": 2, "q8_0": 8}, {1: "f16", 2: "q4_0", 8: "q8_0"}
     kv = getattr(args, "kv", "f16")
     if kv == "auto":  # the pair mesh-llm starts a model file of this size with
@@ -290,7 +296,6 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
                n_ctx=n_ctx, n_seq=n_seq, n_ubatch=512, device=local, kv_type_k=kt, kv_type_v=vt)
     st.generate(20251125)
     tr = Transport(dist, rank, world, pg_fwd, pg_tok)
-    sched = Schedule(world, n_seq)
     h = w["n_embd"]
     # hand-off: peer-memory kernels unless --handoff nccl asks for send / recv
     peer = getattr(args, "handoff", "peer") == "peer"
@@ -310,6 +315,8 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
                 if o is not None:
                     o.close()
             tr_dec, big, peer = tr, None, False
+            spp, n_seq = 1, world
+    sched = Schedule(world, n_seq)
     rng = np.random.default_rng(1234)
     prompts = torch.from_numpy(rng.integers(0, w["n_vocab"], (n_seq, w["prefill"])).astype(np.int32)).to(dev)
     hid_big = torch.empty((512, h), dtype=torch.float32, device=dev)
@@ -420,6 +427,10 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
     # ---- one sequence alone through all stages: the latency-bound batch-1 figure
     k1 = max(4, steps // 2)
     t_single = timed(lambda: decode(k1, pos_base + warm + 2 * steps, first, sch=Schedule(world, 1)))
+    # ---- one sequence per stage in flight: every tick then also waits for the token's way back to the first stage
+    t_one = None
+    if spp > 1:
+        t_one = timed(lambda: decode(k1, pos_base + warm + 2 * steps + k1, first, sch=Schedule(world, world)))
     if peer:
         tr_dec.check()
         big.check()
@@ -487,6 +498,7 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
         "gpu_launches": int(launches.item()), "clocks": clocks, "n_seq": n_seq,
         "prefill_tok_s": None if args.no_prefill else n_seq * w["prefill"] / (float(t_prefill.item()) * 1e-3),
         "single_sequence_tok_s": k1 / (t_single * 1e-3),
+        "one_sequence_per_stage_tok_s": None if t_one is None else k1 * world / (t_one * 1e-3),
         "tokens_match_single_stage": None if getattr(args, "no_match", False) else bool(match.item() == 1.0),
         "tokens_compared": 1 + n_tok, "roofline": roofline, "kv_cache": names[kt] + "-" + names[vt], "peer": peer,
         "split": "weighted by bytes (output head counted)" if head_cost > 0 else "equal layer counts",
@@ -494,7 +506,8 @@ def run_pipeline(args, w, rank, world, local, pg_fwd, pg_tok, steps, warm, full=
 
 
 def bench_pipeline(args, w, metric, rank, world, local):
-    """bench.py body for N > 1: N stages, N sequences in flight, value = all tokens / max time."""
+    """bench.py body for N > 1: N stages, `--seqs-per-stage` x N sequences in flight (one sequence per stage and tick,
+    batch 1), value = all tokens / max time."""
     import torch
     import torch.distributed as dist
 
@@ -523,9 +536,10 @@ def bench_pipeline(args, w, metric, rank, world, local):
         r3 = run_pipeline(args, w3, rank, world, local, pg_fwd, pg_tok, max(8, min(steps, 16)), 3, full=False)
         extra.update({"cfg3_decode_tok_s": r3["value"], "cfg3_e2e_tok_s": r3["e2e_value"],
                  "cfg3_single_sequence_tok_s": r3["single_sequence_tok_s"], "cfg3_prefill_tok_s": r3["prefill_tok_s"],
+                 "cfg3_one_sequence_per_stage_tok_s": r3["one_sequence_per_stage_tok_s"],
                  "cfg3_tokens_match_single_stage": r3["tokens_match_single_stage"],
                  "cfg3_gemv_frac_of_hbm_peak": r3["roofline"]["frac"],
-                 "cfg3_workload": f"{w3['name']} ({w3['n_layer']} layers) over {world} stages, {world} sequences in flight, "
+                 "cfg3_workload": f"{w3['name']} ({w3['n_layer']} layers) over {world} stages, {r3['n_seq']} sequences in flight, "
                                   f"prefill {w3['prefill']}, decode at context {w3['prefill']}+"})
     cpu = None
     if rank == 0 and not args.no_cpu:
@@ -549,6 +563,7 @@ def bench_pipeline(args, w, metric, rank, world, local):
                     "d2h_bytes_per_step": 4 * r["n_seq"]},
             "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "roofline": r["roofline"], "cpu_baseline": cpu,
             "prefill_tok_s": r["prefill_tok_s"], "single_sequence_tok_s": r["single_sequence_tok_s"],
+            "one_sequence_per_stage_tok_s": r["one_sequence_per_stage_tok_s"],
             "tokens_match_single_stage": r["tokens_match_single_stage"], "tokens_compared": r["tokens_compared"],
             "handoff": "peer-memory landing rings written by the sending stage's kernels over NVLink (decode rows and "
                        "prefill micro-batches)" if r["peer"] else "torch.distributed send/recv (NCCL P2P over NVLink)",

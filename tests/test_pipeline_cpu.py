@@ -55,7 +55,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, steps, first, q):
+def _worker(rank, world, port, steps, first, q, n_seq):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     lo, hi = layer_range(N_LAYER, world, rank)
@@ -63,7 +63,7 @@ def _worker(rank, world, port, steps, first, q):
     hin = torch.zeros(1, dtype=torch.int64)
     hout = [torch.zeros(1, dtype=torch.int64) for _ in range(2)]
     tok = torch.zeros(1, dtype=torch.int64)
-    tout = [torch.zeros(1, dtype=torch.int64) for _ in range(2)]
+    tout = [torch.zeros(1, dtype=torch.int64) for _ in range(max(2, n_seq))]
     got = {}
 
     def stage_step(seq, step, token, hidden_in, out):
@@ -72,7 +72,7 @@ def _worker(rank, world, port, steps, first, q):
             v = layer_fn(l, v)
         out[0] = v % VOCAB if last else v
 
-    run_decode(stage_step, Schedule(world, world), rank, steps, Transport(dist, rank, world), hin, hout, tok,
+    run_decode(stage_step, Schedule(world, n_seq), rank, steps, Transport(dist, rank, world), hin, hout, tok,
                tout, torch.tensor(first, dtype=torch.int64),
                on_token=(lambda s, k, t: got.__setitem__((s, k), int(t.item()))) if last else None)
     if last:
@@ -81,21 +81,22 @@ def _worker(rank, world, port, steps, first, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_pipelined_decode_equals_sequential(world):
+@pytest.mark.parametrize("world,n_seq", [(2, 2), (3, 3), (2, 4), (3, 5)])
+def test_pipelined_decode_equals_sequential(world, n_seq):
+    """n_seq > world: more sequences in flight than stages (the token's way back is then off the critical path)"""
     steps = 5
-    first = [3 + 11 * s for s in range(world)]
+    first = [3 + 11 * s for s in range(n_seq)]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, steps, first, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, steps, first, q, n_seq)) for r in range(world)]
     for p in procs:
         p.start()
     got = q.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for s in range(world):
+    for s in range(n_seq):
         t = first[s]
         for k in range(steps):
             t = full_step(t)
