@@ -42,6 +42,13 @@ namespace {
 constexpr int MAX_UNITS = 160 * 16;
 constexpr uint32_t SPIN_LIMIT = 1u << 16;
 constexpr int ACT_BLK = 272; // 256 int8 codes + 16 bytes of padding
+// Bytes between the staged activations of consecutive tokens, beyond a multiple of 128: the kernels for 3 to 8
+// tokens read one token per group of four lanes, and the offset puts those loads on different banks (8-byte
+// loads of the Q4_K form: 32; 16-byte loads of the 8-token Q6_K form: 16).
+template <uint32_t TYPE, int M>
+constexpr int tok_pad() {
+    return M <= 2 ? 0 : (TYPE == B200_TYPE_Q6_K && M > 4 ? 16 : 32);
+}
 
 // Cross-warp fix-up scratch, one 128-byte line per warp of the grid.  An entry is a partial sum and
 // its ready flag in one 8-byte word (low half: float bits, high half: 1 when valid), written and
@@ -100,6 +107,11 @@ struct StreamParams {
     // (n_cta == 0: the whole grid); the fix-up scratch is indexed by the warp's number in the whole grid
     int32_t cta0, n_cta;
     int32_t m_actual; // tokens really present (the 8-token kernel pads the rest with zeros)
+    // A launch may cover a range of K only (rows too long for all tokens' activations to sit in shared memory
+    // are done in several launches, each adding to the output of the one before): K, nb, nsteps then describe
+    // the range, K_row the whole row (stride of the matrix), ks0 the range's first K slice, and the activation
+    // pointers already point at the range while their token strides stay those of the whole row.
+    int32_t K_row, ks0, a_ldk, a_ldb;
     const int8_t *aq;
     const float *ad;
     const int16_t *abs16;
@@ -194,7 +206,7 @@ struct Issuer {
     __device__ __forceinline__ void init(const StreamParams &p, int64_t first, int lane) {
         rg = (int)(first / p.nsteps);
         ks = (int)(first % p.nsteps);
-        stride = kq_device_row_bytes(TYPE, p.K);
+        stride = kq_device_row_bytes(TYPE, p.K_row);
         row = nullptr;
         if (!p.use_tma) seek(p, lane);
     }
@@ -206,7 +218,7 @@ struct Issuer {
             if (lane == 0) {
                 int seg, row0;
                 locate<TYPE>(p, rg, seg, row0);
-                const int x = ks * (F::PITCH / 8);
+                const int x = (ks + p.ks0) * (F::PITCH / 8);
                 mbar_expect_tx(bar, F::ROWS * F::PITCH);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (p.swiglu) {
@@ -227,10 +239,10 @@ struct Issuer {
         int64_t off;
         if (TYPE == B200_TYPE_Q4_K) {
             bytes = kbn * KQ_Q4K_BYTES;
-            off = (int64_t)ks * F::KB * KQ_Q4K_BYTES;
+            off = (int64_t)(ks + p.ks0) * F::KB * KQ_Q4K_BYTES;
         } else {
             bytes = (uint32_t)kq_q6_group_bytes(kbn);
-            off = (int64_t)ks * KQ_Q6_GROUP_BYTES;
+            off = (int64_t)(ks + p.ks0) * KQ_Q6_GROUP_BYTES;
         }
         if (lane == 0) mbar_expect_tx(bar, bytes * F::ROWS);
         __syncwarp();
@@ -537,6 +549,164 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
     }
 }
 
+// ---- 5 to 8 tokens, Q6_K: the same idea on 4-row units ---------------------------------------------
+// A Q6_K unit is four rows by one group of eight blocks, and its scales cover 16 elements, half of the
+// k = 32 of one instruction.  So the 8 x 32 A tile holds, for weight row w = (lane / 4) % 4, one scale
+// group in k = 0..15 of tile row w (zeros in k = 16..31) and another in k = 16..31 of tile row w + 4 (zeros
+// in k = 0..15): one instruction gives the 16-element products of two scale groups of four rows against
+// eight tokens, each in its own accumulator.  Lanes 0..15 (h2 = 0) assemble the codes that sit in the low
+// nibbles of the block's ql bytes (q = 0, 1), lanes 16..31 (h2 = 1) those in the high nibbles (q = 2, 3);
+// both take word lane % 4 of the 16-byte chunks, so the weight loads are conflict free (rows are 1680 bytes
+// apart).  The activations are staged for this kernel as [block][lane % 4][scale group][4 codes], which
+// makes the B fragments of a block four 16-byte loads per lane.  Integer sums, the -32 offset through
+// the staged sums and the f32 combination are those of the dp4a form, block by block.
+template <int M>
+__device__ __forceinline__ void mma_units_q6(const StreamParams &p, const uint8_t *smem, int act_tok, int act_q, int act_s,
+                                             const uint8_t *ring, uint32_t ring_addr, uint32_t bar_addr,
+                                             Issuer<B200_TYPE_Q6_K> &iss, int count, int64_t begin, int unit, int n_units,
+                                             int64_t total, volatile int *s_abort) {
+    using F = Fmt<B200_TYPE_Q6_K>;
+    static_assert(M == 8, "eight staged tokens (padding tokens are zeros)");
+    const int lane = threadIdx.x & 31, g8 = lane >> 2, t = lane & 3, nb = p.nb;
+    const int rw = g8 & 3, h2 = g8 >> 2;               // weight row of the unit; nibble half this lane assembles
+    const uint8_t *actB = smem + g8 * act_tok;          // token whose activations this lane feeds to the MMA
+    const int tok0 = 2 * t, tok1 = 2 * t + 1;           // tokens of this lane's accumulators
+    const uint8_t *act0 = smem + tok0 * act_tok, *act1 = smem + tok1 * act_tok;
+    const uint8_t *actS = h2 ? act1 : act0;             // token whose -32 term this lane works out
+    const uint32_t m_lo = h2 ? 0u : 0x3F3F3F3Fu, m_hi = h2 ? 0x3F3F3F3Fu : 0u;
+    const int sh4 = 4 * h2, r1 = h2 ? 0 : 4, r2 = h2 ? 30 : 2;
+    float acc0 = 0.f, acc1 = 0.f;
+    int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
+    for (int j = 0; j < count; j++) {
+        const int slot = j % p.ns;
+        wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), s_abort);
+        const uint8_t *grp = ring + (size_t)slot * F::SLOT + rw * F::PITCH;
+        const int gn = min(F::KB, nb - ks * F::KB); // blocks in this group
+        const int cs = gn * 16;                      // distance between consecutive chunks of one block
+        for (int bl = 0; bl < gn; bl++) {
+            const int blk = ks * F::KB + bl;
+            const uint8_t *ql = grp + bl * 16 + 4 * t, *qh = grp + gn * 128 + bl * 16 + 4 * t;
+            const uint4 scv = *reinterpret_cast<const uint4 *>(grp + gn * 192 + bl * 16);
+            const float dw = kq_h2f(*reinterpret_cast<const uint16_t *>(grp + gn * 208 + bl * 2));
+            const uint32_t sw[2] = {h2 ? scv.y : scv.x, h2 ? scv.w : scv.z}; // scale groups 8h + 4 h2 .. + 3
+            uint32_t xb[16];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(actB + blk * ACT_BLK + 64 * t + 16 * i);
+                xb[4 * i] = v.x; xb[4 * i + 1] = v.y; xb[4 * i + 2] = v.z; xb[4 * i + 3] = v.w;
+            }
+            int is0 = 0, is1 = 0;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                // qh chunk jj = bytes 16 c1 .. of half h; bit pair q of a byte belongs to element 128 h + 32 q + 16 c1 + i,
+                // scale group 8 h + 2 q + c1; its low four bits are in ql chunk 4 h + c1 (q = 0 low, 2 high nibble)
+                // or 4 h + c1 + 2 (q = 1, 3)
+                const int h = jj >> 1, c1 = jj & 1;
+                const uint32_t hv = *reinterpret_cast<const uint32_t *>(qh + jj * cs);
+                const uint32_t la = *reinterpret_cast<const uint32_t *>(ql + (4 * h + c1) * cs);
+                const uint32_t lb = *reinterpret_cast<const uint32_t *>(ql + (4 * h + c1 + 2) * cs);
+                // q = 0 (h2 = 0) in k 0..15, q = 2 (h2 = 1) in k 16..31
+                const uint32_t a1 = (((la >> sh4) & 0x0F0F0F0Fu) | (__funnelshift_l(hv, hv, r1) & 0xF0F0F0F0u));
+                int c0, c1v;
+                mma_u8s8(c0, c1v, a1 & m_lo, a1 & m_hi, xb[8 * h + c1], xb[8 * h + 4 + c1]);
+                const int s1 = KQ_SBYTE(sw[h], c1);
+                is0 += s1 * c0;
+                is1 += s1 * c1v;
+                // q = 1 (h2 = 0), q = 3 (h2 = 1)
+                const uint32_t a2 = (((lb >> sh4) & 0x0F0F0F0Fu) | (__funnelshift_l(hv, hv, r2) & 0xF0F0F0F0u));
+                int e0, e1;
+                mma_u8s8(e0, e1, a2 & m_lo, a2 & m_hi, xb[8 * h + 2 + c1], xb[8 * h + 6 + c1]);
+                const int s2 = KQ_SBYTE(sw[h], c1 + 2);
+                is0 += s2 * e0;
+                is1 += s2 * e1;
+            }
+            // the two nibble halves of a row add up; each half works out the -32 term of one of the two tokens
+            is0 += __shfl_xor_sync(0xffffffffu, is0, 16);
+            is1 += __shfl_xor_sync(0xffffffffu, is1, 16);
+            const uint4 b0 = *reinterpret_cast<const uint4 *>(actS + act_q + blk * 32);
+            const uint4 b1 = *reinterpret_cast<const uint4 *>(actS + act_q + blk * 32 + 16);
+            int bias = __dp2a_lo((int)b0.x, (int)scv.x, 0);
+            bias = __dp2a_hi((int)b0.y, (int)scv.x, bias);
+            bias = __dp2a_lo((int)b0.z, (int)scv.y, bias);
+            bias = __dp2a_hi((int)b0.w, (int)scv.y, bias);
+            bias = __dp2a_lo((int)b1.x, (int)scv.z, bias);
+            bias = __dp2a_hi((int)b1.y, (int)scv.z, bias);
+            bias = __dp2a_lo((int)b1.z, (int)scv.w, bias);
+            bias = __dp2a_hi((int)b1.w, (int)scv.w, bias);
+            const int other = __shfl_xor_sync(0xffffffffu, bias, 16);
+            const int bias0 = h2 ? other : bias, bias1 = h2 ? bias : other;
+            const float da0 = reinterpret_cast<const float *>(act0 + act_q + act_s)[blk];
+            const float da1 = reinterpret_cast<const float *>(act1 + act_q + act_s)[blk];
+            acc0 = fmaf(dw * da0, (float)(is0 - 32 * bias0), acc0);
+            acc1 = fmaf(dw * da1, (float)(is1 - 32 * bias1), acc1);
+        }
+        __syncwarp();
+        if (j + p.ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
+        const bool last_slice = ks == p.nsteps - 1, last_unit = j == count - 1;
+        if (last_slice || last_unit) {
+            float v0 = acc0, v1 = acc1;
+            acc0 = acc1 = 0.f;
+            const int64_t rg_first = (int64_t)rg * p.nsteps;
+            if (h2 == 0) { // lanes 16..31 hold the same values
+                if (rg_first < begin) { // the head of this row group belongs to an earlier warp
+                    *(volatile unsigned long long *)&g_partials8[unit][rw * 8 + tok0] = (unsigned long long)__float_as_uint(v0) | (1ull << 32);
+                    *(volatile unsigned long long *)&g_partials8[unit][rw * 8 + tok1] = (unsigned long long)__float_as_uint(v1) | (1ull << 32);
+                } else {
+                    if (!last_slice) { // later warps hold the tail: every lane collects its own two entries, in unit order
+                        const int64_t rg_last = rg_first + p.nsteps;
+                        for (int u2 = unit + 1; u2 < n_units; u2++) {
+                            const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                            if (b2 >= rg_last) break;
+                            if (e2 <= b2) continue;
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                volatile unsigned long long *e = &g_partials8[u2][rw * 8 + tok0 + i];
+                                unsigned long long wv = 0;
+                                bool ok = false;
+                                const uint64_t t0 = kq_globaltimer_ns();
+                                while (true) {
+                                    wv = *e;
+                                    ok = (wv >> 32) != 0;
+                                    if (ok || *s_abort || kq_globaltimer_ns() - t0 > KQ_WAIT_LIMIT_NS) break;
+                                    __nanosleep(64);
+                                }
+                                if (!ok && !*s_abort) {
+                                    *s_abort = 1;
+                                    atomicExch(&g_stream_error, 2);
+                                }
+                                *e = 0ull;
+                                (i == 0 ? v0 : v1) += __uint_as_float((uint32_t)wv);
+                            }
+                        }
+                    }
+                    int seg, row0;
+                    locate<B200_TYPE_Q6_K>(p, rg, seg, row0);
+                    const KqGemvSeg &sg = p.seg[seg];
+                    const int row = row0 + rw;
+                    if (row < sg.n_rows) {
+                        const float bb = sg.bias ? sg.bias[row] : 0.f;
+                        if (tok0 < p.m_actual) {
+                            float x = v0 + bb;
+                            if (p.residual) x += p.residual[(int64_t)tok0 * sg.ldy + row];
+                            sg.y[(int64_t)tok0 * sg.ldy + row] = x;
+                        }
+                        if (tok1 < p.m_actual) {
+                            float x = v1 + bb;
+                            if (p.residual) x += p.residual[(int64_t)tok1 * sg.ldy + row];
+                            sg.y[(int64_t)tok1 * sg.ldy + row] = x;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        if (++ks == p.nsteps) {
+            ks = 0;
+            rg++;
+        }
+    }
+}
+
 // ---- several dependent matmuls in one launch ------------------------------------------------------
 // A decode layer is a chain of matrix-vector products, each needing the whole output of the one
 // before.  As separate launches every link costs the tail of one kernel (the last warps finishing,
@@ -620,7 +790,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
     const int act_q = (nb * ACT_BLK + 127) & ~127, act_s = (nb * SUMS + 127) & ~127, act_d = (nb * 4 + 127) & ~127;
     // 8-token kernel: tokens 32 bytes apart modulo 128, so that the B-fragment loads of the eight
     // token lanes of a warp fall on different banks
-    const int act_tok = act_q + act_s + act_d + (M > 2 ? 32 : 0);
+    const int act_tok = act_q + act_s + act_d + tok_pad<TYPE, M>();
     if (FUSED && fx.phase > 0) fused_grid_arrive(); // everything this CTA wrote in the phase before is published
     const int ns = FUSED ? min(4, fx.ring_bytes / F::SLOT) : p.ns; // ring depth
     uint8_t *ring = FUSED ? smem + fx.act_bytes + (size_t)warp * fx.ring_bytes : smem + M * act_tok + (size_t)warp * ns * F::SLOT;
@@ -795,12 +965,12 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         for (int m = 0; m < M; m++) {
             uint8_t *tq = smem + m * act_tok;
             if (M > 2 && m >= p.m_actual) { // padding token: all-zero codes, sums and scales
-                for (int i = threadIdx.x * 16; i < act_tok - 32; i += WARPS * 32 * 16)
+                for (int i = threadIdx.x * 16; i < act_tok - tok_pad<TYPE, M>(); i += WARPS * 32 * 16)
                     *reinterpret_cast<int4 *>(tq + i) = make_int4(0, 0, 0, 0);
                 continue;
             }
-            const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.K);
-            const int16_t *b16 = p.abs16 + (int64_t)m * nb * 16;
+            const int4 *src = reinterpret_cast<const int4 *>(p.aq + (int64_t)m * p.a_ldk);
+            const int16_t *b16 = p.abs16 + (int64_t)m * p.a_ldb * 16;
             const int n16 = nb * 16;
             // first wave of loads (codes, sums, scales) in flight together, behind the posting
             constexpr int NT = WARPS * 32;
@@ -810,12 +980,23 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
             if (i0 < n16) c0 = src[i0];
             if (i1 < n16) c1 = src[i1];
             if (i0 < nb * 2) s0 = reinterpret_cast<const int4 *>(b16)[i0]; // 8 sums of 16
-            if (i0 < nb) d0 = p.ad[m * nb + i0];
+            if (i0 < nb) d0 = p.ad[m * p.a_ldb + i0];
             post_rest();
-            if (i0 < n16) *reinterpret_cast<int4 *>(tq + (i0 >> 4) * ACT_BLK + (i0 & 15) * 16) = c0;
-            if (i1 < n16) *reinterpret_cast<int4 *>(tq + (i1 >> 4) * ACT_BLK + (i1 & 15) * 16) = c1;
-            for (int i = threadIdx.x + 2 * NT; i < n16; i += NT)
-                *reinterpret_cast<int4 *>(tq + (i >> 4) * ACT_BLK + (i & 15) * 16) = src[i];
+            // 16 codes of scale group i % 16 of block i / 16
+            auto put = [&](int i, const int4 &c) {
+                if constexpr (TYPE == B200_TYPE_Q6_K && M > 4) { // [lane % 4][scale group][4 codes], see mma_units_q6
+                    uint32_t *dst = reinterpret_cast<uint32_t *>(tq + (i >> 4) * ACT_BLK) + (i & 15);
+                    dst[0] = (uint32_t)c.x;
+                    dst[16] = (uint32_t)c.y;
+                    dst[32] = (uint32_t)c.z;
+                    dst[48] = (uint32_t)c.w;
+                } else {
+                    *reinterpret_cast<int4 *>(tq + (i >> 4) * ACT_BLK + (i & 15) * 16) = c;
+                }
+            };
+            if (i0 < n16) put(i0, c0);
+            if (i1 < n16) put(i1, c1);
+            for (int i = threadIdx.x + 2 * NT; i < n16; i += NT) put(i, src[i]);
             for (int i = threadIdx.x; i < nb * 2; i += NT) {
                 const int4 sv = i == i0 ? s0 : reinterpret_cast<const int4 *>(b16)[i];
                 const int16_t *h = reinterpret_cast<const int16_t *>(&sv);
@@ -829,7 +1010,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                 }
             }
             for (int i = threadIdx.x; i < nb; i += NT)
-                reinterpret_cast<float *>(tq + act_q + act_s)[i] = i == i0 ? d0 : p.ad[m * nb + i];
+                reinterpret_cast<float *>(tq + act_q + act_s)[i] = i == i0 ? d0 : p.ad[m * p.a_ldb + i];
         }
     }
     post_rest();
@@ -841,9 +1022,13 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                            &s_abort);
         return;
     }
+    if constexpr (M > 4 && TYPE == B200_TYPE_Q6_K) {
+        mma_units_q6<M>(p, smem, act_tok, act_q, act_s, ring, ring_addr, bar_addr, iss, count, begin, unit, n_units, total, &s_abort);
+        return;
+    }
     // Q6_K with 3 or 4 tokens takes the loop below: one lane per block against all staged tokens, the block
     // decoded once; rows x tokens = 16 partial sums per unit is what a line of the fix-up scratch holds
-    static_assert(M <= 2 || TYPE == B200_TYPE_Q4_K || F::ROWS * M <= 16, "a unit's partial sums must fit one line of the fix-up scratch");
+    static_assert(M <= 2 || TYPE == B200_TYPE_Q4_K || M > 4 || F::ROWS * M <= 16, "a unit's partial sums must fit one line of the fix-up scratch");
 
     float acc[M];
 #pragma unroll
@@ -1056,6 +1241,10 @@ void fill_params(StreamParams &p, const KqGemvSeg *segs, int nseg, const int8_t 
     p.n_rg = tot;
     p.nb = (int)(K / 256);
     p.K = (int)K;
+    p.K_row = (int)K;
+    p.ks0 = 0;
+    p.a_ldk = (int)K;
+    p.a_ldb = p.nb;
     p.nsteps = (int)kq_div_up(p.nb, F::KB);
     p.swiglu = swiglu_pairs;
     p.aq = q;
@@ -1084,7 +1273,7 @@ b200_status make_maps(StreamParams &p, int nseg_all) {
     memset(p.map, 0, sizeof(p.map));
     const int box_rows = p.swiglu ? F::ROWS / 2 : F::ROWS;
     if (!on || (p.swiglu && ((box_rows * F::PITCH) & 127) != 0)) return B200_OK;
-    const int64_t row_bytes = kq_device_row_bytes(TYPE, p.K);
+    const int64_t row_bytes = kq_device_row_bytes(TYPE, p.K_row);
     if (row_bytes % 16 != 0) return B200_OK;
     for (int i = 0; i < nseg_all; i++) {
         if (p.seg[i].expert_stride != 0 || ((uintptr_t)p.seg[i].W & 15) != 0) return B200_OK;
@@ -1107,17 +1296,23 @@ inline int act_tok_bytes(uint32_t type, int nb, int M) {
 template <uint32_t TYPE, int M>
 b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
                          int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st,
-                         int m_actual = M) {
+                         int m_actual = M, int64_t K_row = 0, int blk0 = 0) {
     using F = Fmt<TYPE>;
     StreamParams p;
     fill_params<TYPE>(p, segs, nseg, q, d, bs, K, residual, swiglu_pairs, prep);
+    if (K_row) { // a range of K: blocks blk0 .. blk0 + K / 256 of rows of K_row elements; q, d, bs point at the range
+        if (blk0 % F::KB != 0 || (prep && prep->x)) return B200_ERR_INVALID;
+        p.K_row = (int)K_row;
+        p.ks0 = blk0 / F::KB;
+        p.a_ldk = (int)K_row;
+        p.a_ldb = (int)(K_row / 256);
+    }
     {
         const b200_status rm = make_maps<TYPE>(p, nseg);
         if (rm != B200_OK) return rm;
     }
     const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
-    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) +
-                        (M > 2 ? 32 : 0);
+    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) + tok_pad<TYPE, M>();
     p.m_actual = m_actual;
     constexpr int WARPS = F::WARPS;
     int cap = F::SMEM_CAP;
@@ -1146,12 +1341,47 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     return B200_OK;
 }
 
+// MT staged tokens (3 to 8) in one pass over the matrix.  Rows too long for the activations of MT tokens to sit
+// in shared memory next to the ring go out as up to four launches over ranges of K, each adding to the output
+// of the one before (one segment, no fused gate / up); B200_GEMV_KPARTS=0 refuses those instead.
+template <uint32_t TYPE, int MT>
+bool batch_fits(int nb) {
+    using F = Fmt<TYPE>;
+    const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
+    const int act_tok = ((nb * ACT_BLK + 127) & ~127) + ((nb * sums + 127) & ~127) + ((nb * 4 + 127) & ~127) + tok_pad<TYPE, MT>();
+    return (size_t)MT * act_tok + (size_t)F::WARPS * F::SLOT + (size_t)F::WARPS * 8 * 8 <= 216 * 1024;
+}
+
+template <uint32_t TYPE, int MT>
+b200_status launch_parts(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs, int64_t K,
+                         const float *residual, int swiglu_pairs, cudaStream_t st, int m_actual) {
+    using F = Fmt<TYPE>;
+    const int nb = (int)(K / 256);
+    if (batch_fits<TYPE, MT>(nb)) return launch_block<TYPE, MT>(segs, nseg, q, d, bs, K, residual, swiglu_pairs, nullptr, st, m_actual);
+    if (nseg != 1 || swiglu_pairs || env_int2("B200_GEMV_KPARTS", 1) == 0) return B200_ERR_UNSUPPORTED;
+    const int nsteps = (int)kq_div_up(nb, F::KB);
+    for (int parts = 2; parts <= 4; parts++) {
+        const int per = (int)kq_div_up(nsteps, parts) * F::KB; // blocks per range, whole K slices
+        if (!batch_fits<TYPE, MT>(per)) continue;
+        for (int b0 = 0, i = 0; b0 < nb; b0 += per, i++) {
+            const int nbp = nb - b0 < per ? nb - b0 : per;
+            KqGemvSeg sg = segs[0];
+            if (i > 0) sg.bias = nullptr;
+            const b200_status rc = launch_block<TYPE, MT>(&sg, 1, q + (int64_t)b0 * 256, d + b0, bs + (int64_t)b0 * 16, (int64_t)nbp * 256,
+                                                          i == 0 ? residual : sg.y, 0, nullptr, st, m_actual, K, b0);
+            if (rc != B200_OK) return i == 0 ? rc : B200_ERR_INVALID; // the output already holds the first ranges
+        }
+        return B200_OK;
+    }
+    return B200_ERR_UNSUPPORTED;
+}
+
 // ring depth and shared-memory bytes of one launch part; false when the row does not fit
 template <uint32_t TYPE, int M>
 bool plan_part(StreamParams &p, size_t &smem) {
     using F = Fmt<TYPE>;
     const int sums = TYPE == B200_TYPE_Q4_K ? 16 : 32;
-    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) + (M > 2 ? 32 : 0);
+    const int act_tok = ((p.nb * ACT_BLK + 127) & ~127) + ((p.nb * sums + 127) & ~127) + ((p.nb * 4 + 127) & ~127) + tok_pad<TYPE, M>();
     int cap = F::SMEM_CAP;
     if (M * act_tok + F::WARPS * F::SLOT + 1024 > cap) cap = 216 * 1024;
     int ns = (cap - M * act_tok - F::WARPS * 8 * 8) / (F::WARPS * F::SLOT);
@@ -1315,8 +1545,12 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
         }
         if ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0) return B200_ERR_UNSUPPORTED;
         if (all6 && !swiglu_pairs && env_int2("B200_GEMV_Q6_BATCH", 1)) {
-            // Q6_K: the streaming kernel's dp4a form with four tokens staged, the matrix streamed once per
-            // group of four
+            // Q6_K, 5 to 8 tokens: the tensor-core form, one pass over the matrix
+            if (M > 4 && env_int2("B200_GEMV_Q6_MMA", 1)) {
+                const b200_status rc = launch_parts<B200_TYPE_Q6_K, 8>(segs, nseg, q, d, bs, K, residual, 0, st, M);
+                if (rc != B200_ERR_UNSUPPORTED) return rc;
+            }
+            // else the streaming kernel's dp4a form with four tokens staged, the matrix streamed once per group of four
             const int64_t nb6 = K / 256;
             for (int m0 = 0; m0 < M; m0 += 4) {
                 KqGemvSeg sh[3];
@@ -1325,16 +1559,15 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
                     sh[i].y = segs[i].y + (int64_t)m0 * segs[i].ldy;
                 }
                 const int mc = M - m0 < 4 ? M - m0 : 4;
-                const b200_status rc = launch_block<B200_TYPE_Q6_K, 4>(sh, nseg, q + (int64_t)m0 * K, d + m0 * nb6, bs + m0 * nb6 * 16, K,
-                                                                       residual ? residual + (int64_t)m0 * segs[0].ldy : nullptr, 0,
-                                                                       nullptr, st, mc);
+                const b200_status rc = launch_parts<B200_TYPE_Q6_K, 4>(sh, nseg, q + (int64_t)m0 * K, d + m0 * nb6, bs + m0 * nb6 * 16, K,
+                                                                       residual ? residual + (int64_t)m0 * segs[0].ldy : nullptr, 0, st, mc);
                 if (rc != B200_OK) return m0 == 0 ? rc : B200_ERR_INVALID;
             }
             return B200_OK;
         }
         if (!all4) return B200_ERR_UNSUPPORTED;
         if (M > 4) {
-            const b200_status rc = launch_block<B200_TYPE_Q4_K, 8>(segs, nseg, q, d, bs, K, residual, swiglu_pairs, nullptr, st, M);
+            const b200_status rc = launch_parts<B200_TYPE_Q4_K, 8>(segs, nseg, q, d, bs, K, residual, swiglu_pairs, st, M);
             if (rc != B200_ERR_UNSUPPORTED) return rc;
         }
         const int64_t nb = K / 256;

@@ -35,7 +35,7 @@ b200_status kq_attention(const float *q, const uint16_t *kc, const uint16_t *vc,
                          int64_t seq_stride, float *out, float *scratch, size_t scratch_bytes,
                          int force_splits, KqKvTypes kvt, cudaStream_t st);
 int kq_attention_splits(int64_t rows, int n_kv, int64_t L);
-int kq_attention_decode_splits(int64_t L);
+int kq_attention_decode_splits(int64_t L, int pairs);
 b200_status kq_attention_decode(const float *q, const float *k, const float *v, uint16_t *kc, uint16_t *vc,
                                 int n_seq, const int32_t *pos_dev, int pos, int n_head, int n_kv, int hd,
                                 int64_t seq_stride, float theta, int neox, int n_split, float *out, float *scratch,
@@ -277,7 +277,7 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
         }
         if (T == 1) {
             // decode: RoPE, KV store, attention and the split combine are one launch
-            const int ns = kq_attention_decode_splits(pos0 + 1);
+            const int ns = kq_attention_decode_splits(pos0 + 1, n_seq * c.n_head_kv);
             ATTN_(kq_attention_decode(st->q, st->k, st->v, kc, vc, n_seq, pos_dev, pos0, c.n_head, c.n_head_kv, hd,
                                       seq_stride, c.rope_theta, c.rope_neox, ns, st->att, st->att_scratch,
                                       st->att_scratch_bytes, st->attn_counters, kvt, s));
@@ -818,7 +818,7 @@ b200_status b200_stage_forward(b200_stage *st, const int32_t *tokens, const floa
     const long long before = g_kq_launches;
     if (T == 1 && st->use_graph) {
         // decode step: positions come from device memory so one captured graph serves every step
-        const int n_split = kq_attention_decode_splits(pos0 + 1);
+        const int n_split = kq_attention_decode_splits(pos0 + 1, n_seq * st->c.n_head_kv);
         GraphKey key;
         memset(&key, 0, sizeof(key));
         key.n_seq = n_seq;

@@ -121,25 +121,54 @@ def test_gemv_random_blocks_and_split_k(ops, ty, monkeypatch):
     np.testing.assert_array_equal(again, outs[-1])
 
 
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
 @pytest.mark.parametrize("M", [3, 5, 8])
-@pytest.mark.parametrize("N,K", [(96, 27648), (200, 5120), (40, 256)])
-def test_gemv_batch_tensor_core_form(ops, M, N, K, monkeypatch):
-    """3..8 tokens of Q4_K run the integer products on mma.m16n8k32; long rows are staged four tokens
-    at a time.  Same integers, same f32 combination as the plain kernel: compared with the oracle and,
-    bit for bit, with the plain kernel's per-token result order (token-wise identical sums)."""
+@pytest.mark.parametrize("N,K", [(96, 27648), (200, 5120), (40, 256), (50, 2304)])
+def test_gemv_batch_tensor_core_form(ops, ty, M, N, K, monkeypatch):
+    """3..8 tokens of Q4_K and 5..8 tokens of Q6_K run the integer products on mma.m16n8k32; long rows
+    go out as launches over ranges of K.  Same integers, same f32 combination per block as the plain
+    kernel: compared with the oracle and with the plain kernel's result."""
     import torch
 
-    W = _weights(orc.TYPE_Q4_K, N, K, 16, random_bytes=True)
+    W = _weights(ty, N, K, 16, random_bytes=True)
     x = np.random.default_rng(17 + M).standard_normal((M, K)).astype(np.float32)
-    ref = orc.mul_mat(orc.TYPE_Q4_K, W, x, N, K)
-    dev = ops.upload_weights(orc.TYPE_Q4_K, W, N, K)
+    ref = orc.mul_mat(ty, W, x, N, K)
+    dev = ops.upload_weights(ty, W, N, K)
     xd = torch.from_numpy(x).cuda()
-    y = ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy()
+    y = ops.mul_mat(ty, dev, xd, N, K).cpu().numpy()
     assert rel_err(y, ref) <= REL
-    np.testing.assert_array_equal(ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy(), y)  # deterministic
+    np.testing.assert_array_equal(ops.mul_mat(ty, dev, xd, N, K).cpu().numpy(), y)  # deterministic
     monkeypatch.setenv("B200_GEMV_MMA", "0")
-    plain = ops.mul_mat(orc.TYPE_Q4_K, dev, xd, N, K).cpu().numpy()
+    monkeypatch.setenv("B200_GEMV_Q6_MMA", "0")
+    plain = ops.mul_mat(ty, dev, xd, N, K).cpu().numpy()
     assert rel_err(plain, ref) <= REL and rel_err(y, plain) <= 1e-5
+    monkeypatch.delenv("B200_GEMV_MMA")
+    monkeypatch.delenv("B200_GEMV_Q6_MMA")
+    monkeypatch.setenv("B200_GEMV_KPARTS", "0")  # long rows: four tokens at a time instead of ranges of K
+    whole = ops.mul_mat(ty, dev, xd, N, K).cpu().numpy()
+    assert rel_err(whole, ref) <= REL and rel_err(y, whole) <= 1e-5
+
+
+@pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
+@pytest.mark.parametrize("M", [4, 7, 8])
+def test_gemv_batch_long_rows_bias_residual(ops, ty, M):
+    """rows of 27648 at 4..8 tokens: several launches over ranges of K, the first adds bias and residual, the
+    others add to the output"""
+    import torch
+
+    N, K = 300, 27648
+    W = _weights(ty, N, K, 18, random_bytes=True)
+    rng = np.random.default_rng(19 + M)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = (rng.standard_normal((M, N)) * 30).astype(np.float32)
+    ref = orc.mul_mat(ty, W, x, N, K) + bias + res
+    dev = ops.upload_weights(ty, W, N, K)
+    q, d, bs = ops.quantize_act(torch.from_numpy(x).cuda())
+    y = ops.mul_mat_q8(ty, dev, q, d, bs, N, K, bias=torch.from_numpy(bias).cuda(), residual=torch.from_numpy(res).cuda())
+    assert rel_err(y.cpu().numpy(), ref) <= REL
+    y2 = ops.mul_mat_q8(ty, dev, q, d, bs, N, K, bias=torch.from_numpy(bias).cuda(), residual=torch.from_numpy(res).cuda())
+    assert torch.equal(y, y2)
 
 
 @pytest.mark.parametrize("ty", [orc.TYPE_Q4_K, orc.TYPE_Q6_K])
