@@ -112,6 +112,10 @@ struct StreamParams {
     // the range, K_row the whole row (stride of the matrix), ks0 the range's first K slice, and the activation
     // pointers already point at the range while their token strides stay those of the whole row.
     int32_t K_row, ks0, a_ldk, a_ldb;
+    // The (row group, K slice) work items are dealt to the warps of the launch part as evenly as possible, in
+    // order: the first ur warps get uq + 1 items, the others uq (set by the host, which knows the grid: the
+    // kernel then needs no division before its first copy can go out).
+    int32_t uq, ur;
     const int8_t *aq;
     const float *ad;
     const int16_t *abs16;
@@ -165,6 +169,9 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
 #define KQ_BYTE(w, k) (((w) >> (8 * (k))) & 0xFFu)
 #define KQ_SBYTE(w, k) ((int)(int8_t)(((w) >> (8 * (k))) & 0xFFu))
 
+// first work item of warp u of the launch part
+__device__ __forceinline__ int unit_first(const StreamParams &p, int u) { return u * p.uq + min(u, p.ur); }
+
 template <uint32_t TYPE>
 __device__ __forceinline__ void locate(const StreamParams &p, int rg, int &seg, int &row0) {
     int si = 0, rg0 = 0;
@@ -203,15 +210,17 @@ struct Issuer {
             row = row_ptr<TYPE>(p, seg, row0, lane, stride);
         }
     }
-    __device__ __forceinline__ void init(const StreamParams &p, int64_t first, int lane) {
-        rg = (int)(first / p.nsteps);
-        ks = (int)(first % p.nsteps);
+    __device__ __forceinline__ void init(const StreamParams &p, int first, int lane) {
+        rg = first / p.nsteps;
+        ks = first % p.nsteps;
         stride = kq_device_row_bytes(TYPE, p.K_row);
         row = nullptr;
         if (!p.use_tma) seek(p, lane);
     }
-    // post the next unit into the slot at slot_addr
-    __device__ __forceinline__ void post(const StreamParams &p, int lane, uint32_t slot_addr, uint32_t bar) {
+    // post the next unit into the slot at slot_addr.  reuse: the slot has been read by this warp before (the
+    // proxy fence orders those reads before the copy engine's writes); a slot that is filled for the first
+    // time needs none.
+    __device__ __forceinline__ void post(const StreamParams &p, int lane, uint32_t slot_addr, uint32_t bar, bool reuse = true) {
         if (p.use_tma) {
             // one box per unit (two with fused gate / up: half the rows from each matrix).  Rows past the
             // matrix and blocks past the row arrive as zeros; the box always counts its full size.
@@ -220,7 +229,7 @@ struct Issuer {
                 locate<TYPE>(p, rg, seg, row0);
                 const int x = (ks + p.ks0) * (F::PITCH / 8);
                 mbar_expect_tx(bar, F::ROWS * F::PITCH);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (reuse) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (p.swiglu) {
                     tma_box(slot_addr, &p.map[0], x, row0, bar);
                     tma_box(slot_addr + (F::ROWS / 2) * F::PITCH, &p.map[1], x, row0, bar);
@@ -247,7 +256,7 @@ struct Issuer {
         if (lane == 0) mbar_expect_tx(bar, bytes * F::ROWS);
         __syncwarp();
         if (lane < F::ROWS) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (reuse) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             bulk_g2s(slot_addr + lane * F::PITCH, row + off, bytes, bar);
         }
         if (++ks == p.nsteps) {
@@ -407,7 +416,7 @@ __device__ __forceinline__ void mma_u8s8(int &d0, int &d1, uint32_t a0, uint32_t
 template <uint32_t TYPE, int M>
 __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *smem, int act_tok, int act_q, int act_s,
                                           const uint8_t *ring, uint32_t ring_addr, uint32_t bar_addr, Issuer<TYPE> &iss,
-                                          int count, int64_t begin, int unit, int n_units, int64_t total,
+                                          int count, int begin, int unit, int n_units, int total,
                                           volatile int *s_abort) {
     using F = Fmt<TYPE>;
     static_assert(TYPE == B200_TYPE_Q4_K, "the tensor-core batch path is built for Q4_K");
@@ -418,7 +427,7 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
     const int tok0 = 2 * t, tok1 = 2 * t + 1;         // tokens of this lane's accumulators
     const uint8_t *act0 = smem + (tok0 < M ? tok0 : 0) * act_tok, *act1 = smem + (tok1 < M ? tok1 : 0) * act_tok;
     float acc0 = 0.f, acc1 = 0.f;
-    int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
+    int rg = begin / p.nsteps, ks = begin % p.nsteps;
     for (int j = 0; j < count; j++) {
         const int slot = j % p.ns;
         wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), s_abort);
@@ -483,7 +492,7 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
                 if (!last_slice) { // later warps hold the tail: every lane collects its own two entries, in unit order
                     const int64_t rg_last = rg_first + p.nsteps;
                     for (int u2 = unit + 1; u2 < n_units; u2++) {
-                        const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                        const int b2 = unit_first(p, u2), e2 = unit_first(p, u2 + 1);
                         if (b2 >= rg_last) break;
                         if (e2 <= b2) continue;
 #pragma unroll
@@ -563,8 +572,8 @@ __device__ __forceinline__ void mma_units(const StreamParams &p, const uint8_t *
 template <int M>
 __device__ __forceinline__ void mma_units_q6(const StreamParams &p, const uint8_t *smem, int act_tok, int act_q, int act_s,
                                              const uint8_t *ring, uint32_t ring_addr, uint32_t bar_addr,
-                                             Issuer<B200_TYPE_Q6_K> &iss, int count, int64_t begin, int unit, int n_units,
-                                             int64_t total, volatile int *s_abort) {
+                                             Issuer<B200_TYPE_Q6_K> &iss, int count, int begin, int unit, int n_units,
+                                             int total, volatile int *s_abort) {
     using F = Fmt<B200_TYPE_Q6_K>;
     static_assert(M == 8, "eight staged tokens (padding tokens are zeros)");
     const int lane = threadIdx.x & 31, g8 = lane >> 2, t = lane & 3, nb = p.nb;
@@ -576,7 +585,7 @@ __device__ __forceinline__ void mma_units_q6(const StreamParams &p, const uint8_
     const uint32_t m_lo = h2 ? 0u : 0x3F3F3F3Fu, m_hi = h2 ? 0x3F3F3F3Fu : 0u;
     const int sh4 = 4 * h2, r1 = h2 ? 0 : 4, r2 = h2 ? 30 : 2;
     float acc0 = 0.f, acc1 = 0.f;
-    int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
+    int rg = begin / p.nsteps, ks = begin % p.nsteps;
     for (int j = 0; j < count; j++) {
         const int slot = j % p.ns;
         wait_slot(bar_addr + slot * 8, (uint32_t)((j / p.ns) & 1), s_abort);
@@ -655,7 +664,7 @@ __device__ __forceinline__ void mma_units_q6(const StreamParams &p, const uint8_
                     if (!last_slice) { // later warps hold the tail: every lane collects its own two entries, in unit order
                         const int64_t rg_last = rg_first + p.nsteps;
                         for (int u2 = unit + 1; u2 < n_units; u2++) {
-                            const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                            const int b2 = unit_first(p, u2), e2 = unit_first(p, u2 + 1);
                             if (b2 >= rg_last) break;
                             if (e2 <= b2) continue;
 #pragma unroll
@@ -779,11 +788,16 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
     if (threadIdx.x == 0 && s_trace < 32768u) {
         g_trace[s_trace][7] = ((unsigned long long)blockIdx.x << 32) | (unsigned)p.n_rg;
         g_trace[s_trace][8] = kq_globaltimer_ns();
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_trace[s_trace][13] = smid;
     }
 #endif
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rs = lane / F::LPR, t = lane % F::LPR;
     const int nb = p.nb;
+    // the copy engine's descriptors: fetched now, so that the first copy does not wait for them
+    if (p.use_tma && lane == 0 && warp < (p.swiglu ? 2 : p.nseg)) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map[warp]) : "memory");
 
     // ---- shared memory: per token [padded int8 codes][int16 sums][f32 scales], then rings, then mbarriers
     constexpr int SUMS = TYPE == B200_TYPE_Q4_K ? 16 : 32; // bytes of sums per block
@@ -805,24 +819,26 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         for (int s = 0; s < (FUSED ? 4 : ns); s++) mbar_init(smem_u32(&bars[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncwarp();
+    TRACE_MARK(14);
     const int unit = ((int)blockIdx.x - p.cta0) * WARPS + warp, n_units = (p.n_cta ? p.n_cta : (int)gridDim.x) * WARPS;
     const int pbase = p.cta0 * WARPS; // this launch part's first line of the fix-up scratch
-    const int64_t total = (int64_t)p.n_rg * p.nsteps;
-    const int64_t begin = total * unit / n_units, end = total * (unit + 1) / n_units;
-    const int count = (int)(end - begin);
+    const int total = p.n_rg * p.nsteps;
+    const int begin = unit_first(p, unit), end = unit_first(p, unit + 1);
+    const int count = end - begin;
     const uint32_t ring_addr = smem_u32(ring), bar_addr = smem_u32(bars);
     Issuer<TYPE> iss;
     iss.init(p, begin, lane);
+    TRACE_MARK(15);
     // The first slot of the ring goes out at once; the remaining slots are posted only after the loads of
     // the activations have been issued.  Measured both ways: with everything posted before the dependency
     // wait the activation loads queue behind twice the weight traffic and the step is 2 % slower; with
     // nothing posted before it, 1.5 % slower.
     const int pre = min(count, ns);
-    if (pre > 0) iss.post(p, lane, ring_addr, bar_addr);
+    if (pre > 0) iss.post(p, lane, ring_addr, bar_addr, FUSED && fx.phase > 0);
     bool rest_posted = false;
     auto post_rest = [&]() {
         if (!rest_posted) {
-            for (int j = 1; j < pre; j++) iss.post(p, lane, ring_addr + j * F::SLOT, bar_addr + j * 8);
+            for (int j = 1; j < pre; j++) iss.post(p, lane, ring_addr + j * F::SLOT, bar_addr + j * 8, FUSED && fx.phase > 0);
             rest_posted = true;
         }
     };
@@ -1033,7 +1049,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; m++) acc[m] = 0.f;
-    int rg = (int)(begin / p.nsteps), ks = (int)(begin % p.nsteps);
+    int rg = begin / p.nsteps, ks = begin % p.nsteps;
     for (int j = 0; j < count; j++) {
         const int slot = j % ns;
         wait_slot(bar_addr + slot * 8, (uint32_t)(((FUSED ? uses[slot] : 0u) + j / ns) & 1), &s_abort);
@@ -1078,12 +1094,12 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                     // what they fetched in warp order.
                     const int64_t rg_last = rg_first + p.nsteps;
                     for (int base = unit + 1; base < n_units; base += F::LPR) {
-                        const int64_t b0 = total * base / n_units;
+                        const int b0 = unit_first(p, base);
                         if (b0 >= rg_last) break;
                         const int u2 = base + t;
                         bool mine = false;
                         if (u2 < n_units) {
-                            const int64_t b2 = total * u2 / n_units, e2 = total * (u2 + 1) / n_units;
+                            const int b2 = unit_first(p, u2), e2 = unit_first(p, u2 + 1);
                             mine = b2 < rg_last && e2 > b2;
                         }
                         float got[M];
@@ -1259,6 +1275,15 @@ void fill_params(StreamParams &p, const KqGemvSeg *segs, int nseg, const int8_t 
     }
 }
 
+// how the work items of a launch part are dealt to its n_units warps (StreamParams::uq, ur)
+inline bool set_split(StreamParams &p, int n_units) {
+    const int64_t total = (int64_t)p.n_rg * p.nsteps;
+    if (total >= (1ll << 30) || n_units < 1) return false;
+    p.uq = (int32_t)(total / n_units);
+    p.ur = (int32_t)(total % n_units);
+    return true;
+}
+
 // Tensor maps of the segments for the tiled-copy form of the ring (B200_GEMV_TMA=0 keeps one bulk copy per
 // row).  Not used where a box would not start on a 128-byte boundary of the slot (Q6_K with fused gate / up).
 template <uint32_t TYPE>
@@ -1328,6 +1353,7 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     if (grid * WARPS > MAX_UNITS) grid = MAX_UNITS / WARPS;
     const int64_t want = kq_div_up((int64_t)p.n_rg * p.nsteps, WARPS);
     if (want < grid) grid = (int)(want < 1 ? 1 : want);
+    if (!set_split(p, grid * WARPS)) return B200_ERR_UNSUPPORTED;
     static bool attr_done[16]; // the attribute belongs to a (kernel, device) pair
     int dev = 0;
     KQ_CUDA(cudaGetDevice(&dev));
@@ -1427,6 +1453,7 @@ b200_status launch_mixed(const KqGemvSeg *s4, int n4, const KqGemvSeg *s6, int n
     p4.n_cta = c4;
     p6.cta0 = c4;
     p6.n_cta = c6;
+    if (!set_split(p4, c4 * KQ_GEMV_WARPS) || !set_split(p6, c6 * KQ_GEMV_WARPS)) return B200_ERR_UNSUPPORTED;
     const size_t smem = sm4 > sm6 ? sm4 : sm6;
     static bool attr_done[16];
     int dev = 0;
@@ -1481,6 +1508,7 @@ b200_status kq_launch_gemv_fused(const KqFusedPhase *ph, int n_phase, int M, cud
         else
             fill_params<B200_TYPE_Q6_K>(fp.ph[i], f.segs, f.nseg, nullptr, nullptr, nullptr, f.K, f.residual, f.swiglu, &f.prep);
         fp.ph[i].m_actual = M;
+        if (!set_split(fp.ph[i], kq_sm_count() * KQ_GEMV_WARPS)) return B200_ERR_UNSUPPORTED;
         const int a = M * act_tok_bytes(type, (int)(f.K / 256), M);
         if (a > act) act = a;
     }
