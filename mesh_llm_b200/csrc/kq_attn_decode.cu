@@ -85,6 +85,9 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
                                                               RopeTab tab, float *out, float *part_o, float *part_ml,
                                                               int *counters, KqKvTypes kvt) {
     KQ_PDL_TRIGGER();
+    // the copy engine's descriptors: fetched while the position is being read
+    if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
+    if (threadIdx.x == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
     constexpr int DPL = HD / 32, HALF = HD / 2, NBOX = HD / 64, NT = MMA ? 256 : 128 * G;
     static_assert(!MMA || (HD == 128 && G <= 8), "the tensor-core form is built for head_dim 128 and up to 8 heads per KV head");
     extern __shared__ __align__(1024) uint8_t dsm_raw[];

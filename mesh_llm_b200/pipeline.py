@@ -511,7 +511,7 @@ def bench_pipeline(args, w, metric, rank, world, local):
     import torch
     import torch.distributed as dist
 
-    from bench import WORKLOADS, cpu_decode_sample
+    from bench import WORKLOADS, cpu_decode_sample, host_threads
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -543,7 +543,10 @@ def bench_pipeline(args, w, metric, rank, world, local):
                                   f"prefill {w3['prefill']}, decode at context {w3['prefill']}+"})
     cpu = None
     if rank == 0 and not args.no_cpu:
-        v, cores, sample = cpu_decode_sample(w)
+        # the other ranks wait for this one in a barrier, each spinning on a core: one OpenMP thread more than
+        # there are free cores makes every parallel loop wait for a descheduled thread (measured at 2 ranks on 24
+        # cores: 24 threads 0.28 tok/s, 16 threads 1.56, 24 threads with the other rank asleep 2.36)
+        v, cores, sample = cpu_decode_sample(w, threads=max(1, host_threads() - world))
         cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
     h = w["n_embd"]
     bad = (r["tokens_match_single_stage"] is False or extra.get("cfg3_tokens_match_single_stage") is False or
