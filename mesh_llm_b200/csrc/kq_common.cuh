@@ -266,6 +266,18 @@ struct KqActPrep {
     int32_t do_norm;
 };
 
+// The Q8 form of a fused gate / up launch's output (SwiGLU values), written by that launch itself for the
+// matmul that follows: whichever warp completes the last row of a 256-element block quantises the block.
+// counters: one zero-initialised int per block, returned to zero by the launch.  done is set by the
+// launcher when the launch will write q / d / bs (rows a multiple of 256, streaming kernel, 1 or 2 tokens).
+struct KqEmitQ8 {
+    int8_t *q;
+    float *d;
+    int16_t *bs;
+    int32_t *counters;
+    int32_t done;
+};
+
 // one phase of a fused chain of decode matmuls: y = W . prep(x) (+ residual / SwiGLU of a gate-up pair)
 struct KqFusedPhase {
     KqGemvSeg segs[2];
@@ -280,10 +292,10 @@ b200_status kq_launch_gemv_fused(const KqFusedPhase *ph, int n_phase, int M, cud
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
                            int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st,
-                           const KqActPrep *prep = nullptr);
+                           const KqActPrep *prep = nullptr, KqEmitQ8 *emit = nullptr);
 b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                                   const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
-                                  const KqActPrep *prep, cudaStream_t st);
+                                  const KqActPrep *prep, cudaStream_t st, KqEmitQ8 *emit = nullptr);
 b200_status kq_rms_norm(const float *x, const float *w, int64_t T, int64_t h, float eps, float *y, int8_t *q,
                         float *d, int16_t *bs, cudaStream_t st, int64_t x_row_stride);
 // MUL_MAT_ID over many tokens: stable expert-major order of the (token, slot) pairs, then one grouped

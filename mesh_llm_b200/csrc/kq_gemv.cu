@@ -287,7 +287,9 @@ b200_status launch_mr(const GemvParams &p, int wn, int n_pairs, cudaStream_t st)
 
 b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                            const int16_t *bs, int M, int64_t K, const float *residual,
-                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st, const KqActPrep *prep) {
+                           int swiglu_pairs, const KqGemvIndirect *ind, cudaStream_t st, const KqActPrep *prep,
+                           KqEmitQ8 *emit) {
+    if (emit) emit->done = 0;
     KQ_REQUIRE(nseg >= 1 && nseg <= 3, "gemv: 1..3 segments");
     KQ_REQUIRE(M >= 1 && M <= 8, "gemv: M must be 1..8 (got %d)", M);
     KQ_REQUIRE(K > 0 && K % 256 == 0, "gemv: K must be a positive multiple of 256");
@@ -296,7 +298,7 @@ b200_status kq_launch_gemv(const KqGemvSeg *segs, int nseg, const int8_t *q, con
                "gemv: swiglu needs two equal segments");
     KQ_REQUIRE(!residual || nseg == 1, "gemv: residual only with one segment");
     if (!(ind && ind->expert_ids) && K % 256 == 0) { // M <= 2: streaming kernel; 3..8 tokens of Q4_K: its tensor-core form
-        const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, prep, st);
+        const b200_status rs = kq_launch_gemv_stream(segs, nseg, q, d, bs, M, K, residual, swiglu_pairs, prep, st, emit);
         if (rs != B200_ERR_UNSUPPORTED) return rs;
         if (M > 2 && nseg > 1 && !swiglu_pairs && !(prep && prep->x)) {
             // a fused projection of mixed types: its Q4_K matrices still take the tensor-core form,

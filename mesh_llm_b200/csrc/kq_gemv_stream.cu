@@ -71,6 +71,7 @@ __device__ int g_stream_error; // 0 ok, 1 mbarrier wait gave up, 2 partial-sum w
 // debug build only: per CTA and launch, %globaltimer at the phase boundaries of the kernel
 __device__ unsigned long long g_trace[32768][16];
 __device__ unsigned long long g_trace_w[32768][16]; // per warp: clock at the end of its work
+__device__ unsigned long long g_trace_p[32768][16]; // per warp: cycles in post (bits 0..23), in wait_slot (24..47), units (48..63)
 __device__ unsigned int g_trace_n;
 #define TRACE_MARK(i) do { if (threadIdx.x == 0 && s_trace < 32768u) g_trace[s_trace][i] = (unsigned long long)clock64(); } while (0)
 #else
@@ -119,6 +120,11 @@ struct StreamParams {
     // step; a linear tilt of the CTAs' shares towards the CTAs that start first, tried next, only costs).  Set
     // by the host, which knows the grid: the kernel needs no division before its first copy can go out.
     int32_t uq, ur;
+    // fused gate / up only: the Q8 form of the output for the matmul that follows (see KqEmitQ8); e_q null = off
+    int8_t *e_q;
+    float *e_d;
+    int16_t *e_bs;
+    int32_t *e_cnt;
     const int8_t *aq;
     const float *ad;
     const int16_t *abs16;
@@ -232,7 +238,9 @@ struct Issuer {
                 locate<TYPE>(p, rg, seg, row0);
                 const int x = (ks + p.ks0) * (F::PITCH / 8);
                 mbar_expect_tx(bar, F::ROWS * F::PITCH);
+#ifndef KQ_NO_REPOST_FENCE
                 if (reuse) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
                 if (p.swiglu) {
                     tma_box(slot_addr, &p.map[0], x, row0, bar);
                     tma_box(slot_addr + (F::ROWS / 2) * F::PITCH, &p.map[1], x, row0, bar);
@@ -1053,9 +1061,18 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
 #pragma unroll
     for (int m = 0; m < M; m++) acc[m] = 0.f;
     int rg = begin / p.nsteps, ks = begin % p.nsteps;
+#ifdef KQ_GEMV_TRACE
+    unsigned long long tr_post = 0, tr_wait = 0;
+#endif
     for (int j = 0; j < count; j++) {
         const int slot = j % ns;
+#ifdef KQ_GEMV_TRACE
+        const long long tw0 = clock64();
+#endif
         wait_slot(bar_addr + slot * 8, (uint32_t)(((FUSED ? uses[slot] : 0u) + j / ns) & 1), &s_abort);
+#ifdef KQ_GEMV_TRACE
+        tr_wait += (unsigned long long)(clock64() - tw0);
+#endif
 #ifdef KQ_GEMV_TRACE
         if (j == 0) TRACE_MARK(4);
 #endif
@@ -1069,7 +1086,13 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         }
         // the slot has been read by every lane: hand it back to the copy engine for unit j + ns
         __syncwarp();
+#ifdef KQ_GEMV_TRACE
+        const long long tp0 = clock64();
+#endif
         if (j + ns < count) iss.post(p, lane, ring_addr + slot * F::SLOT, bar_addr + slot * 8);
+#ifdef KQ_GEMV_TRACE
+        tr_post += (unsigned long long)(clock64() - tp0);
+#endif
         const bool last_slice = ks == p.nsteps - 1, last_unit = j == count - 1;
         if (last_slice || last_unit) {
             // row totals: the LPR lanes of a row add up; afterwards the row's first lane has it
@@ -1170,6 +1193,33 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
             rg++;
         }
     }
+    if (!FUSED && M <= 2 && p.swiglu && p.e_q) {
+        // Q8 of the SwiGLU values for the down projection.  This warp wrote the rows of the row groups whose
+        // first K slice it holds; it adds their number to the counter of each 256-element block they lie in,
+        // and the warp that completes a block quantises it (the values come back from L2).
+        constexpr int RPB = 256 / (F::ROWS / 2); // row groups per block
+        __threadfence(); // this lane's stores of y before the counts below
+        __syncwarp();
+        const int r_lo = (begin + p.nsteps - 1) / p.nsteps, r_hi = (end - 1) / p.nsteps;
+        const int nbo = p.seg[0].n_rows / 256; // blocks of an output row
+        for (int b = r_lo / RPB; r_lo <= r_hi && b <= r_hi / RPB; b++) {
+            const int lo = max(r_lo, b * RPB), hi = min(r_hi, b * RPB + RPB - 1);
+            int last = 0;
+            if (lane == 0) last = (atomicAdd(&p.e_cnt[b], hi - lo + 1) + (hi - lo + 1) == RPB) ? 1 : 0;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (!last) continue;
+            __threadfence();
+            if (lane == 0) p.e_cnt[b] = 0; // ready for the next launch
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float *src = p.seg[0].y + (int64_t)m * p.seg[0].ldy + b * 256 + lane * 8;
+                const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(src)), a1 = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+                const float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                kq_quantize_block_warp(v, lane, p.e_q + (int64_t)m * p.seg[0].n_rows + b * 256, p.e_d + m * nbo + b,
+                                       p.e_bs + ((int64_t)m * nbo + b) * 16);
+            }
+        }
+    }
     if (FUSED)
 #pragma unroll
         for (int sl = 0; sl < 4; sl++)
@@ -1177,6 +1227,8 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
 #ifdef KQ_GEMV_TRACE
     TRACE_MARK(5);
     if (lane == 0 && s_trace < 32768u) g_trace_w[s_trace][warp & 15] = (unsigned long long)clock64();
+    if (lane == 0 && s_trace < 32768u)
+        g_trace_p[s_trace][warp & 15] = (tr_post & 0xFFFFFFull) | ((tr_wait & 0xFFFFFFull) << 24) | ((unsigned long long)count << 48);
     if (lane == 0 && s_trace < 32768u) {
         atomicMax(&g_trace[s_trace][6], (unsigned long long)clock64());
         atomicMax(&g_trace[s_trace][9], kq_globaltimer_ns());
@@ -1325,10 +1377,18 @@ inline int act_tok_bytes(uint32_t type, int nb, int M) {
 template <uint32_t TYPE, int M>
 b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d, const int16_t *bs,
                          int64_t K, const float *residual, int swiglu_pairs, const KqActPrep *prep, cudaStream_t st,
-                         int m_actual = M, int64_t K_row = 0, int blk0 = 0) {
+                         int m_actual = M, int64_t K_row = 0, int blk0 = 0, KqEmitQ8 *emit = nullptr) {
     using F = Fmt<TYPE>;
     StreamParams p;
     fill_params<TYPE>(p, segs, nseg, q, d, bs, K, residual, swiglu_pairs, prep);
+    const bool emit_on = emit && emit->q && emit->d && emit->bs && emit->counters && M <= 2 && swiglu_pairs &&
+                         segs[0].n_rows % 256 == 0 && segs[0].ldy % 4 == 0 && ((uintptr_t)segs[0].y & 15) == 0;
+    if (emit_on) {
+        p.e_q = emit->q;
+        p.e_d = emit->d;
+        p.e_bs = emit->bs;
+        p.e_cnt = emit->counters;
+    }
     if (K_row) { // a range of K: blocks blk0 .. blk0 + K / 256 of rows of K_row elements; q, d, bs point at the range
         if (blk0 % F::KB != 0 || (prep && prep->x)) return B200_ERR_INVALID;
         p.K_row = (int)K_row;
@@ -1368,6 +1428,7 @@ b200_status launch_block(const KqGemvSeg *segs, int nseg, const int8_t *q, const
     kq_launch(gemv_block_kernel<TYPE, M>, grid, WARPS * 32, smem, st, p);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
+    if (emit_on) emit->done = 1;
     return B200_OK;
 }
 
@@ -1538,6 +1599,7 @@ extern "C" __attribute__((visibility("default"))) int kq_gemv_trace_fetch(unsign
     if (n > 32768u) n = 32768u;
     if (out && n) cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 16 * n);
     if (out && n) cudaMemcpyFromSymbol(out + 16 * (size_t)max_rec, g_trace_w, sizeof(unsigned long long) * 16 * n);
+    if (out && n) cudaMemcpyFromSymbol(out + 32 * (size_t)max_rec, g_trace_p, sizeof(unsigned long long) * 16 * n);
     cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
     return (int)n;
 }
@@ -1563,7 +1625,8 @@ int kq_stream_error_fetch() {
 // per type.
 b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t *q, const float *d,
                                   const int16_t *bs, int M, int64_t K, const float *residual, int swiglu_pairs,
-                                  const KqActPrep *prep, cudaStream_t st) {
+                                  const KqActPrep *prep, cudaStream_t st, KqEmitQ8 *emit) {
+    if (emit) emit->done = 0;
     if (M < 1 || M > 8 || K % 256 != 0 || env_int2("B200_GEMV_STREAM", 1) == 0) return B200_ERR_UNSUPPORTED;
     if (M > 2) {
         // 3..8 tokens: the tensor-core kernel, Q4_K only, on activations that are already quantised.
@@ -1644,11 +1707,11 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
         if (swiglu_pairs && n != 2) return B200_ERR_UNSUPPORTED;
         b200_status rc;
         if (type == B200_TYPE_Q4_K)
-            rc = M == 1 ? launch_block<B200_TYPE_Q4_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st)
-                        : launch_block<B200_TYPE_Q4_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st);
+            rc = M == 1 ? launch_block<B200_TYPE_Q4_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st, 1, 0, 0, emit)
+                        : launch_block<B200_TYPE_Q4_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st, 2, 0, 0, emit);
         else
-            rc = M == 1 ? launch_block<B200_TYPE_Q6_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st)
-                        : launch_block<B200_TYPE_Q6_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st);
+            rc = M == 1 ? launch_block<B200_TYPE_Q6_K, 1>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st, 1, 0, 0, emit)
+                        : launch_block<B200_TYPE_Q6_K, 2>(sel, n, q, d, bs, K, residual, swiglu_pairs, prep, st, 2, 0, 0, emit);
         if (rc != B200_OK) return rc;
     }
     return B200_OK;

@@ -155,6 +155,7 @@ struct b200_stage {
     uint8_t *expert_mask = nullptr; // one byte per expert, 1 = allowed (all ones when no mask is set)
     int32_t *rid = nullptr, *pos0_dev = nullptr, *rid_scratch = nullptr, *attn_counters = nullptr;
     unsigned int *moe_counters = nullptr; // one word per token row, zero between launches (moe_router_fused_kernel)
+    int32_t *emit_counters = nullptr;     // one word per 256 rows of the feed-forward width, zero between launches (KqEmitQ8)
     size_t att_scratch_bytes = 0;
     void *scan_scratch = nullptr; // slices and counters of the vocabulary scan
     size_t scan_scratch_bytes = 0;
@@ -419,21 +420,27 @@ b200_status forward_body(b200_stage *st, const int32_t *tokens, const float *hid
             }
         } else {
             if (!fuse) OTHER_(kq_rms_norm(st->x, L.ffn_norm, rows, h, c.rms_eps, nullptr, st->aq, st->ad, st->abs16, s));
+            KqEmitQ8 emit = {st->aq, st->ad, st->abs16, st->emit_counters, 0};
             if (rows <= 8) {
                 KqGemvSeg gu[2] = {
                     {(const uint8_t *)L.gate->dev, L.gate->type, c.n_ff, st->g, nullptr, c.n_ff, 0},
                     {(const uint8_t *)L.up->dev, L.up->type, c.n_ff, st->g, nullptr, c.n_ff, 0},
                 };
                 KqActPrep pr = {st->x, L.ffn_norm, c.rms_eps, 1};
+                // the launch also leaves the Q8 form of its output for the down projection (B200_GEMV_EMIT_Q8=0: off)
+                const char *ev = getenv("B200_GEMV_EMIT_Q8"); // read when a step is captured
+                const bool want = fuse && (ev ? atoi(ev) : 1) && (classes & CLS_GEMV);
                 GEMV_(kq_launch_gemv(gu, 2, st->aq, st->ad, st->abs16, rows, h, nullptr, 1, nullptr, s,
-                                     fuse ? &pr : nullptr));
+                                     fuse ? &pr : nullptr, want ? &emit : nullptr));
             } else {
                 GEMV_(mm(st, L.gate, rows, st->g, nullptr, nullptr, s));
                 GEMV_(mm(st, L.up, rows, st->u, nullptr, nullptr, s));
                 // SwiGLU and the Q8 form the down projection reads, in one pass
                 OTHER_(kq_swiglu_quantize(st->g, st->u, rows, c.n_ff, st->g, st->aq, st->ad, st->abs16, s));
             }
-            if (fuse) {
+            if (fuse && emit.done) {
+                GEMV_(mm(st, L.down, rows, xout, nullptr, st->x, s)); // reads the Q8 form the gate / up launch wrote
+            } else if (fuse) {
                 KqGemvSeg sd = {(const uint8_t *)L.down->dev, L.down->type, h, xout, nullptr, h, 0};
                 KqActPrep pr = {st->g, nullptr, 0.f, 0};
                 GEMV_(kq_launch_gemv(&sd, 1, st->aq, st->ad, st->abs16, rows, c.n_ff, st->x, 0, nullptr, s, &pr));
@@ -626,6 +633,8 @@ b200_status b200_stage_create(const b200_stage_config *cfg, b200_stage **out) {
     A((void **)&st->pos0_dev, 256);
     A((void **)&st->rid_scratch, 1024);
     A((void **)&st->attn_counters, (size_t)c.n_seq * c.n_head_kv * 4 + 256);
+    A((void **)&st->emit_counters, (size_t)(c.n_ff / 256 + 1) * 4);
+    if (rc == B200_OK && cudaMemset(st->emit_counters, 0, (size_t)(c.n_ff / 256 + 1) * 4) != cudaSuccess) rc = B200_ERR_CUDA;
     if (c.has_output) A((void **)&st->logits_int, (size_t)c.n_seq * c.n_vocab * 4);
     if (c.has_output) {
         st->scan_scratch_bytes = b200_logit_signals_scratch_bytes(std::max<int64_t>(R, c.n_seq));

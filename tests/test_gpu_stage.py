@@ -392,3 +392,31 @@ def test_layer_parity_with_the_matmuls_of_a_layer_fused_into_one_launch(mode):
                        cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "2 passed" in r.stdout
+
+
+@pytest.mark.parametrize("cfg,n_seq", [(DENSE, 1), (DENSE, 2), (LLAMA, 1)])
+def test_down_projection_input_quantised_by_the_gate_up_launch(cfg, n_seq, monkeypatch):
+    """In a decode step of 1 or 2 sequences the fused gate / up launch leaves the Q8 form of its output for the
+    down projection (the warp that completes a 256-element block quantises it).  Same values, same quantiser:
+    the logits are bit for bit those of the step in which the down projection quantises its own input."""
+    import torch
+
+    from mesh_llm_b200.stage import Stage
+
+    outs = []
+    for env in ("1", "0"):
+        monkeypatch.setenv("B200_GEMV_EMIT_Q8", env)
+        st = Stage(**dict(cfg, n_seq=n_seq), n_ubatch=16)
+        st.generate(77)
+        rng = np.random.default_rng(5)
+        prompts = rng.integers(0, cfg["n_vocab"], (n_seq, 6)).astype(np.int32)
+        _, lg, nx = st.forward(tokens=torch.from_numpy(prompts.reshape(-1)).cuda(), n_seq=n_seq, T=6)
+        got = [lg.clone()]
+        toks = nx.clone()
+        for step in range(5):
+            _, lg, nx = st.forward(tokens=toks, n_seq=n_seq, T=1, pos0=6 + step)
+            got.append(lg.clone())
+            toks = nx.clone()
+        outs.append(torch.stack([g[-n_seq:] if g.shape[0] > n_seq else g for g in got[1:]]))
+        st.close()
+    assert torch.equal(outs[0], outs[1])
