@@ -1064,6 +1064,9 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
 #ifdef KQ_GEMV_TRACE
     unsigned long long tr_post = 0, tr_wait = 0;
 #endif
+    float pre_bias = 0.f, pre_res[M];
+#pragma unroll
+    for (int m = 0; m < M; m++) pre_res[m] = 0.f;
     for (int j = 0; j < count; j++) {
         const int slot = j % ns;
 #ifdef KQ_GEMV_TRACE
@@ -1076,6 +1079,24 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
 #ifdef KQ_GEMV_TRACE
         if (j == 0) TRACE_MARK(4);
 #endif
+        if (!p.swiglu && ks == 0 && t == 0) {
+            // this warp will write the rows of this row group: fetch their bias and residual now, so that the
+            // last instructions of the row group do not wait for a round trip to L2
+            int seg, row0;
+            locate<TYPE>(p, rg, seg, row0);
+            const KqGemvSeg &sg = p.seg[seg];
+            const int row = row0 + rs;
+            pre_bias = 0.f;
+#pragma unroll
+            for (int m = 0; m < M; m++) pre_res[m] = 0.f;
+            if (row < sg.n_rows) {
+                if (sg.bias) pre_bias = sg.bias[row];
+                if (p.residual)
+#pragma unroll
+                    for (int m = 0; m < M; m++)
+                        if (M <= 2 || m < p.m_actual) pre_res[m] = ld_act1<FUSED>(p.residual + (int64_t)m * sg.ldy + row);
+            }
+        }
         const int blk = ks * F::KB + t;
         if (blk < nb) {
             const uint8_t *row = ring + (size_t)slot * F::SLOT + rs * F::PITCH;
@@ -1180,8 +1201,8 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
                         for (int m = 0; m < M; m++) {
                             if (M > 2 && m >= p.m_actual) continue; // a padding token
                             float x = v[m];
-                            if (sg.bias) x += sg.bias[row];
-                            if (p.residual) x += ld_act1<FUSED>(p.residual + (int64_t)m * sg.ldy + row);
+                            if (sg.bias) x += pre_bias;
+                            if (p.residual) x += pre_res[m];
                             sg.y[(int64_t)m * sg.ldy + row] = x;
                         }
                     }
