@@ -42,7 +42,8 @@ B200_API const char *b200_status_string(b200_status s);
 B200_API const char *b200_last_error(void); /* thread-local, valid until the next failing call */
 /* Synchronises the current device and reports B200_ERR_TIMEOUT if any bounded device-side wait
  * (copy barrier, tensor-core commit, cross-CTA flag) gave up since the last check; the results of
- * the affected launch are then invalid.  Clears the condition.                                  */
+ * the affected launch are then invalid.  Clears the condition.  A stage whose step was affected
+ * keeps arrival counters of that step in its own memory: close it and create it again.          */
 B200_API b200_status b200_check_device_waits(void);
 
 /* ---- tensor types: ggml type ids (mesh-client/src/models/gguf.rs:19-35) -------------------- */
