@@ -64,6 +64,9 @@ __device__ int g_stream_error; // 0 ok, 1 mbarrier wait gave up, 2 partial-sum w
 #ifndef KQ_GEMV_CTAS
 #define KQ_GEMV_CTAS 1
 #endif
+#ifndef KQ_GEMV_PB
+#define KQ_GEMV_PB 2 // 256-blocks of the activation row a warp holds in registers while it prepares them (rows up to 8192 in one round)
+#endif
 #ifndef KQ_GEMV_GRIDMUL
 #define KQ_GEMV_GRIDMUL 1
 #endif
@@ -885,7 +888,7 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
         // Every CTA prepares the activations for itself: RMSNorm with the sum of squares in double,
         // then the Q8 quantiser, one warp per 256-block, PB blocks per warp in flight.  A row of up
         // to PB * WARPS blocks is read from L2 once and stays in registers for both steps.
-        constexpr int PB = 4;
+        constexpr int PB = KQ_GEMV_PB;
         __shared__ double s_part[WARPS];
         __shared__ float s_scale[2];
         const bool in_regs = nb <= PB * WARPS;
@@ -1506,40 +1509,62 @@ bool plan_part(StreamParams &p, size_t &smem) {
 
 template <int M>
 b200_status launch_mixed(const KqGemvSeg *s4, int n4, const KqGemvSeg *s6, int n6, const int8_t *q, const float *d,
-                         const int16_t *bs, int64_t K, const KqActPrep *prep, cudaStream_t st) {
-    StreamParams p4, p6;
-    fill_params<B200_TYPE_Q4_K>(p4, s4, n4, q, d, bs, K, nullptr, 0, prep);
-    fill_params<B200_TYPE_Q6_K>(p6, s6, n6, q, d, bs, K, nullptr, 0, prep);
+                         const int16_t *bs, int64_t K, const KqActPrep *prep, cudaStream_t st, const float *residual = nullptr,
+                         int swiglu_pairs = 0, KqEmitQ8 *emit = nullptr) {
+    // n4 == 0 or n6 == 0: a projection of one type through the same kernel (all CTAs on that type)
+    if (n4 + n6 < 1 || (swiglu_pairs && !((n4 == 2 && n6 == 0) || (n4 == 0 && n6 == 2)))) return B200_ERR_UNSUPPORTED;
+    if (residual && n4 + n6 != 1) return B200_ERR_UNSUPPORTED;
+    StreamParams p4 = {}, p6 = {};
+    if (n4) fill_params<B200_TYPE_Q4_K>(p4, s4, n4, q, d, bs, K, residual, swiglu_pairs, prep);
+    if (n6) fill_params<B200_TYPE_Q6_K>(p6, s6, n6, q, d, bs, K, residual, swiglu_pairs, prep);
     p4.m_actual = p6.m_actual = M;
     {
-        b200_status rm = make_maps<B200_TYPE_Q4_K>(p4, n4);
-        if (rm == B200_OK) rm = make_maps<B200_TYPE_Q6_K>(p6, n6);
+        b200_status rm = n4 ? make_maps<B200_TYPE_Q4_K>(p4, n4) : B200_OK;
+        if (rm == B200_OK && n6) rm = make_maps<B200_TYPE_Q6_K>(p6, n6);
         if (rm != B200_OK) return rm;
     }
     size_t sm4 = 0, sm6 = 0;
-    if (!plan_part<B200_TYPE_Q4_K, M>(p4, sm4) || !plan_part<B200_TYPE_Q6_K, M>(p6, sm6)) return B200_ERR_UNSUPPORTED;
+    if ((n4 && !plan_part<B200_TYPE_Q4_K, M>(p4, sm4)) || (n6 && !plan_part<B200_TYPE_Q6_K, M>(p6, sm6))) return B200_ERR_UNSUPPORTED;
     int total = kq_sm_count();
     if (total * KQ_GEMV_WARPS > MAX_UNITS) total = MAX_UNITS / KQ_GEMV_WARPS;
-    double b4 = 0, b6 = 0;
-    for (int i = 0; i < n4; i++) b4 += (double)s4[i].n_rows * kq_device_row_bytes(B200_TYPE_Q4_K, K);
-    for (int i = 0; i < n6; i++) b6 += (double)s6[i].n_rows * kq_device_row_bytes(B200_TYPE_Q6_K, K);
-    // a Q6_K CTA needs longer for its bytes than a Q4_K CTA (larger units, more arithmetic per weight, and at
-    // these sizes a warp holds one or two units): its bytes count more when the CTAs are divided
-    static int w6_pct = -1;
-    if (w6_pct < 0) w6_pct = env_int2("B200_GEMV_MIX_W6", 225);
-    b6 *= w6_pct / 100.0;
-    int c6 = (int)(total * b6 / (b4 + b6) + 0.5);
-    if (c6 < 1) c6 = 1;
-    if (c6 > total - 1) c6 = total - 1;
-    int c4 = total - c6;
-    const int64_t want4 = kq_div_up((int64_t)p4.n_rg * p4.nsteps, KQ_GEMV_WARPS), want6 = kq_div_up((int64_t)p6.n_rg * p6.nsteps, KQ_GEMV_WARPS);
-    if (want4 < c4) c4 = (int)(want4 < 1 ? 1 : want4);
-    if (want6 < c6) c6 = (int)(want6 < 1 ? 1 : want6);
+    const int64_t want4 = n4 ? kq_div_up((int64_t)p4.n_rg * p4.nsteps, KQ_GEMV_WARPS) : 0;
+    const int64_t want6 = n6 ? kq_div_up((int64_t)p6.n_rg * p6.nsteps, KQ_GEMV_WARPS) : 0;
+    int c4 = 0, c6 = 0;
+    if (n4 && n6) {
+        double b4 = 0, b6 = 0;
+        for (int i = 0; i < n4; i++) b4 += (double)s4[i].n_rows * kq_device_row_bytes(B200_TYPE_Q4_K, K);
+        for (int i = 0; i < n6; i++) b6 += (double)s6[i].n_rows * kq_device_row_bytes(B200_TYPE_Q6_K, K);
+        // a Q6_K CTA needs longer for its bytes than a Q4_K CTA (larger units, more arithmetic per weight, and at
+        // these sizes a warp holds one or two units): its bytes count more when the CTAs are divided
+        static int w6_pct = -1;
+        if (w6_pct < 0) w6_pct = env_int2("B200_GEMV_MIX_W6", 225);
+        b6 *= w6_pct / 100.0;
+        c6 = (int)(total * b6 / (b4 + b6) + 0.5);
+        if (c6 < 1) c6 = 1;
+        if (c6 > total - 1) c6 = total - 1;
+        c4 = total - c6;
+    } else if (n4) {
+        c4 = total;
+    } else {
+        c6 = total;
+    }
+    if (n4 && want4 < c4) c4 = (int)(want4 < 1 ? 1 : want4);
+    if (n6 && want6 < c6) c6 = (int)(want6 < 1 ? 1 : want6);
     p4.cta0 = 0;
-    p4.n_cta = c4;
+    p4.n_cta = c4; // 0: no CTA takes the Q4_K branch
     p6.cta0 = c4;
     p6.n_cta = c6;
-    if (!set_split(p4, c4 * KQ_GEMV_WARPS) || !set_split(p6, c6 * KQ_GEMV_WARPS)) return B200_ERR_UNSUPPORTED;
+    if ((n4 && !set_split(p4, c4 * KQ_GEMV_WARPS)) || (n6 && !set_split(p6, c6 * KQ_GEMV_WARPS))) return B200_ERR_UNSUPPORTED;
+    StreamParams &pe = n4 ? p4 : p6; // where the fused gate / up lives, if any
+    const KqGemvSeg *se = n4 ? s4 : s6;
+    const bool emit_on = emit && emit->q && emit->d && emit->bs && emit->counters && swiglu_pairs && se[0].n_rows % 256 == 0 &&
+                         se[0].ldy % 4 == 0 && ((uintptr_t)se[0].y & 15) == 0;
+    if (emit_on) {
+        pe.e_q = emit->q;
+        pe.e_d = emit->d;
+        pe.e_bs = emit->bs;
+        pe.e_cnt = emit->counters;
+    }
     const size_t smem = sm4 > sm6 ? sm4 : sm6;
     static bool attr_done[16];
     int dev = 0;
@@ -1551,6 +1576,7 @@ b200_status launch_mixed(const KqGemvSeg *s4, int n4, const KqGemvSeg *s6, int n
     kq_launch(gemv_mixed_kernel<M>, c4 + c6, KQ_GEMV_WARPS * 32, smem, st, p4, p6);
     KQ_COUNT_LAUNCH();
     KQ_LAUNCH_CHECK();
+    if (emit_on) emit->done = 1;
     return B200_OK;
 }
 
@@ -1708,6 +1734,18 @@ b200_status kq_launch_gemv_stream(const KqGemvSeg *segs, int nseg, const int8_t 
     }
     if (!(prep && prep->x) && ((((uintptr_t)q | (uintptr_t)bs) & 15) != 0 || ((uintptr_t)d & 3) != 0)) return B200_ERR_UNSUPPORTED;
     if (prep && prep->x && ((uintptr_t)prep->x & 15) != 0) return B200_ERR_UNSUPPORTED;
+    // B200_GEMV_ONE_KERNEL=1: every projection of 1 or 2 tokens through the two-type kernel, so that a decode step
+    // alternates between two kernels' code only (this one and the attention) instead of four
+    static int one_kernel = -1;
+    if (one_kernel < 0) one_kernel = env_int2("B200_GEMV_ONE_KERNEL", 0);
+    if (one_kernel) {
+        KqGemvSeg s4[3], s6[3];
+        int n4 = 0, n6 = 0;
+        for (int i = 0; i < nseg; i++) (segs[i].type == B200_TYPE_Q4_K ? s4[n4++] : s6[n6++]) = segs[i];
+        const b200_status rc = M == 1 ? launch_mixed<1>(s4, n4, s6, n6, q, d, bs, K, prep, st, residual, swiglu_pairs, emit)
+                                      : launch_mixed<2>(s4, n4, s6, n6, q, d, bs, K, prep, st, residual, swiglu_pairs, emit);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+    }
     if (!swiglu_pairs && !residual && env_int2("B200_GEMV_MIXED", 1)) {
         // matrices of both types in one projection: one launch with the CTAs divided between the types
         KqGemvSeg s4[3], s6[3];
