@@ -1004,11 +1004,13 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
             const int n16 = nb * 16;
             // first wave of loads (codes, sums, scales) in flight together, behind the posting
             constexpr int NT = WARPS * 32;
-            int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, s0 = c0;
+            int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, c2 = c0, c3 = c0, s0 = c0;
             float d0 = 0.f;
-            const int i0 = threadIdx.x, i1 = threadIdx.x + NT;
+            const int i0 = threadIdx.x, i1 = threadIdx.x + NT, i2 = threadIdx.x + 2 * NT, i3 = threadIdx.x + 3 * NT;
             if (i0 < n16) c0 = src[i0];
             if (i1 < n16) c1 = src[i1];
+            if (i2 < n16) c2 = src[i2]; // rows of up to 32768 codes in one round of loads
+            if (i3 < n16) c3 = src[i3];
             if (i0 < nb * 2) s0 = reinterpret_cast<const int4 *>(b16)[i0]; // 8 sums of 16
             if (i0 < nb) d0 = p.ad[m * p.a_ldb + i0];
             post_rest();
@@ -1026,7 +1028,9 @@ __device__ __forceinline__ void stream_body(const StreamParams &p, uint8_t *smem
             };
             if (i0 < n16) put(i0, c0);
             if (i1 < n16) put(i1, c1);
-            for (int i = threadIdx.x + 2 * NT; i < n16; i += NT) put(i, src[i]);
+            if (i2 < n16) put(i2, c2);
+            if (i3 < n16) put(i3, c3);
+            for (int i = threadIdx.x + 4 * NT; i < n16; i += NT) put(i, src[i]);
             for (int i = threadIdx.x; i < nb * 2; i += NT) {
                 const int4 sv = i == i0 ? s0 : reinterpret_cast<const int4 *>(b16)[i];
                 const int16_t *h = reinterpret_cast<const int16_t *>(&sv);
