@@ -103,8 +103,6 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
     __shared__ float p_s[4 * G][32];
     __shared__ float ml_s[4][G][2];
     __shared__ float w_s[G][64];
-    __shared__ float l_s[G][64];
-    __shared__ float inv_s[G];
     __shared__ uint64_t bar;
     __shared__ int s_last, s_abort;
     const int kh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
@@ -480,44 +478,60 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
     __threadfence();
     for (int g = MMA ? warp : (ti == 0 ? warp % G : G); g < G; g += MMA ? 8 : G) {
         const int head = kh * G + g;
-        // splits were written by other SMs: read them through L2 (ld.cg); max / weights once per head
-        for (int sp = lane; sp < n_split; sp += 32) {
-            const int64_t e = (((int64_t)seq * n_head + head) * n_split + sp) * 2;
-            w_s[g][sp] = __ldcg(&part_ml[e]);
-            l_s[g][sp] = __ldcg(&part_ml[e + 1]);
-        }
-        __syncwarp();
-        if (lane == 0) {
-            float mm = -INFINITY;
-            for (int sp = 0; sp < n_split; sp++) mm = fmaxf(mm, w_s[g][sp]);
-            float ll = 0.f;
-            for (int sp = 0; sp < n_split; sp++) {
-                const float ms = w_s[g][sp];
-                const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - mm);
-                ll += wgt * l_s[g][sp];
-                w_s[g][sp] = wgt;
+        // splits were written by other SMs: read them through L2 (ld.cg).  Lane sp (and sp + 32) holds split sp's
+        // maximum and sum; the head's maximum and the weighted sum of sums are warp reductions in a fixed order
+        float m_sp[2], l_sp[2], mm = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int sp = lane + 32 * u;
+            m_sp[u] = -INFINITY;
+            l_sp[u] = 0.f;
+            if (sp < n_split) {
+                const int64_t e = (((int64_t)seq * n_head + head) * n_split + sp) * 2;
+                m_sp[u] = __ldcg(&part_ml[e]);
+                l_sp[u] = __ldcg(&part_ml[e + 1]);
             }
-            inv_s[g] = ll;
         }
-        __syncwarp();
+        // the first round of the partial outputs goes out before the weights are worked out
         const float *po = part_o + (((int64_t)seq * n_head + head) * n_split) * HD + lane * DPL;
+        constexpr int RND = 16; // splits whose loads are in flight together
+        float t[RND][DPL];
+#pragma unroll
+        for (int u = 0; u < RND; u++)
+#pragma unroll
+            for (int i = 0; i < DPL; i++) t[u][i] = u < n_split ? __ldcg(po + (int64_t)u * HD + i) : 0.f;
+        mm = fmaxf(m_sp[0], m_sp[1]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        float ll = 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const float wgt = (m_sp[u] == -INFINITY) ? 0.f : expf(m_sp[u] - mm);
+            const int sp = lane + 32 * u;
+            if (sp < n_split) w_s[g][sp] = wgt;
+            ll += wgt * l_sp[u];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+        __syncwarp();
         float acc[DPL];
 #pragma unroll
         for (int i = 0; i < DPL; i++) acc[i] = 0.f;
-        for (int s0 = 0; s0 < n_split; s0 += 8) { // 8 splits' loads in flight at a time
-            float t[8][DPL];
+        for (int s0 = 0; s0 < n_split; s0 += RND) {
+            if (s0 > 0) {
 #pragma unroll
-            for (int u = 0; u < 8; u++)
+                for (int u = 0; u < RND; u++)
 #pragma unroll
-                for (int i = 0; i < DPL; i++) t[u][i] = s0 + u < n_split ? __ldcg(po + (int64_t)(s0 + u) * HD + i) : 0.f;
+                    for (int i = 0; i < DPL; i++) t[u][i] = s0 + u < n_split ? __ldcg(po + (int64_t)(s0 + u) * HD + i) : 0.f;
+            }
 #pragma unroll
-            for (int u = 0; u < 8; u++)
+            for (int u = 0; u < RND; u++)
                 if (s0 + u < n_split)
 #pragma unroll
                     for (int i = 0; i < DPL; i++) acc[i] += w_s[g][s0 + u] * t[u][i];
         }
 #pragma unroll
-        for (int i = 0; i < DPL; i++) out[((int64_t)seq * n_head + head) * HD + lane * DPL + i] = acc[i] / inv_s[g];
+        for (int i = 0; i < DPL; i++) out[((int64_t)seq * n_head + head) * HD + lane * DPL + i] = acc[i] / ll;
     }
     __syncthreads();
     if (threadIdx.x == 0) counters[seq * n_kv + kh] = 0;
