@@ -81,9 +81,9 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
                                                               const float *q, const float *k_new,
                                                               const float *v_new, __half *kc, __half *vc,
                                                               const int32_t *pos_dev, int pos_val, int n_head, int n_kv,
-                                                              int64_t seq_stride, int n_split, float scale, int neox,
-                                                              RopeTab tab, float *out, float *part_o, float *part_ml,
-                                                              int *counters, KqKvTypes kvt) {
+                                                              int64_t seq_stride, int n_split, int unit_chunk, float scale,
+                                                              int neox, RopeTab tab, float *out, float *part_o,
+                                                              float *part_ml, int *counters, KqKvTypes kvt) {
     KQ_PDL_TRIGGER();
     // the copy engine's descriptors: fetched while the position is being read
     if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
@@ -108,13 +108,9 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
     const int kh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = MMA ? 0 : warp % G, ti = MMA ? warp : warp / G;
-    const int pos = pos_dev ? *pos_dev : pos_val; // written before this step started
-    const int L = pos + 1;
-    int chunk = (L + n_split - 1) / n_split;
-    chunk = (chunk + ROWS_PER_CTA - 1) / ROWS_PER_CTA * ROWS_PER_CTA;
-    const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
     __half *kbase = kc + seq * seq_stride + (int64_t)kh * HD;
     __half *vbase = vc + seq * seq_stride + (int64_t)kh * HD;
+    const int pos = pos_dev ? *pos_dev : pos_val; // written before this step started; first used after the early copy request
     const int64_t pstride = (int64_t)n_kv * HD;
     const int64_t cache_row0 = seq * (seq_stride / HD) + kh; // row index of (seq, position 0, kh) in a quantised cache
     const uint32_t bar_a = smem_u32(&bar);
@@ -123,7 +119,56 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0;
     }
+    // thread 0: request the 128-row chunk that starts at position cb (whole boxes always: rows past the context
+    // arrive as zeros, rows not yet written are never read)
+    auto issue_chunk = [&](int cb) {
+        const int tx = (kq ? ROWS_PER_CTA * k_row : NBOX * BOX_BYTES) + (vq ? ROWS_PER_CTA * v_row : NBOX * BOX_BYTES);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(tx) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (kq)
+            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                             smem_u32(kraw_s)),
+                         "l"(&kmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                         : "memory");
+        if (vq)
+            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                             smem_u32(vraw_s)),
+                         "l"(&vmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                         : "memory");
+#pragma unroll
+        for (int bx = 0; bx < NBOX; bx++) {
+            if (!kq)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(k_s + bx * BOX_BYTES)),
+                             "l"(&kmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                             : "memory");
+            if (!vq)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                                 smem_u32(v_s + bx * BOX_BYTES)),
+                             "l"(&vmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
+                             : "memory");
+        }
+    };
+    // unit_chunk: the launcher knows that every slice is one 128-row chunk (one slice per 128 positions), so the
+    // chunk's rows are known without the position and their copy goes out while the position is still on its way
+    if (unit_chunk && threadIdx.x == 0) issue_chunk(split * ROWS_PER_CTA);
+    const int L = pos + 1;
+    int chunk = (L + n_split - 1) / n_split;
+    chunk = (chunk + ROWS_PER_CTA - 1) / ROWS_PER_CTA * ROWS_PER_CTA;
+    const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
     __syncthreads();
+    uint32_t phase = 0;
+    bool early_done = unit_chunk != 0;
+    if (early_done && (chunk != ROWS_PER_CTA || p_begin >= p_end)) {
+        // not what the launcher promised: let the early copy land, report, and go on without it
+        if (threadIdx.x == 0) {
+            kq_mbar_wait(bar_a, phase, KQ_WAIT_LIMIT_NS);
+            atomicExch(&g_attn_error, 3);
+        }
+        __syncthreads();
+        phase ^= 1;
+        early_done = false;
+    }
 
     float m = -INFINITY, l = 0.f, o[DPL]; // MMA: m and l belong to head lane / 4 (all four lanes of a quad hold them)
 #pragma unroll
@@ -131,40 +176,12 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
     float oacc[MMA ? 8 : 1][4]; // MMA: O^T tiles: rows = dims 16 mt + lane/4 (+8), columns = heads 2 (lane%4), +1
 #pragma unroll
     for (int i = 0; i < (MMA ? 8 : 1); i++) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
-    uint32_t phase = 0;
     bool first = true;
     for (int cb = p_begin; cb < p_end || first; cb += ROWS_PER_CTA) {
         const int ccnt = max(0, min(ROWS_PER_CTA, p_end - cb));
         const bool has_new = pos >= cb && pos < cb + ccnt;
-        if (ccnt > 0 && threadIdx.x == 0) {
-            // whole boxes always: rows past the context arrive as zeros, rows not yet written are never read
-            const int tx = (kq ? ROWS_PER_CTA * k_row : NBOX * BOX_BYTES) + (vq ? ROWS_PER_CTA * v_row : NBOX * BOX_BYTES);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(tx) : "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (kq)
-                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                 smem_u32(kraw_s)),
-                             "l"(&kmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                             : "memory");
-            if (vq)
-                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                 smem_u32(vraw_s)),
-                             "l"(&vmap), "r"(0), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                             : "memory");
-#pragma unroll
-            for (int bx = 0; bx < NBOX; bx++) {
-                if (!kq)
-                    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                     smem_u32(k_s + bx * BOX_BYTES)),
-                                 "l"(&kmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                                 : "memory");
-                if (!vq)
-                    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
-                                     smem_u32(v_s + bx * BOX_BYTES)),
-                                 "l"(&vmap), "r"(64 * bx), "r"(kh), "r"(cb), "r"(seq), "r"(bar_a)
-                                 : "memory");
-            }
-        }
+        if (ccnt > 0 && threadIdx.x == 0 && !early_done) issue_chunk(cb);
+        early_done = false;
         if (first) {
             KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
             if (MMA) {
@@ -540,8 +557,8 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
 template <int HD>
 b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap, const CUtensorMap &vmap, const float *q,
                      const float *k, const float *v, __half *kc, __half *vc, const int32_t *pos_dev, int pos, int n_head,
-                     int n_kv, int64_t seq_stride, int n_split, float scale, int neox, const RopeTab &tab, float *out, float *po,
-                     float *pml, int *counters, KqKvTypes kvt) {
+                     int n_kv, int64_t seq_stride, int n_split, int unit_chunk, float scale, int neox, const RopeTab &tab, float *out,
+                     float *po, float *pml, int *counters, KqKvTypes kvt) {
     const size_t raw = (kvt.k != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.k, HD) : 0) +
                        (kvt.v != KQ_KV_F16 ? ROWS_PER_CTA * kq_kv_row_bytes(kvt.v, HD) : 0);
     const size_t smem = 2 * (HD / 64) * BOX_BYTES + (size_t)4 * G * HD * sizeof(float) + raw + 1024; // + room to align to 1 KB
@@ -557,14 +574,14 @@ b200_status launch_g(int G, dim3 grid, cudaStream_t st, const CUtensorMap &kmap,
             if (smem > 48 * 1024)                                                                              \
                 cudaFuncSetAttribute(attn_decode_kernel<HD, GG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             kq_launch(attn_decode_kernel<HD, GG, true>, grid, 256, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head,  \
-                      n_kv, seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);                 \
+                      n_kv, seq_stride, n_split, unit_chunk, scale, neox, tab, out, po, pml, counters, kvt);                 \
             break;                                                                                             \
         }                                                                                                      \
     }                                                                                                          \
     if (smem > 48 * 1024)                                                                                      \
         cudaFuncSetAttribute(attn_decode_kernel<HD, GG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     kq_launch(attn_decode_kernel<HD, GG, false>, grid, 128 * GG, smem, st, kmap, vmap, q, k, v, kc, vc, pos_dev, pos, n_head, n_kv, \
-              seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt)
+              seq_stride, n_split, unit_chunk, scale, neox, tab, out, po, pml, counters, kvt)
     switch (G) {
     case 1: KQ_AD(1); break;
     case 2: KQ_AD(2); break;
@@ -659,6 +676,13 @@ b200_status kq_attention_decode(const float *q, const float *k, const float *v, 
     float *po = scratch, *pml = scratch ? scratch + (size_t)n_seq * n_head * n_split * hd : nullptr;
     const float scale = 1.0f / sqrtf((float)hd);
     dim3 grid(n_kv, n_split, n_seq);
+    // one slice per 128 positions (not capped): a CTA's only chunk starts at slice * 128 whatever the position is
+    static int early_env = -1;
+    if (early_env < 0) {
+        const char *e = getenv("B200_ATTN_DECODE_EARLY");
+        early_env = e ? atoi(e) : 1;
+    }
+    const int unit_chunk = early_env && n_split == (pos + 1 + ROWS_PER_CTA - 1) / ROWS_PER_CTA ? 1 : 0;
     const int G = n_head / n_kv;
     KQ_REQUIRE((((uintptr_t)kc | (uintptr_t)vc) & 15) == 0, "attention: the cache must be 16-byte aligned");
     const CacheMaps *maps = nullptr;
@@ -666,7 +690,7 @@ b200_status kq_attention_decode(const float *q, const float *k, const float *v, 
     if (rc != B200_OK) return rc;
     if (hd == 128)
         return launch_g<128>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
-                             seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);
+                             seq_stride, n_split, unit_chunk, scale, neox, tab, out, po, pml, counters, kvt);
     return launch_g<64>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
-                        seq_stride, n_split, scale, neox, tab, out, po, pml, counters, kvt);
+                        seq_stride, n_split, unit_chunk, scale, neox, tab, out, po, pml, counters, kvt);
 }
