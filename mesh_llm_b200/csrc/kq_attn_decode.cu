@@ -76,7 +76,7 @@ constexpr int QH_PITCH = 128 * 2 + 16; // bytes per row of the f16 copy of q: ei
 // enter as hi + lo pairs of f16 (two MMAs each), K and V are f16 as stored, accumulation is f32: the result
 // agrees with the f32 scalar form to rounding of the sums.
 template <int HD, int G, bool MMA>
-__global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
+__global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                                                               const __grid_constant__ CUtensorMap vmap,
                                                               const float *q, const float *k_new,
                                                               const float *v_new, __half *kc, __half *vc,
@@ -177,6 +177,22 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
 #pragma unroll
     for (int i = 0; i < (MMA ? 8 : 1); i++) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
     bool first = true;
+    // rotation factors of this lane's frequencies (lane, lane + 32, ..): they need the position only, so they are
+    // worked out before the dependency wait
+    constexpr int NF = HALF / 32;
+    float rc[NF], rs[NF];
+#pragma unroll
+    for (int u = 0; u < NF; u++) {
+        const float ang = (float)pos * tab.inv_freq[lane + 32 * u];
+        rc[u] = cosf(ang);
+        rs[u] = sinf(ang);
+    }
+    // MMA form, f16 cache: the new position's k and v rows are fetched and rotated next to q (warps KW and VW), parked
+    // in shared memory (each lane reads back what it wrote), and put over the stale copy of that row once the
+    // chunk has landed
+    constexpr int KW = G % 8, VW = (G + 1) % 8;
+    __shared__ __half new_s[2][HD];
+    bool new_in_regs = false;
     for (int cb = p_begin; cb < p_end || first; cb += ROWS_PER_CTA) {
         const int ccnt = max(0, min(ROWS_PER_CTA, p_end - cb));
         const bool has_new = pos >= cb && pos < cb + ccnt;
@@ -190,9 +206,10 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
             }
             for (int gg = MMA ? warp : g; gg < (MMA ? G : g + 1); gg += 8) {
                 if (!MMA && ti != 0) break;
-                for (int f = lane; f < HALF; f += 32) { // query head gg, rotated and pre-scaled
-                    const float ang = (float)pos * tab.inv_freq[f];
-                    const float c = cosf(ang), sn = sinf(ang);
+#pragma unroll
+                for (int u = 0; u < NF; u++) { // query head gg, rotated and pre-scaled
+                    const int f = lane + 32 * u;
+                    const float c = rc[u], sn = rs[u];
                     const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
                     const float *qv = q + ((int64_t)seq * n_head + kh * G + gg) * HD;
                     const float a = qv[i0], b = qv[i1];
@@ -206,6 +223,32 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
                     } else {
                         q_s[gg][i0] = r0;
                         q_s[gg][i1] = r1;
+                    }
+                }
+            }
+            if (MMA && has_new && !kq && !vq) {
+                new_in_regs = true;
+                if (warp == KW) {
+                    const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
+#pragma unroll
+                    for (int u = 0; u < NF; u++) {
+                        const int f = lane + 32 * u;
+                        const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
+                        const float a = kv[i0], b = kv[i1];
+                        const __half r0 = __float2half_rn(a * rc[u] - b * rs[u]), r1 = __float2half_rn(a * rs[u] + b * rc[u]);
+                        new_s[0][i0] = r0;
+                        new_s[0][i1] = r1;
+                        kbase[pos * pstride + i0] = r0;
+                        kbase[pos * pstride + i1] = r1;
+                    }
+                }
+                if (warp == VW) {
+                    const float *vv = v_new + ((int64_t)seq * n_kv + kh) * HD;
+#pragma unroll
+                    for (int u = 0; u < HD / 32; u++) {
+                        const __half r = __float2half_rn(vv[lane + 32 * u]);
+                        new_s[1][lane + 32 * u] = r;
+                        vbase[pos * pstride + lane + 32 * u] = r;
                     }
                 }
             }
@@ -273,7 +316,23 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G) attn_decode_kernel(const 
                 *reinterpret_cast<__half *>(sw_elem(is_k ? k_s : v_s, rr, e)) = r;
             }
         }
-        if (has_new) {
+        if (has_new && new_in_regs) {
+            const int rr = pos - cb;
+            if (warp == KW) {
+#pragma unroll
+                for (int u = 0; u < NF; u++) {
+                    const int f = lane + 32 * u;
+                    const int i0 = neox ? f : 2 * f, i1 = neox ? f + HALF : 2 * f + 1;
+                    *reinterpret_cast<__half *>(sw_elem(k_s, rr, i0)) = new_s[0][i0];
+                    *reinterpret_cast<__half *>(sw_elem(k_s, rr, i1)) = new_s[0][i1];
+                }
+            }
+            if (warp == VW) {
+#pragma unroll
+                for (int u = 0; u < HD / 32; u++) *reinterpret_cast<__half *>(sw_elem(v_s, rr, lane + 32 * u)) = new_s[1][lane + 32 * u];
+            }
+            new_in_regs = false;
+        } else if (has_new) {
             // rotate k, round k and v to f16 as later steps will read them, into the cache and over the
             // stale copy of that row in the chunk
             const float *kv = k_new + ((int64_t)seq * n_kv + kh) * HD;
