@@ -542,16 +542,18 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
     if (n_split == 1) return;
     // the CTA that finishes last combines the splits of its G heads (in split order) and re-arms
     // the counter for the next launch
-    __threadfence();
+    // the CTA's partial results are ordered before its arrival by the barrier and one thread's fence (fences are
+    // cumulative), and the arrival before the last CTA's reads by that thread's second fence and the barrier
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();
         const int prev = atomicAdd(&counters[seq * n_kv + kh], 1);
         if (prev < 0 || prev >= n_split) atomicExch(&g_attn_error, 1);
         s_last = prev == n_split - 1;
+        __threadfence();
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     for (int g = MMA ? warp : (ti == 0 ? warp % G : G); g < G; g += MMA ? 8 : G) {
         const int head = kh * G + g;
         // splits were written by other SMs: read them through L2 (ld.cg).  Lane sp (and sp + 32) holds split sp's
