@@ -95,7 +95,12 @@ def test_every_layer_output_matches_given_the_same_input(cfg):
     print(f"worst segment row error {worst:.2e}, rows with a code other than the oracle's {flips}")
 
 
-@pytest.mark.parametrize("cfg", [DENSE, LLAMA, MOE], ids=["qwen2-dense", "llama-dense", "qwen3-moe"])
+# rows of more than 8192 values: the decode GEMV's norm prologue takes its statistics in a pass of its own
+WIDE = dict(n_layer=1, n_embd=9216, n_head=4, n_head_kv=2, head_dim=128, n_ff=512, n_vocab=512, n_ctx=64,
+            qkv_bias=0, rope_neox=1, rope_theta=1e6, rms_eps=1e-6)
+
+
+@pytest.mark.parametrize("cfg", [DENSE, LLAMA, MOE, WIDE], ids=["qwen2-dense", "llama-dense", "qwen3-moe", "wide-rows"])
 def test_prefill_and_greedy_decode_logits_agree_with_oracle(cfg):
     """End to end through all layers: logits are compared by top-1 agreement and KL divergence
     (reported), with the oracle fed the GPU's own greedy tokens so both see the same history."""
