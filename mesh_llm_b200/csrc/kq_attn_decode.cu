@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
         }
         // the first round of the partial outputs goes out before the weights are worked out
         const float *po = part_o + (((int64_t)seq * n_head + head) * n_split) * HD + lane * DPL;
-        constexpr int RND = 16; // splits whose loads are in flight together
+        constexpr int RND = 24; // splits whose loads are in flight together (context up to 3072 in one round)
         float t[RND][DPL];
 #pragma unroll
         for (int u = 0; u < RND; u++)
