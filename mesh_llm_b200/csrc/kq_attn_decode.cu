@@ -199,11 +199,11 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
         if (ccnt > 0 && threadIdx.x == 0 && !early_done) issue_chunk(cb);
         early_done = false;
         if (first) {
-            KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
-            if (MMA) {
+            if (MMA) { // rows of the q tile that no head fills must be zero: cleared while the projection still runs
                 for (int i = threadIdx.x; i < 2 * 16 * QH_PITCH / 16; i += NT) reinterpret_cast<uint4 *>(qh_s)[i] = make_uint4(0, 0, 0, 0);
                 __syncthreads();
             }
+            KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
             for (int gg = MMA ? warp : g; gg < (MMA ? G : g + 1); gg += 8) {
                 if (!MMA && ti != 0) break;
 #pragma unroll
