@@ -20,6 +20,15 @@ b200_status kq_tmap_encode(void *map128, int elem_bytes, int rank, const void *b
                            const uint64_t *strides_bytes, const uint32_t *box, int swizzle128);
 
 namespace {
+#ifdef KQ_ATTN_TRACE
+// debug build only: clock64 at the phase boundaries of the decode attention kernel, one record per CTA
+// ([10]: block index, [11]: %globaltimer at the start); read with kq_attn_trace_fetch()
+__device__ unsigned long long g_atr[8192][12];
+__device__ unsigned int g_atr_n;
+#define AT_MARK(i) do { if (threadIdx.x == 0 && s_tr < 8192u) g_atr[s_tr][i] = (unsigned long long)clock64(); } while (0)
+#else
+#define AT_MARK(i)
+#endif
 
 struct RopeTab {
     float inv_freq[64];
@@ -85,6 +94,18 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
                                                               int neox, RopeTab tab, float *out, float *part_o,
                                                               float *part_ml, int *counters, KqKvTypes kvt) {
     KQ_PDL_TRIGGER();
+#ifdef KQ_ATTN_TRACE
+    __shared__ unsigned int s_tr;
+    if (threadIdx.x == 0) {
+        s_tr = atomicAdd(&g_atr_n, 1u);
+        if (s_tr < 8192u) {
+            g_atr[s_tr][10] = ((unsigned long long)blockIdx.x << 40) | ((unsigned long long)blockIdx.y << 20) | blockIdx.z;
+            g_atr[s_tr][11] = kq_globaltimer_ns();
+        }
+    }
+    __syncthreads();
+#endif
+    AT_MARK(0);
     // the copy engine's descriptors: fetched while the position is being read
     if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
     if (threadIdx.x == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
@@ -152,11 +173,13 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
     // unit_chunk: the launcher knows that every slice is one 128-row chunk (one slice per 128 positions), so the
     // chunk's rows are known without the position and their copy goes out while the position is still on its way
     if (unit_chunk && threadIdx.x == 0) issue_chunk(split * ROWS_PER_CTA);
+    AT_MARK(1); // chunk copy requested
     const int L = pos + 1;
     int chunk = (L + n_split - 1) / n_split;
     chunk = (chunk + ROWS_PER_CTA - 1) / ROWS_PER_CTA * ROWS_PER_CTA;
     const int p_begin = split * chunk, p_end = min(L, p_begin + chunk);
     __syncthreads();
+    AT_MARK(2); // position known, barrier
     uint32_t phase = 0;
     bool early_done = unit_chunk != 0;
     if (early_done && (chunk != ROWS_PER_CTA || p_begin >= p_end)) {
@@ -204,6 +227,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
                 __syncthreads();
             }
             KQ_PDL_WAIT(); // q, k_new, v_new come from the projection that precedes this kernel
+            AT_MARK(3); // dependency wait over
             for (int gg = MMA ? warp : g; gg < (MMA ? G : g + 1); gg += 8) {
                 if (!MMA && ti != 0) break;
 #pragma unroll
@@ -254,6 +278,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
             }
             first = false;
         }
+        AT_MARK(4); // q (and the new row) staged
         if (ccnt == 0) break; // CTA-uniform: an empty slice only takes part in the combine below
         { // bounded wait for the chunk
             const bool ok = s_abort ? false : kq_mbar_wait(bar_a, phase, KQ_WAIT_LIMIT_NS);
@@ -263,6 +288,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
             }
             phase ^= 1;
         }
+        AT_MARK(5); // chunk arrived
         // raw rows of a quantised chunk -> the swizzled f16 chunk (the new position's row comes from below)
         if (kq || vq) {
             const int rr_new = has_new ? pos - cb : -1;
@@ -484,6 +510,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
         __syncthreads(); // the chunk may be overwritten by the next one
     }
 
+    AT_MARK(6); // products, softmax, values done
     // combine the 4 tiles of each head inside the CTA (tile order)
     if constexpr (MMA) {
         const int g4 = lane >> 2, t4 = lane & 3;
@@ -539,6 +566,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
         }
     }
     }
+    AT_MARK(7); // CTA combine done, partial results written
     if (n_split == 1) return;
     // the CTA that finishes last combines the splits of its G heads (in split order) and re-arms
     // the counter for the next launch
@@ -553,6 +581,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
         __threadfence();
     }
     __syncthreads();
+    AT_MARK(8); // arrival counted
     if (!s_last) return;
     for (int g = MMA ? warp : (ti == 0 ? warp % G : G); g < G; g += MMA ? 8 : G) {
         const int head = kh * G + g;
@@ -613,6 +642,7 @@ __global__ void __launch_bounds__(MMA ? 256 : 128 * G, MMA ? 2 : 1) attn_decode_
     }
     __syncthreads();
     if (threadIdx.x == 0) counters[seq * n_kv + kh] = 0;
+    AT_MARK(9); // last CTA: merge of the slices done
 }
 
 template <int HD>
@@ -755,3 +785,16 @@ b200_status kq_attention_decode(const float *q, const float *k, const float *v, 
     return launch_g<64>(G, grid, st, maps->k, maps->v, q, k, v, (__half *)kc, (__half *)vc, pos_dev, pos, n_head, n_kv,
                         seq_stride, n_split, unit_chunk, scale, neox, tab, out, po, pml, counters, kvt);
 }
+
+#ifdef KQ_ATTN_TRACE
+extern "C" __attribute__((visibility("default"))) int kq_attn_trace_fetch(unsigned long long *out, int max_rec) {
+    unsigned int n = 0, zero = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, g_atr_n, sizeof(n));
+    if ((int)n > max_rec) n = max_rec;
+    if (n > 8192u) n = 8192u;
+    if (out && n) cudaMemcpyFromSymbol(out, g_atr, sizeof(unsigned long long) * 12 * n);
+    cudaMemcpyToSymbol(g_atr_n, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
