@@ -47,6 +47,15 @@ def test_schedule_and_layer_ranges():
     for r in range(4):
         seen = [s.work(r, t) for t in range(s.ticks(3)) if s.work(r, t) and s.work(r, t)[1] < 3]
         assert sorted(seen) == [(q, k) for q in range(4) for k in range(3)]
+    # two sequences per stage in flight: the same, and a sequence's next step comes up on the first stage
+    # world + 1 ticks after the last stage has produced its token
+    s2 = Schedule(4, 8)
+    for r in range(4):
+        seen = [s2.work(r, t) for t in range(s2.ticks(3)) if s2.work(r, t) and s2.work(r, t)[1] < 3]
+        assert sorted(seen) == [(q, k) for q in range(8) for k in range(3)]
+    t_last = next(t for t in range(64) if s2.work(3, t) == (0, 0))
+    t_first = next(t for t in range(64) if s2.work(0, t) == (0, 1))
+    assert t_first - t_last == 8 - 4 + 1
 
 
 def _free_port():
